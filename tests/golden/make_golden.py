@@ -1,0 +1,309 @@
+"""Generate the golden vectors under tests/golden/ by running the REFERENCE.
+
+Run once, in a container that has the reference checkout, as
+
+    PYTHONPATH=<reference checkout> python tests/golden/make_golden.py
+
+It imports the reference's own CPU modules (smartkv.core._quant_cpu,
+smartkv.core.fused_cpu, smartkv.core.cache, smartkv.kernels) and records
+their outputs on seeded inputs.  The resulting ``*.npz`` files are small and
+are committed; the tests never import the reference.
+
+Where the reference refuses packed-budget accounting on CPU
+(``use_packing`` is forced off for device "cpu"), the cache object is switched
+to packed accounting after construction exactly as a CUDA cache would be:
+``use_packing=True``, ``min_budget`` recomputed, ``layer_store`` re-initialised.
+Nothing else of the reference is modified.
+"""
+import hashlib
+import os
+import sys
+import warnings
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "..", ".."))
+
+warnings.filterwarnings("ignore")
+
+from smartkv.core._quant_cpu import quantize_per_head            # noqa: E402
+from smartkv.core.allocation import compute_memory_usage, compute_minimum_budget  # noqa: E402
+from smartkv.core.cache import SmartKVCache                      # noqa: E402
+from smartkv.core.fused_cpu import quantized_attention_streaming_cpu  # noqa: E402
+from smartkv.kernels import _quantized_attention_pytorch         # noqa: E402
+
+from oracle import smartkv_oracle as orc                         # noqa: E402
+
+
+def sha(a: np.ndarray) -> np.ndarray:
+    return np.frombuffer(hashlib.sha256(np.ascontiguousarray(a).tobytes()).digest(), dtype=np.uint8).copy()
+
+
+def packed_cache(L, H, D, beta, bits=(2, 3, 4, 8), **kw):
+    c = SmartKVCache(num_layers=L, num_heads=H, head_dim=D, memory_budget=0.9,
+                     available_bits=list(bits), device="cpu", **kw)
+    c.use_packing = True
+    c.min_budget = compute_minimum_budget(H, D, c.scale_dtype, True)
+    c.memory_budget = beta
+    c.layer_store = [c._init_layer_store() for _ in range(L)]
+    return c
+
+
+def tie_inputs(n, h, d, seed):
+    """Rows whose x/scale lands exactly on .5 boundaries, plus zeros and outliers."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, h, d)).astype(np.float32)
+    x[0] = 0.0                                   # zero row -> scale 1
+    x[1, :, 0] = 7.0                             # absmax 7 -> scale 1.0 at 4 bits
+    x[1, :, 1:9] = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 3.5, -3.5], np.float32)
+    x[1, :, 9:] = np.round(x[1, :, 9:] * 2) / 2  # halves
+    x[2, :, 0] = 127.0
+    x[2, :, 1:5] = np.array([0.5, -0.5, 126.5, -126.5], np.float32)
+    if n > 3:
+        x[3, :, :4] *= 8.0
+    return x
+
+
+def gen_quant(out):
+    for tag, (n, h, d) in {"a": (6, 4, 64), "b": (5, 8, 128)}.items():
+        k = tie_inputs(n, h, d, 11)
+        v = tie_inputs(n, h, d, 12)[::-1].copy()
+        out[f"quant_{tag}_k"] = k
+        out[f"quant_{tag}_v"] = v
+        for bits in (2, 3, 4, 8):
+            kq, vq, ks, vs = quantize_per_head(torch.from_numpy(k), torch.from_numpy(v), bits)
+            out[f"quant_{tag}_kq{bits}"] = kq.numpy()
+            out[f"quant_{tag}_vq{bits}"] = vq.numpy()
+            out[f"quant_{tag}_ks{bits}"] = ks.numpy()
+            out[f"quant_{tag}_vs{bits}"] = vs.numpy()
+    # bulk random: only digests (codes and scale bits)
+    k, v = orc.synth_kv(512, 8, 128, seed=3)
+    for bits in (2, 3, 4, 8):
+        kq, vq, ks, vs = quantize_per_head(torch.from_numpy(k), torch.from_numpy(v), bits)
+        out[f"quant_bulk_sha_kq{bits}"] = sha(kq.numpy())
+        out[f"quant_bulk_sha_vq{bits}"] = sha(vq.numpy())
+        out[f"quant_bulk_sha_ks{bits}"] = sha(ks.numpy())
+        out[f"quant_bulk_sha_vs{bits}"] = sha(vs.numpy())
+
+
+def gen_attention(out):
+    # mixed-precision cache through the reference store, then both attention oracles
+    for tag, (hq, hkv, d, n, b) in {"c0s": (32, 4, 64, 200, 1), "l8s": (32, 8, 128, 150, 2)}.items():
+        g = hq // hkv
+        k, v = orc.synth_kv(n, hkv, d, seed=21)
+        rng = np.random.default_rng(22)
+        bits = rng.choice([2, 3, 4, 8], size=n).astype(np.int64)
+        q = rng.standard_normal((b, hq, 1, d)).astype(np.float32)
+        ck = rng.standard_normal((b, hkv, d)).astype(np.float32)
+        cv = rng.standard_normal((b, hkv, d)).astype(np.float32)
+        c = SmartKVCache(num_layers=1, num_heads=hkv, head_dim=d, memory_budget=0.9, device="cpu")
+        c.precision_map.update({t: int(bits[t]) for t in range(n)})
+        c.quantize_and_store_batch(0, list(range(n)), torch.from_numpy(k), torch.from_numpy(v))
+        pq = c.retrieve_all_quantized(0)
+        kq = pq["k_qx"].repeat_interleave(g, dim=1)
+        vq = pq["v_qx"].repeat_interleave(g, dim=1)
+        ks = pq["k_scale"].repeat_interleave(g, dim=1)
+        vs = pq["v_scale"].repeat_interleave(g, dim=1)
+        cke = torch.from_numpy(ck).repeat_interleave(g, dim=1)
+        cve = torch.from_numpy(cv).repeat_interleave(g, dim=1)
+        # The reference's streaming path slices its flattened query as if it were
+        # ordered (head, batch) (fused_cpu.py:78-84), which is only right for
+        # batch 1; every sequence is therefore run as its own batch-1 call.
+        outs, probs, outs_nc, probs_nc = [], [], [], []
+        for bi in range(b):
+            qb = torch.from_numpy(q[bi:bi + 1])
+            o, p = quantized_attention_streaming_cpu(qb, kq, ks, vq, vs, tile_size=64, current_k=cke[bi:bi + 1],
+                                                     current_v=cve[bi:bi + 1], return_attn=True)
+            o_n, p_n = quantized_attention_streaming_cpu(qb, kq, ks, vq, vs, tile_size=None, return_attn=True)
+            outs.append(o); probs.append(p); outs_nc.append(o_n); probs_nc.append(p_n)
+        o, p = torch.cat(outs), torch.cat(probs)
+        o_nocur, p_nocur = torch.cat(outs_nc), torch.cat(probs_nc)
+        kk = kq.permute(1, 0, 2).unsqueeze(0).expand(b, -1, -1, -1)
+        vv = vq.permute(1, 0, 2).unsqueeze(0).expand(b, -1, -1, -1)
+        o2 = _quantized_attention_pytorch(torch.from_numpy(q), kk, ks.t().unsqueeze(0).expand(b, -1, -1),
+                                          vv, vs.t().unsqueeze(0).expand(b, -1, -1))
+        out[f"attn_{tag}_shape"] = np.array([hq, hkv, d, n, b])
+        out[f"attn_{tag}_bits"] = bits
+        out[f"attn_{tag}_q"] = q
+        out[f"attn_{tag}_ck"] = ck
+        out[f"attn_{tag}_cv"] = cv
+        out[f"attn_{tag}_kq"] = pq["k_qx"].numpy()
+        out[f"attn_{tag}_vq"] = pq["v_qx"].numpy()
+        out[f"attn_{tag}_ks"] = pq["k_scale"].numpy()
+        out[f"attn_{tag}_vs"] = pq["v_scale"].numpy()
+        out[f"attn_{tag}_stream_out"] = o.numpy()
+        out[f"attn_{tag}_stream_probs"] = p.numpy()
+        out[f"attn_{tag}_nocur_out"] = o_nocur.numpy()
+        out[f"attn_{tag}_nocur_probs"] = p_nocur.numpy()
+        out[f"attn_{tag}_dequant_out"] = o2.numpy()
+
+
+def gen_importance(out):
+    L, hq, n = 3, 8, 40
+    rng = np.random.default_rng(31)
+    c = SmartKVCache(num_layers=L, num_heads=2, head_dim=16, memory_budget=0.9, device="cpu", realloc_freq=10 ** 9)
+    c.token_counter = 1          # keeps the reallocation trigger from firing (cache.py:277)
+    probs_all = []
+    for step in range(4):
+        for layer in range(L):
+            nk = n + step
+            lg = rng.standard_normal((2, hq, 1, nk)).astype(np.float32) * 2
+            p = torch.softmax(torch.from_numpy(lg), dim=-1)
+            probs_all.append(p.numpy())
+            c.update_attention(layer, p, list(range(nk)))
+    out["imp_shape"] = np.array([L, hq, n, 4])
+    for i, p in enumerate(probs_all):
+        out[f"imp_probs_{i}"] = p
+    ids = sorted(c.importance_tracker.token_importance)
+    out["imp_token_ids"] = np.array(ids)
+    out["imp_cumulative"] = np.array([c.importance_tracker.token_importance[t] for t in ids], np.float64)
+    out["imp_layer_ema"] = np.array([[c.importance_tracker.layer_importance.get((l, t), np.nan) for t in ids]
+                                     for l in range(L)], np.float64)
+    out["imp_head_importance"] = c.head_importance.numpy()
+    out["imp_global_step"] = np.array([c.global_step])
+
+
+def gen_allocation(out):
+    cases = []
+    rng = np.random.default_rng(41)
+    specs = [
+        (2048, 4, 64, 0.35, (2, 3, 4, 8), 1.1, False, {}),       # config-0 shape
+        (777, 8, 128, 0.25, (2, 3, 4, 8), 1.2, False, {}),
+        (600, 8, 128, 0.35, (2, 4, 8), 1.1, True, {}),            # ties / zeros
+        (300, 4, 64, 0.5, (2, 3, 4, 8), 1.1, True, {}),
+        (1000, 8, 128, 0.25, (2, 4, 8), 1.1, False,
+         dict(utility_alpha=0.75, high_precision_fraction=0.05, high_precision_boost=3.0,
+              min_high_precision_tokens=128)),                    # the reference benchmark's settings
+        (400, 8, 128, 0.17, (2, 3, 4, 8), 1.1, False, {}),        # baseline already above 85% of budget
+        (40, 4, 64, 0.35, (2, 3, 4, 8), 1.1, False, {}),          # tiny
+        (500, 8, 128, 0.2, (2, 3, 4, 8), 1.1, False, dict(high_precision_fraction=0.3)),  # post-pass active
+    ]
+    for ci, (n, h, d, beta, bits, s, ties, kw) in enumerate(specs):
+        imp = orc.synth_importance(n, seed=100 + ci, zipf_s=s)
+        if ties:
+            imp = np.round(imp, 4).astype(np.float32)
+        c = packed_cache(1, h, d, beta, bits, **kw)
+        scores = {t: (float("inf") if t < 4 else float(imp[t])) for t in range(n)}
+        prot = c.protected_tokens | c.special_token_ids
+        a1 = c._solve_allocation(set(range(n)), scores, prot)
+        # second call on perturbed scores exercises the persistent rank state
+        imp2 = imp.copy()
+        sw = rng.permutation(n)[: n // 5]
+        imp2[sw] = imp2[sw[::-1]]
+        scores2 = {t: (float("inf") if t < 4 else float(imp2[t])) for t in range(n)}
+        a2 = c._solve_allocation(set(range(n)), scores2, prot)
+        a3 = c._solve_allocation(set(range(n)), scores2, prot)
+        out[f"alloc_{ci}_spec"] = np.array([n, h, d, len(bits)] + list(bits))
+        out[f"alloc_{ci}_beta"] = np.array([beta, kw.get("utility_alpha", 0.5),
+                                            kw.get("high_precision_fraction", 0.02),
+                                            kw.get("high_precision_boost", 1.5),
+                                            kw.get("min_high_precision_tokens", 0)], np.float64)
+        out[f"alloc_{ci}_imp"] = imp
+        out[f"alloc_{ci}_imp2"] = imp2
+        out[f"alloc_{ci}_bits1"] = np.array([a1[t] for t in range(n)], np.uint8)
+        out[f"alloc_{ci}_bits2"] = np.array([a2[t] for t in range(n)], np.uint8)
+        out[f"alloc_{ci}_bits3"] = np.array([a3[t] for t in range(n)], np.uint8)
+        out[f"alloc_{ci}_ratio1"] = np.array([compute_memory_usage(a1, num_heads=h, head_dim=d, scale_dtype="fp32",
+                                                                   use_packing=True)["memory_ratio_true"]])
+        cases.append(ci)
+    out["alloc_cases"] = np.array(cases)
+    out["min_budget"] = np.array([compute_minimum_budget(8, 128, "fp32", False), compute_minimum_budget(8, 128, "fp16", False),
+                                  compute_minimum_budget(8, 128, "fp32", True), compute_minimum_budget(8, 128, "fp16", True)])
+
+
+def gen_requant(out):
+    """Cache-level flow in packed accounting: store at default 4 bits, inject
+    importance, allocate_precision (requantises changed tokens from their
+    dequantised codes), then read everything back."""
+    L, h, d, n = 2, 4, 64, 256
+    c = packed_cache(L, h, d, 0.35)
+    ks, vs = [], []
+    for l in range(L):
+        k, v = orc.synth_kv(n, h, d, seed=50 + l)
+        ks.append(k)
+        vs.append(v)
+        c.quantize_and_store_batch(l, list(range(n)), torch.from_numpy(k), torch.from_numpy(v))
+    imp = orc.synth_importance(n, seed=55)
+    for t in range(n):
+        c.importance_tracker.token_importance[t] = float(imp[t])
+        c.last_seen[t] = c.global_step
+    c.allocate_precision(0, list(range(n)))
+    bits = np.array([c.precision_map[t] for t in range(n)], np.uint8)
+    out["requant_shape"] = np.array([L, h, d, n])
+    out["requant_imp"] = imp
+    out["requant_bits"] = bits
+    for l in range(L):
+        kd, vd = c.retrieve_all(l)
+        out[f"requant_k_deq_{l}"] = kd.numpy()
+        out[f"requant_v_deq_{l}"] = vd.numpy()
+        out[f"requant_k_scale_{l}"] = c.layer_store[l]["k_scale"][:n].numpy().copy()
+        out[f"requant_v_scale_{l}"] = c.layer_store[l]["v_scale"][:n].numpy().copy()
+    # second reallocation with shuffled importance -> codes requantised twice
+    imp2 = orc.synth_importance(n, seed=56)
+    for t in range(n):
+        c.importance_tracker.token_importance[t] = float(imp2[t])
+    c._rank_state.clear()
+    c.allocate_precision(0, list(range(n)))
+    out["requant_imp2"] = imp2
+    out["requant_bits2"] = np.array([c.precision_map[t] for t in range(n)], np.uint8)
+    for l in range(L):
+        kd, vd = c.retrieve_all(l)
+        out[f"requant2_k_deq_{l}"] = kd.numpy()
+        out[f"requant2_v_deq_{l}"] = vd.numpy()
+
+
+def gen_config0(out):
+    """BASELINE config 0 end to end on the reference CPU path: TinyLlama
+    attention shape, context 2048, budget 0.35, one decode step."""
+    hq, hkv, d, n = 32, 4, 64, 2048
+    g = hq // hkv
+    k, v = orc.synth_kv(n, hkv, d, seed=0)
+    imp = orc.synth_importance(n, seed=0, zipf_s=1.1)
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, hq, 1, d)).astype(np.float32)
+    ck = rng.standard_normal((1, hkv, d)).astype(np.float32)
+    cv = rng.standard_normal((1, hkv, d)).astype(np.float32)
+    c = packed_cache(1, hkv, d, 0.35)
+    for t in range(n):
+        c.importance_tracker.token_importance[t] = float(imp[t])
+        c.last_seen[t] = c.global_step
+    c.precision_map = c._solve_allocation(set(range(n)), {t: (float("inf") if t < 4 else float(imp[t])) for t in range(n)},
+                                          c.protected_tokens | c.special_token_ids)
+    bits = np.array([c.precision_map[t] for t in range(n)], np.uint8)
+    c.quantize_and_store_batch(0, list(range(n)), torch.from_numpy(k), torch.from_numpy(v))
+    kd, vd = c.retrieve_all(0)      # dequantised fp32 [N,Hkv,D]
+    # rebuild integer codes from the store for the fused CPU call
+    kq = torch.round(kd / c.layer_store[0]["k_scale"][:n].unsqueeze(-1)).to(torch.int8)
+    vq = torch.round(vd / c.layer_store[0]["v_scale"][:n].unsqueeze(-1)).to(torch.int8)
+    ks = c.layer_store[0]["k_scale"][:n]
+    vs = c.layer_store[0]["v_scale"][:n]
+    o, p = quantized_attention_streaming_cpu(torch.from_numpy(q), kq.repeat_interleave(g, 1), ks.repeat_interleave(g, 1),
+                                             vq.repeat_interleave(g, 1), vs.repeat_interleave(g, 1), tile_size=2048,
+                                             current_k=torch.from_numpy(ck).repeat_interleave(g, 1),
+                                             current_v=torch.from_numpy(cv).repeat_interleave(g, 1), return_attn=True)
+    out["c0_bits"] = bits
+    out["c0_hist"] = np.array([(bits == b).sum() for b in (2, 3, 4, 8)])
+    out["c0_sha_kcodes"] = sha(kq.numpy())
+    out["c0_sha_vcodes"] = sha(vq.numpy())
+    out["c0_sha_kscale"] = sha(ks.numpy())
+    out["c0_out"] = o.numpy()
+    out["c0_keymass"] = p.numpy().sum(axis=(0, 1, 2))
+    out["c0_probs_head0"] = p.numpy()[0, 0, 0]
+
+
+def main():
+    torch.manual_seed(0)
+    torch.set_num_threads(4)
+    for name, fn in [("quant", gen_quant), ("attention", gen_attention), ("importance", gen_importance),
+                     ("allocation", gen_allocation), ("requant", gen_requant), ("config0", gen_config0)]:
+        out = {}
+        fn(out)
+        path = os.path.join(HERE, f"{name}.npz")
+        np.savez_compressed(path, **out)
+        print(name, os.path.getsize(path) // 1024, "KiB")
+
+
+if __name__ == "__main__":
+    main()
