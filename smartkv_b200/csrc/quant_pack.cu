@@ -1,0 +1,322 @@
+// Per-(token, head) symmetric quantisation, bit packing, and the append into
+// the bucketed store.  One warp owns one row of head_dim values.
+//
+// Arithmetic follows the reference CPU quantiser (smartkv/core/_quant_cpu.py:20-34):
+// scale = absmax / max(max_code, 1) with an IEEE fp32 divide, 0 -> 1,
+// code = clamp(rint(x / scale)) with round-half-even.  No fast-math anywhere in
+// this file: codes and scales are bit-exact with the CPU path.
+// Packed format: smartkv/csrc/bit_packing.cu:20-43, 69-95, 128-151.
+#include "common.cuh"
+
+namespace skv {
+
+template <int EPL>  // elements per lane: head_dim / 32
+struct RowVals {
+  float v[EPL];
+};
+
+template <int EPL>
+__device__ __forceinline__ RowVals<EPL> load_row(const void* base, int dtype, long long row, int lane) {
+  RowVals<EPL> r;
+  constexpr int D = EPL * 32;
+  if (dtype == SKV_DTYPE_F32) {
+    const float* p = static_cast<const float*>(base) + row * D + lane * EPL;
+    if constexpr (EPL == 4) {
+      float4 f = *reinterpret_cast<const float4*>(p);
+      r.v[0] = f.x; r.v[1] = f.y; r.v[2] = f.z; r.v[3] = f.w;
+    } else {
+      float2 f = *reinterpret_cast<const float2*>(p);
+      r.v[0] = f.x; r.v[1] = f.y;
+    }
+  } else {
+    const __half* p = static_cast<const __half*>(base) + row * D + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < EPL; i += 2) {
+      __half2 h = *reinterpret_cast<const __half2*>(p + i);
+      r.v[i] = __low2float(h);
+      r.v[i + 1] = __high2float(h);
+    }
+  }
+  return r;
+}
+
+// Quantise one row held across a warp.  Returns this lane's EPL codes and the row scale.
+template <int EPL>
+__device__ __forceinline__ float quantize_row(const RowVals<EPL>& x, int bits, int (&code)[EPL]) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) amax = fmaxf(amax, fabsf(x.v[i]));
+  amax = warp_max(amax);
+  const int hi = (1 << (bits - 1)) - 1, lo = -(1 << (bits - 1));
+  float scale = __fdiv_rn(amax, (float)(hi > 1 ? hi : 1));
+  if (scale == 0.f) scale = 1.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    float q = rintf(__fdiv_rn(x.v[i], scale));
+    q = fminf(fmaxf(q, (float)lo), (float)hi);
+    code[i] = (int)q;
+  }
+  return scale;
+}
+
+// Packs the warp's row (EPL codes per lane, element index = lane*EPL + i) and
+// stores row_bytes = 32*EPL*bits/8 bytes at dst (4-byte aligned).
+template <int EPL>
+__device__ __forceinline__ void pack_store_row(const int (&code)[EPL], int bits, uint8_t* dst, int lane) {
+  const int wbits = bits * EPL;  // bits this lane contributes
+  uint32_t mine = 0;
+  if (bits == 8) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) mine |= ((uint32_t)code[i] & 0xffu) << (8 * i);
+  } else {
+    const int off = 1 << (bits - 1);
+    const uint32_t fm = (1u << bits) - 1u;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) mine |= (((uint32_t)(code[i] + off)) & fm) << (bits * i);
+  }
+  // output word `lane` covers row bits [32*lane, 32*lane+32): gather the lanes that overlap it
+  const int nwords = wbits;  // 32 lanes * wbits bits / 32
+  const int first = (32 * lane) / wbits;
+  uint32_t word = 0;
+  const int max_src = 32 / wbits + 2;
+  for (int j = 0; j < max_src; ++j) {
+    int src = first + j;
+    uint32_t v = __shfl_sync(0xffffffffu, mine, src & 31);
+    int pos = src * wbits - 32 * lane;  // bit position of that lane's field inside my word
+    if (src < 32 && pos < 32 && pos + wbits > 0) word |= (pos >= 0) ? (v << pos) : (v >> (-pos));
+  }
+  if (lane < nwords) reinterpret_cast<uint32_t*>(dst)[lane] = word;
+}
+
+// ---- append into the store ----------------------------------------------------
+template <int EPL>
+__global__ void quantize_pack_append_kernel(StoreGeom g, uint8_t* store, int layer, const void* k, const void* v,
+                                            int dtype, int rows, const int32_t* dst_seq, const int32_t* dst_bucket,
+                                            const int32_t* dst_pos, int32_t* err) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)rows * g.num_kv_heads * 2;
+  if (warp >= total) return;
+  const int which = (int)(warp & 1);  // 0 = K, 1 = V
+  const long long rh = warp >> 1;
+  const int h = (int)(rh % g.num_kv_heads);
+  const int r = (int)(rh / g.num_kv_heads);
+  const int seq = dst_seq[r], bucket = dst_bucket[r], pos = dst_pos[r];
+  if (seq < 0 || seq >= g.num_seqs || bucket < 0 || bucket >= kNumBuckets || pos < 0 || pos >= g.cap[bucket]) {
+    if (lane == 0 && err) atomicExch(err, 2);
+    return;
+  }
+  const int bits = bucket_bits(bucket);
+  RowVals<EPL> x = load_row<EPL>(which ? v : k, dtype, rh, lane);
+  int code[EPL];
+  const float scale = quantize_row<EPL>(x, bits, code);
+  uint8_t* arena = arena_ptr(g, store, layer, seq);
+  const long long row_index = (long long)h * g.cap[bucket] + pos;
+  uint8_t* dst = arena + (which ? g.v_off[bucket] : g.k_off[bucket]) + row_index * g.row_bytes[bucket];
+  pack_store_row<EPL>(code, bits, dst, lane);
+  if (lane == 0) {
+    float* sc = reinterpret_cast<float*>(arena + (which ? g.vs_off[bucket] : g.ks_off[bucket]));
+    sc[row_index] = scale;
+  }
+}
+
+// ---- plain quantise (parity helper) --------------------------------------------
+template <int EPL>
+__global__ void quantize_rows_kernel(const void* in, int dtype, long long rows, int bits, int8_t* codes,
+                                     float* scales) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp >= rows) return;
+  RowVals<EPL> x = load_row<EPL>(in, dtype, warp, lane);
+  int code[EPL];
+  const float scale = quantize_row<EPL>(x, bits, code);
+  constexpr int D = EPL * 32;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) codes[warp * D + lane * EPL + i] = (int8_t)code[i];
+  if (lane == 0) scales[warp] = scale;
+}
+
+// Generic row quantiser for any head_dim (one warp per row, strided); used when
+// head_dim is not 64 or 128.
+__global__ void quantize_rows_generic_kernel(const void* in, int dtype, long long rows, int D, int bits,
+                                             int8_t* codes, float* scales) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp >= rows) return;
+  auto ld = [&](int d) -> float {
+    return dtype == SKV_DTYPE_F32 ? static_cast<const float*>(in)[warp * D + d]
+                                  : __half2float(static_cast<const __half*>(in)[warp * D + d]);
+  };
+  float amax = 0.f;
+  for (int d = lane; d < D; d += 32) amax = fmaxf(amax, fabsf(ld(d)));
+  amax = warp_max(amax);
+  const int hi = (1 << (bits - 1)) - 1, lo = -(1 << (bits - 1));
+  float scale = __fdiv_rn(amax, (float)(hi > 1 ? hi : 1));
+  if (scale == 0.f) scale = 1.f;
+  for (int d = lane; d < D; d += 32) {
+    float q = rintf(__fdiv_rn(ld(d), scale));
+    codes[warp * D + d] = (int8_t)(int)fminf(fmaxf(q, (float)lo), (float)hi);
+  }
+  if (lane == 0) scales[warp] = scale;
+}
+
+// ---- flat pack / unpack (parity helpers) ---------------------------------------
+// One thread per output byte group; partial trailing groups are zero filled.
+__global__ void pack_flat_kernel(const int8_t* codes, long long n, int bits, uint8_t* packed) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (bits == 8) {
+    if (i < n) packed[i] = (uint8_t)codes[i];
+    return;
+  }
+  const int per = bits == 2 ? 4 : bits == 4 ? 2 : 8;
+  const long long groups = (n + per - 1) / per;
+  if (i >= groups) return;
+  const int off = 1 << (bits - 1);
+  const uint32_t fm = (1u << bits) - 1u;
+  uint32_t w = 0;
+  for (int j = 0; j < per; ++j) {
+    long long e = i * per + j;
+    if (e < n) w |= (((uint32_t)(codes[e] + off)) & fm) << (bits * j);
+  }
+  if (bits == 3) {
+    packed[3 * i + 0] = (uint8_t)(w & 0xff);
+    packed[3 * i + 1] = (uint8_t)((w >> 8) & 0xff);
+    packed[3 * i + 2] = (uint8_t)((w >> 16) & 0xff);
+  } else {
+    packed[i] = (uint8_t)w;
+  }
+}
+
+__global__ void unpack_flat_kernel(const uint8_t* packed, long long n, int bits, int8_t* codes) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (bits == 8) {
+    codes[i] = (int8_t)packed[i];
+    return;
+  }
+  const long long bitpos = i * bits;
+  const long long byte = bitpos >> 3;
+  const int sh = (int)(bitpos & 7);
+  uint32_t win = packed[byte];
+  if (sh + bits > 8) win |= (uint32_t)packed[byte + 1] << 8;
+  const uint32_t fm = (1u << bits) - 1u;
+  codes[i] = (int8_t)((int)((win >> sh) & fm) - (1 << (bits - 1)));
+}
+
+// ---- export rows from the store as int8 codes + scales ---------------------------
+__global__ void export_rows_kernel(StoreGeom g, const uint8_t* store, int layer, int rows, const int32_t* src_seq,
+                                   const int32_t* src_bucket, const int32_t* src_pos, int8_t* k_codes,
+                                   int8_t* v_codes, float* k_scale, float* v_scale) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)rows * g.num_kv_heads * 2;
+  if (warp >= total) return;
+  const int which = (int)(warp & 1);
+  const long long rh = warp >> 1;
+  const int h = (int)(rh % g.num_kv_heads);
+  const int r = (int)(rh / g.num_kv_heads);
+  const int seq = src_seq[r], bucket = src_bucket[r], pos = src_pos[r];
+  if (seq < 0 || seq >= g.num_seqs || bucket < 0 || bucket >= kNumBuckets || pos < 0 || pos >= g.cap[bucket]) return;
+  const int bits = bucket_bits(bucket);
+  const uint8_t* arena = arena_ptr(g, store, layer, seq);
+  const long long row_index = (long long)h * g.cap[bucket] + pos;
+  const uint8_t* src = arena + (which ? g.v_off[bucket] : g.k_off[bucket]) + row_index * g.row_bytes[bucket];
+  int8_t* out = (which ? v_codes : k_codes) + rh * g.head_dim;
+  const uint32_t fm = (1u << bits) - 1u;
+  for (int d = lane; d < g.head_dim; d += 32) {
+    int c;
+    if (bits == 8) {
+      c = (int8_t)src[d];
+    } else {
+      const int bitpos = d * bits, byte = bitpos >> 3, sh = bitpos & 7;
+      uint32_t win = src[byte];
+      if (sh + bits > 8) win |= (uint32_t)src[byte + 1] << 8;
+      c = (int)((win >> sh) & fm) - (1 << (bits - 1));
+    }
+    out[d] = (int8_t)c;
+  }
+  if (lane == 0) {
+    const float* sc = reinterpret_cast<const float*>(arena + (which ? g.vs_off[bucket] : g.ks_off[bucket]));
+    (which ? v_scale : k_scale)[rh] = sc[row_index];
+  }
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+static inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+static inline int launch_status() { return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA; }
+
+extern "C" int skv_quantize_per_head(const void* input, int input_dtype, int64_t rows, int head_dim, int bits,
+                                     int8_t* codes, float* scales, void* stream) {
+  if (!input || !codes || !scales || rows < 0 || head_dim <= 0) return SKV_ERR_INVALID;
+  if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return SKV_ERR_INVALID;
+  if (input_dtype != SKV_DTYPE_F32 && input_dtype != SKV_DTYPE_F16) return SKV_ERR_INVALID;
+  if (rows == 0) return SKV_OK;
+  const int wpb = 8;
+  const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+  if (head_dim == 128)
+    quantize_rows_kernel<4><<<grid, wpb * 32, 0, as_stream(stream)>>>(input, input_dtype, rows, bits, codes, scales);
+  else if (head_dim == 64)
+    quantize_rows_kernel<2><<<grid, wpb * 32, 0, as_stream(stream)>>>(input, input_dtype, rows, bits, codes, scales);
+  else
+    quantize_rows_generic_kernel<<<grid, wpb * 32, 0, as_stream(stream)>>>(input, input_dtype, rows, head_dim, bits,
+                                                                          codes, scales);
+  return launch_status();
+}
+
+extern "C" int skv_pack(const int8_t* codes, int64_t n, int bits, uint8_t* packed, void* stream) {
+  if (!codes || !packed || n < 0) return SKV_ERR_INVALID;
+  if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return SKV_ERR_INVALID;
+  if (n == 0) return SKV_OK;
+  const int per = bits == 8 ? 1 : bits == 2 ? 4 : bits == 4 ? 2 : 8;
+  const long long groups = (n + per - 1) / per;
+  pack_flat_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, as_stream(stream)>>>(codes, n, bits, packed);
+  return launch_status();
+}
+
+extern "C" int skv_unpack(const uint8_t* packed, int64_t n, int bits, int8_t* codes, void* stream) {
+  if (!codes || !packed || n < 0) return SKV_ERR_INVALID;
+  if (bits != 2 && bits != 3 && bits != 4 && bits != 8) return SKV_ERR_INVALID;
+  if (n == 0) return SKV_OK;
+  unpack_flat_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(packed, n, bits, codes);
+  return launch_status();
+}
+
+extern "C" int skv_quantize_pack_append(const SkvStoreDesc* desc, void* store, int layer, const void* k,
+                                        const void* v, int input_dtype, int rows, const int32_t* dst_seq,
+                                        const int32_t* dst_bucket, const int32_t* dst_pos, void* stream) {
+  if (!desc || !store || !k || !v || !dst_seq || !dst_bucket || !dst_pos) return SKV_ERR_INVALID;
+  if (layer < 0 || layer >= desc->num_layers || rows < 0) return SKV_ERR_INVALID;
+  if (input_dtype != SKV_DTYPE_F32 && input_dtype != SKV_DTYPE_F16) return SKV_ERR_INVALID;
+  if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
+  if (rows == 0) return SKV_OK;
+  StoreGeom g = make_geom(*desc);
+  const int wpb = 8;
+  const long long warps = (long long)rows * g.num_kv_heads * 2;
+  const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
+  if (desc->head_dim == 128)
+    quantize_pack_append_kernel<4><<<grid, wpb * 32, 0, as_stream(stream)>>>(
+        g, static_cast<uint8_t*>(store), layer, k, v, input_dtype, rows, dst_seq, dst_bucket, dst_pos, nullptr);
+  else
+    quantize_pack_append_kernel<2><<<grid, wpb * 32, 0, as_stream(stream)>>>(
+        g, static_cast<uint8_t*>(store), layer, k, v, input_dtype, rows, dst_seq, dst_bucket, dst_pos, nullptr);
+  return launch_status();
+}
+
+extern "C" int skv_export_rows(const SkvStoreDesc* desc, const void* store, int layer, int rows,
+                               const int32_t* src_seq, const int32_t* src_bucket, const int32_t* src_pos,
+                               int8_t* k_codes, int8_t* v_codes, float* k_scale, float* v_scale, void* stream) {
+  if (!desc || !store || !src_seq || !src_bucket || !src_pos || !k_codes || !v_codes || !k_scale || !v_scale)
+    return SKV_ERR_INVALID;
+  if (layer < 0 || layer >= desc->num_layers || rows < 0) return SKV_ERR_INVALID;
+  if (rows == 0) return SKV_OK;
+  StoreGeom g = make_geom(*desc);
+  const int wpb = 8;
+  const long long warps = (long long)rows * g.num_kv_heads * 2;
+  export_rows_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, as_stream(stream)>>>(
+      g, static_cast<const uint8_t*>(store), layer, rows, src_seq, src_bucket, src_pos, k_codes, v_codes, k_scale,
+      v_scale);
+  return launch_status();
+}

@@ -1,0 +1,262 @@
+"""Device-resident bucketed KV store and the decode-step driver over the C ABI.
+
+``PackedKVStore`` owns the HBM arenas (one per layer and sequence, four packed
+buckets each), the per-sequence bookkeeping kept in *storage order* and the
+scratch buffers of the attention path.  Every compute step is a call into
+``libsmartkv_b200.so``; torch is used for device memory, streams and the few
+index computations that place tokens into buckets.
+
+What it replaces in the reference: the growable int8 buffers, per-token dicts
+and per-bucket tensors of ``SmartKVCache`` (smartkv/core/cache.py:928-1161) and
+the clone-everything read path (``retrieve_all_quantized``, cache.py:1441-1491).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import BITS_TO_BUCKET, BUCKET_BITS, NUM_BUCKETS, StoreDesc, check, ptr
+
+
+def round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def bucket_capacities(max_tokens: int, memory_budget: Optional[float] = None, head_dim: int = 128,
+                      available_bits: Sequence[int] = (2, 3, 4, 8), slack: int = 128) -> Tuple[int, ...]:
+    """Capacity (tokens) of each bucket for sequences of up to ``max_tokens``.
+
+    Without a budget every bucket can hold every token.  With a budget, a
+    bucket of width w can never hold more than ``budget*16*N / w`` tokens plus
+    the protected ones, because those tokens alone would exhaust the byte
+    budget the allocator enforces (smartkv/core/cache.py:374-388, 502-505).
+    New tokens enter at 4 bits (cache.py:1214), so that bucket keeps room for
+    a reallocation interval's worth of appends.
+    """
+    caps = []
+    for bits in BUCKET_BITS:
+        if bits not in available_bits and bits != 4:
+            caps.append(0)
+            continue
+        cap = max_tokens
+        if memory_budget is not None and bits > min(available_bits):
+            cap = min(max_tokens, int(memory_budget * 16.0 * max_tokens / bits) + 64)
+        caps.append(round_up(cap + slack, 128))
+    return tuple(caps)
+
+
+class PackedKVStore:
+    def __init__(self, num_layers: int, num_seqs: int, num_kv_heads: int, head_dim: int, num_q_heads: int,
+                 caps: Sequence[int], device="cuda", decay: float = 0.9, head_decay: float = 0.9,
+                 track_importance: bool = True):
+        self.lib = _lib.lib()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise _lib.SmartKVLibraryError("PackedKVStore needs a CUDA device; there is no CPU path")
+        self.num_layers, self.num_seqs = num_layers, num_seqs
+        self.num_kv_heads, self.head_dim, self.num_q_heads = num_kv_heads, head_dim, num_q_heads
+        self.group = num_q_heads // num_kv_heads
+        self.decay, self.head_decay = float(decay), float(head_decay)
+        d = StoreDesc()
+        d.num_layers, d.num_seqs, d.num_kv_heads, d.head_dim = num_layers, num_seqs, num_kv_heads, head_dim
+        for i, c in enumerate(caps):
+            d.cap[i] = int(c)
+        check(self.lib.skv_store_layout(ctypes.byref(d)), "skv_store_layout")
+        self.desc = d
+        self.slots = int(d.slots)
+        self.caps = tuple(int(c) for c in d.cap)
+        self.bucket_base = tuple(int(c) for c in d.bucket_base)
+        dev = self.device
+        # zero-filled so that rows never written decode to finite numbers
+        self.arena = torch.zeros(int(d.total_bytes), dtype=torch.uint8, device=dev)
+        self.counts = torch.zeros((num_seqs, NUM_BUCKETS), dtype=torch.int32, device=dev)
+        self.slot_token = torch.full((num_seqs, self.slots), -1, dtype=torch.int32, device=dev)
+        self.next_token = torch.zeros(num_seqs, dtype=torch.int32, device=dev)
+        self.err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.num_ctas = int(self.lib.skv_attn_num_ctas(dev.index if dev.index is not None else torch.cuda.current_device()))
+        pbytes = int(self.lib.skv_attn_partials_bytes(ctypes.byref(d), num_q_heads, self.num_ctas))
+        self.partials = torch.empty(pbytes // 4, dtype=torch.float32, device=dev)
+        self.out = torch.empty((num_seqs, num_q_heads, head_dim), dtype=torch.float32, device=dev)
+        self.lse_max = torch.empty((num_seqs, num_q_heads), dtype=torch.float32, device=dev)
+        self.lse_sum = torch.empty((num_seqs, num_q_heads), dtype=torch.float32, device=dev)
+        self.cur_prob = torch.empty((num_seqs, num_q_heads), dtype=torch.float32, device=dev)
+        self.track_importance = track_importance
+        if track_importance:
+            self.logits = torch.empty((num_seqs, num_q_heads, self.slots), dtype=torch.float32, device=dev)
+            self.cumulative = torch.zeros((num_seqs, self.slots), dtype=torch.float64, device=dev)
+            self.layer_ema = torch.zeros((num_layers, num_seqs, self.slots), dtype=torch.float32, device=dev)
+            self.touched = torch.zeros((num_layers, num_seqs, self.slots), dtype=torch.uint8, device=dev)
+            self.head_state = torch.ones((num_seqs, 2, num_q_heads), dtype=torch.float32, device=dev)
+        else:
+            self.logits = self.cumulative = self.layer_ema = self.touched = self.head_state = None
+        self.head_parity = 0
+        self._bits_lut = torch.full((9,), -1, dtype=torch.int32, device=dev)
+        for bits, b in BITS_TO_BUCKET.items():
+            self._bits_lut[bits] = b
+        self._base_t = torch.tensor(self.bucket_base, dtype=torch.int32, device=dev)
+        self._seq_ids = torch.arange(num_seqs, dtype=torch.int32, device=dev)
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    @staticmethod
+    def _dtype_code(t: torch.Tensor) -> int:
+        if t.dtype == torch.float32:
+            return _lib.DTYPE_F32
+        if t.dtype == torch.float16:
+            return _lib.DTYPE_F16
+        raise TypeError(f"expected float32 or float16, got {t.dtype}")
+
+    def algorithmic_bytes(self) -> int:
+        """Packed bytes one decode step streams per layer: sum over sequences and
+        buckets of n_b * Hkv * 2 * (row_bytes + 4) (reads the live counts: syncs)."""
+        c = self.counts.to("cpu", torch.int64)
+        per_tok = torch.tensor([self.num_kv_heads * 2 * (int(self.desc.row_bytes[i]) + 4) for i in range(NUM_BUCKETS)])
+        return int((c * per_tok).sum())
+
+    # ------------------------------------------------------------------ placement
+    def plan_bulk(self, bits: torch.Tensor):
+        """Place ``bits.shape[1]`` new tokens per sequence (ids continue each
+        sequence's numbering).  bits int [B, n] on the device.  Returns the flat
+        (dst_seq, dst_bucket, dst_pos) arrays for skv_quantize_pack_append and
+        commits the bookkeeping (counts, storage-order token ids)."""
+        B, n = bits.shape
+        assert B == self.num_seqs
+        bucket = self._bits_lut[bits.long()]                        # [B, n]
+        if bool((bucket < 0).any()):
+            raise ValueError("bits must be in {2,3,4,8}")
+        onehot = torch.nn.functional.one_hot(bucket.long(), NUM_BUCKETS).to(torch.int32)   # [B,n,4]
+        rank = torch.cumsum(onehot, dim=1) - onehot                 # tokens of the same bucket before this one
+        pos = (rank * onehot).sum(-1).to(torch.int32) + self.counts.gather(1, bucket.long())
+        added = onehot.sum(1).to(torch.int32)
+        new_counts = self.counts + added
+        caps = torch.tensor(self.caps, dtype=torch.int32, device=self.device)
+        if bool((new_counts > caps).any()):
+            raise _lib.SmartKVLibraryError("bucket capacity exceeded (SKV_ERR_CAPACITY)")
+        token_ids = self.next_token[:, None] + torch.arange(n, dtype=torch.int32, device=self.device)[None]
+        storage = self._base_t[bucket.long()] + pos
+        self.slot_token.scatter_(1, storage.long(), token_ids)
+        self.counts.copy_(new_counts)
+        self.next_token += n
+        dst_seq = self._seq_ids[:, None].expand(B, n).contiguous().view(-1)
+        return dst_seq, bucket.contiguous().view(-1), pos.contiguous().view(-1), storage
+
+    def plan_step(self, bits: Optional[torch.Tensor] = None):
+        """Destination of the token each sequence appends this decode step
+        (same bucket position in every layer); does not commit."""
+        if bits is None:
+            bucket = torch.full((self.num_seqs,), BITS_TO_BUCKET[4], dtype=torch.int32, device=self.device)
+        else:
+            bucket = self._bits_lut[bits.long()]
+        pos = self.counts.gather(1, bucket.long()[:, None])[:, 0].contiguous()
+        storage = (self._base_t[bucket.long()] + pos).to(torch.int32)
+        return self._seq_ids, bucket, pos, storage
+
+    def commit_step(self, plan):
+        _seq, bucket, _pos, storage = plan
+        self.slot_token.scatter_(1, storage.long()[:, None], self.next_token[:, None])
+        self.counts.scatter_add_(1, bucket.long()[:, None], torch.ones((self.num_seqs, 1), dtype=torch.int32, device=self.device))
+        self.next_token += 1
+
+    # ------------------------------------------------------------------ kernels
+    def append(self, layer: int, k: torch.Tensor, v: torch.Tensor, dst_seq, dst_bucket, dst_pos):
+        """k, v: [rows, Hkv, D] fp32/fp16 on the device."""
+        k = k.contiguous()
+        v = v.contiguous()
+        rows = k.shape[0]
+        assert k.shape == (rows, self.num_kv_heads, self.head_dim) and v.shape == k.shape and k.dtype == v.dtype
+        check(self.lib.skv_quantize_pack_append(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(k), ptr(v),
+                                                self._dtype_code(k), rows, ptr(dst_seq), ptr(dst_bucket),
+                                                ptr(dst_pos), self._stream()), "skv_quantize_pack_append")
+
+    def attention(self, layer: int, query: torch.Tensor, cur_k: Optional[torch.Tensor] = None,
+                  cur_v: Optional[torch.Tensor] = None, update_importance: bool = False,
+                  cur_storage: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One decode-attention call for ``layer``: query [B, Hq, D] (fp32/fp16),
+        optional current token cur_k/cur_v [B, Hkv, D].  Returns fp32 [B, Hq, D]."""
+        q = query.contiguous()
+        assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
+        want_logits = update_importance and self.track_importance
+        st = self._stream()
+        check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.counts), ptr(q),
+                                            self._dtype_code(q), self.num_q_heads, ptr(self.partials), self.num_ctas,
+                                            ptr(self.logits) if want_logits else None, ptr(self.err), st),
+              "skv_decode_attention")
+        out = self.out if out is None else out
+        kv_code = _lib.DTYPE_F32
+        if cur_k is not None:
+            cur_k = cur_k.contiguous()
+            cur_v = cur_v.contiguous()
+            kv_code = self._dtype_code(cur_k)
+        check(self.lib.skv_lse_combine(ctypes.byref(self.desc), ptr(self.counts), ptr(q), self._dtype_code(q),
+                                       self.num_q_heads, ptr(self.partials), self.num_ctas, ptr(cur_k), ptr(cur_v),
+                                       kv_code, ptr(out), ptr(self.lse_max), ptr(self.lse_sum), ptr(self.cur_prob), st),
+              "skv_lse_combine")
+        if want_logits:
+            has_cur = cur_k is not None and cur_storage is not None
+            check(self.lib.skv_importance_update(ctypes.byref(self.desc), layer, ptr(self.counts), self.num_q_heads,
+                                                 ptr(self.logits), ptr(self.lse_max), ptr(self.lse_sum),
+                                                 ptr(self.cur_prob) if has_cur else None,
+                                                 ptr(cur_storage) if has_cur else None, ptr(self.head_state),
+                                                 self.head_parity, ptr(self.cumulative), ptr(self.layer_ema),
+                                                 ptr(self.touched), self.decay, self.head_decay, st),
+                  "skv_importance_update")
+            self.head_parity ^= 1
+        return out
+
+    def check_errors(self):
+        """Reads the device error flag (synchronises)."""
+        val = ctypes.c_int32(0)
+        check(self.lib.skv_read_error_flag(ptr(self.err), ctypes.byref(val), self._stream()), "device error flag")
+
+    # ------------------------------------------------------------------ read back (tests, API mirror)
+    def export_sequence(self, layer: int, seq: int):
+        """All cached tokens of one sequence in token-id order: (token_ids, bits,
+        k_codes int8 [n,Hkv,D], v_codes, k_scale fp32 [n,Hkv], v_scale)."""
+        counts = self.counts[seq].tolist()
+        seqs, buckets, poss, ids, bits = [], [], [], [], []
+        for i, c in enumerate(counts):
+            if c == 0:
+                continue
+            poss.append(torch.arange(c, dtype=torch.int32, device=self.device))
+            buckets.append(torch.full((c,), i, dtype=torch.int32, device=self.device))
+            ids.append(self.slot_token[seq, self.bucket_base[i]: self.bucket_base[i] + c])
+            bits.append(torch.full((c,), BUCKET_BITS[i], dtype=torch.int32, device=self.device))
+        n = sum(counts)
+        H, D = self.num_kv_heads, self.head_dim
+        if n == 0:
+            e8 = torch.empty((0, H, D), dtype=torch.int8, device=self.device)
+            ef = torch.empty((0, H), dtype=torch.float32, device=self.device)
+            ei = torch.empty(0, dtype=torch.int32, device=self.device)
+            return ei, ei.clone(), e8, e8.clone(), ef, ef.clone()
+        pos, bucket, ids, bits = torch.cat(poss), torch.cat(buckets), torch.cat(ids), torch.cat(bits)
+        order = torch.argsort(ids)
+        pos, bucket, ids, bits = pos[order].contiguous(), bucket[order].contiguous(), ids[order], bits[order]
+        sq = torch.full((n,), seq, dtype=torch.int32, device=self.device)
+        kc = torch.empty((n, H, D), dtype=torch.int8, device=self.device)
+        vc = torch.empty_like(kc)
+        ks = torch.empty((n, H), dtype=torch.float32, device=self.device)
+        vs = torch.empty_like(ks)
+        check(self.lib.skv_export_rows(ctypes.byref(self.desc), ptr(self.arena), layer, n, ptr(sq), ptr(bucket), ptr(pos),
+                                       ptr(kc), ptr(vc), ptr(ks), ptr(vs), self._stream()), "skv_export_rows")
+        return ids, bits, kc, vc, ks, vs
+
+    def bucket_rows(self, layer: int, seq: int, bucket: int):
+        """Raw packed bytes of one bucket: (K rows uint8 [Hkv, n, row_bytes], V rows, k_scale [Hkv, n], v_scale)."""
+        d = self.desc
+        n = int(self.counts[seq, bucket])
+        base = (layer * self.num_seqs + seq) * int(d.arena_bytes)
+        H, cap, rb = self.num_kv_heads, self.caps[bucket], int(d.row_bytes[bucket])
+
+        def region(off, nbytes_row, dtype):
+            raw = self.arena[base + off: base + off + H * cap * nbytes_row]
+            return raw.view(dtype).view(H, cap, -1)[:, :n]
+        k = region(int(d.k_off[bucket]), rb, torch.uint8)
+        v = region(int(d.v_off[bucket]), rb, torch.uint8)
+        ks = region(int(d.ks_off[bucket]), 4, torch.float32)[..., 0]
+        vs = region(int(d.vs_off[bucket]), 4, torch.float32)[..., 0]
+        return k, v, ks, vs

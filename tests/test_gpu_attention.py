@@ -1,0 +1,159 @@
+"""Fused packed decode attention vs the CPU oracle (dequantise-then-attend / streaming,
+fp32).  Tolerance from the north star: 2e-3 max-abs + 1e-3 relative."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import smartkv_oracle as orc
+from tests.gpu_util import assert_close, fill_store, make_store, oracle_attention, oracle_quantized
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-3, 1e-3
+LOG2E = 1.4426950408889634
+
+
+def run_case(hq, hkv, d, lens, seed, q_dtype=np.float32, with_current=True, bits_choices=(2, 3, 4, 8),
+             zipf_bits=False):
+    """lens: tokens per sequence (ragged, zeros allowed)."""
+    B = len(lens)
+    n = max(max(lens), 1)
+    g = hq // hkv
+    rng = np.random.default_rng(seed)
+    store = make_store(1, B, hkv, d, hq, n)
+    # ragged fill: one plan_bulk call per distinct prefix keeps ids dense per sequence
+    ks, vs, bs = [], [], []
+    for b in range(B):
+        k, v = orc.synth_kv(max(lens[b], 1), hkv, d, seed=seed * 100 + b)
+        bits = rng.choice(bits_choices, size=max(lens[b], 1))
+        bits[: min(4, bits.size)] = max(bits_choices)
+        ks.append(k[: lens[b]]); vs.append(v[: lens[b]]); bs.append(bits[: lens[b]])
+    # place tokens sequence by sequence (different lengths): emulate with per-sequence rows
+    for b in range(B):
+        if lens[b] == 0:
+            continue
+        bt = torch.zeros((B, lens[b]), dtype=torch.int64, device="cuda")
+        # only sequence b receives tokens in this call: build the plan by hand
+        bucket = store._bits_lut[torch.from_numpy(bs[b].astype(np.int64)).cuda()]
+        onehot = torch.nn.functional.one_hot(bucket.long(), 4).to(torch.int32)
+        pos = ((torch.cumsum(onehot, 0) - onehot) * onehot).sum(-1).to(torch.int32)
+        store.counts[b] = onehot.sum(0).to(torch.int32)
+        storage = store._base_t[bucket.long()] + pos
+        store.slot_token[b, storage.long()] = torch.arange(lens[b], dtype=torch.int32, device="cuda")
+        store.next_token[b] = lens[b]
+        seq = torch.full((lens[b],), b, dtype=torch.int32, device="cuda")
+        store.append(0, torch.from_numpy(ks[b]).cuda(), torch.from_numpy(vs[b]).cuda(), seq, bucket.contiguous(),
+                     pos.contiguous())
+    q = rng.standard_normal((B, hq, d)).astype(q_dtype)
+    ck = rng.standard_normal((B, hkv, d)).astype(np.float32) if with_current else None
+    cv = rng.standard_normal((B, hkv, d)).astype(np.float32) if with_current else None
+    plan = store.plan_step()
+    out = store.attention(0, torch.from_numpy(q).cuda(), None if ck is None else torch.from_numpy(ck).cuda(),
+                          None if cv is None else torch.from_numpy(cv).cuda(), update_importance=True,
+                          cur_storage=plan[3])
+    store.check_errors()
+    out = out.cpu().numpy()
+    logits = store.logits.cpu().numpy()
+    lmax, lsum = store.lse_max.cpu().numpy(), store.lse_sum.cpu().numpy()
+    cur_prob = store.cur_prob.cpu().numpy()
+    slot_token = store.slot_token.cpu().numpy()
+    for b in range(B):
+        if lens[b] == 0 and not with_current:
+            assert np.all(out[b] == 0)
+            continue
+        kq, vq, kso, vso = oracle_quantized(ks[b], vs[b], bs[b]) if lens[b] else (
+            np.zeros((0, hkv, d), np.int8), np.zeros((0, hkv, d), np.int8), np.zeros((0, hkv), np.float32),
+            np.zeros((0, hkv), np.float32))
+        ref_o, ref_p = oracle_attention(q[b].astype(np.float32), kq, vq, kso, vso, g,
+                                        None if ck is None else ck[b], None if cv is None else cv[b])
+        assert_close(out[b], ref_o, ATOL, RTOL, f"out seq {b}")
+        # probabilities rebuilt from the emitted logits, in token order
+        valid = slot_token[b] >= 0
+        order = np.argsort(slot_token[b][valid])
+        p = np.exp2(logits[b][:, valid][:, order] - lmax[b][:, None]) / lsum[b][:, None]
+        assert_close(p, ref_p[:, : lens[b]], 2e-4, 2e-3, f"probs seq {b}")
+        if with_current:
+            assert_close(cur_prob[b], ref_p[:, lens[b]], 2e-4, 2e-3, f"current-token prob seq {b}")
+            assert_close(p.sum(-1) + cur_prob[b], np.ones(hq), 1e-4, 0, "probabilities sum to one")
+    return store
+
+
+@pytest.mark.parametrize("q_dtype", [np.float32, np.float16])
+def test_config0_shape(q_dtype):
+    # TinyLlama attention shape, context 2048, one decode step
+    run_case(32, 4, 64, [2048], seed=0, q_dtype=q_dtype)
+
+
+@pytest.mark.parametrize("q_dtype", [np.float32, np.float16])
+def test_llama8b_shape_ragged_batch(q_dtype):
+    run_case(32, 8, 128, [700, 1, 0, 333, 2049, 16], seed=1, q_dtype=q_dtype)
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(64, 8, 128), (8, 8, 64), (16, 8, 128), (4, 4, 128), (32, 4, 64)])
+def test_group_sizes(hq, hkv, d):
+    run_case(hq, hkv, d, [257, 100], seed=2)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+@pytest.mark.parametrize("d", [64, 128])
+def test_uniform_width(bits, d):
+    run_case(16, 4, d, [415], seed=3 + bits, bits_choices=(bits,))
+
+
+def test_no_current_token_and_empty():
+    run_case(32, 8, 128, [0, 77], seed=9, with_current=False)
+
+
+def test_long_context_many_ctas():
+    # more blocks than CTAs, several CTAs per (sequence, head) segment
+    run_case(32, 8, 128, [40000], seed=11, bits_choices=(2, 3, 4, 8))
+
+
+def test_golden_reference_outputs(golden):
+    """Stored codes recorded from the reference cache + its streaming CPU attention output."""
+    g = golden("attention")
+    for tag in ("c0s", "l8s"):
+        hq, hkv, d, n, b = [int(x) for x in g[f"attn_{tag}_shape"]]
+        bits = g[f"attn_{tag}_bits"]
+        k, v = orc.synth_kv(n, hkv, d, seed=21)
+        store = make_store(1, b, hkv, d, hq, n)
+        fill_store(store, [(np.broadcast_to(k, (b,) + k.shape).copy(), np.broadcast_to(v, (b,) + v.shape).copy())],
+                   np.broadcast_to(bits, (b, n)).copy())
+        for bi in range(b):
+            ids, wb, kc, vc, ks, vs = store.export_sequence(0, bi)
+            assert np.array_equal(kc.cpu().numpy(), g[f"attn_{tag}_kq"])
+            assert np.array_equal(vc.cpu().numpy(), g[f"attn_{tag}_vq"])
+            assert np.array_equal(ks.cpu().numpy(), g[f"attn_{tag}_ks"])
+        q = torch.from_numpy(g[f"attn_{tag}_q"][:, :, 0]).cuda()
+        out = store.attention(0, q, torch.from_numpy(g[f"attn_{tag}_ck"]).cuda(), torch.from_numpy(g[f"attn_{tag}_cv"]).cuda())
+        store.check_errors()
+        assert_close(out.cpu().numpy(), g[f"attn_{tag}_stream_out"][:, :, 0], ATOL, RTOL, tag)
+        out = store.attention(0, q)
+        assert_close(out.cpu().numpy(), g[f"attn_{tag}_dequant_out"][:, :, 0], ATOL, RTOL, tag + " no current")
+
+
+def test_config0_golden_pipeline(golden):
+    g = golden("config0")
+    hq, hkv, d, n = 32, 4, 64, 2048
+    k, v = orc.synth_kv(n, hkv, d, seed=0)
+    bits = g["c0_bits"].astype(np.int64)
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, hq, 1, d)).astype(np.float32)
+    ck = rng.standard_normal((1, hkv, d)).astype(np.float32)
+    cv = rng.standard_normal((1, hkv, d)).astype(np.float32)
+    store = make_store(1, 1, hkv, d, hq, n)
+    fill_store(store, [(k[None], v[None])], bits[None])
+    plan = store.plan_step()
+    out = store.attention(0, torch.from_numpy(q[:, :, 0]).cuda(), torch.from_numpy(ck).cuda(), torch.from_numpy(cv).cuda(),
+                          update_importance=True, cur_storage=plan[3])
+    store.check_errors()
+    assert_close(out.cpu().numpy(), g["c0_out"][:, :, 0], ATOL, RTOL, "config 0 output")
+    # per-key probability mass summed over heads (unweighted) against the reference's
+    logits = store.logits.cpu().numpy()[0]
+    lmax, lsum = store.lse_max.cpu().numpy()[0], store.lse_sum.cpu().numpy()[0]
+    st = store.slot_token.cpu().numpy()[0]
+    valid = st >= 0
+    order = np.argsort(st[valid])
+    p = np.exp2(logits[:, valid][:, order] - lmax[:, None]) / lsum[:, None]
+    mass = np.concatenate([p.sum(0), [store.cur_prob.cpu().numpy()[0].sum()]])
+    assert_close(mass, g["c0_keymass"], 1e-4, 2e-3, "config 0 key mass")

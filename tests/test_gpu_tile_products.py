@@ -1,0 +1,36 @@
+"""The tensor-core fragment path (register unpack + mma.sync) on integer inputs: exact."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import smartkv_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+def test_tile_products_exact(d, bits):
+    from smartkv_b200 import _lib as L
+    lo, hi = orc.code_range(bits)
+    for seed in range(3):
+        rng = np.random.default_rng(seed * 10 + bits + d)
+        kc = rng.integers(lo, hi + 1, size=(16, d)).astype(np.int8)
+        vc = rng.integers(lo, hi + 1, size=(16, d)).astype(np.int8)
+        if seed == 0:      # every code value appears, extremes included
+            kc.reshape(-1)[: hi - lo + 1] = np.arange(lo, hi + 1)
+            vc.reshape(-1)[-(hi - lo + 1):] = np.arange(lo, hi + 1)
+        q = rng.integers(-3, 4, size=(16, d)).astype(np.float16)
+        p = rng.integers(-2, 3, size=(16, 16)).astype(np.float16)
+        kr = torch.from_numpy(orc.pack_rows(kc, bits)).cuda().contiguous()
+        vr = torch.from_numpy(orc.pack_rows(vc, bits)).cuda().contiguous()
+        qt, pt = torch.from_numpy(q).cuda(), torch.from_numpy(p).cuda()
+        scores = torch.empty((16, 16), dtype=torch.float32, device="cuda")
+        out = torch.empty((16, d), dtype=torch.float32, device="cuda")
+        L.check(L.lib().skv_debug_tile_products(d, bits, L.ptr(kr), L.ptr(vr), L.ptr(qt), L.ptr(pt), L.ptr(scores),
+                                                L.ptr(out), L.stream_ptr()))
+        torch.cuda.synchronize()
+        want_s = q.astype(np.float64) @ kc.astype(np.float64).T
+        want_o = p.astype(np.float64) @ vc.astype(np.float64)
+        assert np.array_equal(scores.cpu().numpy().astype(np.float64), want_s), (d, bits, "scores")
+        assert np.array_equal(out.cpu().numpy().astype(np.float64), want_o), (d, bits, "out")
