@@ -1,0 +1,445 @@
+"""Benchmark of the packed-KV decode path (BASELINE config 1).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One *step* = one decode step of the Llama-3.1-8B attention shape (32 query heads,
+8 KV heads, head_dim 128, fp16 query) over 32 layers, batch 16, KV context 8192:
+per layer the fused packed decode attention (+ current fp token, LSE combine),
+the importance update and the quantize-pack append of the new token.  K/V are
+seeded synthetic N(0,1) with 4 outlier channels per head scaled x8, bit-widths come
+from a Zipf(1.1) importance under memory_budget 0.35 (stand-ins for the reference's
+benchmark inputs, which are synthetic randn as well).
+
+metric  = packed-KV bytes streamed per second (algorithmic bytes: sum over buckets of
+          n_b * Hkv * 2 * (row_bytes + 4) per sequence and layer) over the whole step.
+value   = inputs resident in HBM; e2e = the same step driven with HOST buffers
+          (queries / new K,V copied in from pinned memory, outputs copied back).
+roofline= the attention kernel alone (CUDA events around every launch in the timed
+          region) against the measured HBM copy bandwidth in MEASURED_PEAKS.json.
+Under torchrun every rank owns its own shard of KV heads (weak scaling: 8 KV heads
+per GPU); timing is barrier + device events, max over ranks.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(num_layers=32, num_q_heads=32, num_kv_heads=8, head_dim=128, batch=16, context=8192,
+           memory_budget=0.35, available_bits=(2, 3, 4, 8), zipf_s=1.1, realloc_every=16)
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def zipf_importance(n, seed, s):
+    """Zipf(s) mass over positions, rank -> position by a seeded permutation, first 4 = sinks."""
+    rng = np.random.default_rng(seed + 7919)
+    mass = 1.0 / np.arange(1, n + 1, dtype=np.float64) ** s
+    order = rng.permutation(n)
+    order = np.concatenate([np.arange(4), order[order >= 4]])
+    imp = np.empty(n)
+    imp[order] = mass
+    return (imp / imp.sum()).astype(np.float32)
+
+
+def budget_bits(imp, cfg):
+    """Bit-width per token for the benchmark's initial cache state: greedy marginal-gain fill
+    of the byte budget in importance order (utility bits^0.5, steps 2->3->4->8), first four
+    tokens at 8 bits.  Host-side setup only."""
+    n = imp.size
+    H, D = cfg["num_kv_heads"], cfg["head_dim"]
+    bits_asc = sorted(cfg["available_bits"])
+    elements = 2 * H * D
+    budget_units = (cfg["memory_budget"] * n * elements * 16 - n * 2 * H * 32) / elements  # payload bits / elements
+    bits = np.full(n, bits_asc[0], np.int64)
+    bits[:4] = bits_asc[-1]
+    used = float(bits.sum())
+    items = []
+    for j in range(len(bits_asc) - 1):
+        cur, nxt = bits_asc[j], bits_asc[j + 1]
+        gain = (nxt ** 0.5 - cur ** 0.5) / (nxt - cur)
+        for t in range(4, n):
+            items.append((-float(imp[t]) * gain, t, cur, nxt))
+    items.sort()
+    for _neg, t, cur, nxt in items:
+        if bits[t] != cur:
+            continue
+        if used + (nxt - cur) > budget_units:
+            continue
+        bits[t] = nxt
+        used += nxt - cur
+    return bits
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampler running beside the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        try:
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            sm = [float(r[1]) for r in rows if len(r) >= 9]
+            if sm:
+                out["sm_mhz"] = float(np.median(sm))
+                out["sm_max_mhz"] = float(rows[0][2])
+                out["samples"] = len(sm)
+                names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+                for i, nm in enumerate(names):
+                    if any(r[5 + i].strip().lower().startswith("active") for r in rows if len(r) >= 9):
+                        out["reasons"].append(nm)
+        except Exception:
+            pass
+        finally:
+            try:
+                os.unlink(self.path)
+            except Exception:
+                pass
+        return out
+
+
+def algorithmic_bytes_per_layer(counts, cfg):
+    """sum_b n_b * Hkv * 2 * (row_bytes + 4); counts int array [B, 4]."""
+    D, H = cfg["head_dim"], cfg["num_kv_heads"]
+    per_tok = np.array([H * 2 * (D * w // 8 + 4) for w in (2, 3, 4, 8)], np.int64)
+    return int((np.asarray(counts, np.int64) * per_tok).sum())
+
+
+# ----------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from smartkv_b200.store import PackedKVStore, bucket_capacities
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(CFG)
+    if args.layers:
+        cfg["num_layers"] = args.layers      # profiler captures only: fewer layers = less device memory
+    L, Hq, Hkv, D, B, N = (cfg[k] for k in ("num_layers", "num_q_heads", "num_kv_heads", "head_dim", "batch", "context"))
+    steps, warmup = args.steps, args.warmup
+    total_steps = steps * 3 + warmup * 2 + 8
+    caps = bucket_capacities(N + total_steps, cfg["memory_budget"], D, cfg["available_bits"])
+    store = PackedKVStore(L, B, Hkv, D, Hq, caps, device=dev)
+
+    # ---- populate the cache: seeded synthetic K/V, widths from the Zipf importance ----------
+    bits_np = np.stack([budget_bits(zipf_importance(N, 1000 * rank + b, cfg["zipf_s"]), cfg) for b in range(B)])
+    dst = store.plan_bulk(torch.from_numpy(bits_np).to(dev))
+    gen = torch.Generator(device=dev)
+    chan = torch.Generator(device="cpu").manual_seed(1234)
+    out_k = torch.stack([torch.randperm(D, generator=chan)[:4] for _ in range(Hkv)]).to(dev)
+    out_v = torch.stack([torch.randperm(D, generator=chan)[:4] for _ in range(Hkv)]).to(dev)
+    hidx = torch.arange(Hkv, device=dev)[:, None]
+    for layer in range(L):
+        gen.manual_seed(rank * 100003 + 1000 * layer)
+        k = torch.randn((B * N, Hkv, D), generator=gen, device=dev, dtype=torch.float32)
+        v = torch.randn((B * N, Hkv, D), generator=gen, device=dev, dtype=torch.float32)
+        k[:, hidx, out_k] *= 8.0
+        v[:, hidx, out_v] *= 8.0
+        store.append(layer, k, v, dst[0], dst[1], dst[2])
+        del k, v
+    torch.cuda.synchronize()
+    counts0 = store.counts.cpu().numpy()
+    hist = counts0.sum(0).tolist()
+
+    # ---- per-step inputs (resident) -----------------------------------------------------------
+    gen.manual_seed(rank + 99)
+    n_in = 4  # distinct input sets cycled through (each is small; the cache is what is streamed)
+    q_dev = torch.randn((n_in, L, B, Hq, D), generator=gen, device=dev, dtype=torch.float32).half()
+    k_dev = torch.randn((n_in, L, B, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half()
+    v_dev = torch.randn((n_in, L, B, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half()
+    out_dev = torch.empty((L, B, Hq, D), dtype=torch.float32, device=dev)
+    q_host = q_dev.cpu().pin_memory()
+    k_host = k_dev.cpu().pin_memory()
+    v_host = v_dev.cpu().pin_memory()
+    out_host = torch.empty((L, B, Hq, D), dtype=torch.float32).pin_memory()
+    q_stage = torch.empty_like(q_dev[0])
+    k_stage = torch.empty_like(k_dev[0])
+    v_stage = torch.empty_like(v_dev[0])
+
+    attn_events = []
+    launches = [0]
+
+    def decode_step(q, k, v, record=False):
+        """One decode step: 4 kernels of this library per layer (attention, combine, importance,
+        append) plus the torch index ops that place / commit the new token."""
+        plan = store.plan_step()
+        for layer in range(L):
+            ev = None
+            if record:
+                ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                attn_events.append(ev)
+            store.attention(layer, q[layer], k[layer], v[layer], update_importance=True, cur_storage=plan[3],
+                            out=out_dev[layer], kernel_events=ev)
+            store.append(layer, k[layer], v[layer], plan[0], plan[1], plan[2])
+        store.commit_step(plan)
+
+    graph = None
+    if not args.no_graph:
+        # the whole step (every layer's launches) as one CUDA graph over static input buffers
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            q_stage.copy_(q_dev[0]); k_stage.copy_(k_dev[0]); v_stage.copy_(v_dev[0])
+            decode_step(q_stage, k_stage, v_stage)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            decode_step(q_stage, k_stage, v_stage)
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            decode_step(q_stage, k_stage, v_stage)
+        launches[0] += 4 * L
+
+    def resident_step(i):
+        j = i % n_in
+        q_stage.copy_(q_dev[j]); k_stage.copy_(k_dev[j]); v_stage.copy_(v_dev[j])
+        run_step()
+
+    def kernel_timing_step(i):
+        j = i % n_in
+        decode_step(q_dev[j], k_dev[j], v_dev[j], record=True)
+
+    def host_step(i):
+        j = i % n_in
+        q_stage.copy_(q_host[j], non_blocking=True)
+        k_stage.copy_(k_host[j], non_blocking=True)
+        v_stage.copy_(v_host[j], non_blocking=True)
+        run_step()
+        out_host.copy_(out_dev, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n_warm, n_steps, first):
+        for i in range(n_warm):
+            fn(first + i)
+        barrier()
+        c_before = store.counts.cpu().numpy()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(n_steps):
+            fn(first + n_warm + i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if rank == 0 else None
+        c_after = store.counts.cpu().numpy()
+        # bytes streamed: every step reads the cache as it stood at that step
+        per_layer = [algorithmic_bytes_per_layer(c_before, cfg), algorithmic_bytes_per_layer(c_after, cfg)]
+        step_bytes = L * (per_layer[0] + per_layer[1]) / 2.0
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            bt = torch.tensor([step_bytes], device=dev, dtype=torch.float64)
+            dist.all_reduce(bt, op=dist.ReduceOp.SUM)
+            step_bytes = float(bt.item())
+        return ms, step_bytes, clocks
+
+    launches[0] = 0
+    ms, step_bytes, clocks = timed(resident_step, warmup, steps, 0)
+    store.check_errors()
+    n_launch = launches[0] - warmup * L * 4
+    # kernel-only time of the attention kernel: the same steps launched un-graphed with a CUDA
+    # event pair around every attention launch
+    attn_events.clear()
+    ms_k, step_bytes_k, _ = timed(kernel_timing_step, 1, steps, 0)
+    timed_events = attn_events[L:]
+    attn_ms = float(np.mean([a.elapsed_time(b) for a, b in timed_events]))
+    per_layer_bytes = step_bytes_k / L / world
+    peak, peak_kind = measured_peak()
+    achieved = per_layer_bytes / (attn_ms * 1e-3) / 1e9
+    ms_e2e, step_bytes_e2e, _ = timed(host_step, warmup, steps, steps + warmup)
+    store.check_errors()
+
+    value = step_bytes * steps / (ms * 1e-3) / 1e9
+    e2e_value = step_bytes_e2e * steps / (ms_e2e * 1e-3) / 1e9
+    h2d = q_stage.numel() * 2 + k_stage.numel() * 2 + v_stage.numel() * 2
+    d2h = out_dev.numel() * 4
+    line = {
+        "metric": "packed_kv_decode_attention_throughput", "value": round(value, 2), "unit": "GB/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma, f32 accumulate",
+        "data": "synthetic (seeded N(0,1) K/V, 4 outlier channels x8 per head, Zipf(1.1) importance)",
+        "config": {"workload": f"BASELINE config 1: Llama-3.1-8B attention shape, {L} layers, batch 16, context 8192, "
+                               "budget 0.35, bits [2,3,4,8], fp16 query; one decode step per step",
+                   "kv_heads_per_gpu": Hkv, "l2": "inputs larger than L2 (packed cache per step >> 126 MB)",
+                   "bucket_histogram_2_3_4_8": hist, "reallocation": "not in the timed region yet",
+                   "packed_bytes_per_step": int(step_bytes)},
+        "decode_tokens_per_s": round(B * world * steps / (ms * 1e-3), 1),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
+                     "kernel": "decode_attn_kernel", "kernel_ms": round(attn_ms, 4),
+                     "timing": "CUDA event pair around every launch, un-graphed pass of the same steps",
+                     "algorithmic_bytes_per_launch": int(per_layer_bytes)},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / steps, 4)},
+        "gpu_launches": int(n_launch), "cuda_graph": graph is not None,
+        "clocks": clocks,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(cfg, budget_s=args.cpu_seconds)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(cfg, budget_s=15.0):
+    """The oracle port of the reference CPU path (streaming attention over int8 codes with the
+    reference's GQA expansion, importance update) timed on this host for one (sequence, layer)
+    at the full context; GB/s counts the same algorithmic packed bytes."""
+    from oracle import smartkv_oracle as orc
+    try:
+        from threadpoolctl import threadpool_info
+        threads = max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+    except Exception:
+        threads = os.cpu_count() or 1
+    Hq, Hkv, D, N = cfg["num_q_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["context"]
+    g = Hq // Hkv
+    k, v = orc.synth_kv(N, Hkv, D, seed=0)
+    bits = budget_bits(zipf_importance(N, 0, cfg["zipf_s"]), cfg)
+    kq = np.empty(k.shape, np.int8); vq = np.empty(v.shape, np.int8)
+    ks = np.empty(k.shape[:2], np.float32); vs = np.empty(k.shape[:2], np.float32)
+    for w in (2, 3, 4, 8):
+        sel = bits == w
+        kq[sel], ks[sel] = orc.quantize_rows(k[sel], w)
+        vq[sel], vs[sel] = orc.quantize_rows(v[sel], w)
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, Hq, 1, D)).astype(np.float32)
+    ck = rng.standard_normal((1, Hkv, D)).astype(np.float32)
+    cv = rng.standard_normal((1, Hkv, D)).astype(np.float32)
+    counts = np.array([[(bits == w).sum() for w in (2, 3, 4, 8)]])
+    nbytes = algorithmic_bytes_per_layer(counts, cfg)
+    imp = orc.ImportanceState(1)
+
+    def one():
+        # the reference expands K/V to the query heads on every call (llama_smartkv.py:274-281)
+        o, p = orc.streaming_attention(q, orc.expand_gqa(kq, g), orc.expand_gqa(ks, g), orc.expand_gqa(vq, g),
+                                       orc.expand_gqa(vs, g), tile_size=2048, current_k=orc.expand_gqa(ck, g),
+                                       current_v=orc.expand_gqa(cv, g))
+        imp.update(0, p, range(N + 1))
+        orc.quantize_per_head(ck[0][None], cv[0][None], 4)
+    one()
+    t0 = time.perf_counter()
+    it = 0
+    while True:
+        one()
+        it += 1
+        if time.perf_counter() - t0 > budget_s or it >= 200:
+            break
+    dt = (time.perf_counter() - t0) / it
+    return {"value": round(nbytes / dt / 1e9, 4), "unit": "GB/s", "cores": int(threads), "kind": "port",
+            "sample": f"1 sequence x 1 layer at context {N} (attention + importance + append-quantize), {it} iterations, "
+                      f"{dt * 1e3:.1f} ms each; the full step is batch {cfg['batch']} x {cfg['num_layers']} layers of this",
+            "ms_per_sequence_layer": round(dt * 1e3, 3)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(CFG)
+    t0 = time.perf_counter()
+    per_step_budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    vals = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(cfg, budget_s=per_step_budget)
+        if i >= args.warmup:
+            vals.append(base["value"])
+    value = float(np.mean(vals))
+    step_ms = base["ms_per_sequence_layer"] * cfg["batch"] * cfg["num_layers"]
+    base["value"] = round(value, 4)
+    line = {
+        "impl": "reference", "metric": "packed_kv_decode_attention_throughput", "value": round(value, 4),
+        "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(step_ms, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic (seeded N(0,1) K/V, 4 outlier channels x8 per head, Zipf(1.1) importance)",
+        "config": {"workload": "BASELINE config 1 shape; each step a bounded sample: one (sequence, layer) at the full "
+                               "context on the host cores, ms_per_step scaled by batch x layers"},
+        "cpu_baseline": base,
+        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": round(time.perf_counter() - t0, 1),
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--layers", type=int, default=0,
+                    help="override the layer count (profiler captures of a small case only; not a bench line)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -175,17 +175,24 @@ class PackedKVStore:
 
     def attention(self, layer: int, query: torch.Tensor, cur_k: Optional[torch.Tensor] = None,
                   cur_v: Optional[torch.Tensor] = None, update_importance: bool = False,
-                  cur_storage: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  cur_storage: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  kernel_events=None) -> torch.Tensor:
         """One decode-attention call for ``layer``: query [B, Hq, D] (fp32/fp16),
-        optional current token cur_k/cur_v [B, Hkv, D].  Returns fp32 [B, Hq, D]."""
+        optional current token cur_k/cur_v [B, Hkv, D].  Returns fp32 [B, Hq, D].
+        ``kernel_events`` = (start, end) torch CUDA events recorded around the
+        streaming attention kernel alone (for roofline timing)."""
         q = query.contiguous()
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
         st = self._stream()
+        if kernel_events is not None:
+            kernel_events[0].record()
         check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.counts), ptr(q),
                                             self._dtype_code(q), self.num_q_heads, ptr(self.partials), self.num_ctas,
                                             ptr(self.logits) if want_logits else None, ptr(self.err), st),
               "skv_decode_attention")
+        if kernel_events is not None:
+            kernel_events[1].record()
         out = self.out if out is None else out
         kv_code = _lib.DTYPE_F32
         if cur_k is not None:
