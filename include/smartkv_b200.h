@@ -13,12 +13,11 @@
  * Python hot loops around them; each declaration cites what it replaces.
  *
  * Storage model ("the store").  One byte arena per (layer, sequence).  Inside
- * an arena every bit-width w in {2,3,4,8} owns a *bucket*: four contiguous,
+ * an arena every bit-width w in {2,3,4,8} owns a *bucket*: three contiguous,
  * 256-byte aligned regions
  *     K rows   [num_kv_heads][cap_w][row_bytes_w]   packed codes
  *     V rows   [num_kv_heads][cap_w][row_bytes_w]
- *     K scales [num_kv_heads][cap_w]                fp32
- *     V scales [num_kv_heads][cap_w]                fp32
+ *     scales   [num_kv_heads][cap_w][2]             fp32 (K scale, V scale) of the same row
  * row_bytes_w = head_dim*w/8.  Rows use the reference's packed format
  * (smartkv/csrc/bit_packing.cu:20-43,69-95,128-151: code + 2^(w-1), low bits
  * first, 8 three-bit codes per 24-bit little-endian group; 8-bit rows are the
@@ -64,8 +63,7 @@ typedef struct SkvStoreDesc {
   int32_t reserved_;
   int64_t k_off[SKV_NUM_BUCKETS];
   int64_t v_off[SKV_NUM_BUCKETS];
-  int64_t ks_off[SKV_NUM_BUCKETS];
-  int64_t vs_off[SKV_NUM_BUCKETS];
+  int64_t sc_off[SKV_NUM_BUCKETS];
   int64_t arena_bytes;             /* one (layer, sequence) arena */
   int64_t total_bytes;             /* num_layers * num_seqs * arena_bytes */
 } SkvStoreDesc;
@@ -118,21 +116,29 @@ int skv_export_rows(const SkvStoreDesc* desc, const void* store, int layer, int 
 /* Size queries (host only). */
 int skv_attn_num_ctas(int device);                       /* persistent CTAs the kernel launches */
 int64_t skv_attn_partials_bytes(const SkvStoreDesc* desc, int num_q_heads, int num_ctas);
+int64_t skv_attn_plan_bytes(const SkvStoreDesc* desc, int num_ctas);
+
+/* Builds the work partition of one decode step: which 16-key tiles of which
+ * (sequence, KV head) every persistent CTA streams, balanced by packed bytes.  It
+ * depends only on the bucket counts, which are the same for every layer of the
+ * step, so one call serves all layers.  No counterpart in the reference (its kernel
+ * walks one head per CTA, smartkv/csrc/quantized_attention.cu:679-777).
+ *   counts int32 [num_seqs][4] live tokens per bucket (device); plan: device buffer
+ *   of skv_attn_plan_bytes() bytes. */
+int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, int num_ctas, void* plan, void* stream);
 
 /* Replaces quantized_attention_bucket_forward + the host cross-bucket LSE combine
  * (smartkv/csrc/quantized_attention.cu:460-828, smartkv/kernels/__init__.py:269-386)
  * and the CPU streaming path (smartkv/core/fused_cpu.py:7-167) for q_len == 1.
  *
  * Streams the packed buckets of `layer` for every sequence, split-KV over
- * persistent CTAs balanced by bytes, and writes per-(CTA, sequence, KV head)
- * partial (max, sum, out) triples into `partials`; if `logits` is not NULL it also
- * writes the scaled logit (log2 units) of every cached key,
- * logits[seq][q_head][storage index].
- *   counts   int32 [num_seqs][4]   live tokens per bucket (device)
+ * persistent CTAs as laid out by `plan`, and writes one partial (max, sum, out)
+ * triple per run into `partials`; if `logits` is not NULL it also writes the scaled
+ * logit (log2 units) of every cached key, logits[seq][q_head][storage index].
  *   query    [num_seqs][num_q_heads][head_dim] fp32 or fp16
  * num_q_heads must be a multiple of num_kv_heads with group size <= 8.
  * err_flag: device int32, set non-zero if a bounded wait inside the kernel gave up. */
-int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const int32_t* counts,
+int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
                          const void* query, int query_dtype, int num_q_heads, void* partials, int num_ctas,
                          float* logits, int32_t* err_flag, void* stream);
 
@@ -142,7 +148,7 @@ int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer,
  * current token).  out fp32 [num_seqs][num_q_heads][head_dim]; lse_max / lse_sum fp32
  * [num_seqs][num_q_heads] (final max in log2 units, final sum); cur_prob fp32
  * [num_seqs][num_q_heads] = probability of the current token (may be NULL). */
-int skv_lse_combine(const SkvStoreDesc* desc, const int32_t* counts, const void* query, int query_dtype,
+int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
                     int num_q_heads, const void* partials, int num_ctas, const void* cur_k, const void* cur_v,
                     int kv_dtype, float* out, float* lse_max, float* lse_sum, float* cur_prob, void* stream);
 
@@ -165,8 +171,11 @@ int skv_importance_update(const SkvStoreDesc* desc, int layer, const int32_t* co
 /* ---- debug / test hooks ---------------------------------------------------- */
 
 /* Raw tensor-core tile products through the same fragment code as the attention
- * kernel: scores[16][16] = Q[16][head_dim] . Kcodes^T and out[16][head_dim] = P[16][16] . Vcodes
- * for one 16-key tile of packed rows (row_bytes apart).  Q and P are fp16. */
+ * kernel, for one 16-key tile of packed rows (row_bytes apart):
+ *   scores[8][16] = (Q[0..7] + Q[8..15]) . Kcodes^T      Q fp16 [16][head_dim]
+ *   out[8][head_dim] = (P[0..7] + P[8..15]) . Vcodes      P fp16 [16][16] ([row][key])
+ * Rows 0..7 are the query heads of a group, rows 8..15 the residual rows the
+ * precise (fp32-query) mode adds. */
 int skv_debug_tile_products(int head_dim, int bits, const uint8_t* k_rows, const uint8_t* v_rows,
                             const void* q_half, const void* p_half, float* scores, float* out, void* stream);
 

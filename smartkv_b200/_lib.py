@@ -8,7 +8,8 @@ import os
 from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libsmartkv_b200.so")
+# SMARTKV_B200_LIB points the loader at another build of the same ABI (e.g. an instrumented one)
+LIB_PATH = os.environ.get("SMARTKV_B200_LIB") or os.path.join(HERE, "libsmartkv_b200.so")
 
 NUM_BUCKETS = 4
 BUCKET_BITS = (2, 3, 4, 8)
@@ -24,8 +25,7 @@ class StoreDesc(Structure):
         ("cap", c_int32 * NUM_BUCKETS),
         ("row_bytes", c_int32 * NUM_BUCKETS), ("bucket_base", c_int32 * NUM_BUCKETS),
         ("slots", c_int32), ("reserved_", c_int32),
-        ("k_off", c_int64 * NUM_BUCKETS), ("v_off", c_int64 * NUM_BUCKETS),
-        ("ks_off", c_int64 * NUM_BUCKETS), ("vs_off", c_int64 * NUM_BUCKETS),
+        ("k_off", c_int64 * NUM_BUCKETS), ("v_off", c_int64 * NUM_BUCKETS), ("sc_off", c_int64 * NUM_BUCKETS),
         ("arena_bytes", c_int64), ("total_bytes", c_int64),
     ]
 
@@ -49,6 +49,8 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_attn_num_ctas": (c_int, [c_int]),
     "skv_attn_partials_bytes": (c_int64, [POINTER(StoreDesc), c_int, c_int]),
+    "skv_attn_plan_bytes": (c_int64, [POINTER(StoreDesc), c_int]),
+    "skv_attn_plan": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p]),
     "skv_decode_attention": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "skv_lse_combine": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,

@@ -35,10 +35,8 @@ extern "C" int skv_store_layout(SkvStoreDesc* d) {
     off = align_up(off + rows * d->row_bytes[i], 256);
     d->v_off[i] = off;
     off = align_up(off + rows * d->row_bytes[i], 256);
-    d->ks_off[i] = off;
-    off = align_up(off + rows * 4, 256);
-    d->vs_off[i] = off;
-    off = align_up(off + rows * 4, 256);
+    d->sc_off[i] = off;
+    off = align_up(off + rows * 8, 256);
   }
   d->slots = base;
   d->reserved_ = 0;

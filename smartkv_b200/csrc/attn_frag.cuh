@@ -1,23 +1,25 @@
 // Register-level unpack of packed K/V rows straight into mma.sync m16n8k16
 // fragments, for the fused decode-attention kernel.
 //
-// Layout of one 16-key tile (one KV head) in shared memory: 16 packed K rows,
-// row_bytes apart; same for V.  lane = 4*g + t.
+// One 16-key tile (one KV head) sits in shared memory as 16 packed K rows,
+// row_bytes apart, and 16 packed V rows.  lane = 4*g + t.  Keys are the M
+// dimension of both products and the (up to 8) query heads of the GQA group
+// are the N dimension, so nothing of the 16x8 tile is padding:
 //
-//  scores = Q (A operand, 16 x D, rows 0..7 = query heads of the group, rows
-//           8..15 = their fp16 residuals or zero)  x  K^T (B operand).
-//     For n-tile n (keys 8n..8n+7) lane (g,t) supplies key 8n+g, and of that
-//     key the D/4 consecutive elements [t*D/4, (t+1)*D/4) -- its "K slice".
-//     The order in which a slice's elements are fed to the k-steps is free as
-//     long as Q uses the same order, so each bit-width uses whichever order
-//     its cheapest bit extraction produces (kelem<BITS>() records it and the
-//     Q fragments are gathered through it).
+//  S^T[16 keys x 8 heads] = K (A operand, 16 x D)  x  Q^T (B operand, D x 8)
+//     Lane (g,t) supplies keys g and g+8, and of each the D/4 consecutive
+//     elements [t*D/4, (t+1)*D/4) -- its "K slice"; the B fragment is head g,
+//     same slice.  The order in which a slice's elements are fed to the k-steps
+//     is free as long as Q uses the same order, so each bit-width uses whichever
+//     order its cheapest bit extraction produces (kelem<BITS>() records it and
+//     the Q fragments are gathered through it).
 //
-//  out = P (A operand, 16 x 16 keys)  x  V (B operand, 16 keys x D).
-//     For n-tile j lane (g,t) supplies column d = g*D/8 + j for the key pairs
-//     (2t,2t+1) and (2t+8,2t+9); a half2 therefore pairs the SAME element of
-//     two different rows, which a byte permute of the two rows' words gives
-//     for free, in natural element order.
+//  O^T[D x 8 heads] = V^T (A operand, D x 16 keys)  x  P^T (B operand, 16 keys x 8)
+//     For m-tile j lane (g,t) supplies rows d = g*D/8 + 2j and d+1 for the key
+//     pairs (2t,2t+1) and (2t+8,2t+9); a half2 therefore pairs the SAME element
+//     of two different rows, which a byte permute of the two rows' words gives
+//     for free, in natural element order.  P^T comes from the S^T accumulator
+//     layout through movmatrix (8x8 b16 transpose).
 //
 // Sub-byte fields become fp16 through the 0x6400 trick: OR a field that sits
 // at bit p (p+width <= 10) of a 16-bit lane into the mantissa of 1024.0, then
@@ -129,55 +131,61 @@ __device__ __forceinline__ void k3_group(uint32_t a, uint32_t b, uint32_t* o) {
   o[7] = extract2<5, 5, 3>(x2);  // (f7 , f15)
 }
 
-// Loads lane (g,t)'s K slice of `row` and unpacks it to D/8 half2 registers.
+// Words a lane loads for its K slice (D/4 elements) and for its V slice of one row (D/8 elements).
 template <int D, int BITS>
-__device__ __forceinline__ void load_unpack_kslice(const uint8_t* tile, int row, int t, uint32_t* o) {
-  constexpr int PD = D * BITS / 8;      // row bytes
-  constexpr int SB = PD / 4;            // slice bytes
+struct SliceWords {
+  static constexpr int K = (D * BITS / 32 + 3) / 4;   // 128: 8,4,3,2   64: 4,2,2,1
+  static constexpr int V = (BITS == 3) ? 2 : (D * BITS / 64 + 3) / 4;   // 128: 4,2,2,1   64: 2,1,2,1
+};
+
+// Loads lane (g,t)'s K slice of `row` as raw words (unpacked later, so the loads of a whole
+// tile can be issued before any arithmetic).
+template <int D, int BITS>
+__device__ __forceinline__ void load_kslice(const uint8_t* tile, int row, int t, uint32_t (&w)[SliceWords<D, BITS>::K]) {
+  constexpr int PD = D * BITS / 8;  // row bytes
+  constexpr int SB = PD / 4;        // slice bytes
   const uint8_t* p = tile + row * PD + t * SB;
-  if constexpr (BITS == 8) {
+  if constexpr (SB % 16 == 0) {
 #pragma unroll
     for (int i = 0; i < SB / 16; ++i) {
-      uint4 v = *reinterpret_cast<const uint4*>(p + 16 * i);
-      k8_word(v.x, o + 8 * i + 0);
-      k8_word(v.y, o + 8 * i + 2);
-      k8_word(v.z, o + 8 * i + 4);
-      k8_word(v.w, o + 8 * i + 6);
+      const uint4 v = *reinterpret_cast<const uint4*>(p + 16 * i);
+      w[4 * i + 0] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
     }
+  } else if constexpr (SB == 8) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    w[0] = v.x; w[1] = v.y;
+  } else if constexpr (SB == 4) {
+    w[0] = *reinterpret_cast<const uint32_t*>(p);
+  } else if constexpr (SB == 12) {
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
+    w[0] = q[0]; w[1] = q[1]; w[2] = q[2];
+  } else {  // 6 bytes at offset 6t: 4-byte aligned only for even t -> load from the aligned word below
+    static_assert(SB == 6, "unexpected K slice size");
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(p - (t & 1) * 2);
+    w[0] = q[0]; w[1] = q[1];
+  }
+}
+
+// Unpacks a raw K slice to D/8 half2 registers in the order kelem<BITS> records.
+template <int D, int BITS>
+__device__ __forceinline__ void unpack_kslice(const uint32_t (&w)[SliceWords<D, BITS>::K], int t, uint32_t* o) {
+  constexpr int NW = SliceWords<D, BITS>::K;
+  if constexpr (BITS == 8) {
+#pragma unroll
+    for (int i = 0; i < NW; ++i) k8_word(w[i], o + 2 * i);
   } else if constexpr (BITS == 4) {
-    if constexpr (SB == 16) {
-      uint4 v = *reinterpret_cast<const uint4*>(p);
-      k4_word(v.x, o + 0);
-      k4_word(v.y, o + 4);
-      k4_word(v.z, o + 8);
-      k4_word(v.w, o + 12);
-    } else {
-      uint2 v = *reinterpret_cast<const uint2*>(p);
-      k4_word(v.x, o + 0);
-      k4_word(v.y, o + 4);
-    }
+#pragma unroll
+    for (int i = 0; i < NW; ++i) k4_word(w[i], o + 4 * i);
   } else if constexpr (BITS == 2) {
-    if constexpr (SB == 8) {
-      uint2 v = *reinterpret_cast<const uint2*>(p);
-      k2_word(v.x, o + 0);
-      k2_word(v.y, o + 8);
-    } else {
-      uint32_t v = *reinterpret_cast<const uint32_t*>(p);
-      k2_word(v, o + 0);
-    }
-  } else {  // 3-bit
-    if constexpr (SB == 12) {
-      const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
-      uint32_t w0 = q[0], w1 = q[1], w2 = q[2];
-      k3_group<0x2110, 0x5443, 0x5532>(w0, w1, o + 0);   // bytes 0..5
-      k3_group<0x4332, 0x7665, 0x7754>(w1, w2, o + 8);   // bytes 6..11
-    } else {  // 6 bytes at offset 6t: 4-byte aligned only for even t
-      const int sh = (t & 1) * 16;
-      const uint32_t* q = reinterpret_cast<const uint32_t*>(p - (t & 1) * 2);
-      uint32_t w0 = q[0], w1 = q[1];
-      uint32_t lo = __funnelshift_r(w0, w1, sh), hi = w1 >> sh;
-      k3_group<0x2110, 0x5443, 0x5532>(lo, hi, o + 0);
-    }
+#pragma unroll
+    for (int i = 0; i < NW; ++i) k2_word(w[i], o + 8 * i);
+  } else if constexpr (D == 128) {
+    k3_group<0x2110, 0x5443, 0x5532>(w[0], w[1], o + 0);  // bytes 0..5
+    k3_group<0x4332, 0x7665, 0x7754>(w[1], w[2], o + 8);  // bytes 6..11
+  } else {
+    const int sh = (t & 1) * 16;
+    const uint32_t lo = __funnelshift_r(w[0], w[1], sh), hi = w[1] >> sh;
+    k3_group<0x2110, 0x5443, 0x5532>(lo, hi, o + 0);
   }
 }
 
@@ -225,115 +233,131 @@ __device__ __forceinline__ void v3_pair_half(uint32_t a, uint32_t b, uint32_t* o
   o[7] = extract2<5, 5, 3>(x2);
 }
 
-// Loads lane (g,t)'s V slices of rows rowA, rowA+1 and unpacks to D/8 half2.
+// Loads lane (g,t)'s V slice of one row as raw words.
 template <int D, int BITS>
-__device__ __forceinline__ void load_unpack_vpair(const uint8_t* tile, int rowA, int g, uint32_t* o) {
+__device__ __forceinline__ void load_vrow(const uint8_t* tile, int row, int g, uint32_t (&w)[SliceWords<D, BITS>::V]) {
   constexpr int PD = D * BITS / 8;
   constexpr int SB = PD / 8;  // slice bytes
-  const uint8_t* pa = tile + rowA * PD + g * SB;
-  const uint8_t* pb = pa + PD;
+  const uint8_t* p = tile + row * PD + g * SB;
+  if constexpr (SB == 16) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else if constexpr (SB == 8) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    w[0] = v.x; w[1] = v.y;
+  } else if constexpr (SB == 4) {
+    w[0] = *reinterpret_cast<const uint32_t*>(p);
+  } else if constexpr (SB == 2) {
+    w[0] = *reinterpret_cast<const uint16_t*>(p);
+  } else if constexpr (SB == 6) {  // 6 bytes at offset 6g: aligned for even g
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(p - (g & 1) * 2);
+    w[0] = q[0]; w[1] = q[1];
+  } else {  // 3 bytes at offset 3g
+    static_assert(SB == 3, "unexpected V slice size");
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(p - ((g * 3) & 3));
+    w[0] = q[0]; w[1] = q[1];
+  }
+}
+
+// Unpacks the raw V slices of rows A (key 2t or 2t+8) and B (the next key) to D/8 half2
+// registers (A.e_j, B.e_j), natural element order j.
+template <int D, int BITS>
+__device__ __forceinline__ void unpack_vpair(const uint32_t (&a)[SliceWords<D, BITS>::V],
+                                             const uint32_t (&b)[SliceWords<D, BITS>::V], int g, uint32_t* o) {
+  constexpr int NW = SliceWords<D, BITS>::V;
   if constexpr (BITS == 8) {
-    if constexpr (SB == 16) {
-      uint4 a = *reinterpret_cast<const uint4*>(pa), b = *reinterpret_cast<const uint4*>(pb);
-      v8_pair_word(a.x, b.x, o + 0);
-      v8_pair_word(a.y, b.y, o + 4);
-      v8_pair_word(a.z, b.z, o + 8);
-      v8_pair_word(a.w, b.w, o + 12);
-    } else {
-      uint2 a = *reinterpret_cast<const uint2*>(pa), b = *reinterpret_cast<const uint2*>(pb);
-      v8_pair_word(a.x, b.x, o + 0);
-      v8_pair_word(a.y, b.y, o + 4);
-    }
+#pragma unroll
+    for (int i = 0; i < NW; ++i) v8_pair_word(a[i], b[i], o + 4 * i);
   } else if constexpr (BITS == 4) {
-    if constexpr (SB == 8) {
-      uint2 a = *reinterpret_cast<const uint2*>(pa), b = *reinterpret_cast<const uint2*>(pb);
-      v4_pair_x(prmt(a.x, b.x, 0x5410), o + 0);
-      v4_pair_x(prmt(a.x, b.x, 0x7632), o + 4);
-      v4_pair_x(prmt(a.y, b.y, 0x5410), o + 8);
-      v4_pair_x(prmt(a.y, b.y, 0x7632), o + 12);
-    } else {
-      uint32_t a = *reinterpret_cast<const uint32_t*>(pa), b = *reinterpret_cast<const uint32_t*>(pb);
-      v4_pair_x(prmt(a, b, 0x5410), o + 0);
-      v4_pair_x(prmt(a, b, 0x7632), o + 4);
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+      v4_pair_x(prmt(a[i], b[i], 0x5410), o + 8 * i);
+      v4_pair_x(prmt(a[i], b[i], 0x7632), o + 8 * i + 4);
     }
   } else if constexpr (BITS == 2) {
-    if constexpr (SB == 4) {
-      uint32_t a = *reinterpret_cast<const uint32_t*>(pa), b = *reinterpret_cast<const uint32_t*>(pb);
-      v2_pair_x(prmt(a, b, 0x5410), o + 0);
-      v2_pair_x(prmt(a, b, 0x7632), o + 8);
+    if constexpr (D == 128) {
+      v2_pair_x(prmt(a[0], b[0], 0x5410), o + 0);
+      v2_pair_x(prmt(a[0], b[0], 0x7632), o + 8);
     } else {
-      uint32_t a = *reinterpret_cast<const uint16_t*>(pa), b = *reinterpret_cast<const uint16_t*>(pb);
-      v2_pair_x(a | (b << 16), o + 0);
+      v2_pair_x(a[0] | (b[0] << 16), o + 0);
     }
-  } else {  // 3-bit
-    if constexpr (SB == 6) {  // 6 bytes at offset 6g: aligned for even g
-      const int sh = (g & 1) * 16;
-      const uint32_t* qa = reinterpret_cast<const uint32_t*>(pa - (g & 1) * 2);
-      const uint32_t* qb = reinterpret_cast<const uint32_t*>(pb - (g & 1) * 2);
-      uint32_t a0 = qa[0], a1 = qa[1], b0 = qb[0], b1 = qb[1];
-      uint32_t alo = __funnelshift_r(a0, a1, sh), ahi = a1 >> sh;
-      uint32_t blo = __funnelshift_r(b0, b1, sh), bhi = b1 >> sh;
-      v3_pair_half(alo, blo, o + 0);
-      v3_pair_half(__funnelshift_r(alo, ahi, 24), __funnelshift_r(blo, bhi, 24), o + 8);
-    } else {  // 3 bytes at offset 3g
-      const int mis = (g * 3) & 3;
-      const uint32_t* qa = reinterpret_cast<const uint32_t*>(pa - mis);
-      const uint32_t* qb = reinterpret_cast<const uint32_t*>(pb - mis);
-      uint32_t a = __funnelshift_r(qa[0], qa[1], mis * 8);
-      uint32_t b = __funnelshift_r(qb[0], qb[1], mis * 8);
-      v3_pair_half(a, b, o + 0);
-    }
+  } else if constexpr (D == 128) {
+    const int sh = (g & 1) * 16;
+    const uint32_t alo = __funnelshift_r(a[0], a[1], sh), ahi = a[1] >> sh;
+    const uint32_t blo = __funnelshift_r(b[0], b[1], sh), bhi = b[1] >> sh;
+    v3_pair_half(alo, blo, o + 0);
+    v3_pair_half(__funnelshift_r(alo, ahi, 24), __funnelshift_r(blo, bhi, 24), o + 8);
+  } else {
+    const int sh = ((g * 3) & 3) * 8;
+    v3_pair_half(__funnelshift_r(a[0], a[1], sh), __funnelshift_r(b[0], b[1], sh), o + 0);
   }
 }
 
 // ---------------------------------------------------------------------------
-// Query fragments for one bit-width.  qs: shared fp16 [16][D + QPAD]
+// Query fragments (B operand of S^T) for one bit-width.
+// qs: shared fp16 [8 or 16][D]: rows 0..7 = heads of the group, rows 8..15 = their
+// fp16 residuals (precise mode).  `row0` = 0 or 8 selects which.
 // ---------------------------------------------------------------------------
-constexpr int kQPad = 8;
+constexpr int kQPad = 0;  // query rows are dense in shared memory (they arrive by bulk copy)
 
 template <int D, int BITS>
-__device__ __forceinline__ void gather_q_frags(const __half* qs, int lane, uint32_t (&qa)[D / 16][4]) {
+__device__ __forceinline__ void gather_q_frags(const __half* qs, int lane, int row0, uint32_t (&qb)[D / 16][2]) {
   const int g = lane >> 2, t = lane & 3;
-  const unsigned short* r0 = reinterpret_cast<const unsigned short*>(qs) + g * (D + kQPad) + t * (D / 4);
-  const unsigned short* r1 = r0 + 8 * (D + kQPad);
+  const unsigned short* r = reinterpret_cast<const unsigned short*>(qs) + (g + row0) * (D + kQPad) + t * (D / 4);
 #pragma unroll
   for (int s = 0; s < D / 16; ++s) {
-    const int e00 = kelem<BITS>(2 * s, 0), e01 = kelem<BITS>(2 * s, 1);
-    const int e10 = kelem<BITS>(2 * s + 1, 0), e11 = kelem<BITS>(2 * s + 1, 1);
-    qa[s][0] = (uint32_t)r0[e00] | ((uint32_t)r0[e01] << 16);
-    qa[s][1] = (uint32_t)r1[e00] | ((uint32_t)r1[e01] << 16);
-    qa[s][2] = (uint32_t)r0[e10] | ((uint32_t)r0[e11] << 16);
-    qa[s][3] = (uint32_t)r1[e10] | ((uint32_t)r1[e11] << 16);
+    qb[s][0] = (uint32_t)r[kelem<BITS>(2 * s, 0)] | ((uint32_t)r[kelem<BITS>(2 * s, 1)] << 16);
+    qb[s][1] = (uint32_t)r[kelem<BITS>(2 * s + 1, 0)] | ((uint32_t)r[kelem<BITS>(2 * s + 1, 1)] << 16);
   }
 }
 
-// scores for one 16-key tile: s[n][0..1] = rows g of keys 8n+2t, 8n+2t+1; s[n][2..3] = rows g+8
-template <int D, int BITS>
-__device__ __forceinline__ void qk_tile(const uint8_t* ktile, int lane, const uint32_t (&qa)[D / 16][4],
-                                        float (&s)[2][4]) {
-  const int g = lane >> 2, t = lane & 3;
+// Raw scores of one 16-key tile from the raw K slices of keys g (k0) and g+8 (k1):
+//   s[0] = (key g, head 2t)  s[1] = (key g, head 2t+1)  s[2] = (key g+8, head 2t)  s[3] = (key g+8, head 2t+1)
+// Two accumulators (even / odd k-steps) halve the dependent-MMA chain.
+template <int D, int BITS, bool PRECISE>
+__device__ __forceinline__ void qk_tile(const uint32_t (&k0)[SliceWords<D, BITS>::K],
+                                        const uint32_t (&k1)[SliceWords<D, BITS>::K], int lane,
+                                        const uint32_t (&qb)[D / 16][2], const uint32_t (&ql)[D / 16][2],
+                                        float (&s)[4]) {
+  const int t = lane & 3;
   uint32_t kb0[D / 8], kb1[D / 8];
-  load_unpack_kslice<D, BITS>(ktile, g, t, kb0);
-  load_unpack_kslice<D, BITS>(ktile, g + 8, t, kb1);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) s[0][i] = s[1][i] = 0.f;
+  unpack_kslice<D, BITS>(k0, t, kb0);
+  unpack_kslice<D, BITS>(k1, t, kb1);
+  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int k = 0; k < D / 16; ++k) {
-    mma_16816(s[0], qa[k], kb0[2 * k], kb0[2 * k + 1]);
-    mma_16816(s[1], qa[k], kb1[2 * k], kb1[2 * k + 1]);
+    const uint32_t a[4] = {kb0[2 * k], kb1[2 * k], kb0[2 * k + 1], kb1[2 * k + 1]};
+    if (k & 1) {
+      mma_16816(acc1, a, qb[k][0], qb[k][1]);
+      if (PRECISE) mma_16816(acc0, a, ql[k][0], ql[k][1]);
+    } else {
+      mma_16816(acc0, a, qb[k][0], qb[k][1]);
+      if (PRECISE) mma_16816(acc1, a, ql[k][0], ql[k][1]);
+    }
   }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i] = acc0[i] + acc1[i];
 }
 
-// o[j][0..1] += rows g, columns d = (D/8)*(2t) + j and (D/8)*(2t+1) + j ; o[j][2..3] rows g+8
-template <int D, int BITS>
-__device__ __forceinline__ void pv_tile(const uint8_t* vtile, int lane, const uint32_t (&pa)[4],
-                                        float (&o)[D / 8][4]) {
-  const int g = lane >> 2, t = lane & 3;
-  uint32_t v0[D / 8], v1[D / 8];
-  load_unpack_vpair<D, BITS>(vtile, 2 * t, g, v0);
-  load_unpack_vpair<D, BITS>(vtile, 2 * t + 8, g, v1);
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+// o[j][0] = (d = g*D/8 + 2j, head 2t)   o[j][1] = (same d, head 2t+1)
+// o[j][2] = (d + 1,          head 2t)   o[j][3] = (d + 1,  head 2t+1)
+// v0 / v1: unpacked V fragments of the key pairs (2t,2t+1) / (2t+8,2t+9);
+// pb0/pb1: P^T fragments for those pairs, head g; pl0/pl1 their fp16 residuals.
+template <int D, bool PRECISE>
+__device__ __forceinline__ void pv_tile(const uint32_t (&v0)[D / 8], const uint32_t (&v1)[D / 8], uint32_t pb0,
+                                        uint32_t pb1, uint32_t pl0, uint32_t pl1, float (&o)[D / 16][4]) {
 #pragma unroll
-  for (int j = 0; j < D / 8; ++j) mma_16816(o[j], pa, v0[j], v1[j]);
+  for (int j = 0; j < D / 16; ++j) {
+    const uint32_t a[4] = {v0[2 * j], v0[2 * j + 1], v1[2 * j], v1[2 * j + 1]};
+    mma_16816(o[j], a, pb0, pb1);
+    if (PRECISE) mma_16816(o[j], a, pl0, pl1);
+  }
 }
 
 }  // namespace skv

@@ -1,0 +1,110 @@
+// Work partition of the fused decode attention: which 16-key tiles of which
+// (sequence, KV head) segment a persistent CTA owns.
+//
+// Every segment is a byte string: for each bucket in turn, ceil(count/16) tiles of
+// tile_bytes(bucket) = 16 * (2*row_bytes + 8) bytes (packed K rows, V rows and a
+// float2 of scales per key).  All heads of a sequence have the same length W[b].
+// The global string concatenates the segments in (sequence, head) order; CTA c
+// owns the tiles whose first byte lies in [ceil(c*T/C), ceil((c+1)*T/C)), i.e. the
+// CTAs are balanced by bytes and never share a tile.  A maximal piece of one
+// segment owned by one CTA is a *run*; runs are numbered in byte order, which is
+// both (CTA, segment) order and (segment, CTA) order, so a CTA's runs and a
+// segment's runs are each consecutive.  The partition depends only on the bucket
+// counts, which are the same for every layer of a decode step, so it is built once
+// per step into a small plan buffer and read by every layer's launches.
+#pragma once
+
+#include "common.cuh"
+
+namespace skv {
+
+__host__ __device__ constexpr int tile_bytes_for(int head_dim, int bits) {
+  return 16 * (2 * row_bytes_for(head_dim, bits) + 8);
+}
+
+struct SegLayout {
+  int cnt[kNumBuckets];          // live keys per bucket
+  int nt[kNumBuckets];           // tiles per bucket
+  long long start[kNumBuckets];  // first byte of the bucket inside the segment
+  long long bytes;               // W: bytes of one segment of this sequence
+};
+
+__host__ __device__ inline SegLayout seg_layout(const int32_t* counts4, int head_dim) {
+  SegLayout s;
+  long long off = 0;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) {
+    s.cnt[i] = counts4[i];
+    s.nt[i] = (counts4[i] + 15) >> 4;
+    s.start[i] = off;
+    off += (long long)s.nt[i] * tile_bytes_for(head_dim, bucket_bits(i));
+  }
+  s.bytes = off;
+  return s;
+}
+
+__host__ __device__ inline long long cta_range_begin(long long total, int c, int num_ctas) {
+  return (total * c + num_ctas - 1) / num_ctas;
+}
+
+// Tiles [ka, kb) of every bucket whose first byte lies in the segment-local range [lo, hi).
+// Returns the number of tiles.
+__host__ __device__ inline int seg_tiles_in_range(const SegLayout& s, int head_dim, long long lo, long long hi,
+                                                  int (&ka)[kNumBuckets], int (&kb)[kNumBuckets]) {
+  int total = 0;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) {
+    const long long tb = tile_bytes_for(head_dim, bucket_bits(i));
+    long long a = lo - s.start[i], b = hi - s.start[i];
+    a = a <= 0 ? 0 : (a + tb - 1) / tb;
+    b = b <= 0 ? 0 : (b + tb - 1) / tb;
+    if (a > s.nt[i]) a = s.nt[i];
+    if (b > s.nt[i]) b = s.nt[i];
+    ka[i] = (int)a;
+    kb[i] = (int)b;
+    total += (int)(b - a);
+  }
+  return total;
+}
+
+// One run: the tiles [ka, kb) of each bucket of segment (seq, head) that one CTA streams.
+struct __align__(16) RunDesc {
+  int seq, head;
+  int ka[kNumBuckets];
+  int kb[kNumBuckets];
+  int cnt[kNumBuckets];  // live keys per bucket of the sequence
+  int pad_[2];
+};
+static_assert(sizeof(RunDesc) == 64, "RunDesc is one 64-byte record");
+
+// Plan buffer (int32 words):
+//   [0] number of runs  [1] number of CTAs  [2] number of segments  [3] reserved
+//   cta_begin[C + 1]     first run of every CTA
+//   seg_begin[nseg]      first run of every segment (undefined when seg_count is 0)
+//   seg_count[nseg]      runs of every segment
+//   (padding to 16 words)  RunDesc runs[C + nseg]
+struct PlanView {
+  int* header;
+  int* cta_begin;
+  int* seg_begin;
+  int* seg_count;
+  RunDesc* runs;
+};
+__host__ __device__ inline long long plan_words(int num_ctas, int nseg) {
+  long long head = 4 + (num_ctas + 1) + 2LL * nseg;
+  head = (head + 15) / 16 * 16;
+  return head + 16LL * (num_ctas + nseg);
+}
+__host__ __device__ inline PlanView plan_view(int* base, int num_ctas, int nseg) {
+  PlanView v;
+  v.header = base;
+  v.cta_begin = base + 4;
+  v.seg_begin = v.cta_begin + (num_ctas + 1);
+  v.seg_count = v.seg_begin + nseg;
+  long long head = 4 + (num_ctas + 1) + 2LL * nseg;
+  head = (head + 15) / 16 * 16;
+  v.runs = reinterpret_cast<RunDesc*>(base + head);
+  return v;
+}
+
+}  // namespace skv

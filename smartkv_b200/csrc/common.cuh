@@ -26,7 +26,7 @@ struct StoreGeom {
   int row_bytes[kNumBuckets];
   int bucket_base[kNumBuckets];
   int slots;
-  long long k_off[kNumBuckets], v_off[kNumBuckets], ks_off[kNumBuckets], vs_off[kNumBuckets];
+  long long k_off[kNumBuckets], v_off[kNumBuckets], sc_off[kNumBuckets];
   long long arena_bytes;
 };
 
@@ -42,8 +42,7 @@ inline StoreGeom make_geom(const SkvStoreDesc& d) {
     g.bucket_base[i] = d.bucket_base[i];
     g.k_off[i] = d.k_off[i];
     g.v_off[i] = d.v_off[i];
-    g.ks_off[i] = d.ks_off[i];
-    g.vs_off[i] = d.vs_off[i];
+    g.sc_off[i] = d.sc_off[i];
   }
   g.slots = d.slots;
   g.arena_bytes = d.arena_bytes;
@@ -103,6 +102,9 @@ __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -115,7 +117,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: returns false when the limit ran out (caller sets the error flag).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 17)) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
@@ -128,6 +130,10 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
           smem_u32(smem_dst)),
       "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
+}
+// asks the memory system to bring [gsrc, gsrc+bytes) into L2 (no destination, no completion)
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

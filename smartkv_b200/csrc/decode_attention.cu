@@ -1,40 +1,54 @@
 // Fused packed-KV decode attention for sm_100a (q_len == 1, GQA group <= 8).
 //
 // Persistent CTAs (one per SM).  The packed buckets of every (sequence, KV head)
-// are cut into blocks of a few KB (uniform bit-width per block); the global
-// block list is split evenly -- i.e. by bytes -- over the CTAs, so a CTA owns a
-// contiguous run of blocks that may span several (sequence, head) segments.
-// Inside a segment the CTA's warps take blocks round-robin.  Each warp runs its
-// own bulk-async-copy (TMA 1-D) pipeline into private shared-memory stages,
-// unpacks the codes in registers straight into tensor-core fragments
-// (attn_frag.cuh), keeps an online softmax and accumulates P.V in registers.
-// At the end of a segment the warps' (max, sum, out) are merged through shared
-// memory and one partial per (CTA, segment) is written; skv_lse_combine merges
-// partials, adds the full-precision current token and normalises.
+// segment form one byte string of 16-key tiles; the global string is split evenly
+// -- i.e. by bytes -- over the CTAs (attn_sched.cuh) by a tiny plan kernel that runs
+// once per decode step.  A CTA streams its runs through a ring of shared-memory
+// stages: one producer warp issues bulk async copies (TMA 1-D: packed K rows,
+// packed V rows, scales, and the query rows of the group), the consumer warps take
+// the tiles of a block round-robin, unpack the codes in registers straight into
+// tensor-core fragments (attn_frag.cuh), keep an online softmax and accumulate P.V
+// in registers.  Full/empty mbarriers order producer and consumers; every wait is
+// bounded.  At the end of a run the consumers merge their (max, sum, out) through
+// shared memory and write one partial per run; skv_lse_combine merges the partials
+// of a segment, adds the full-precision current token and normalises.
 //
 // Replaces smartkv/csrc/quantized_attention.cu:460-828 (per-bucket kernel, one
 // CTA per head walking the whole context) and the host LSE combine in
 // smartkv/kernels/__init__.py:350-371; numerics follow the CPU streaming path
 // smartkv/core/fused_cpu.py:70-113 (dequantise, q.k/sqrt(d), online softmax).
+#include <cstdio>
+#include <cstdlib>
+#include <type_traits>
+
 #include "attn_frag.cuh"
+#include "attn_sched.cuh"
 
 namespace skv {
 
-constexpr int kAttnWarps = 8;
-constexpr int kAttnStages = 3;
-constexpr int kStageBytes = 8448;
-constexpr int kMaxSeqs = 4096;
+constexpr int kMaxSeqs = 1024;
+constexpr int kMaxCtas = 1024;
+constexpr int kQBufs = 4;        // query / run-descriptor ring (the producer runs at most STAGES blocks ahead)
+constexpr int kMergeWarps = 4;   // warps merged per round at the end of a run
 
-// keys per block for a bit-width: as many as fit one stage (K rows + V rows + 2 fp32 scales per key)
-__host__ __device__ constexpr int block_keys(int head_dim, int bits) {
-  return (kStageBytes / (2 * row_bytes_for(head_dim, bits) + 8)) / 16 * 16;
+// Shape of the persistent CTA: NCONS consumer warps + 1 producer warp share STAGES stages.
+template <int NCONS_, int STAGES_, int STAGE_BYTES_>
+struct AttnCfg {
+  static constexpr int NCONS = NCONS_, STAGES = STAGES_, STAGE_BYTES = STAGE_BYTES_;
+};
+using AttnCfgFast = AttnCfg<15, 3, 63360>;     // fp16 queries: 16 warps x 128 registers; 15 8-bit tiles per stage
+using AttnCfgPrecise = AttnCfg<7, 3, 63360>;   // fp32 queries (hi/lo split): 8 warps, more registers per thread
+
+// tiles per block for a bit-width: as many 16-key tiles as fit one stage
+__host__ __device__ constexpr int block_tiles(int stage_bytes, int head_dim, int bits) {
+  return stage_bytes / tile_bytes_for(head_dim, bits);
 }
 
 struct AttnParams {
   StoreGeom g;
   const uint8_t* store;
   int layer;
-  const int32_t* counts;
+  const int* plan;
   const void* query;
   int q_is_half;
   int num_q_heads;
@@ -44,7 +58,25 @@ struct AttnParams {
   float* logits;
   int32_t* err;
   float scale_log2;
+  int debug_mode;  // 0 = normal; timing probes: 1 = stream only (no math), 2 = math only (no copies), 3 = neither
+#ifdef SKV_TIMELINE
+  unsigned long long* timeline;  // [num_ctas][16] globaltimer samples (debug builds only)
+#endif
 };
+
+#ifdef SKV_TIMELINE
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define SKV_TL(slot)                                                                              \
+  do {                                                                                            \
+    if (p.timeline != nullptr && (threadIdx.x == 0) && (slot) < 16) p.timeline[blockIdx.x * 16 + (slot)] = gtimer(); \
+  } while (0)
+#else
+#define SKV_TL(slot) do { } while (0)
+#endif
 
 __host__ __device__ inline int partial_stride(int group, int head_dim) { return group * (head_dim + 2); }
 
@@ -57,327 +89,487 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return h2_bits(h);
 }
-
-struct WarpState {
-  float m;  // running max (log2 units) of this lane's query row
-  float l;  // this lane's share of the running sum
-};
-
-template <int D, int BITS, bool PRECISE>
-__device__ __forceinline__ void process_block(const uint8_t* sb, int nkeys, int lane,
-                                              const uint32_t (&qa)[D / 16][4], WarpState& st, float (&o)[D / 8][4],
-                                              float scale_log2, float* logit_row) {
-  constexpr int PD = D * BITS / 8;
-  constexpr int KB = block_keys(D, BITS);
-  const uint8_t* kbase = sb;
-  const uint8_t* vbase = sb + KB * PD;
-  const float* ks = reinterpret_cast<const float*>(sb + 2 * KB * PD);
-  const float* vs = ks + KB;
-  const int t = lane & 3;
-  const int ntiles = (nkeys + 15) >> 4;
-  const float ninf = -INFINITY;
-  for (int tile = 0; tile < ntiles; ++tile) {
-    float s[2][4];
-    qk_tile<D, BITS>(kbase + tile * 16 * PD, lane, qa, s);
-    const int kk = tile * 16 + 2 * t;
-    const float2 ks01 = *reinterpret_cast<const float2*>(ks + kk);
-    const float2 ks23 = *reinterpret_cast<const float2*>(ks + kk + 8);
-    float sv0 = s[0][0], sv1 = s[0][1], sv2 = s[1][0], sv3 = s[1][1];
-    if (PRECISE) {
-      sv0 += s[0][2];
-      sv1 += s[0][3];
-      sv2 += s[1][2];
-      sv3 += s[1][3];
-    }
-    const bool ok0 = kk < nkeys, ok1 = kk + 1 < nkeys, ok2 = kk + 8 < nkeys, ok3 = kk + 9 < nkeys;
-    sv0 = ok0 ? sv0 * (ks01.x * scale_log2) : ninf;
-    sv1 = ok1 ? sv1 * (ks01.y * scale_log2) : ninf;
-    sv2 = ok2 ? sv2 * (ks23.x * scale_log2) : ninf;
-    sv3 = ok3 ? sv3 * (ks23.y * scale_log2) : ninf;
-    if (logit_row != nullptr) {
-      *reinterpret_cast<float2*>(logit_row + kk) = make_float2(sv0, sv1);
-      *reinterpret_cast<float2*>(logit_row + kk + 8) = make_float2(sv2, sv3);
-    }
-    float mt = fmaxf(fmaxf(sv0, sv1), fmaxf(sv2, sv3));
-    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
-    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
-    if (__any_sync(0xffffffffu, mt > st.m)) {
-      const float m_new = fmaxf(st.m, mt);
-      const float alpha = (m_new == ninf) ? 1.f : ex2f(st.m - m_new);
-      st.l *= alpha;
-#pragma unroll
-      for (int j = 0; j < D / 8; ++j) {
-        o[j][0] *= alpha;
-        o[j][1] *= alpha;
-        if (PRECISE) {
-          o[j][2] *= alpha;
-          o[j][3] *= alpha;
-        }
-      }
-      st.m = m_new;
-    }
-    const float mu = (st.m == ninf) ? 0.f : st.m;
-    const float p0 = ex2f(sv0 - mu), p1 = ex2f(sv1 - mu), p2 = ex2f(sv2 - mu), p3 = ex2f(sv3 - mu);
-    st.l += (p0 + p1) + (p2 + p3);
-    const float2 vs01 = *reinterpret_cast<const float2*>(vs + kk);
-    const float2 vs23 = *reinterpret_cast<const float2*>(vs + kk + 8);
-    const float a0 = ok0 ? p0 * vs01.x : 0.f, a1 = ok1 ? p1 * vs01.y : 0.f;
-    const float a2 = ok2 ? p2 * vs23.x : 0.f, a3 = ok3 ? p3 * vs23.y : 0.f;
-    uint32_t pa[4];
-    pa[0] = pack_h2(a0, a1);
-    pa[2] = pack_h2(a2, a3);
-    if (PRECISE) {
-      const __half2 h01 = bits_h2(pa[0]), h23 = bits_h2(pa[2]);
-      pa[1] = pack_h2(a0 - __low2float(h01), a1 - __high2float(h01));
-      pa[3] = pack_h2(a2 - __low2float(h23), a3 - __high2float(h23));
-    } else {
-      pa[1] = 0u;
-      pa[3] = 0u;
-    }
-    pv_tile<D, BITS>(vbase + tile * 16 * PD, lane, pa, o);
-  }
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-template <int D, bool PRECISE>
-__global__ void __launch_bounds__(kAttnWarps * 32, 1) decode_attn_kernel(const AttnParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const StoreGeom& g = p.g;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int G = p.group, Hkv = g.num_kv_heads, B = g.num_seqs;
-  constexpr int NT = kAttnWarps * 32;
-
-  uint8_t* stages = smem;                                         // [warps][stages][kStageBytes]
-  __half* qs = reinterpret_cast<__half*>(smem + kAttnWarps * kAttnStages * kStageBytes);  // [16][D+pad]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(qs) + 16 * (D + kQPad) * 2);
-  int* prefix = reinterpret_cast<int*>(bars + kAttnWarps * kAttnStages);  // [B+1] blocks before sequence b (per head)
-
-  // ---- block schedule --------------------------------------------------------
-  int kb[kNumBuckets];
-#pragma unroll
-  for (int i = 0; i < kNumBuckets; ++i) kb[i] = block_keys(D, bucket_bits(i));
-  for (int b = tid; b < B; b += NT) {
-    int n = 0;
-#pragma unroll
-    for (int i = 0; i < kNumBuckets; ++i) n += (p.counts[b * kNumBuckets + i] + kb[i] - 1) / kb[i];
-    prefix[b + 1] = n;
+// ---- plan: the byte-balanced partition, built once per decode step --------------------
+__global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int32_t* counts, int C, int* plan_base) {
+  __shared__ long long cumw[kMaxSeqs + 1];
+  __shared__ int nruns_of[kMaxCtas + 1];
+  const int tid = threadIdx.x, NT = blockDim.x;
+  const int B = g.num_seqs, Hkv = g.num_kv_heads, D = g.head_dim, nseg = B * Hkv;
+  PlanView pv = plan_view(plan_base, C, nseg);
+  for (int b = tid; b < B; b += NT) cumw[b + 1] = seg_layout(counts + b * kNumBuckets, D).bytes;
+  for (int s = tid; s < nseg; s += NT) {
+    pv.seg_begin[s] = 0x7fffffff;
+    pv.seg_count[s] = 0;
   }
-  for (int i = tid; i < 16 * (D + kQPad); i += NT) qs[i] = __float2half(0.f);
-  if (tid < kAttnWarps * kAttnStages) mbar_init(&bars[tid], 1);
-  mbar_fence_init();
+  __syncthreads();
+  if (tid == 0) {
+    long long acc = 0;
+    cumw[0] = 0;
+    for (int b = 0; b < B; ++b) {
+      acc += cumw[b + 1];
+      cumw[b + 1] = acc;
+    }
+  }
+  __syncthreads();
+  const long long total = cumw[B] * Hkv;
+  // walks the segments CTA c overlaps; with `out` set, writes the runs starting at run index `first`
+  auto walk = [&](int c, RunDesc* out, int first) {
+    int n = 0;
+    long long y = cta_range_begin(total, c, C);
+    const long long y_end = cta_range_begin(total, c + 1, C);
+    int b = 0;
+    while (y < y_end) {
+      int lo = b, hi = B;  // last b with Hkv*cumw[b] <= y
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (cumw[mid] * Hkv <= y) lo = mid; else hi = mid;
+      }
+      b = lo;
+      const SegLayout sl = seg_layout(counts + b * kNumBuckets, D);
+      const long long seq_first = cumw[b] * Hkv;
+      const int h = (int)((y - seq_first) / sl.bytes);
+      const long long seg_off = seq_first + (long long)h * sl.bytes;
+      const long long seg_end = seg_off + sl.bytes;
+      const long long y_next = seg_end < y_end ? seg_end : y_end;
+      int ka[kNumBuckets], kb[kNumBuckets];
+      if (seg_tiles_in_range(sl, D, y - seg_off, y_next - seg_off, ka, kb) > 0) {
+        if (out != nullptr) {
+          RunDesc r;
+          r.seq = b;
+          r.head = h;
+#pragma unroll
+          for (int i = 0; i < kNumBuckets; ++i) {
+            r.ka[i] = ka[i];
+            r.kb[i] = kb[i];
+            r.cnt[i] = sl.cnt[i];
+          }
+          r.pad_[0] = r.pad_[1] = 0;
+          out[first + n] = r;
+          const int seg = b * Hkv + h;
+          atomicMin(&pv.seg_begin[seg], first + n);
+          atomicAdd(&pv.seg_count[seg], 1);
+        }
+        ++n;
+      }
+      y = y_next;
+    }
+    return n;
+  };
+  for (int c = tid; c < C; c += NT) nruns_of[c + 1] = total > 0 ? walk(c, nullptr, 0) : 0;
   __syncthreads();
   if (tid == 0) {
     int acc = 0;
-    prefix[0] = 0;
-    for (int b = 0; b < B; ++b) {
-      acc += prefix[b + 1];
-      prefix[b + 1] = acc;
+    nruns_of[0] = 0;
+    for (int c = 0; c < C; ++c) {
+      acc += nruns_of[c + 1];
+      nruns_of[c + 1] = acc;
     }
+    pv.header[0] = acc;
+    pv.header[1] = C;
+    pv.header[2] = nseg;
+    pv.header[3] = 0;
   }
   __syncthreads();
-  const long long total_blocks = (long long)prefix[B] * Hkv;
-  const int C = p.num_ctas, c = blockIdx.x;
-  const long long x_begin = (total_blocks * c + C - 1) / C;
-  const long long x_end = (total_blocks * (c + 1) + C - 1) / C;
+  for (int c = tid; c <= C; c += NT) pv.cta_begin[c] = nruns_of[c];
+  for (int c = tid; c < C; c += NT)
+    if (total > 0) walk(c, pv.runs, nruns_of[c]);
+}
 
-  uint8_t* my_stages = stages + warp * kAttnStages * kStageBytes;
-  uint64_t* my_bars = bars + warp * kAttnStages;
-  uint32_t issued = 0, waited = 0;  // per-warp running counters (identical in all lanes)
-  bool failed = false;
+// Online-softmax state of one lane: query heads 2t and 2t+1 (t = lane & 3).
+struct LaneState {
+  float m0, m1;  // running reference maxima (log2 units); identical in the 8 lanes that share t
+  float l0, l1;  // this lane's share of the running sums
+};
 
-  long long x = x_begin;
-  while (x < x_end) {
-    // ---- locate the segment (sequence b, KV head h) holding global block x ----
-    int lo = 0, hi = B;  // last b with Hkv*prefix[b] <= x
-    while (hi - lo > 1) {
-      int mid = (lo + hi) >> 1;
-      if ((long long)prefix[mid] * Hkv <= x) lo = mid; else hi = mid;
-    }
-    const int b = lo;
-    const int nblk = prefix[b + 1] - prefix[b];
-    const long long seq_first = (long long)prefix[b] * Hkv;
-    const int h = (int)((x - seq_first) / nblk);
-    const int r0 = (int)((x - seq_first) - (long long)h * nblk);
-    const long long seg_end = seq_first + (long long)(h + 1) * nblk;
-    const long long e = seg_end < x_end ? seg_end : x_end;
-    const int r1 = r0 + (int)(e - x);
-    const int seg = b * Hkv + h;
+// The running maximum is only raised when a score exceeds it by more than kLazyTau (log2
+// units), so most tiles need no cross-lane reduction and no rescale of the accumulators;
+// probabilities then reach at most 2^kLazyTau, well inside fp16 / fp32 range.
+constexpr float kLazyTau = 8.0f;
 
-    int cnt[kNumBuckets], nb[kNumBuckets];
+template <int D, int BITS, bool PRECISE>
+__device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t* vtile, const float2* sc, int nvalid,
+                                             int lane, const uint32_t (&qb)[D / 16][2],
+                                             const uint32_t (&ql)[D / 16][2], LaneState& st, float (&o)[D / 16][4],
+                                             float scale_log2, float* lp0, float* lp1) {
+  const int g = lane >> 2, t = lane & 3;
+  // ---- every shared-memory load of the tile up front ---------------------------------
+  uint32_t kr0[SliceWords<D, BITS>::K], kr1[SliceWords<D, BITS>::K];
+  uint32_t vr0[SliceWords<D, BITS>::V], vr1[SliceWords<D, BITS>::V], vr2[SliceWords<D, BITS>::V],
+      vr3[SliceWords<D, BITS>::V];
+  load_kslice<D, BITS>(ktile, g, t, kr0);
+  load_kslice<D, BITS>(ktile, g + 8, t, kr1);
+  load_vrow<D, BITS>(vtile, 2 * t, g, vr0);
+  load_vrow<D, BITS>(vtile, 2 * t + 1, g, vr1);
+  load_vrow<D, BITS>(vtile, 2 * t + 8, g, vr2);
+  load_vrow<D, BITS>(vtile, 2 * t + 9, g, vr3);
+  const float2 scA = sc[g], scB = sc[g + 8];  // (k scale, v scale) of keys g, g+8
+  // ---- scores; the V unpack is independent integer work that overlaps the MMA latency ----
+  float s[4];
+  qk_tile<D, BITS, PRECISE>(kr0, kr1, lane, qb, ql, s);
+  uint32_t v0[D / 8], v1[D / 8];
+  unpack_vpair<D, BITS>(vr0, vr1, g, v0);
+  unpack_vpair<D, BITS>(vr2, vr3, g, v1);
+  const float kcA = scA.x * scale_log2, kcB = scB.x * scale_log2;
+  float x00 = s[0] * kcA, x01 = s[1] * kcA, x10 = s[2] * kcB, x11 = s[3] * kcB;
+  float vsA = scA.y, vsB = scB.y;
+  if (nvalid < 16) {  // last tile of a bucket: rows past its end may hold anything, scales included
+    if (g >= nvalid) { x00 = x01 = -INFINITY; vsA = 0.f; }
+    if (g + 8 >= nvalid) { x10 = x11 = -INFINITY; vsB = 0.f; }
+  }
+  if (lp0 != nullptr) {
+    lp0[g] = x00;
+    lp0[g + 8] = x10;
+  }
+  if (lp1 != nullptr) {
+    lp1[g] = x01;
+    lp1[g + 8] = x11;
+  }
+  float mx0 = fmaxf(x00, x10), mx1 = fmaxf(x01, x11);
+  if (__any_sync(0xffffffffu, (mx0 > st.m0 + kLazyTau) | (mx1 > st.m1 + kLazyTau))) {
 #pragma unroll
-    for (int i = 0; i < kNumBuckets; ++i) {
-      cnt[i] = p.counts[b * kNumBuckets + i];
-      nb[i] = (cnt[i] + kb[i] - 1) / kb[i];
+    for (int off = 4; off < 32; off <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
     }
-
-    __syncthreads();  // previous segment's merge has finished with qs and the stages
-    // ---- query rows of this group -> shared fp16 (rows 0..G-1 hi, 8..8+G-1 residual)
-    for (int i = tid; i < G * D; i += NT) {
-      const int gq = i / D, d = i - gq * D;
-      const long long qi = ((long long)b * p.num_q_heads + h * G + gq) * D + d;
-      float q = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[qi])
-                            : static_cast<const float*>(p.query)[qi];
-      const __half qh = __float2half_rn(q);
-      qs[gq * (D + kQPad) + d] = qh;
-      if (PRECISE) qs[(gq + 8) * (D + kQPad) + d] = __float2half_rn(q - __half2float(qh));
+    const float n0 = fmaxf(st.m0, mx0), n1 = fmaxf(st.m1, mx1);
+    const float a0 = (n0 == -INFINITY) ? 1.f : ex2f(st.m0 - n0);
+    const float a1 = (n1 == -INFINITY) ? 1.f : ex2f(st.m1 - n1);
+    st.l0 *= a0;
+    st.l1 *= a1;
+#pragma unroll
+    for (int j = 0; j < D / 16; ++j) {
+      o[j][0] *= a0;
+      o[j][2] *= a0;
+      o[j][1] *= a1;
+      o[j][3] *= a1;
     }
-    __syncthreads();
+    st.m0 = n0;
+    st.m1 = n1;
+  }
+  const float mu0 = (st.m0 == -INFINITY) ? 0.f : st.m0, mu1 = (st.m1 == -INFINITY) ? 0.f : st.m1;
+  const float p00 = ex2f(x00 - mu0), p01 = ex2f(x01 - mu1), p10 = ex2f(x10 - mu0), p11 = ex2f(x11 - mu1);
+  st.l0 += p00 + p10;
+  st.l1 += p01 + p11;
+  const float a00 = p00 * vsA, a01 = p01 * vsA, a10 = p10 * vsB, a11 = p11 * vsB;
+  const uint32_t ph0 = pack_h2(a00, a01), ph1 = pack_h2(a10, a11);
+  const uint32_t pb0 = movmatrix_trans(ph0), pb1 = movmatrix_trans(ph1);
+  uint32_t pl0 = 0u, pl1 = 0u;
+  if (PRECISE) {
+    const __half2 h0 = bits_h2(ph0), h1 = bits_h2(ph1);
+    pl0 = movmatrix_trans(pack_h2(a00 - __low2float(h0), a01 - __high2float(h0)));
+    pl1 = movmatrix_trans(pack_h2(a10 - __low2float(h1), a11 - __high2float(h1)));
+  }
+  pv_tile<D, PRECISE>(v0, v1, pb0, pb1, pl0, pl1, o);
+}
 
-    // ---- this warp's blocks: r0 + warp, r0 + warp + W, ... < r1 ----------------
-    WarpState st;
-    st.m = -INFINITY;
-    st.l = 0.f;
-    float o[D / 8][4];
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-    uint32_t qa[D / 16][4];
-    int cur_bucket = -1;
-    const uint8_t* arena = arena_ptr(g, p.store, p.layer, b);
-    const int nmine = (r1 - r0 - warp + kAttnWarps - 1) / kAttnWarps;  // may be <= 0
+// One block = up to KBKEYS keys of one bucket, staged at `sb`: [K rows][V rows][float2 scales].
+// This warp owns tiles first, first + NCONS, ... of it.
+template <int D, int BITS, bool PRECISE, int KBKEYS, int NCONS>
+__device__ __forceinline__ void process_block(const uint8_t* sb, int nkeys, int first, int lane,
+                                              const uint32_t (&qb)[D / 16][2], const uint32_t (&ql)[D / 16][2],
+                                              LaneState& st, float (&o)[D / 16][4], float scale_log2, float* lp0,
+                                              float* lp1) {
+  constexpr int PD = D * BITS / 8;
+  const uint8_t* kbase = sb;
+  const uint8_t* vbase = sb + KBKEYS * PD;
+  const float2* sc = reinterpret_cast<const float2*>(sb + 2 * KBKEYS * PD);
+  const int ntl = (nkeys + 15) >> 4;
+  for (int tile = first; tile < ntl; tile += NCONS) {
+    const int nvalid = nkeys - tile * 16;  // >= 16 for every tile but possibly the last
+    process_tile<D, BITS, PRECISE>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 16, nvalid, lane, qb,
+                                   ql, st, o, scale_log2, lp0 ? lp0 + tile * 16 : nullptr,
+                                   lp1 ? lp1 + tile * 16 : nullptr);
+  }
+}
 
-    auto locate = [&](int r, int& bucket, int& k0, int& nkeys) {
-      bucket = 0;
-      int rr = r;
-#pragma unroll
-      for (int i = 0; i < kNumBuckets - 1; ++i) {
-        if (bucket == i && rr >= nb[i]) {
-          rr -= nb[i];
-          bucket = i + 1;
+// Bounded mbarrier wait that also gives up as soon as another thread of the CTA has given up.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              int32_t* err) {
+  for (uint32_t i = 0; i < (1u << 20); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(err, 1);
+  return false;
+}
+
+template <int D, bool PRECISE, class CFG>
+__global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(const AttnParams p) {
+  constexpr int NCONS = CFG::NCONS, STAGES = CFG::STAGES, STAGE_BYTES = CFG::STAGE_BYTES;
+  constexpr int NTC = NCONS * 32;  // consumer threads
+  constexpr int QROWS = PRECISE ? 16 : 8;
+  constexpr int KBT0 = block_tiles(STAGE_BYTES, D, 2), KBT1 = block_tiles(STAGE_BYTES, D, 3),
+                KBT2 = block_tiles(STAGE_BYTES, D, 4), KBT3 = block_tiles(STAGE_BYTES, D, 8);
+  static_assert(KBT3 >= 1, "stage too small for one tile");
+  extern __shared__ __align__(128) uint8_t smem[];
+  const StoreGeom& g = p.g;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = p.group, Hkv = g.num_kv_heads;
+  SKV_TL(0);
+
+  uint8_t* stages = smem;                                                          // [STAGES][STAGE_BYTES]
+  float* scratch = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);          // [kMergeWarps][8][D+2]
+  __half* qbuf = reinterpret_cast<__half*>(scratch + kMergeWarps * 8 * (D + 2));   // [kQBufs][QROWS][D]
+  RunDesc* rdesc = reinterpret_cast<RunDesc*>(qbuf + kQBufs * QROWS * D);          // [kQBufs]
+  float* mpub = reinterpret_cast<float*>(rdesc + kQBufs);                          // [NCONS][8] per-warp maxima
+  uint64_t* full = reinterpret_cast<uint64_t*>(mpub + NCONS * 8);                  // [STAGES]
+  uint64_t* empty = full + STAGES;                                                 // [STAGES]
+  uint64_t* qfull = empty + STAGES;                                                // [kQBufs]
+  uint64_t* qempty = qfull + kQBufs;                                               // [kQBufs]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(qempty + kQBufs);
+
+  for (int i = tid; i < kQBufs * QROWS * D; i += (NCONS + 1) * 32) qbuf[i] = __float2half(0.f);
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], NCONS);
+    }
+    for (int s = 0; s < kQBufs; ++s) {
+      mbar_init(&qfull[s], 1);
+      mbar_init(&qempty[s], NCONS);
+    }
+    *abort_flag = 0;
+  }
+  mbar_fence_init();
+  __syncthreads();
+
+  const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
+  const int run_begin = pv.cta_begin[blockIdx.x], run_end = pv.cta_begin[blockIdx.x + 1];
+  SKV_TL(1);
+
+  if (warp == NCONS) {
+    // ================================ producer warp ================================
+    int stg = 0, qi = 0;
+    uint32_t epar = 1, qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
+    const int kbt[kNumBuckets] = {KBT0, KBT1, KBT2, KBT3};
+    for (int r = run_begin; r < run_end; ++r) {
+      const RunDesc d = pv.runs[r];
+      if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err)) break;
+      const long long q_off = ((long long)d.seq * p.num_q_heads + (long long)d.head * G) * D;
+      __half* qdst = qbuf + qi * QROWS * D;
+      if (lane == 0) rdesc[qi] = d;
+      if (!PRECISE && p.q_is_half) {
+        if (lane == 0) {
+          fence_proxy_async();
+          mbar_expect_tx(&qfull[qi], (uint32_t)(G * D * 2));
+          bulk_g2s(qdst, static_cast<const __half*>(p.query) + q_off, (uint32_t)(G * D * 2), &qfull[qi]);
         }
-      }
-      k0 = rr * kb[bucket];
-      nkeys = min(kb[bucket], cnt[bucket] - k0);
-    };
-    auto issue = [&](int i) {  // lane 0 only
-      int bucket, k0, nkeys;
-      locate(r0 + warp + i * kAttnWarps, bucket, k0, nkeys);
-      const int n16 = (nkeys + 15) & ~15;
-      const int pd = g.row_bytes[bucket];
-      const uint32_t stg = issued % kAttnStages;
-      uint8_t* sb = my_stages + stg * kStageBytes;
-      const long long row = (long long)h * g.cap[bucket] + k0;
-      const uint32_t kbytes = (uint32_t)(n16 * pd), sbytes = (uint32_t)(n16 * 4);
-      fence_proxy_async();
-      mbar_expect_tx(&my_bars[stg], 2 * kbytes + 2 * sbytes);
-      bulk_g2s(sb, arena + g.k_off[bucket] + row * pd, kbytes, &my_bars[stg]);
-      bulk_g2s(sb + kb[bucket] * pd, arena + g.v_off[bucket] + row * pd, kbytes, &my_bars[stg]);
-      bulk_g2s(sb + 2 * kb[bucket] * pd, arena + g.ks_off[bucket] + row * 4, sbytes, &my_bars[stg]);
-      bulk_g2s(sb + 2 * kb[bucket] * pd + kb[bucket] * 4, arena + g.vs_off[bucket] + row * 4, sbytes,
-               &my_bars[stg]);
-    };
-
-    if (!failed) {
-      for (int i = 0; i < kAttnStages - 1 && i < nmine; ++i) {
-        if (lane == 0) issue(i);
-        ++issued;
-      }
-      for (int i = 0; i < nmine; ++i) {
+      } else {
+        for (int i = lane; i < G * D; i += 32) {
+          const float q = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[q_off + i])
+                                      : static_cast<const float*>(p.query)[q_off + i];
+          const __half qh = __float2half_rn(q);
+          qdst[i] = qh;
+          if (PRECISE) qdst[8 * D + i] = __float2half_rn(q - __half2float(qh));
+        }
         __syncwarp();
-        if (i + kAttnStages - 1 < nmine) {
-          if (lane == 0) issue(i + kAttnStages - 1);
-          ++issued;
-        }
-        const uint32_t stg = waited % kAttnStages, par = (waited / kAttnStages) & 1;
-        if (!mbar_wait_bounded(&my_bars[stg], par)) {
-          failed = true;
-          if (lane == 0) atomicExch(p.err, 1);
-          break;
-        }
-        ++waited;
-        int bucket, k0, nkeys;
-        locate(r0 + warp + i * kAttnWarps, bucket, k0, nkeys);
-        const uint8_t* sb = my_stages + stg * kStageBytes;
-        const int gq = lane >> 2;
-        float* logit_row = nullptr;
-        if (p.logits != nullptr && gq < G)
-          logit_row = p.logits + ((long long)b * p.num_q_heads + h * G + gq) * g.slots + g.bucket_base[bucket] + k0;
-        if (bucket != cur_bucket) {
-          cur_bucket = bucket;
-          switch (bucket) {
-            case 0: gather_q_frags<D, 2>(qs, lane, qa); break;
-            case 1: gather_q_frags<D, 3>(qs, lane, qa); break;
-            case 2: gather_q_frags<D, 4>(qs, lane, qa); break;
-            default: gather_q_frags<D, 8>(qs, lane, qa); break;
+        if (lane == 0) mbar_arrive(&qfull[qi]);
+      }
+      const uint8_t* arena = arena_ptr(g, p.store, p.layer, d.seq);
+      bool ok = true;
+      for (int i = 0; i < kNumBuckets && ok; ++i) {
+        const int pd = g.row_bytes[i], kbkeys = kbt[i] * 16;
+        for (int t0 = d.ka[i]; t0 < d.kb[i]; t0 += kbt[i]) {
+          if (!wait_or_abort(&empty[stg], epar, abort_flag, p.err)) {
+            ok = false;
+            break;
+          }
+          if (lane == 0 && p.debug_mode < 2) {
+            const int ntl = (d.kb[i] - t0) < kbt[i] ? (d.kb[i] - t0) : kbt[i];
+            const int key0 = t0 * 16;
+            const int nkeys = (d.cnt[i] - key0) < ntl * 16 ? (d.cnt[i] - key0) : ntl * 16;
+            const int n16 = (nkeys + 15) & ~15;
+            uint8_t* sb = stages + (long long)stg * STAGE_BYTES;
+            const long long row = (long long)d.head * g.cap[i] + key0;
+            const uint32_t kbytes = (uint32_t)(n16 * pd), sbytes = (uint32_t)(n16 * 8);
+            fence_proxy_async();
+            mbar_expect_tx(&full[stg], 2 * kbytes + sbytes);
+            bulk_g2s(sb, arena + g.k_off[i] + row * pd, kbytes, &full[stg]);
+            bulk_g2s(sb + kbkeys * pd, arena + g.v_off[i] + row * pd, kbytes, &full[stg]);
+            bulk_g2s(sb + 2 * kbkeys * pd, arena + g.sc_off[i] + row * 8, sbytes, &full[stg]);
+          } else if (lane == 0) {
+            mbar_arrive(&full[stg]);
+          }
+          if (++stg == STAGES) {
+            stg = 0;
+            epar ^= 1u;
           }
         }
-        switch (bucket) {
-          case 0: process_block<D, 2, PRECISE>(sb, nkeys, lane, qa, st, o, p.scale_log2, logit_row); break;
-          case 1: process_block<D, 3, PRECISE>(sb, nkeys, lane, qa, st, o, p.scale_log2, logit_row); break;
-          case 2: process_block<D, 4, PRECISE>(sb, nkeys, lane, qa, st, o, p.scale_log2, logit_row); break;
-          default: process_block<D, 8, PRECISE>(sb, nkeys, lane, qa, st, o, p.scale_log2, logit_row); break;
-        }
+      }
+      if (!ok) break;
+      if (++qi == kQBufs) {
+        qi = 0;
+        qepar ^= 1u;
       }
     }
-    // drain anything still in flight (only after a failed wait)
-    while (waited < issued) {
-      const uint32_t stg = waited % kAttnStages, par = (waited / kAttnStages) & 1;
-      mbar_wait_bounded(&my_bars[stg], par);
-      ++waited;
-    }
-    __syncwarp();
+    return;
+  }
 
-    // ---- merge the warps of this CTA and write the partial -----------------------
+  // ================================== consumer warps ==================================
+  int stg = 0, qi = 0;
+  uint32_t fpar = 0, qfpar = 0;
+  bool aborted = false;
+  for (int r = run_begin; r < run_end; ++r) {
+    if (!aborted && !wait_or_abort(&qfull[qi], qfpar, abort_flag, p.err)) aborted = true;
+    SKV_TL(2 + 4 * (r - run_begin));
+    const RunDesc& d = rdesc[qi];  // stays valid until this warp arrives on qempty below
+    const __half* qs = qbuf + qi * QROWS * D;
+    const int b = d.seq, h = d.head;
+
+    LaneState st;
+    st.m0 = st.m1 = -INFINITY;
+    st.l0 = st.l1 = 0.f;
+    float o[D / 16][4];
+#pragma unroll
+    for (int j = 0; j < D / 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const int hq0 = h * G + 2 * (lane & 3);  // first of this lane's two query heads
+    float* lbase = nullptr;
+    if (p.logits != nullptr) lbase = p.logits + ((long long)b * p.num_q_heads + hq0) * g.slots;
+    const bool head0_ok = 2 * (lane & 3) < G, head1_ok = 2 * (lane & 3) + 1 < G;
+    int tile_base = 0;  // tile i of a block goes to warp (tile_base + i) % NCONS
+
+    auto run_bucket = [&](auto bits_tag, auto kbt_tag, int bucket) {
+      constexpr int BITS = decltype(bits_tag)::value;
+      constexpr int KBT = decltype(kbt_tag)::value;
+      if (d.ka[bucket] >= d.kb[bucket]) return;
+      uint32_t qb[D / 16][2];
+      uint32_t ql[D / 16][2];
+      if (!aborted) {
+        gather_q_frags<D, BITS>(qs, lane, 0, qb);
+        if (PRECISE) gather_q_frags<D, BITS>(qs, lane, 8, ql);
+      }
+      for (int t0 = d.ka[bucket]; t0 < d.kb[bucket]; t0 += KBT) {
+        const int ntl = (d.kb[bucket] - t0) < KBT ? (d.kb[bucket] - t0) : KBT;
+        const int key0 = t0 * 16;
+        const int nkeys = (d.cnt[bucket] - key0) < ntl * 16 ? (d.cnt[bucket] - key0) : ntl * 16;
+        if (!aborted && !wait_or_abort(&full[stg], fpar, abort_flag, p.err)) aborted = true;
+        int first = warp - tile_base;
+        if (first < 0) first += NCONS;
+        if (!aborted && first < ntl && p.debug_mode != 1 && p.debug_mode != 3) {
+          float* lrow = lbase != nullptr ? lbase + g.bucket_base[bucket] + key0 : nullptr;
+          float* lp0 = (lrow != nullptr && head0_ok) ? lrow : nullptr;
+          float* lp1 = (lrow != nullptr && head1_ok) ? lrow + g.slots : nullptr;
+          process_block<D, BITS, PRECISE, KBT * 16, NCONS>(stages + (long long)stg * STAGE_BYTES, nkeys, first, lane,
+                                                           qb, ql, st, o, p.scale_log2, lp0, lp1);
+        }
+        tile_base = (tile_base + ntl) % NCONS;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stg]);
+        if (++stg == STAGES) {
+          stg = 0;
+          fpar ^= 1u;
+        }
+      }
+    };
+    run_bucket(std::integral_constant<int, 2>{}, std::integral_constant<int, KBT0>{}, 0);
+    run_bucket(std::integral_constant<int, 3>{}, std::integral_constant<int, KBT1>{}, 1);
+    run_bucket(std::integral_constant<int, 4>{}, std::integral_constant<int, KBT2>{}, 2);
+    run_bucket(std::integral_constant<int, 8>{}, std::integral_constant<int, KBT3>{}, 3);
+
+    // ---- merge the consumer warps and write the partial of this run ------------------------
+    SKV_TL(3 + 4 * (r - run_begin));
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&qempty[qi]);  // query rows and descriptor are no longer needed
+    const int gq = lane >> 2, t = lane & 3;
+    if (gq == 0) {
+      mpub[warp * 8 + 2 * t] = st.m0;
+      mpub[warp * 8 + 2 * t + 1] = st.m1;
+    }
+    named_bar_sync(1, NTC);
+    float M0 = -INFINITY, M1 = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NCONS; ++w) {
+      M0 = fmaxf(M0, mpub[w * 8 + 2 * t]);
+      M1 = fmaxf(M1, mpub[w * 8 + 2 * t + 1]);
+    }
     {
-      float lsum = st.l;
-      lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-      lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-      float* scratch = reinterpret_cast<float*>(my_stages);  // [G][D+2], this warp's stage 0
-      const int gq = lane >> 2, t = lane & 3;
-      if (gq < G) {
-        float* row = scratch + gq * (D + 2);
-        if (t == 0) {
-          row[0] = st.m;
-          row[1] = lsum;
+      const float f0 = (st.m0 == -INFINITY) ? 0.f : ex2f(st.m0 - M0);
+      const float f1 = (st.m1 == -INFINITY) ? 0.f : ex2f(st.m1 - M1);
+      st.l0 *= f0;
+      st.l1 *= f1;
+#pragma unroll
+      for (int j = 0; j < D / 16; ++j) {
+        o[j][0] *= f0;
+        o[j][2] *= f0;
+        o[j][1] *= f1;
+        o[j][3] *= f1;
+      }
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, off);
+        st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, off);
+      }
+    }
+    constexpr int NEL = 8 * (D + 2);            // scratch elements per warp ([8 heads][D+2])
+    constexpr int EPT = (NEL + NTC - 1) / NTC;  // elements per reducing thread
+    float acc[EPT];
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) acc[k] = 0.f;
+    for (int base = 0; base < NCONS; base += kMergeWarps) {
+      if (warp >= base && warp < base + kMergeWarps) {
+        float* row0 = scratch + (warp - base) * NEL + (2 * t) * (D + 2);
+        float* row1 = row0 + (D + 2);
+        if (gq == 0) {
+          row0[0] = 0.f;
+          row0[1] = st.l0;
+          row1[0] = 0.f;
+          row1[1] = st.l1;
         }
 #pragma unroll
-        for (int j = 0; j < D / 8; ++j) {
-          float v0 = o[j][0], v1 = o[j][1];
-          if (PRECISE) {
-            v0 += o[j][2];
-            v1 += o[j][3];
+        for (int j = 0; j < D / 16; ++j) {
+          const int dd = gq * (D / 8) + 2 * j;
+          row0[2 + dd] = o[j][0];
+          row0[2 + dd + 1] = o[j][2];
+          row1[2 + dd] = o[j][1];
+          row1[2 + dd + 1] = o[j][3];
+        }
+      }
+      named_bar_sync(1, NTC);
+      const int nw = (NCONS - base) < kMergeWarps ? (NCONS - base) : kMergeWarps;
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) {
+        const int e = tid + k * NTC;
+        if (e < NEL) {
+          for (int w = 0; w < nw; ++w) acc[k] += scratch[w * NEL + e];
+        }
+      }
+      named_bar_sync(1, NTC);
+    }
+    {
+      float* out = p.partials + (long long)r * partial_stride(G, D);
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) {
+        const int e = tid + k * NTC;
+        if (e < G * (D + 2)) {
+          const int hd = e / (D + 2), col = e - hd * (D + 2);
+          float v = acc[k];
+          if (col == 0) {
+            v = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < NCONS; ++w) v = fmaxf(v, mpub[w * 8 + hd]);
           }
-          row[2 + (D / 8) * (2 * t) + j] = v0;
-          row[2 + (D / 8) * (2 * t + 1) + j] = v1;
+          out[e] = v;
         }
       }
     }
-    __syncthreads();
-    {
-      float* out = p.partials + (long long)(c + seg) * partial_stride(G, D);
-      for (int i = tid; i < G * D; i += NT) {
-        const int gq = i / D, d = i - gq * D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) {
-          const float* row = reinterpret_cast<const float*>(stages + w * kAttnStages * kStageBytes) + gq * (D + 2);
-          M = fmaxf(M, row[0]);
-        }
-        float acc = 0.f, L = 0.f;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) {
-          const float* row = reinterpret_cast<const float*>(stages + w * kAttnStages * kStageBytes) + gq * (D + 2);
-          const float mw = row[0];
-          if (mw != -INFINITY) {
-            const float f = ex2f(mw - M);
-            acc += row[2 + d] * f;
-            L += row[1] * f;
-          }
-        }
-        float* orow = out + gq * (D + 2);
-        orow[2 + d] = acc;
-        if (d == 0) {
-          orow[0] = M;
-          orow[1] = L;
-        }
-      }
+    named_bar_sync(1, NTC);  // mpub and scratch are free again
+    SKV_TL(4 + 4 * (r - run_begin));
+    if (++qi == kQBufs) {
+      qi = 0;
+      qfpar ^= 1u;
     }
-    x = e;
   }
 }
 
 // ---- combine ----------------------------------------------------------------------
 struct CombineParams {
   StoreGeom g;
-  const int32_t* counts;
+  const int* plan;
   const void* query;
   int q_is_half;
   int num_q_heads;
@@ -397,45 +589,13 @@ struct CombineParams {
 // one block (128 threads) per (sequence, KV head) segment
 __global__ void lse_combine_kernel(const CombineParams p) {
   const StoreGeom& g = p.g;
-  const int D = g.head_dim, G = p.group, Hkv = g.num_kv_heads, B = g.num_seqs;
+  const int D = g.head_dim, G = p.group, Hkv = g.num_kv_heads;
   const int seg = blockIdx.x, b = seg / Hkv, h = seg - b * Hkv;
   const int tid = threadIdx.x, NT = blockDim.x;
-  __shared__ long long s_before;  // blocks (per head) of the sequences before b
-  __shared__ long long s_total;   // blocks (per head) of all sequences
-  __shared__ int s_nblk;
   __shared__ float s_cur[8];
-
-  int kb[kNumBuckets];
-  for (int i = 0; i < kNumBuckets; ++i) kb[i] = block_keys(D, bucket_bits(i));
-  if (tid == 0) {
-    long long before = 0, total = 0;
-    int mine = 0;
-    for (int bb = 0; bb < B; ++bb) {
-      int n = 0;
-      for (int i = 0; i < kNumBuckets; ++i) n += (p.counts[bb * kNumBuckets + i] + kb[i] - 1) / kb[i];
-      if (bb < b) before += n;
-      if (bb == b) mine = n;
-      total += n;
-    }
-    s_before = before;
-    s_total = total;
-    s_nblk = mine;
-  }
-  __syncthreads();
-  const long long total_blocks = s_total * Hkv;
-  const int nblk = s_nblk;
-  const long long S = s_before * Hkv + (long long)h * nblk, E = S + nblk;
-  const int C = p.num_ctas;
-  int c_first = 0, c_last = -1;
-  if (nblk > 0) {
-    c_first = (int)((S * C) / total_blocks);
-    c_last = (int)(((E - 1) * C) / total_blocks);
-  }
-  // CTA c holds a partial of this segment iff its block range meets [S, E)
-  auto cta_has = [&](int c) {
-    const long long lo = (total_blocks * c + C - 1) / C, hi = (total_blocks * (c + 1) + C - 1) / C;
-    return (lo > S ? lo : S) < (hi < E ? hi : E);
-  };
+  const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
+  const int nsplit = pv.seg_count[seg];
+  const int r0 = nsplit > 0 ? pv.seg_begin[seg] : 0;
 
   // ---- current-token logits (full precision), one warp per group row -------------
   const bool has_cur = p.cur_k != nullptr && p.cur_v != nullptr;
@@ -462,15 +622,10 @@ __global__ void lse_combine_kernel(const CombineParams p) {
   for (int i = tid; i < G * D; i += NT) {
     const int gq = i / D, d = i - gq * D;
     float M = has_cur ? s_cur[gq] : -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (!cta_has(c)) continue;
-      const float* row = p.partials + (long long)(c + seg) * pstride + gq * (D + 2);
-      M = fmaxf(M, row[0]);
-    }
+    for (int k = 0; k < nsplit; ++k) M = fmaxf(M, p.partials[(long long)(r0 + k) * pstride + gq * (D + 2)]);
     float acc = 0.f, L = 0.f;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (!cta_has(c)) continue;
-      const float* row = p.partials + (long long)(c + seg) * pstride + gq * (D + 2);
+    for (int k = 0; k < nsplit; ++k) {
+      const float* row = p.partials + (long long)(r0 + k) * pstride + gq * (D + 2);
       const float mw = row[0];
       if (mw != -INFINITY) {
         const float f = ex2f(mw - M);
@@ -503,43 +658,60 @@ using namespace skv;
 
 static inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
-static size_t attn_smem_bytes(int head_dim, int num_seqs) {
-  return (size_t)kAttnWarps * kAttnStages * kStageBytes + 16 * (head_dim + kQPad) * 2 +
-         kAttnWarps * kAttnStages * sizeof(uint64_t) + (size_t)(num_seqs + 1) * sizeof(int) + 16;
+template <class CFG, bool PRECISE>
+static size_t attn_smem_bytes(int head_dim) {
+  const int qrows = PRECISE ? 16 : 8;
+  return (size_t)CFG::STAGES * CFG::STAGE_BYTES + (size_t)kMergeWarps * 8 * (head_dim + 2) * 4 +
+         (size_t)kQBufs * qrows * head_dim * 2 + kQBufs * sizeof(RunDesc) + (size_t)CFG::NCONS * 8 * 4 +
+         (2 * CFG::STAGES + 2 * kQBufs) * sizeof(uint64_t) + 64;
 }
 
 extern "C" int skv_attn_num_ctas(int device) {
   int sms = 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return SKV_ERR_CUDA;
-  return sms;
+  return sms < kMaxCtas ? sms : kMaxCtas;
 }
 
 extern "C" int64_t skv_attn_partials_bytes(const SkvStoreDesc* desc, int num_q_heads, int num_ctas) {
   if (!desc || num_ctas <= 0 || num_q_heads <= 0 || desc->num_kv_heads <= 0) return SKV_ERR_INVALID;
   const int group = num_q_heads / desc->num_kv_heads;
-  const int64_t slots = (int64_t)num_ctas + (int64_t)desc->num_seqs * desc->num_kv_heads;
-  return slots * partial_stride(group, desc->head_dim) * (int64_t)sizeof(float);
+  const int64_t runs = (int64_t)num_ctas + (int64_t)desc->num_seqs * desc->num_kv_heads;
+  return runs * partial_stride(group, desc->head_dim) * (int64_t)sizeof(float);
 }
 
-template <int D, bool PRECISE>
-static int launch_attn(const AttnParams& p, size_t smem, cudaStream_t st) {
-  static bool configured = false;  // per template instance
-  if (!configured) {
-    if (cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(kAttnWarps * kAttnStages * kStageBytes + 16 * (D + kQPad) * 2 +
-                                   kAttnWarps * kAttnStages * 8 + (kMaxSeqs + 1) * 4 + 16)) != cudaSuccess)
-      return SKV_ERR_CUDA;
-    configured = true;
-  }
-  decode_attn_kernel<D, PRECISE><<<p.num_ctas, kAttnWarps * 32, smem, st>>>(p);
+extern "C" int64_t skv_attn_plan_bytes(const SkvStoreDesc* desc, int num_ctas) {
+  if (!desc || num_ctas <= 0) return SKV_ERR_INVALID;
+  return plan_words(num_ctas, desc->num_seqs * desc->num_kv_heads) * (int64_t)sizeof(int);
+}
+
+extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, int num_ctas, void* plan,
+                             void* stream) {
+  if (!desc || !counts || !plan) return SKV_ERR_INVALID;
+  if (num_ctas <= 0 || num_ctas > kMaxCtas || desc->num_seqs > kMaxSeqs) return SKV_ERR_UNSUPPORTED;
+  if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
+  attn_plan_kernel<<<1, 1024, 0, as_stream(stream)>>>(make_geom(*desc), counts, num_ctas, static_cast<int*>(plan));
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 
-extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const int32_t* counts,
+template <int D, bool PRECISE, class CFG>
+static int launch_attn(AttnParams& p, cudaStream_t st) {
+  static bool configured = false;  // per template instance
+  const size_t smem = attn_smem_bytes<CFG, PRECISE>(D);
+  if (!configured) {
+    if (cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE, CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return SKV_ERR_CUDA;
+    configured = true;
+  }
+  decode_attn_kernel<D, PRECISE, CFG><<<p.num_ctas, (CFG::NCONS + 1) * 32, smem, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
                                     const void* query, int query_dtype, int num_q_heads, void* partials,
                                     int num_ctas, float* logits, int32_t* err_flag, void* stream) {
-  if (!desc || !store || !counts || !query || !partials || !err_flag) return SKV_ERR_INVALID;
-  if (layer < 0 || layer >= desc->num_layers || num_ctas <= 0) return SKV_ERR_INVALID;
+  if (!desc || !store || !plan || !query || !partials || !err_flag) return SKV_ERR_INVALID;
+  if (layer < 0 || layer >= desc->num_layers || num_ctas <= 0 || num_ctas > kMaxCtas) return SKV_ERR_INVALID;
   if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
   if (desc->num_seqs > kMaxSeqs) return SKV_ERR_UNSUPPORTED;
   if (num_q_heads % desc->num_kv_heads != 0) return SKV_ERR_INVALID;
@@ -550,7 +722,7 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
   p.g = make_geom(*desc);
   p.store = static_cast<const uint8_t*>(store);
   p.layer = layer;
-  p.counts = counts;
+  p.plan = static_cast<const int*>(plan);
   p.query = query;
   p.q_is_half = query_dtype == SKV_DTYPE_F16;
   p.num_q_heads = num_q_heads;
@@ -560,27 +732,56 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
   p.logits = logits;
   p.err = err_flag;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)desc->head_dim));
-  const size_t smem = attn_smem_bytes(desc->head_dim, desc->num_seqs);
+  static const int debug_mode = getenv("SKV_ATTN_DEBUG") ? atoi(getenv("SKV_ATTN_DEBUG")) : 0;
+  p.debug_mode = debug_mode;
+#ifdef SKV_TIMELINE
+  {
+    static unsigned long long* tl = nullptr;
+    static unsigned long long host_tl[kMaxCtas * 16];
+    if (tl == nullptr) {
+      cudaMalloc(&tl, sizeof(host_tl));
+      cudaMemset(tl, 0, sizeof(host_tl));
+    }
+    p.timeline = tl;
+    if (getenv("SKV_ATTN_TL_DUMP") && layer == 1) {  // dump what the previous launch recorded
+      cudaDeviceSynchronize();
+      cudaMemcpy(host_tl, tl, sizeof(host_tl), cudaMemcpyDeviceToHost);
+      unsigned long long t0 = ~0ull;
+      for (int c = 0; c < num_ctas; ++c) if (host_tl[c * 16] && host_tl[c * 16] < t0) t0 = host_tl[c * 16];
+      for (int c = 0; c < num_ctas; c += 13) {
+        fprintf(stderr, "cta %3d:", c);
+        for (int k = 0; k < 12; ++k) fprintf(stderr, " %6lld", host_tl[c * 16 + k] ? (long long)(host_tl[c * 16 + k] - t0) : -1LL);
+        fprintf(stderr, "\n");
+      }
+      unsigned long long tmax = 0;
+      for (int i = 0; i < num_ctas * 16; ++i) if (host_tl[i] > tmax) tmax = host_tl[i];
+      fprintf(stderr, "span %lld ns\n", (long long)(tmax - t0));
+      cudaMemset(tl, 0, sizeof(host_tl));
+    }
+  }
+#endif
+  static const int no_logits = getenv("SKV_ATTN_NOLOGITS") ? atoi(getenv("SKV_ATTN_NOLOGITS")) : 0;
+  if (no_logits) p.logits = nullptr;
   const bool precise = !p.q_is_half;
   if (desc->head_dim == 128)
-    return precise ? launch_attn<128, true>(p, smem, as_stream(stream))
-                   : launch_attn<128, false>(p, smem, as_stream(stream));
-  return precise ? launch_attn<64, true>(p, smem, as_stream(stream))
-                 : launch_attn<64, false>(p, smem, as_stream(stream));
+    return precise ? launch_attn<128, true, AttnCfgPrecise>(p, as_stream(stream))
+                   : launch_attn<128, false, AttnCfgFast>(p, as_stream(stream));
+  return precise ? launch_attn<64, true, AttnCfgPrecise>(p, as_stream(stream))
+                 : launch_attn<64, false, AttnCfgFast>(p, as_stream(stream));
 }
 
-extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const int32_t* counts, const void* query, int query_dtype,
+extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
                                int num_q_heads, const void* partials, int num_ctas, const void* cur_k,
                                const void* cur_v, int kv_dtype, float* out, float* lse_max, float* lse_sum,
                                float* cur_prob, void* stream) {
-  if (!desc || !counts || !query || !partials || !out) return SKV_ERR_INVALID;
+  if (!desc || !plan || !query || !partials || !out) return SKV_ERR_INVALID;
   if (num_q_heads % desc->num_kv_heads != 0 || num_ctas <= 0) return SKV_ERR_INVALID;
   const int group = num_q_heads / desc->num_kv_heads;
   if (group < 1 || group > 8) return SKV_ERR_UNSUPPORTED;
   if ((cur_k == nullptr) != (cur_v == nullptr)) return SKV_ERR_INVALID;
   CombineParams p;
   p.g = make_geom(*desc);
-  p.counts = counts;
+  p.plan = static_cast<const int*>(plan);
   p.query = query;
   p.q_is_half = query_dtype == SKV_DTYPE_F16;
   p.num_q_heads = num_q_heads;
@@ -601,6 +802,8 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const int32_t* counts, 
 
 // ---- debug: raw tile products through the production fragment code ----------------
 namespace skv {
+// q [16][D] fp16 (rows 0..7 heads, rows 8..15 residual rows), pm [16][16] fp16 laid out
+// [row][key] (rows 0..7 heads, 8..15 residual rows); scores [8][16], out [8][D] (hi + residual).
 template <int D, int BITS>
 __global__ void debug_tile_kernel(const uint8_t* k_rows, const uint8_t* v_rows, const __half* q, const __half* pm,
                                   float* scores, float* out) {
@@ -615,34 +818,44 @@ __global__ void debug_tile_kernel(const uint8_t* k_rows, const uint8_t* v_rows, 
   }
   for (int i = lane; i < 16 * D; i += 32) qs[(i / D) * (D + kQPad) + (i % D)] = q[i];
   __syncwarp();
-  uint32_t qa[D / 16][4];
-  gather_q_frags<D, BITS>(qs, lane, qa);
-  float s[2][4];
-  qk_tile<D, BITS>(ks, lane, qa, s);
+  uint32_t qb[D / 16][2], ql[D / 16][2];
+  gather_q_frags<D, BITS>(qs, lane, 0, qb);
+  gather_q_frags<D, BITS>(qs, lane, 8, ql);
   const int g = lane >> 2, t = lane & 3;
-  for (int n = 0; n < 2; ++n) {
-    scores[g * 16 + 8 * n + 2 * t] = s[n][0];
-    scores[g * 16 + 8 * n + 2 * t + 1] = s[n][1];
-    scores[(g + 8) * 16 + 8 * n + 2 * t] = s[n][2];
-    scores[(g + 8) * 16 + 8 * n + 2 * t + 1] = s[n][3];
-  }
-  uint32_t pa[4];
+  float s[4];
+  uint32_t kr0[SliceWords<D, BITS>::K], kr1[SliceWords<D, BITS>::K];
+  load_kslice<D, BITS>(ks, g, t, kr0);
+  load_kslice<D, BITS>(ks, g + 8, t, kr1);
+  qk_tile<D, BITS, true>(kr0, kr1, lane, qb, ql, s);
+  scores[(2 * t) * 16 + g] = s[0];
+  scores[(2 * t + 1) * 16 + g] = s[1];
+  scores[(2 * t) * 16 + g + 8] = s[2];
+  scores[(2 * t + 1) * 16 + g + 8] = s[3];
   auto ld2 = [&](int r, int cidx) {
     return (uint32_t)reinterpret_cast<const unsigned short*>(pm)[r * 16 + cidx] |
            ((uint32_t)reinterpret_cast<const unsigned short*>(pm)[r * 16 + cidx + 1] << 16);
   };
-  pa[0] = ld2(g, 2 * t);
-  pa[1] = ld2(g + 8, 2 * t);
-  pa[2] = ld2(g, 2 * t + 8);
-  pa[3] = ld2(g + 8, 2 * t + 8);
-  float o[D / 8][4];
-  for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  pv_tile<D, BITS>(vs, lane, pa, o);
-  for (int j = 0; j < D / 8; ++j) {
-    out[g * D + (D / 8) * (2 * t) + j] = o[j][0];
-    out[g * D + (D / 8) * (2 * t + 1) + j] = o[j][1];
-    out[(g + 8) * D + (D / 8) * (2 * t) + j] = o[j][2];
-    out[(g + 8) * D + (D / 8) * (2 * t + 1) + j] = o[j][3];
+  // P^T fragments: keys (2t, 2t+1) and (2t+8, 2t+9) of head g
+  const uint32_t pb0 = ld2(g, 2 * t), pb1 = ld2(g, 2 * t + 8);
+  const uint32_t pl0 = ld2(g + 8, 2 * t), pl1 = ld2(g + 8, 2 * t + 8);
+  float o[D / 16][4];
+  for (int j = 0; j < D / 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  uint32_t vr0[SliceWords<D, BITS>::V], vr1[SliceWords<D, BITS>::V], vr2[SliceWords<D, BITS>::V],
+      vr3[SliceWords<D, BITS>::V];
+  load_vrow<D, BITS>(vs, 2 * t, g, vr0);
+  load_vrow<D, BITS>(vs, 2 * t + 1, g, vr1);
+  load_vrow<D, BITS>(vs, 2 * t + 8, g, vr2);
+  load_vrow<D, BITS>(vs, 2 * t + 9, g, vr3);
+  uint32_t v0[D / 8], v1[D / 8];
+  unpack_vpair<D, BITS>(vr0, vr1, g, v0);
+  unpack_vpair<D, BITS>(vr2, vr3, g, v1);
+  pv_tile<D, true>(v0, v1, pb0, pb1, pl0, pl1, o);
+  for (int j = 0; j < D / 16; ++j) {
+    const int d = g * (D / 8) + 2 * j;
+    out[(2 * t) * D + d] = o[j][0];
+    out[(2 * t + 1) * D + d] = o[j][1];
+    out[(2 * t) * D + d + 1] = o[j][2];
+    out[(2 * t + 1) * D + d + 1] = o[j][3];
   }
 }
 }  // namespace skv

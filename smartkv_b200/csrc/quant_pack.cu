@@ -115,8 +115,8 @@ __global__ void quantize_pack_append_kernel(StoreGeom g, uint8_t* store, int lay
   uint8_t* dst = arena + (which ? g.v_off[bucket] : g.k_off[bucket]) + row_index * g.row_bytes[bucket];
   pack_store_row<EPL>(code, bits, dst, lane);
   if (lane == 0) {
-    float* sc = reinterpret_cast<float*>(arena + (which ? g.vs_off[bucket] : g.ks_off[bucket]));
-    sc[row_index] = scale;
+    float* sc = reinterpret_cast<float*>(arena + g.sc_off[bucket]);
+    sc[2 * row_index + which] = scale;
   }
 }
 
@@ -236,8 +236,8 @@ __global__ void export_rows_kernel(StoreGeom g, const uint8_t* store, int layer,
     out[d] = (int8_t)c;
   }
   if (lane == 0) {
-    const float* sc = reinterpret_cast<const float*>(arena + (which ? g.vs_off[bucket] : g.ks_off[bucket]));
-    (which ? v_scale : k_scale)[rh] = sc[row_index];
+    const float* sc = reinterpret_cast<const float*>(arena + g.sc_off[bucket]);
+    (which ? v_scale : k_scale)[rh] = sc[2 * row_index + which];
   }
 }
 

@@ -79,6 +79,9 @@ class PackedKVStore:
         self.num_ctas = int(self.lib.skv_attn_num_ctas(dev.index if dev.index is not None else torch.cuda.current_device()))
         pbytes = int(self.lib.skv_attn_partials_bytes(ctypes.byref(d), num_q_heads, self.num_ctas))
         self.partials = torch.empty(pbytes // 4, dtype=torch.float32, device=dev)
+        plan_bytes = int(self.lib.skv_attn_plan_bytes(ctypes.byref(d), self.num_ctas))
+        self.plan = torch.zeros(plan_bytes // 4, dtype=torch.int32, device=dev)
+        self._plan_valid = False
         self.out = torch.empty((num_seqs, num_q_heads, head_dim), dtype=torch.float32, device=dev)
         self.lse_max = torch.empty((num_seqs, num_q_heads), dtype=torch.float32, device=dev)
         self.lse_sum = torch.empty((num_seqs, num_q_heads), dtype=torch.float32, device=dev)
@@ -141,6 +144,7 @@ class PackedKVStore:
         storage = self._base_t[bucket.long()] + pos
         self.slot_token.scatter_(1, storage.long(), token_ids)
         self.counts.copy_(new_counts)
+        self._plan_valid = False
         self.next_token += n
         dst_seq = self._seq_ids[:, None].expand(B, n).contiguous().view(-1)
         return dst_seq, bucket.contiguous().view(-1), pos.contiguous().view(-1), storage
@@ -161,6 +165,7 @@ class PackedKVStore:
         self.slot_token.scatter_(1, storage.long()[:, None], self.next_token[:, None])
         self.counts.scatter_add_(1, bucket.long()[:, None], torch.ones((self.num_seqs, 1), dtype=torch.int32, device=self.device))
         self.next_token += 1
+        self._plan_valid = False
 
     # ------------------------------------------------------------------ kernels
     def append(self, layer: int, k: torch.Tensor, v: torch.Tensor, dst_seq, dst_bucket, dst_pos):
@@ -185,9 +190,11 @@ class PackedKVStore:
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
         st = self._stream()
+        if not self._plan_valid:
+            self.build_plan()
         if kernel_events is not None:
             kernel_events[0].record()
-        check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.counts), ptr(q),
+        check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q),
                                             self._dtype_code(q), self.num_q_heads, ptr(self.partials), self.num_ctas,
                                             ptr(self.logits) if want_logits else None, ptr(self.err), st),
               "skv_decode_attention")
@@ -199,7 +206,7 @@ class PackedKVStore:
             cur_k = cur_k.contiguous()
             cur_v = cur_v.contiguous()
             kv_code = self._dtype_code(cur_k)
-        check(self.lib.skv_lse_combine(ctypes.byref(self.desc), ptr(self.counts), ptr(q), self._dtype_code(q),
+        check(self.lib.skv_lse_combine(ctypes.byref(self.desc), ptr(self.plan), ptr(q), self._dtype_code(q),
                                        self.num_q_heads, ptr(self.partials), self.num_ctas, ptr(cur_k), ptr(cur_v),
                                        kv_code, ptr(out), ptr(self.lse_max), ptr(self.lse_sum), ptr(self.cur_prob), st),
               "skv_lse_combine")
@@ -214,6 +221,14 @@ class PackedKVStore:
                   "skv_importance_update")
             self.head_parity ^= 1
         return out
+
+    def build_plan(self):
+        """(Re)build the attention work partition from the live bucket counts.  Needed once
+        after the counts change (bulk store, a committed decode step, a reallocation); every
+        layer of a step shares it."""
+        check(self.lib.skv_attn_plan(ctypes.byref(self.desc), ptr(self.counts), self.num_ctas, ptr(self.plan),
+                                     self._stream()), "skv_attn_plan")
+        self._plan_valid = True
 
     def check_errors(self):
         """Reads the device error flag (synchronises)."""
@@ -264,6 +279,5 @@ class PackedKVStore:
             return raw.view(dtype).view(H, cap, -1)[:, :n]
         k = region(int(d.k_off[bucket]), rb, torch.uint8)
         v = region(int(d.v_off[bucket]), rb, torch.uint8)
-        ks = region(int(d.ks_off[bucket]), 4, torch.float32)[..., 0]
-        vs = region(int(d.vs_off[bucket]), 4, torch.float32)[..., 0]
-        return k, v, ks, vs
+        sc = region(int(d.sc_off[bucket]), 8, torch.float32)
+        return k, v, sc[..., 0], sc[..., 1]

@@ -49,11 +49,11 @@ def test_store_layout(L):
     assert list(d.bucket_base) == [0, 1024, 1536, 1792] and d.slots == 1920
     offs = []
     for i in range(4):
-        for arr in (d.k_off, d.v_off, d.ks_off, d.vs_off):
+        for arr in (d.k_off, d.v_off, d.sc_off):
             offs.append(arr[i])
             assert arr[i] % 256 == 0          # every region 256-byte aligned (>= the 16 bytes bulk copies need)
-    assert offs == sorted(offs) and len(set(offs)) == 16
-    assert d.vs_off[3] + 8 * 128 * 4 <= d.arena_bytes and d.arena_bytes % 256 == 0
+    assert offs == sorted(offs) and len(set(offs)) == 12
+    assert d.sc_off[3] + 8 * 128 * 8 <= d.arena_bytes and d.arena_bytes % 256 == 0
     assert d.total_bytes == d.arena_bytes * 6
     # packed rows of any bucket start on 16-byte boundaries for every multiple-of-16 key offset
     for i in range(4):

@@ -25,12 +25,13 @@ def test_tile_products_exact(d, bits):
         kr = torch.from_numpy(orc.pack_rows(kc, bits)).cuda().contiguous()
         vr = torch.from_numpy(orc.pack_rows(vc, bits)).cuda().contiguous()
         qt, pt = torch.from_numpy(q).cuda(), torch.from_numpy(p).cuda()
-        scores = torch.empty((16, 16), dtype=torch.float32, device="cuda")
-        out = torch.empty((16, d), dtype=torch.float32, device="cuda")
+        scores = torch.empty((8, 16), dtype=torch.float32, device="cuda")
+        out = torch.empty((8, d), dtype=torch.float32, device="cuda")
         L.check(L.lib().skv_debug_tile_products(d, bits, L.ptr(kr), L.ptr(vr), L.ptr(qt), L.ptr(pt), L.ptr(scores),
                                                 L.ptr(out), L.stream_ptr()))
         torch.cuda.synchronize()
-        want_s = q.astype(np.float64) @ kc.astype(np.float64).T
-        want_o = p.astype(np.float64) @ vc.astype(np.float64)
+        # rows 0..7 = heads of the group, rows 8..15 = the residual rows of the precise mode
+        want_s = (q[:8].astype(np.float64) + q[8:].astype(np.float64)) @ kc.astype(np.float64).T
+        want_o = (p[:8].astype(np.float64) + p[8:].astype(np.float64)) @ vc.astype(np.float64)
         assert np.array_equal(scores.cpu().numpy().astype(np.float64), want_s), (d, bits, "scores")
         assert np.array_equal(out.cpu().numpy().astype(np.float64), want_o), (d, bits, "out")
