@@ -179,6 +179,12 @@ int skv_importance_update(const SkvStoreDesc* desc, int layer, const int32_t* co
 int skv_debug_tile_products(int head_dim, int bits, const uint8_t* k_rows, const uint8_t* v_rows,
                             const void* q_half, const void* p_half, float* scores, float* out, void* stream);
 
+/* Integer scores of one 16-key tile through the int8 tensor-core path the attention kernel
+ * uses for 2-, 4- and 8-bit rows: scores int32 [8][16] = sum_d q[h][d] * u[key][d], q int8
+ * [8][head_dim], u = the stored code (offset-binary for 2/4-bit rows, two's complement for 8-bit). */
+int skv_debug_tile_scores_i8(int head_dim, int bits, const uint8_t* k_rows, const int8_t* q_int8, int32_t* scores,
+                             void* stream);
+
 /* Reads and clears a device error flag (synchronises the stream). */
 int skv_read_error_flag(int32_t* err_flag, int32_t* host_value, void* stream);
 

@@ -294,55 +294,140 @@ __device__ __forceinline__ void unpack_vpair(const uint32_t (&a)[SliceWords<D, B
 }
 
 // ---------------------------------------------------------------------------
-// Query fragments (B operand of S^T) for one bit-width.
-// qs: shared fp16 [8 or 16][D]: rows 0..7 = heads of the group, rows 8..15 = their
-// fp16 residuals (precise mode).  `row0` = 0 or 8 selects which.
+// Tile-level products.  lane = 4*g + t.
+//
+// Scores S[heads x keys] = Q (A operand) x K^T (B operand):
+//   * 2/4/8-bit keys: int8 MMA m16n8k32.  A rows 0..7 = most significant int8 limb of the 8
+//     heads, rows 8..15 = next limb (the query is split into radix-128 limbs); the B fragment of
+//     n-tile n is key 8n+g, and its two registers are two consecutive words of that key's slice,
+//     so 8-bit rows feed the tensor core straight from the shared-memory load.
+//   * 3-bit keys: fp16 MMA m16n8k16, A rows 0..7 = fp16 query, rows 8..15 = fp16 residual.
+//   The accumulator layout -- lane (g,t) holds head g, keys 2t,2t+1 (+8) -- is exactly the B
+//   fragment layout P^T needs below, so probabilities go from registers to registers.
+// Output O^T[D x heads] = V^T (A operand) x P^T (B operand), fp16 MMA.
 // ---------------------------------------------------------------------------
-constexpr int kQPad = 0;  // query rows are dense in shared memory (they arrive by bulk copy)
+constexpr int kQPad = 0;  // query rows are dense in shared memory
 
-template <int D, int BITS>
-__device__ __forceinline__ void gather_q_frags(const __half* qs, int lane, int row0, uint32_t (&qb)[D / 16][2]) {
-  const int g = lane >> 2, t = lane & 3;
-  const unsigned short* r = reinterpret_cast<const unsigned short*>(qs) + (g + row0) * (D + kQPad) + t * (D / 4);
-#pragma unroll
-  for (int s = 0; s < D / 16; ++s) {
-    qb[s][0] = (uint32_t)r[kelem<BITS>(2 * s, 0)] | ((uint32_t)r[kelem<BITS>(2 * s, 1)] << 16);
-    qb[s][1] = (uint32_t)r[kelem<BITS>(2 * s + 1, 0)] | ((uint32_t)r[kelem<BITS>(2 * s + 1, 1)] << 16);
+// Element order of the int8 path: k-step s, register r (0/1), byte j holds slice element
+// kelem_i8<BITS>(s, r, j).
+template <int BITS>
+__host__ __device__ constexpr int kelem_i8(int s, int r, int j) {
+  if (BITS == 8) return 8 * s + 4 * r + j;
+  if (BITS == 4) return 8 * s + 2 * j + r;          // word s: even nibbles -> r = 0, odd -> r = 1
+  return 16 * (s / 2) + 4 * j + 2 * (s % 2) + r;    // 2-bit: word s/2, shift index 2*(s%2)+r
+}
+
+// D(16x8,s32) += A(16x32, s8, row) * B(32x8, u8 or s8, col)
+template <bool B_UNSIGNED>
+__device__ __forceinline__ void mma_i8_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (B_UNSIGNED) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 }
 
-// Raw scores of one 16-key tile from the raw K slices of keys g (k0) and g+8 (k1):
-//   s[0] = (key g, head 2t)  s[1] = (key g, head 2t+1)  s[2] = (key g+8, head 2t)  s[3] = (key g+8, head 2t+1)
-// Two accumulators (even / odd k-steps) halve the dependent-MMA chain.
-template <int D, int BITS, bool PRECISE>
-__device__ __forceinline__ void qk_tile(const uint32_t (&k0)[SliceWords<D, BITS>::K],
-                                        const uint32_t (&k1)[SliceWords<D, BITS>::K], int lane,
-                                        const uint32_t (&qb)[D / 16][2], const uint32_t (&ql)[D / 16][2],
-                                        float (&s)[4]) {
-  const int t = lane & 3;
-  uint32_t kb0[D / 8], kb1[D / 8];
-  unpack_kslice<D, BITS>(k0, t, kb0);
-  unpack_kslice<D, BITS>(k1, t, kb1);
-  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+// Raw K slice -> D/16 int8x4 registers (two per k-step).
+template <int D, int BITS>
+__device__ __forceinline__ void unpack_kslice_i8(const uint32_t (&w)[SliceWords<D, BITS>::K], uint32_t* o) {
+  constexpr int NW = SliceWords<D, BITS>::K;
+  static_assert(BITS == 8 || BITS == 4 || BITS == 2, "3-bit rows use the fp16 path");
+  if constexpr (BITS == 8) {
 #pragma unroll
-  for (int k = 0; k < D / 16; ++k) {
-    const uint32_t a[4] = {kb0[2 * k], kb1[2 * k], kb0[2 * k + 1], kb1[2 * k + 1]};
-    if (k & 1) {
-      mma_16816(acc1, a, qb[k][0], qb[k][1]);
-      if (PRECISE) mma_16816(acc0, a, ql[k][0], ql[k][1]);
-    } else {
-      mma_16816(acc0, a, qb[k][0], qb[k][1]);
-      if (PRECISE) mma_16816(acc1, a, ql[k][0], ql[k][1]);
+    for (int i = 0; i < NW; ++i) o[i] = w[i];
+  } else if constexpr (BITS == 4) {
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+      o[2 * i] = w[i] & 0x0f0f0f0fu;
+      o[2 * i + 1] = (w[i] >> 4) & 0x0f0f0f0fu;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+      o[4 * i] = w[i] & 0x03030303u;
+      o[4 * i + 1] = (w[i] >> 2) & 0x03030303u;
+      o[4 * i + 2] = (w[i] >> 4) & 0x03030303u;
+      o[4 * i + 3] = (w[i] >> 6) & 0x03030303u;
     }
   }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) s[i] = acc0[i] + acc1[i];
 }
 
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-  uint32_t y;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
+// A fragments of the int8 query: rows g <- limb_hi[head g], rows g+8 <- limb_lo[head g]
+// (limb_lo may be null: those rows are zero).  limbs int8 [8][D] in shared memory.
+template <int D, int BITS>
+__device__ __forceinline__ void gather_qa_i8(const int8_t* limb_hi, const int8_t* limb_lo, int lane,
+                                             uint32_t (&qa)[D / 32][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint8_t* rh = reinterpret_cast<const uint8_t*>(limb_hi) + g * D + t * (D / 4);
+  const uint8_t* rl = limb_lo ? reinterpret_cast<const uint8_t*>(limb_lo) + g * D + t * (D / 4) : nullptr;
+#pragma unroll
+  for (int s = 0; s < D / 32; ++s) {
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      uint32_t vh = 0, vl = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        vh |= (uint32_t)rh[kelem_i8<BITS>(s, rr, j)] << (8 * j);
+        if (rl) vl |= (uint32_t)rl[kelem_i8<BITS>(s, rr, j)] << (8 * j);
+      }
+      qa[s][2 * rr] = vh;
+      qa[s][2 * rr + 1] = vl;
+    }
+  }
+}
+
+// A fragments of the fp16 query (3-bit keys): rows g <- qs row g, rows g+8 <- qs row g+8 when
+// `with_residual`, else zero.  qs fp16 [8 or 16][D] in shared memory.
+template <int D, int BITS>
+__device__ __forceinline__ void gather_qa_f16(const __half* qs, bool with_residual, int lane,
+                                              uint32_t (&qa)[D / 16][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const unsigned short* r0 = reinterpret_cast<const unsigned short*>(qs) + g * D + t * (D / 4);
+  const unsigned short* r1 = r0 + 8 * D;
+#pragma unroll
+  for (int s = 0; s < D / 16; ++s) {
+    const int e00 = kelem<BITS>(2 * s, 0), e01 = kelem<BITS>(2 * s, 1);
+    const int e10 = kelem<BITS>(2 * s + 1, 0), e11 = kelem<BITS>(2 * s + 1, 1);
+    qa[s][0] = (uint32_t)r0[e00] | ((uint32_t)r0[e01] << 16);
+    qa[s][2] = (uint32_t)r0[e10] | ((uint32_t)r0[e11] << 16);
+    qa[s][1] = with_residual ? ((uint32_t)r1[e00] | ((uint32_t)r1[e01] << 16)) : 0u;
+    qa[s][3] = with_residual ? ((uint32_t)r1[e10] | ((uint32_t)r1[e11] << 16)) : 0u;
+  }
+}
+
+// Integer scores of one n-tile (8 keys; this lane supplies the raw slice `k` of key 8n+g):
+//   acc[0] = (limb_hi of head g, key 2t)  acc[1] = (limb_hi, key 2t+1)  acc[2], acc[3] = limb_lo rows
+// acc is initialised by the caller.
+template <int D, int BITS>
+__device__ __forceinline__ void qk_ntile_i8(const uint32_t (&k)[SliceWords<D, BITS>::K],
+                                            const uint32_t (&qa)[D / 32][4], int (&acc)[4]) {
+  uint32_t b[D / 16];
+  unpack_kslice_i8<D, BITS>(k, b);
+#pragma unroll
+  for (int s = 0; s < D / 32; ++s) mma_i8_16832<BITS != 8>(acc, qa[s], b[2 * s], b[2 * s + 1]);
+}
+
+// fp16 scores of one n-tile: acc[0], acc[1] = (head g, keys 2t, 2t+1) from the query rows,
+// acc[2], acc[3] = the same from the residual rows.  Even / odd k-steps use two accumulators.
+template <int D, int BITS>
+__device__ __forceinline__ void qk_ntile_f16(const uint32_t (&k)[SliceWords<D, BITS>::K], int t,
+                                             const uint32_t (&qa)[D / 16][4], float (&acc)[4]) {
+  uint32_t kb[D / 8];
+  unpack_kslice<D, BITS>(k, t, kb);
+  float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int s = 0; s < D / 16; ++s) {
+    if (s & 1) mma_16816(a1, qa[s], kb[2 * s], kb[2 * s + 1]);
+    else mma_16816(a0, qa[s], kb[2 * s], kb[2 * s + 1]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = a0[i] + a1[i];
 }
 
 // o[j][0] = (d = g*D/8 + 2j, head 2t)   o[j][1] = (same d, head 2t+1)

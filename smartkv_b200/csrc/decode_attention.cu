@@ -29,15 +29,15 @@ namespace skv {
 constexpr int kMaxSeqs = 1024;
 constexpr int kMaxCtas = 1024;
 constexpr int kQBufs = 4;        // query / run-descriptor ring (the producer runs at most STAGES blocks ahead)
-constexpr int kMergeWarps = 4;   // warps merged per round at the end of a run
 
 // Shape of the persistent CTA: NCONS consumer warps + 1 producer warp share STAGES stages.
 template <int NCONS_, int STAGES_, int STAGE_BYTES_>
 struct AttnCfg {
   static constexpr int NCONS = NCONS_, STAGES = STAGES_, STAGE_BYTES = STAGE_BYTES_;
 };
+constexpr int kMaxPartialsPerRun = 15;  // consumer warps of the widest configuration
 using AttnCfgFast = AttnCfg<15, 3, 63360>;     // fp16 queries: 16 warps x 128 registers; 15 8-bit tiles per stage
-using AttnCfgPrecise = AttnCfg<7, 3, 63360>;   // fp32 queries (hi/lo split): 8 warps, more registers per thread
+using AttnCfgPrecise = AttnCfg<7, 3, 42240>;   // fp32 queries (hi/lo split): 8 warps, more registers per thread
 
 // tiles per block for a bit-width: as many 16-key tiles as fit one stage
 __host__ __device__ constexpr int block_tiles(int stage_bytes, int head_dim, int bits) {
@@ -179,10 +179,10 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int3
     if (total > 0) walk(c, pv.runs, nruns_of[c]);
 }
 
-// Online-softmax state of one lane: query heads 2t and 2t+1 (t = lane & 3).
+// Online-softmax state of one lane: query head g = lane >> 2 (the 4 lanes of a head share m).
 struct LaneState {
-  float m0, m1;  // running reference maxima (log2 units); identical in the 8 lanes that share t
-  float l0, l1;  // this lane's share of the running sums
+  float m;  // running reference maximum (log2 units)
+  float l;  // this lane's share of the running sum
 };
 
 // The running maximum is only raised when a score exceeds it by more than kLazyTau (log2
@@ -190,11 +190,52 @@ struct LaneState {
 // probabilities then reach at most 2^kLazyTau, well inside fp16 / fp32 range.
 constexpr float kLazyTau = 8.0f;
 
+// Per-run query data the producer warp prepares in shared memory.
+template <int D, bool PRECISE>
+struct QSlot {
+  static constexpr int NLIMB = PRECISE ? 3 : 2;
+  static constexpr int QROWS = PRECISE ? 16 : 8;
+  __half qh[QROWS][D];       // fp16 rows (rows 8.. = fp16 residuals), for 3-bit keys
+  int8_t limb[NLIMB][8][D];  // int8 limbs (radix 128), most significant first
+  float sq[8];               // limb step per head: q = sq * sum_l limb_l * 128^(NLIMB-1-l)
+  int sumA[8];               // 128*sum(limb0) + sum(limb1)
+  int sumB[8];               // sum(limb2) (precise mode)
+  RunDesc desc;
+};
+
+// Query of one run as a lane sees it, specialised per bit-width of the keys it meets.
 template <int D, int BITS, bool PRECISE>
-__device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t* vtile, const float2* sc, int nvalid,
-                                             int lane, const uint32_t (&qb)[D / 16][2],
-                                             const uint32_t (&ql)[D / 16][2], LaneState& st, float (&o)[D / 16][4],
-                                             float scale_log2, float* lp0, float* lp1) {
+struct QFrags {
+  static constexpr bool INT8 = BITS != 3;
+  uint32_t qa[INT8 ? D / 32 : D / 16][4];   // A fragments: int8 limbs 0/1, or fp16 query/residual
+  uint32_t qa2[(INT8 && PRECISE) ? D / 32 : 1][4];  // precise mode: limb 2
+  float sq;     // limb step of head g
+  int initA;    // -offset * (128*sum(limb0) + sum(limb1)) of head g (offset-binary codes)
+  int initB;    // -offset * sum(limb2)
+};
+
+template <int D, int BITS, bool PRECISE>
+__device__ __forceinline__ void load_qfrags(const QSlot<D, PRECISE>& q, int lane, QFrags<D, BITS, PRECISE>& f) {
+  const int g = lane >> 2;
+  constexpr int off = BITS == 8 ? 0 : (1 << (BITS - 1));  // 8-bit rows are two's complement
+  if constexpr (QFrags<D, BITS, PRECISE>::INT8) {
+    gather_qa_i8<D, BITS>(&q.limb[0][0][0], &q.limb[1][0][0], lane, f.qa);
+    if constexpr (PRECISE) gather_qa_i8<D, BITS>(&q.limb[2][0][0], nullptr, lane, f.qa2);
+    f.sq = q.sq[g];
+    f.initA = -off * q.sumA[g];
+    f.initB = -off * q.sumB[g];
+  } else {
+    gather_qa_f16<D, BITS>(&q.qh[0][0], PRECISE, lane, f.qa);
+  }
+}
+
+// One 16-key tile.  Lane (g,t): supplies the K slices of keys g, g+8 and the V slices of the key
+// pairs (2t,2t+1), (2t+8,2t+9); receives the scores of head g for keys 2t, 2t+1, 2t+8, 2t+9.
+// WRITE_LOGITS: lrow = logits row of head g (first key of the tile), written as two float2.
+template <int D, int BITS, bool PRECISE, bool WRITE_LOGITS>
+__device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t* vtile, const float4* sc, int nvalid,
+                                             int lane, const QFrags<D, BITS, PRECISE>& qf, LaneState& st,
+                                             float (&o)[D / 16][4], float scale_log2, float* lrow) {
   const int g = lane >> 2, t = lane & 3;
   // ---- every shared-memory load of the tile up front ---------------------------------
   uint32_t kr0[SliceWords<D, BITS>::K], kr1[SliceWords<D, BITS>::K];
@@ -206,40 +247,61 @@ __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t
   load_vrow<D, BITS>(vtile, 2 * t + 1, g, vr1);
   load_vrow<D, BITS>(vtile, 2 * t + 8, g, vr2);
   load_vrow<D, BITS>(vtile, 2 * t + 9, g, vr3);
-  const float2 scA = sc[g], scB = sc[g + 8];  // (k scale, v scale) of keys g, g+8
-  // ---- scores; the V unpack is independent integer work that overlaps the MMA latency ----
-  float s[4];
-  qk_tile<D, BITS, PRECISE>(kr0, kr1, lane, qb, ql, s);
-  uint32_t v0[D / 8], v1[D / 8];
-  unpack_vpair<D, BITS>(vr0, vr1, g, v0);
-  unpack_vpair<D, BITS>(vr2, vr3, g, v1);
-  const float kcA = scA.x * scale_log2, kcB = scB.x * scale_log2;
-  float x00 = s[0] * kcA, x01 = s[1] * kcA, x10 = s[2] * kcB, x11 = s[3] * kcB;
-  float vsA = scA.y, vsB = scB.y;
-  if (nvalid < 16) {  // last tile of a bucket: rows past its end may hold anything, scales included
-    if (g >= nvalid) { x00 = x01 = -INFINITY; vsA = 0.f; }
-    if (g + 8 >= nvalid) { x10 = x11 = -INFINITY; vsB = 0.f; }
-  }
-  if (lp0 != nullptr) {
-    lp0[g] = x00;
-    lp0[g + 8] = x10;
-  }
-  if (lp1 != nullptr) {
-    lp1[g] = x01;
-    lp1[g + 8] = x11;
-  }
-  float mx0 = fmaxf(x00, x10), mx1 = fmaxf(x01, x11);
-  if (__any_sync(0xffffffffu, (mx0 > st.m0 + kLazyTau) | (mx1 > st.m1 + kLazyTau))) {
-#pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+  const float4 scA = sc[t], scB = sc[t + 4];  // (ks, vs) of keys 2t, 2t+1 and of keys 2t+8, 2t+9
+  // ---- scores of head g (log2 units): x0, x1 = keys 2t, 2t+1; x2, x3 = keys 2t+8, 2t+9 ----
+  float x0, x1, x2, x3;
+  if constexpr (QFrags<D, BITS, PRECISE>::INT8) {
+    int c0[4] = {0, 0, qf.initA, qf.initA}, c1[4] = {0, 0, qf.initA, qf.initA};
+    qk_ntile_i8<D, BITS>(kr0, qf.qa, c0);
+    qk_ntile_i8<D, BITS>(kr1, qf.qa, c1);
+    float f0 = (float)(c0[0] * 128 + c0[2]), f1 = (float)(c0[1] * 128 + c0[3]);
+    float f2 = (float)(c1[0] * 128 + c1[2]), f3 = (float)(c1[1] * 128 + c1[3]);
+    if constexpr (PRECISE) {
+      int e0[4] = {qf.initB, qf.initB, 0, 0}, e1[4] = {qf.initB, qf.initB, 0, 0};
+      qk_ntile_i8<D, BITS>(kr0, qf.qa2, e0);
+      qk_ntile_i8<D, BITS>(kr1, qf.qa2, e1);
+      f0 = fmaf(f0, 128.f, (float)e0[0]);
+      f1 = fmaf(f1, 128.f, (float)e0[1]);
+      f2 = fmaf(f2, 128.f, (float)e1[0]);
+      f3 = fmaf(f3, 128.f, (float)e1[1]);
     }
-    const float n0 = fmaxf(st.m0, mx0), n1 = fmaxf(st.m1, mx1);
-    const float a0 = (n0 == -INFINITY) ? 1.f : ex2f(st.m0 - n0);
-    const float a1 = (n1 == -INFINITY) ? 1.f : ex2f(st.m1 - n1);
-    st.l0 *= a0;
-    st.l1 *= a1;
+    const float qs = qf.sq * scale_log2;
+    x0 = f0 * (scA.x * qs);
+    x1 = f1 * (scA.z * qs);
+    x2 = f2 * (scB.x * qs);
+    x3 = f3 * (scB.z * qs);
+  } else {
+    float c0[4], c1[4];
+    qk_ntile_f16<D, BITS>(kr0, t, qf.qa, c0);
+    qk_ntile_f16<D, BITS>(kr1, t, qf.qa, c1);
+    x0 = (c0[0] + c0[2]) * (scA.x * scale_log2);
+    x1 = (c0[1] + c0[3]) * (scA.z * scale_log2);
+    x2 = (c1[0] + c1[2]) * (scB.x * scale_log2);
+    x3 = (c1[1] + c1[3]) * (scB.z * scale_log2);
+  }
+  float vs0 = scA.y, vs1 = scA.w, vs2 = scB.y, vs3 = scB.w;
+  if (nvalid < 16) {  // last tile of a bucket: rows past its end may hold anything, scales included
+    if (2 * t >= nvalid) { x0 = -INFINITY; vs0 = 0.f; }
+    if (2 * t + 1 >= nvalid) { x1 = -INFINITY; vs1 = 0.f; }
+    if (2 * t + 8 >= nvalid) { x2 = -INFINITY; vs2 = 0.f; }
+    if (2 * t + 9 >= nvalid) { x3 = -INFINITY; vs3 = 0.f; }
+  }
+  if constexpr (WRITE_LOGITS) {
+    if (lrow != nullptr) {
+      *reinterpret_cast<float2*>(lrow + 2 * t) = make_float2(x0, x1);
+      *reinterpret_cast<float2*>(lrow + 2 * t + 8) = make_float2(x2, x3);
+    }
+  }
+  float mx = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+  if (__any_sync(0xffffffffu, mx > st.m + kLazyTau)) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float n = fmaxf(st.m, mx);
+    const float alpha = (n == -INFINITY) ? 1.f : ex2f(st.m - n);
+    st.l *= alpha;
+    st.m = n;
+    // the accumulators of this lane belong to heads 2t and 2t+1, whose lanes are 8t.. and 8t+4..
+    const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * t), a1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
 #pragma unroll
     for (int j = 0; j < D / 16; ++j) {
       o[j][0] *= a0;
@@ -247,51 +309,57 @@ __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t
       o[j][1] *= a1;
       o[j][3] *= a1;
     }
-    st.m0 = n0;
-    st.m1 = n1;
   }
-  const float mu0 = (st.m0 == -INFINITY) ? 0.f : st.m0, mu1 = (st.m1 == -INFINITY) ? 0.f : st.m1;
-  const float p00 = ex2f(x00 - mu0), p01 = ex2f(x01 - mu1), p10 = ex2f(x10 - mu0), p11 = ex2f(x11 - mu1);
-  st.l0 += p00 + p10;
-  st.l1 += p01 + p11;
-  const float a00 = p00 * vsA, a01 = p01 * vsA, a10 = p10 * vsB, a11 = p11 * vsB;
-  const uint32_t ph0 = pack_h2(a00, a01), ph1 = pack_h2(a10, a11);
-  const uint32_t pb0 = movmatrix_trans(ph0), pb1 = movmatrix_trans(ph1);
+  const float mu = (st.m == -INFINITY) ? 0.f : st.m;
+  const float p0 = ex2f(x0 - mu), p1 = ex2f(x1 - mu), p2 = ex2f(x2 - mu), p3 = ex2f(x3 - mu);
+  st.l += (p0 + p1) + (p2 + p3);
+  const float a0 = p0 * vs0, a1 = p1 * vs1, a2 = p2 * vs2, a3 = p3 * vs3;
+  // P^T B fragments: (keys 2t, 2t+1 ; head g) and (keys 2t+8, 2t+9 ; head g) -- already in place
+  const uint32_t pb0 = pack_h2(a0, a1), pb1 = pack_h2(a2, a3);
   uint32_t pl0 = 0u, pl1 = 0u;
   if (PRECISE) {
-    const __half2 h0 = bits_h2(ph0), h1 = bits_h2(ph1);
-    pl0 = movmatrix_trans(pack_h2(a00 - __low2float(h0), a01 - __high2float(h0)));
-    pl1 = movmatrix_trans(pack_h2(a10 - __low2float(h1), a11 - __high2float(h1)));
+    const __half2 h0 = bits_h2(pb0), h1 = bits_h2(pb1);
+    pl0 = pack_h2(a0 - __low2float(h0), a1 - __high2float(h0));
+    pl1 = pack_h2(a2 - __low2float(h1), a3 - __high2float(h1));
   }
+  uint32_t v0[D / 8], v1[D / 8];
+  unpack_vpair<D, BITS>(vr0, vr1, g, v0);
+  unpack_vpair<D, BITS>(vr2, vr3, g, v1);
   pv_tile<D, PRECISE>(v0, v1, pb0, pb1, pl0, pl1, o);
 }
 
 // One block = up to KBKEYS keys of one bucket, staged at `sb`: [K rows][V rows][float2 scales].
-// This warp owns tiles first, first + NCONS, ... of it.
+// This warp owns tiles first, first + NCONS, ... of it.  lrow: logits row of head g at the
+// block's first key (null in lanes whose head does not exist).
 template <int D, int BITS, bool PRECISE, int KBKEYS, int NCONS>
 __device__ __forceinline__ void process_block(const uint8_t* sb, int nkeys, int first, int lane,
-                                              const uint32_t (&qb)[D / 16][2], const uint32_t (&ql)[D / 16][2],
-                                              LaneState& st, float (&o)[D / 16][4], float scale_log2, float* lp0,
-                                              float* lp1) {
+                                              const QFrags<D, BITS, PRECISE>& qf, LaneState& st,
+                                              float (&o)[D / 16][4], float scale_log2, bool write_logits,
+                                              float* lrow) {
   constexpr int PD = D * BITS / 8;
   const uint8_t* kbase = sb;
   const uint8_t* vbase = sb + KBKEYS * PD;
-  const float2* sc = reinterpret_cast<const float2*>(sb + 2 * KBKEYS * PD);
+  const float4* sc = reinterpret_cast<const float4*>(sb + 2 * KBKEYS * PD);  // two keys per float4
   const int ntl = (nkeys + 15) >> 4;
-  for (int tile = first; tile < ntl; tile += NCONS) {
-    const int nvalid = nkeys - tile * 16;  // >= 16 for every tile but possibly the last
-    process_tile<D, BITS, PRECISE>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 16, nvalid, lane, qb,
-                                   ql, st, o, scale_log2, lp0 ? lp0 + tile * 16 : nullptr,
-                                   lp1 ? lp1 + tile * 16 : nullptr);
+  if (write_logits) {  // warp-uniform; lanes of heads >= G carry a null row
+    for (int tile = first; tile < ntl; tile += NCONS)
+      process_tile<D, BITS, PRECISE, true>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 8,
+                                           nkeys - tile * 16, lane, qf, st, o, scale_log2,
+                                           lrow ? lrow + tile * 16 : nullptr);
+  } else {
+    for (int tile = first; tile < ntl; tile += NCONS)
+      process_tile<D, BITS, PRECISE, false>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 8,
+                                            nkeys - tile * 16, lane, qf, st, o, scale_log2, nullptr);
   }
 }
 
 // Bounded mbarrier wait that also gives up as soon as another thread of the CTA has given up.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                               int32_t* err) {
-  for (uint32_t i = 0; i < (1u << 20); ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
+  // each attempt may sleep up to 20 us in hardware; 50k attempts bound the wait to about a second
+  for (uint32_t i = 0; i < 50000u; ++i) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
   }
   *abort_flag = 1;
   atomicExch(err, 1);
@@ -302,10 +370,10 @@ template <int D, bool PRECISE, class CFG>
 __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(const AttnParams p) {
   constexpr int NCONS = CFG::NCONS, STAGES = CFG::STAGES, STAGE_BYTES = CFG::STAGE_BYTES;
   constexpr int NTC = NCONS * 32;  // consumer threads
-  constexpr int QROWS = PRECISE ? 16 : 8;
   constexpr int KBT0 = block_tiles(STAGE_BYTES, D, 2), KBT1 = block_tiles(STAGE_BYTES, D, 3),
                 KBT2 = block_tiles(STAGE_BYTES, D, 4), KBT3 = block_tiles(STAGE_BYTES, D, 8);
   static_assert(KBT3 >= 1, "stage too small for one tile");
+  using Slot = QSlot<D, PRECISE>;
   extern __shared__ __align__(128) uint8_t smem[];
   const StoreGeom& g = p.g;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -313,17 +381,17 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
   SKV_TL(0);
 
   uint8_t* stages = smem;                                                          // [STAGES][STAGE_BYTES]
-  float* scratch = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);          // [kMergeWarps][8][D+2]
-  __half* qbuf = reinterpret_cast<__half*>(scratch + kMergeWarps * 8 * (D + 2));   // [kQBufs][QROWS][D]
-  RunDesc* rdesc = reinterpret_cast<RunDesc*>(qbuf + kQBufs * QROWS * D);          // [kQBufs]
-  float* mpub = reinterpret_cast<float*>(rdesc + kQBufs);                          // [NCONS][8] per-warp maxima
-  uint64_t* full = reinterpret_cast<uint64_t*>(mpub + NCONS * 8);                  // [STAGES]
+  Slot* qslots = reinterpret_cast<Slot*>(smem + STAGES * STAGE_BYTES);             // [kQBufs]
+  uint64_t* full = reinterpret_cast<uint64_t*>(qslots + kQBufs);                   // [STAGES]
   uint64_t* empty = full + STAGES;                                                 // [STAGES]
   uint64_t* qfull = empty + STAGES;                                                // [kQBufs]
   uint64_t* qempty = qfull + kQBufs;                                               // [kQBufs]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(qempty + kQBufs);
 
-  for (int i = tid; i < kQBufs * QROWS * D; i += (NCONS + 1) * 32) qbuf[i] = __float2half(0.f);
+  {  // rows of heads >= G are never written again and must read as zero
+    uint32_t* z = reinterpret_cast<uint32_t*>(qslots);
+    for (int i = tid; i < (int)(kQBufs * sizeof(Slot) / 4); i += (NCONS + 1) * 32) z[i] = 0u;
+  }
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -347,51 +415,30 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     int stg = 0, qi = 0;
     uint32_t epar = 1, qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
     const int kbt[kNumBuckets] = {KBT0, KBT1, KBT2, KBT3};
-    for (int r = run_begin; r < run_end; ++r) {
-      const RunDesc d = pv.runs[r];
-      if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err)) break;
-      const long long q_off = ((long long)d.seq * p.num_q_heads + (long long)d.head * G) * D;
-      __half* qdst = qbuf + qi * QROWS * D;
-      if (lane == 0) rdesc[qi] = d;
-      if (!PRECISE && p.q_is_half) {
-        if (lane == 0) {
-          fence_proxy_async();
-          mbar_expect_tx(&qfull[qi], (uint32_t)(G * D * 2));
-          bulk_g2s(qdst, static_cast<const __half*>(p.query) + q_off, (uint32_t)(G * D * 2), &qfull[qi]);
-        }
-      } else {
-        for (int i = lane; i < G * D; i += 32) {
-          const float q = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[q_off + i])
-                                      : static_cast<const float*>(p.query)[q_off + i];
-          const __half qh = __float2half_rn(q);
-          qdst[i] = qh;
-          if (PRECISE) qdst[8 * D + i] = __float2half_rn(q - __half2float(qh));
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&qfull[qi]);
-      }
+    constexpr int NL = Slot::NLIMB;
+    constexpr int EPL = D / 32;  // query elements per lane and head
+    // issues up to `limit` further blocks of run d, resuming at (bucket ci, tile ct0)
+    auto issue_blocks = [&](const RunDesc& d, int& ci, int& ct0, int limit) -> bool {
       const uint8_t* arena = arena_ptr(g, p.store, p.layer, d.seq);
-      bool ok = true;
-      for (int i = 0; i < kNumBuckets && ok; ++i) {
-        const int pd = g.row_bytes[i], kbkeys = kbt[i] * 16;
-        for (int t0 = d.ka[i]; t0 < d.kb[i]; t0 += kbt[i]) {
-          if (!wait_or_abort(&empty[stg], epar, abort_flag, p.err)) {
-            ok = false;
-            break;
-          }
+      for (; ci < kNumBuckets; ++ci, ct0 = -1) {
+        if (ct0 < 0) ct0 = d.ka[ci];
+        const int pd = g.row_bytes[ci], kbkeys = kbt[ci] * 16;
+        for (; ct0 < d.kb[ci]; ct0 += kbt[ci]) {
+          if (limit-- <= 0) return true;
+          if (!wait_or_abort(&empty[stg], epar, abort_flag, p.err)) return false;
           if (lane == 0 && p.debug_mode < 2) {
-            const int ntl = (d.kb[i] - t0) < kbt[i] ? (d.kb[i] - t0) : kbt[i];
-            const int key0 = t0 * 16;
-            const int nkeys = (d.cnt[i] - key0) < ntl * 16 ? (d.cnt[i] - key0) : ntl * 16;
+            const int ntl = (d.kb[ci] - ct0) < kbt[ci] ? (d.kb[ci] - ct0) : kbt[ci];
+            const int key0 = ct0 * 16;
+            const int nkeys = (d.cnt[ci] - key0) < ntl * 16 ? (d.cnt[ci] - key0) : ntl * 16;
             const int n16 = (nkeys + 15) & ~15;
             uint8_t* sb = stages + (long long)stg * STAGE_BYTES;
-            const long long row = (long long)d.head * g.cap[i] + key0;
+            const long long row = (long long)d.head * g.cap[ci] + key0;
             const uint32_t kbytes = (uint32_t)(n16 * pd), sbytes = (uint32_t)(n16 * 8);
             fence_proxy_async();
             mbar_expect_tx(&full[stg], 2 * kbytes + sbytes);
-            bulk_g2s(sb, arena + g.k_off[i] + row * pd, kbytes, &full[stg]);
-            bulk_g2s(sb + kbkeys * pd, arena + g.v_off[i] + row * pd, kbytes, &full[stg]);
-            bulk_g2s(sb + 2 * kbkeys * pd, arena + g.sc_off[i] + row * 8, sbytes, &full[stg]);
+            bulk_g2s(sb, arena + g.k_off[ci] + row * pd, kbytes, &full[stg]);
+            bulk_g2s(sb + kbkeys * pd, arena + g.v_off[ci] + row * pd, kbytes, &full[stg]);
+            bulk_g2s(sb + 2 * kbkeys * pd, arena + g.sc_off[ci] + row * 8, sbytes, &full[stg]);
           } else if (lane == 0) {
             mbar_arrive(&full[stg]);
           }
@@ -401,7 +448,69 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
           }
         }
       }
-      if (!ok) break;
+      return true;
+    };
+    for (int r = run_begin; r < run_end; ++r) {
+      const RunDesc d = pv.runs[r];
+      int ci = 0, ct0 = -1;
+      // the first run's copies start before its query is prepared (nothing else is in flight yet)
+      if (r == run_begin && !issue_blocks(d, ci, ct0, STAGES)) break;
+      if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err)) break;
+      Slot& slot = qslots[qi];
+      if (lane == 0) slot.desc = d;
+      // ---- the query rows of this group: fp16 copy and radix-128 int8 limbs --------------
+      const long long q_off = ((long long)d.seq * p.num_q_heads + (long long)d.head * G) * D;
+      for (int gq = 0; gq < G; ++gq) {
+        float q[EPL];
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          const long long idx = q_off + (long long)gq * D + lane * EPL + e;
+          q[e] = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[idx])
+                             : static_cast<const float*>(p.query)[idx];
+          amax = fmaxf(amax, fabsf(q[e]));
+        }
+        amax = warp_max(amax);
+        float range = 127.f;
+#pragma unroll
+        for (int l = 1; l < NL; ++l) range *= 128.f;
+        const float step = amax > 0.f ? amax / range : 1.f;
+        const float inv = 1.f / step;
+        int sum[NL];
+#pragma unroll
+        for (int l = 0; l < NL; ++l) sum[l] = 0;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          const int d_idx = lane * EPL + e;
+          const __half qh = __float2half_rn(q[e]);
+          slot.qh[gq][d_idx] = qh;
+          if (PRECISE) slot.qh[gq + 8][d_idx] = __float2half_rn(q[e] - __half2float(qh));
+          float rem = fminf(fmaxf(rintf(q[e] * inv), -range), range);  // integer in [-range, range]
+#pragma unroll
+          for (int l = NL - 1; l >= 1; --l) {
+            const float hi = rintf(rem * (1.f / 128.f));
+            const int low = (int)(rem - hi * 128.f);  // in [-64, 64]
+            slot.limb[l][gq][d_idx] = (int8_t)low;
+            sum[l] += low;
+            rem = hi;
+          }
+          slot.limb[0][gq][d_idx] = (int8_t)(int)rem;
+          sum[0] += (int)rem;
+        }
+#pragma unroll
+        for (int l = 0; l < NL; ++l) {
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], off);
+        }
+        if (lane == 0) {
+          slot.sq[gq] = step;
+          slot.sumA[gq] = 128 * sum[0] + sum[1];
+          slot.sumB[gq] = NL == 3 ? sum[NL - 1] : 0;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qfull[qi]);
+      if (!issue_blocks(d, ci, ct0, 1 << 30)) break;
       if (++qi == kQBufs) {
         qi = 0;
         qepar ^= 1u;
@@ -417,32 +526,28 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
   for (int r = run_begin; r < run_end; ++r) {
     if (!aborted && !wait_or_abort(&qfull[qi], qfpar, abort_flag, p.err)) aborted = true;
     SKV_TL(2 + 4 * (r - run_begin));
-    const RunDesc& d = rdesc[qi];  // stays valid until this warp arrives on qempty below
-    const __half* qs = qbuf + qi * QROWS * D;
+    const Slot& slot = qslots[qi];  // stays valid until this warp arrives on qempty below
+    const RunDesc& d = slot.desc;
     const int b = d.seq, h = d.head;
 
     LaneState st;
-    st.m0 = st.m1 = -INFINITY;
-    st.l0 = st.l1 = 0.f;
+    st.m = -INFINITY;
+    st.l = 0.f;
     float o[D / 16][4];
 #pragma unroll
     for (int j = 0; j < D / 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-    const int hq0 = h * G + 2 * (lane & 3);  // first of this lane's two query heads
-    float* lbase = nullptr;
-    if (p.logits != nullptr) lbase = p.logits + ((long long)b * p.num_q_heads + hq0) * g.slots;
-    const bool head0_ok = 2 * (lane & 3) < G, head1_ok = 2 * (lane & 3) + 1 < G;
+    const int gq = lane >> 2, t = lane & 3;  // scores: head gq; accumulators: heads 2t, 2t+1
+    float* lbase = nullptr;  // logits row of head gq
+    if (p.logits != nullptr && gq < G) lbase = p.logits + ((long long)b * p.num_q_heads + h * G + gq) * g.slots;
+    const bool write_logits = p.logits != nullptr;
     int tile_base = 0;  // tile i of a block goes to warp (tile_base + i) % NCONS
 
     auto run_bucket = [&](auto bits_tag, auto kbt_tag, int bucket) {
       constexpr int BITS = decltype(bits_tag)::value;
       constexpr int KBT = decltype(kbt_tag)::value;
       if (d.ka[bucket] >= d.kb[bucket]) return;
-      uint32_t qb[D / 16][2];
-      uint32_t ql[D / 16][2];
-      if (!aborted) {
-        gather_q_frags<D, BITS>(qs, lane, 0, qb);
-        if (PRECISE) gather_q_frags<D, BITS>(qs, lane, 8, ql);
-      }
+      QFrags<D, BITS, PRECISE> qf;
+      load_qfrags<D, BITS, PRECISE>(slot, lane, qf);
       for (int t0 = d.ka[bucket]; t0 < d.kb[bucket]; t0 += KBT) {
         const int ntl = (d.kb[bucket] - t0) < KBT ? (d.kb[bucket] - t0) : KBT;
         const int key0 = t0 * 16;
@@ -452,10 +557,8 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
         if (first < 0) first += NCONS;
         if (!aborted && first < ntl && p.debug_mode != 1 && p.debug_mode != 3) {
           float* lrow = lbase != nullptr ? lbase + g.bucket_base[bucket] + key0 : nullptr;
-          float* lp0 = (lrow != nullptr && head0_ok) ? lrow : nullptr;
-          float* lp1 = (lrow != nullptr && head1_ok) ? lrow + g.slots : nullptr;
           process_block<D, BITS, PRECISE, KBT * 16, NCONS>(stages + (long long)stg * STAGE_BYTES, nkeys, first, lane,
-                                                           qb, ql, st, o, p.scale_log2, lp0, lp1);
+                                                           qf, st, o, p.scale_log2, write_logits, lrow);
         }
         tile_base = (tile_base + ntl) % NCONS;
         __syncwarp();
@@ -471,93 +574,31 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     run_bucket(std::integral_constant<int, 4>{}, std::integral_constant<int, KBT2>{}, 2);
     run_bucket(std::integral_constant<int, 8>{}, std::integral_constant<int, KBT3>{}, 3);
 
-    // ---- merge the consumer warps and write the partial of this run ------------------------
+    // ---- every consumer warp writes its own partial (max, sum, out) of this run -------------------
+    // (no cross-warp merge: skv_lse_combine folds the NCONS partials of a run like any others)
     SKV_TL(3 + 4 * (r - run_begin));
     __syncwarp();
     if (lane == 0) mbar_arrive(&qempty[qi]);  // query rows and descriptor are no longer needed
-    const int gq = lane >> 2, t = lane & 3;
-    if (gq == 0) {
-      mpub[warp * 8 + 2 * t] = st.m0;
-      mpub[warp * 8 + 2 * t + 1] = st.m1;
-    }
-    named_bar_sync(1, NTC);
-    float M0 = -INFINITY, M1 = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < NCONS; ++w) {
-      M0 = fmaxf(M0, mpub[w * 8 + 2 * t]);
-      M1 = fmaxf(M1, mpub[w * 8 + 2 * t + 1]);
-    }
     {
-      const float f0 = (st.m0 == -INFINITY) ? 0.f : ex2f(st.m0 - M0);
-      const float f1 = (st.m1 == -INFINITY) ? 0.f : ex2f(st.m1 - M1);
-      st.l0 *= f0;
-      st.l1 *= f1;
-#pragma unroll
-      for (int j = 0; j < D / 16; ++j) {
-        o[j][0] *= f0;
-        o[j][2] *= f0;
-        o[j][1] *= f1;
-        o[j][3] *= f1;
+      float lsum = st.l;
+      lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+      lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+      float* out = p.partials + ((long long)r * NCONS + warp) * partial_stride(G, D);
+      if (t == 0 && gq < G) {
+        out[gq * (D + 2)] = st.m;
+        out[gq * (D + 2) + 1] = lsum;
       }
-#pragma unroll
-      for (int off = 4; off < 32; off <<= 1) {
-        st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, off);
-        st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, off);
-      }
-    }
-    constexpr int NEL = 8 * (D + 2);            // scratch elements per warp ([8 heads][D+2])
-    constexpr int EPT = (NEL + NTC - 1) / NTC;  // elements per reducing thread
-    float acc[EPT];
-#pragma unroll
-    for (int k = 0; k < EPT; ++k) acc[k] = 0.f;
-    for (int base = 0; base < NCONS; base += kMergeWarps) {
-      if (warp >= base && warp < base + kMergeWarps) {
-        float* row0 = scratch + (warp - base) * NEL + (2 * t) * (D + 2);
+      if (__any_sync(0xffffffffu, st.m != -INFINITY)) {  // a warp without tiles in this run has nothing to add
+        float* row0 = out + (2 * t) * (D + 2) + 2 + gq * (D / 8);
         float* row1 = row0 + (D + 2);
-        if (gq == 0) {
-          row0[0] = 0.f;
-          row0[1] = st.l0;
-          row1[0] = 0.f;
-          row1[1] = st.l1;
-        }
+        const bool ok0 = 2 * t < G, ok1 = 2 * t + 1 < G;
 #pragma unroll
         for (int j = 0; j < D / 16; ++j) {
-          const int dd = gq * (D / 8) + 2 * j;
-          row0[2 + dd] = o[j][0];
-          row0[2 + dd + 1] = o[j][2];
-          row1[2 + dd] = o[j][1];
-          row1[2 + dd + 1] = o[j][3];
-        }
-      }
-      named_bar_sync(1, NTC);
-      const int nw = (NCONS - base) < kMergeWarps ? (NCONS - base) : kMergeWarps;
-#pragma unroll
-      for (int k = 0; k < EPT; ++k) {
-        const int e = tid + k * NTC;
-        if (e < NEL) {
-          for (int w = 0; w < nw; ++w) acc[k] += scratch[w * NEL + e];
-        }
-      }
-      named_bar_sync(1, NTC);
-    }
-    {
-      float* out = p.partials + (long long)r * partial_stride(G, D);
-#pragma unroll
-      for (int k = 0; k < EPT; ++k) {
-        const int e = tid + k * NTC;
-        if (e < G * (D + 2)) {
-          const int hd = e / (D + 2), col = e - hd * (D + 2);
-          float v = acc[k];
-          if (col == 0) {
-            v = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < NCONS; ++w) v = fmaxf(v, mpub[w * 8 + hd]);
-          }
-          out[e] = v;
+          if (ok0) *reinterpret_cast<float2*>(row0 + 2 * j) = make_float2(o[j][0], o[j][2]);
+          if (ok1) *reinterpret_cast<float2*>(row1 + 2 * j) = make_float2(o[j][1], o[j][3]);
         }
       }
     }
-    named_bar_sync(1, NTC);  // mpub and scratch are free again
     SKV_TL(4 + 4 * (r - run_begin));
     if (++qi == kQBufs) {
       qi = 0;
@@ -575,6 +616,7 @@ struct CombineParams {
   int num_q_heads;
   int group;
   const float* partials;
+  int per_run;  // partials per run = consumer warps of the attention launch
   int num_ctas;
   const void* cur_k;
   const void* cur_v;
@@ -586,7 +628,7 @@ struct CombineParams {
   float scale_log2;
 };
 
-// one block (128 threads) per (sequence, KV head) segment
+// one block per (sequence, KV head) segment
 __global__ void lse_combine_kernel(const CombineParams p) {
   const StoreGeom& g = p.g;
   const int D = g.head_dim, G = p.group, Hkv = g.num_kv_heads;
@@ -594,8 +636,8 @@ __global__ void lse_combine_kernel(const CombineParams p) {
   const int tid = threadIdx.x, NT = blockDim.x;
   __shared__ float s_cur[8];
   const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
-  const int nsplit = pv.seg_count[seg];
-  const int r0 = nsplit > 0 ? pv.seg_begin[seg] : 0;
+  const int nsplit = pv.seg_count[seg] * p.per_run;
+  const int r0 = nsplit > 0 ? pv.seg_begin[seg] * p.per_run : 0;
 
   // ---- current-token logits (full precision), one warp per group row -------------
   const bool has_cur = p.cur_k != nullptr && p.cur_v != nullptr;
@@ -658,11 +700,9 @@ using namespace skv;
 
 static inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
-template <class CFG, bool PRECISE>
-static size_t attn_smem_bytes(int head_dim) {
-  const int qrows = PRECISE ? 16 : 8;
-  return (size_t)CFG::STAGES * CFG::STAGE_BYTES + (size_t)kMergeWarps * 8 * (head_dim + 2) * 4 +
-         (size_t)kQBufs * qrows * head_dim * 2 + kQBufs * sizeof(RunDesc) + (size_t)CFG::NCONS * 8 * 4 +
+template <int D, class CFG, bool PRECISE>
+static size_t attn_smem_bytes() {
+  return (size_t)CFG::STAGES * CFG::STAGE_BYTES + (size_t)kQBufs * sizeof(QSlot<D, PRECISE>) +
          (2 * CFG::STAGES + 2 * kQBufs) * sizeof(uint64_t) + 64;
 }
 
@@ -676,7 +716,7 @@ extern "C" int64_t skv_attn_partials_bytes(const SkvStoreDesc* desc, int num_q_h
   if (!desc || num_ctas <= 0 || num_q_heads <= 0 || desc->num_kv_heads <= 0) return SKV_ERR_INVALID;
   const int group = num_q_heads / desc->num_kv_heads;
   const int64_t runs = (int64_t)num_ctas + (int64_t)desc->num_seqs * desc->num_kv_heads;
-  return runs * partial_stride(group, desc->head_dim) * (int64_t)sizeof(float);
+  return runs * kMaxPartialsPerRun * partial_stride(group, desc->head_dim) * (int64_t)sizeof(float);
 }
 
 extern "C" int64_t skv_attn_plan_bytes(const SkvStoreDesc* desc, int num_ctas) {
@@ -696,7 +736,7 @@ extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, in
 template <int D, bool PRECISE, class CFG>
 static int launch_attn(AttnParams& p, cudaStream_t st) {
   static bool configured = false;  // per template instance
-  const size_t smem = attn_smem_bytes<CFG, PRECISE>(D);
+  const size_t smem = attn_smem_bytes<D, CFG, PRECISE>();
   if (!configured) {
     if (cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE, CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
@@ -763,6 +803,9 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
   static const int no_logits = getenv("SKV_ATTN_NOLOGITS") ? atoi(getenv("SKV_ATTN_NOLOGITS")) : 0;
   if (no_logits) p.logits = nullptr;
   const bool precise = !p.q_is_half;
+  static const int cfg_sel = getenv("SKV_ATTN_CFG") ? atoi(getenv("SKV_ATTN_CFG")) : 0;
+  if (desc->head_dim == 128 && !precise && cfg_sel == 1) return launch_attn<128, false, AttnCfg<11, 3, 63360>>(p, as_stream(stream));
+  if (desc->head_dim == 128 && !precise && cfg_sel == 2) return launch_attn<128, false, AttnCfg<7, 3, 63360>>(p, as_stream(stream));
   if (desc->head_dim == 128)
     return precise ? launch_attn<128, true, AttnCfgPrecise>(p, as_stream(stream))
                    : launch_attn<128, false, AttnCfgFast>(p, as_stream(stream));
@@ -796,7 +839,14 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const
   p.lse_sum = lse_sum;
   p.cur_prob = cur_prob;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)desc->head_dim));
-  lse_combine_kernel<<<desc->num_seqs * desc->num_kv_heads, 128, 0, as_stream(stream)>>>(p);
+  // partials per run of the attention launch that produced them (chosen by the query dtype)
+  p.per_run = p.q_is_half ? AttnCfgFast::NCONS : AttnCfgPrecise::NCONS;
+  {
+    static const int cfg_sel = getenv("SKV_ATTN_CFG") ? atoi(getenv("SKV_ATTN_CFG")) : 0;
+    if (p.q_is_half && desc->head_dim == 128 && cfg_sel == 1) p.per_run = 11;
+    if (p.q_is_half && desc->head_dim == 128 && cfg_sel == 2) p.per_run = 7;
+  }
+  lse_combine_kernel<<<desc->num_seqs * desc->num_kv_heads, 256, 0, as_stream(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 
@@ -810,27 +860,27 @@ __global__ void debug_tile_kernel(const uint8_t* k_rows, const uint8_t* v_rows, 
   constexpr int PD = D * BITS / 8;
   __shared__ __align__(16) uint8_t ks[16 * PD + 16];
   __shared__ __align__(16) uint8_t vs[16 * PD + 16];
-  __shared__ __align__(16) __half qs[16 * (D + kQPad)];
+  __shared__ __align__(16) __half qs[16 * D];
   const int lane = threadIdx.x;
   for (int i = lane; i < 16 * PD; i += 32) {
     ks[i] = k_rows[i];
     vs[i] = v_rows[i];
   }
-  for (int i = lane; i < 16 * D; i += 32) qs[(i / D) * (D + kQPad) + (i % D)] = q[i];
+  for (int i = lane; i < 16 * D; i += 32) qs[i] = q[i];
   __syncwarp();
-  uint32_t qb[D / 16][2], ql[D / 16][2];
-  gather_q_frags<D, BITS>(qs, lane, 0, qb);
-  gather_q_frags<D, BITS>(qs, lane, 8, ql);
   const int g = lane >> 2, t = lane & 3;
-  float s[4];
+  uint32_t qa[D / 16][4];
+  gather_qa_f16<D, BITS>(qs, true, lane, qa);
   uint32_t kr0[SliceWords<D, BITS>::K], kr1[SliceWords<D, BITS>::K];
   load_kslice<D, BITS>(ks, g, t, kr0);
   load_kslice<D, BITS>(ks, g + 8, t, kr1);
-  qk_tile<D, BITS, true>(kr0, kr1, lane, qb, ql, s);
-  scores[(2 * t) * 16 + g] = s[0];
-  scores[(2 * t + 1) * 16 + g] = s[1];
-  scores[(2 * t) * 16 + g + 8] = s[2];
-  scores[(2 * t + 1) * 16 + g + 8] = s[3];
+  float c0[4], c1[4];
+  qk_ntile_f16<D, BITS>(kr0, t, qa, c0);
+  qk_ntile_f16<D, BITS>(kr1, t, qa, c1);
+  scores[g * 16 + 2 * t] = c0[0] + c0[2];
+  scores[g * 16 + 2 * t + 1] = c0[1] + c0[3];
+  scores[g * 16 + 2 * t + 8] = c1[0] + c1[2];
+  scores[g * 16 + 2 * t + 9] = c1[1] + c1[3];
   auto ld2 = [&](int r, int cidx) {
     return (uint32_t)reinterpret_cast<const unsigned short*>(pm)[r * 16 + cidx] |
            ((uint32_t)reinterpret_cast<const unsigned short*>(pm)[r * 16 + cidx + 1] << 16);
@@ -858,6 +908,32 @@ __global__ void debug_tile_kernel(const uint8_t* k_rows, const uint8_t* v_rows, 
     out[(2 * t + 1) * D + d + 1] = o[j][3];
   }
 }
+
+// q int8 [8][D]; scores int32 [8][16] = sum_d q[h][d] * u[key][d], u = stored code (offset-binary
+// for 2/4-bit rows, two's complement for 8-bit rows).
+template <int D, int BITS>
+__global__ void debug_tile_i8_kernel(const uint8_t* k_rows, const int8_t* q, int* scores) {
+  constexpr int PD = D * BITS / 8;
+  __shared__ __align__(16) uint8_t ks[16 * PD + 16];
+  __shared__ __align__(16) int8_t qs[8 * D];
+  const int lane = threadIdx.x;
+  for (int i = lane; i < 16 * PD; i += 32) ks[i] = k_rows[i];
+  for (int i = lane; i < 8 * D; i += 32) qs[i] = q[i];
+  __syncwarp();
+  const int g = lane >> 2, t = lane & 3;
+  uint32_t qa[D / 32][4];
+  gather_qa_i8<D, BITS>(qs, nullptr, lane, qa);
+  uint32_t kr0[SliceWords<D, BITS>::K], kr1[SliceWords<D, BITS>::K];
+  load_kslice<D, BITS>(ks, g, t, kr0);
+  load_kslice<D, BITS>(ks, g + 8, t, kr1);
+  int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+  qk_ntile_i8<D, BITS>(kr0, qa, c0);
+  qk_ntile_i8<D, BITS>(kr1, qa, c1);
+  scores[g * 16 + 2 * t] = c0[0];
+  scores[g * 16 + 2 * t + 1] = c0[1];
+  scores[g * 16 + 2 * t + 8] = c1[0];
+  scores[g * 16 + 2 * t + 9] = c1[1];
+}
 }  // namespace skv
 
 template <int D>
@@ -884,4 +960,24 @@ extern "C" int skv_debug_tile_products(int head_dim, int bits, const uint8_t* k_
     return launch_debug<64>(bits, k_rows, v_rows, static_cast<const __half*>(q_half),
                             static_cast<const __half*>(p_half), scores, out, as_stream(stream));
   return SKV_ERR_UNSUPPORTED;
+}
+
+extern "C" int skv_debug_tile_scores_i8(int head_dim, int bits, const uint8_t* k_rows, const int8_t* q_int8,
+                                        int32_t* scores, void* stream) {
+  if (!k_rows || !q_int8 || !scores) return SKV_ERR_INVALID;
+  cudaStream_t st = as_stream(stream);
+  if (head_dim == 128) {
+    if (bits == 2) debug_tile_i8_kernel<128, 2><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
+    else if (bits == 4) debug_tile_i8_kernel<128, 4><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
+    else if (bits == 8) debug_tile_i8_kernel<128, 8><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
+    else return SKV_ERR_INVALID;
+  } else if (head_dim == 64) {
+    if (bits == 2) debug_tile_i8_kernel<64, 2><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
+    else if (bits == 4) debug_tile_i8_kernel<64, 4><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
+    else if (bits == 8) debug_tile_i8_kernel<64, 8><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
+    else return SKV_ERR_INVALID;
+  } else {
+    return SKV_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }

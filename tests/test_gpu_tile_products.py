@@ -35,3 +35,25 @@ def test_tile_products_exact(d, bits):
         want_o = (p[:8].astype(np.float64) + p[8:].astype(np.float64)) @ vc.astype(np.float64)
         assert np.array_equal(scores.cpu().numpy().astype(np.float64), want_s), (d, bits, "scores")
         assert np.array_equal(out.cpu().numpy().astype(np.float64), want_o), (d, bits, "out")
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_tile_scores_int8_exact(d, bits):
+    """The int8 tensor-core path used for 2/4/8-bit keys: exact int32 dot products."""
+    from smartkv_b200 import _lib as L
+    lo, hi = orc.code_range(bits)
+    for seed in range(3):
+        rng = np.random.default_rng(seed * 7 + bits + d)
+        kc = rng.integers(lo, hi + 1, size=(16, d)).astype(np.int8)
+        if seed == 0:
+            kc.reshape(-1)[: hi - lo + 1] = np.arange(lo, hi + 1)
+        q = rng.integers(-128, 128, size=(8, d)).astype(np.int8)
+        kr = torch.from_numpy(orc.pack_rows(kc, bits)).cuda().contiguous()
+        qt = torch.from_numpy(q).cuda()
+        scores = torch.empty((8, 16), dtype=torch.int32, device="cuda")
+        L.check(L.lib().skv_debug_tile_scores_i8(d, bits, L.ptr(kr), L.ptr(qt), L.ptr(scores), L.stream_ptr()))
+        torch.cuda.synchronize()
+        stored = kc.astype(np.int64) + (0 if bits == 8 else (1 << (bits - 1)))
+        want = q.astype(np.int64) @ stored.T
+        assert np.array_equal(scores.cpu().numpy().astype(np.int64), want), (d, bits)
