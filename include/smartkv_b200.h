@@ -152,6 +152,29 @@ int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* quer
                     int num_q_heads, const void* partials, int num_ctas, const void* cur_k, const void* cur_v,
                     int kv_dtype, float* out, float* lse_max, float* lse_sum, float* cur_prob, void* stream);
 
+/* ---- attention without a caller-owned scratch buffer --------------------------- */
+
+/* No counterpart in the reference.  Same launch as skv_decode_attention, but the partials go
+ * into a fixed array that is part of the library's device code (16 MiB per device) instead of a
+ * buffer the caller allocated.  It is meant for callers that cannot allocate device memory at
+ * decode time -- a server that froze its memory pool after start-up, a runtime whose allocator
+ * may not be entered from the decode thread.  The call itself allocates nothing and calls no
+ * allocating library routine.
+ *   *partials_out receives the device address of the array; pass it as `partials` to
+ *   skv_lse_combine on the same stream.
+ * Limits and rules:
+ *   - skv_attn_partials_bytes(desc, num_q_heads, num_ctas) must not exceed 16 MiB, otherwise
+ *     the call returns SKV_ERR_CAPACITY, prints the two sizes to stderr and launches nothing.
+ *   - The first call on each device looks the array's address up (cudaGetSymbolAddress); make
+ *     that first call before any stream capture begins.  Later calls only launch.
+ *   - There is one array per device: two calls whose kernels can overlap on the GPU (different
+ *     streams, or a second call issued before the first call's combine step was enqueued on the
+ *     same stream) race on it.  Keep attention -> combine pairs in one stream order.
+ *   - Nothing in the array needs clearing between calls. */
+int skv_decode_attention_static(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
+                                const void* query, int query_dtype, int num_q_heads, int num_ctas, float* logits,
+                                int32_t* err_flag, void** partials_out, void* stream);
+
 /* ---- importance ----------------------------------------------------------- */
 
 /* Replaces SmartKVCache.update_attention's head weighting + ImportanceTracker.update_attention

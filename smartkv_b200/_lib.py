@@ -53,6 +53,8 @@ _SIGNATURES = {
     "skv_attn_plan": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p]),
     "skv_decode_attention": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "skv_decode_attention_static": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                            c_int, c_void_p, c_void_p, POINTER(c_void_p), c_void_p]),
     "skv_lse_combine": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_importance_update": (c_int, [POINTER(StoreDesc), c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,

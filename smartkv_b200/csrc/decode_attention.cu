@@ -19,6 +19,7 @@
 // smartkv/core/fused_cpu.py:70-113 (dequantise, q.k/sqrt(d), online softmax).
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "attn_frag.cuh"
@@ -848,6 +849,58 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const
   }
   lse_combine_kernel<<<desc->num_seqs * desc->num_kv_heads, 256, 0, as_stream(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+// ---- attention with the partials in a fixed device array ------------------------------
+// Some callers cannot hand the library a scratch buffer of their own: a serving loop that
+// froze its device memory pool after start-up, or a host runtime whose allocator must not
+// be entered from the decode thread.  For them the partials live in the array below, which
+// is part of the loaded module, so using it never allocates.
+constexpr long long kStaticPartialsBytes = 16ll << 20;  // the stated maximum: 16 MiB per device
+static __device__ __align__(256) unsigned char g_static_partials[kStaticPartialsBytes];
+
+static constexpr int kStaticMaxDevices = 64;
+static void* g_static_partials_ptr[kStaticMaxDevices];  // address of the array on every device seen so far
+static std::mutex g_static_mutex;
+
+extern "C" int skv_decode_attention_static(const SkvStoreDesc* desc, const void* store, int layer,
+                                           const void* plan, const void* query, int query_dtype,
+                                           int num_q_heads, int num_ctas, float* logits, int32_t* err_flag,
+                                           void** partials_out, void* stream) {
+  if (!desc || !partials_out) return SKV_ERR_INVALID;
+  *partials_out = nullptr;
+  const int64_t need = skv_attn_partials_bytes(desc, num_q_heads, num_ctas);
+  if (need < 0) return (int)need;
+  if (need > kStaticPartialsBytes) {
+    fprintf(stderr,
+            "skv_decode_attention_static: this shape needs %lld bytes of partials, the fixed array holds %lld; "
+            "use skv_decode_attention with a caller-owned buffer\n",
+            (long long)need, kStaticPartialsBytes);
+    return SKV_ERR_CAPACITY;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SKV_ERR_CUDA;
+  if (dev < 0 || dev >= kStaticMaxDevices) return SKV_ERR_UNSUPPORTED;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(g_static_mutex);
+    if (g_static_partials_ptr[dev] == nullptr) {  // set-up, once per device: look the array up in the module
+      void* sym = nullptr;
+      const cudaError_t rc = cudaGetSymbolAddress(&sym, g_static_partials);
+      if (rc != cudaSuccess || sym == nullptr) {
+        fprintf(stderr, "skv_decode_attention_static: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(rc));
+        return SKV_ERR_CUDA;
+      }
+      g_static_partials_ptr[dev] = sym;
+    }
+    scratch = g_static_partials_ptr[dev];
+  }
+  // Nothing in the array has to start at zero: the launch writes the (max, sum) header of every
+  // partial the combine step reads before that step can run on the same stream.
+  const int rc = skv_decode_attention(desc, store, layer, plan, query, query_dtype, num_q_heads, scratch, num_ctas,
+                                      logits, err_flag, stream);
+  if (rc == SKV_OK) *partials_out = scratch;
+  return rc;
 }
 
 // ---- debug: raw tile products through the production fragment code ----------------
