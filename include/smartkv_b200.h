@@ -191,6 +191,88 @@ int skv_importance_update(const SkvStoreDesc* desc, int layer, const int32_t* co
                           const int32_t* cur_slot, float* head_state, int parity, double* cumulative,
                           float* layer_ema, uint8_t* touched, float decay, float head_decay, void* stream);
 
+/* ---- reallocation: bit allocation ------------------------------------------- */
+
+#define SKV_ALLOC_MAX_PROTECTED 16
+
+/* Parameters of the allocator; the fields mirror SmartKVCache.__init__ (smartkv/core/cache.py:42-67)
+ * after the clamping done there (:131-141). */
+typedef struct SkvAllocConfig {
+  int32_t num_heads;            /* KV heads of the whole model (accounting only) */
+  int32_t head_dim;
+  int32_t num_bits;             /* 2..4 widths */
+  int32_t bits[4];              /* ascending, each in {2,3,4,8} */
+  double util[4];               /* bits[i] ** utility_alpha, computed by the host (its libm is the reference's) */
+  double memory_budget;
+  double importance_floor;
+  double rank_threshold;        /* hysteresis_rank_threshold */
+  double high_fraction;         /* high_precision_fraction */
+  double high_boost;            /* high_precision_boost */
+  int32_t hysteresis_intervals;
+  int32_t min_high_tokens;
+  int32_t scale_bits;           /* 32 or 16: bits of one stored scale in the accounting */
+  int32_t use_packing;          /* must be 1 */
+  int32_t critical_window;      /* token ids below it are protected (cache.py:309) */
+  int32_t num_protected;
+  int32_t protected_ids[SKV_ALLOC_MAX_PROTECTED];
+} SkvAllocConfig;
+
+int64_t skv_alloc_workspace_bytes(const SkvStoreDesc* desc);
+
+/* Replaces SmartKVCache.allocate_precision + _solve_allocation (smartkv/core/cache.py:281-351,
+ * 353-601) for every sequence of the store at once: marginal-gain greedy under the memory
+ * budget with the 0.85-budget gate, rank hysteresis and the high-priority pass, bit-exact with
+ * the reference's heap loop (ties: lower token id first).
+ *   counts int32 [num_seqs][4], slot_token int32 [num_seqs][slots] (token id of every storage
+ *   index), scores fp64 [num_seqs][slots] (cumulative importance, storage order), recency fp64
+ *   [num_seqs][slots] or NULL (factor exp(-age/512) of cache.py:304-306; NULL = 1).
+ *   rank_pct fp64 / rank_streak int8 [num_seqs][slots]: the persistent hysteresis record
+ *   (cache.py:423-450); streak -1 marks a token without a record.
+ * Outputs: new_bits uint8 [num_seqs][slots] (0 on unused indices), new_counts int32
+ * [num_seqs][4], changed int32 [num_seqs] (tokens whose width differs from their bucket's). */
+int skv_alloc_bits(const SkvStoreDesc* desc, const SkvAllocConfig* cfg, const int32_t* counts,
+                   const int32_t* slot_token, const double* scores, const double* recency, double* rank_pct,
+                   int8_t* rank_streak, uint8_t* new_bits, int32_t* new_counts, int32_t* changed, void* workspace,
+                   void* stream);
+
+/* ---- reallocation: requantise + repack ------------------------------------------ */
+
+/* The three calls below replace SmartKVCache._requantize_tokens / _requantize_single /
+ * _write_quantized_slot (smartkv/core/cache.py:806-926) and the bucket delete / append around
+ * them (:1046-1083, :1121-1161).  All are stream-ordered and allocate nothing.
+ *
+ * skv_repack_plan: from the new widths (skv_alloc_bits' new_bits) builds, per sequence, the list
+ * of row moves that makes every bucket dense again: move k of sequence b takes the row at storage
+ * index move_src[b][k] to move_dst[b][k] (both int32 [num_seqs][slots]; n_moves int32 [num_seqs]).
+ * counts_new int32 [num_seqs][4].  workspace: skv_repack_plan_workspace_bytes().  If a bucket
+ * would exceed its capacity nothing moves (n_moves = 0, counts_new = counts) and *err_flag = 3. */
+int64_t skv_repack_plan_workspace_bytes(const SkvStoreDesc* desc);
+int skv_repack_plan(const SkvStoreDesc* desc, const int32_t* counts, const uint8_t* new_bits, int32_t* move_src,
+                    int32_t* move_dst, int32_t* n_moves, int32_t* counts_new, void* workspace, int32_t* err_flag,
+                    void* stream);
+
+/* skv_requant_repack: applies the moves to the packed rows of layers [layer_begin, layer_end).
+ * A row whose destination bucket has another width is dequantised (code * scale, fp32) and
+ * quantised again at the new width, from the stored codes as the reference does (cache.py:819-844);
+ * other rows are copied.  Every moved row passes through `staging`
+ * (skv_requant_staging_bytes(desc, upper bound of the moves of all sequences, layers per call));
+ * if the staging buffer is too small for the moves found on the device nothing moves and
+ * *err_flag = 6. */
+int64_t skv_requant_staging_bytes(const SkvStoreDesc* desc, int64_t max_moves, int num_layers);
+int skv_requant_repack(const SkvStoreDesc* desc, void* store, int layer_begin, int layer_end,
+                       const int32_t* move_src, const int32_t* move_dst, const int32_t* n_moves, void* staging,
+                       int64_t staging_bytes, int32_t* err_flag, void* stream);
+
+/* skv_repack_meta: the per-token arrays kept in storage order (token ids, cumulative importance,
+ * hysteresis record, per-layer EMA and its first-touch flags) follow the same moves; indices a
+ * bucket gave up are reset; finally counts <- counts_new.  Call it after the rows of every layer
+ * have moved. */
+int64_t skv_repack_meta_staging_bytes(const SkvStoreDesc* desc, int64_t max_moves);
+int skv_repack_meta(const SkvStoreDesc* desc, const int32_t* move_src, const int32_t* move_dst,
+                    const int32_t* n_moves, int32_t* counts, const int32_t* counts_new, int32_t* slot_token,
+                    double* cumulative, double* rank_pct, int8_t* rank_streak, float* layer_ema, uint8_t* touched,
+                    void* staging, int64_t staging_bytes, int32_t* err_flag, void* stream);
+
 /* ---- debug / test hooks ---------------------------------------------------- */
 
 /* Raw tensor-core tile products through the same fragment code as the attention

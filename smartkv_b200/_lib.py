@@ -30,6 +30,21 @@ class StoreDesc(Structure):
     ]
 
 
+ALLOC_MAX_PROTECTED = 16
+
+
+class AllocConfig(Structure):
+    """SkvAllocConfig of include/smartkv_b200.h."""
+    _fields_ = [
+        ("num_heads", c_int32), ("head_dim", c_int32), ("num_bits", c_int32), ("bits", c_int32 * 4),
+        ("util", c_double * 4), ("memory_budget", c_double), ("importance_floor", c_double),
+        ("rank_threshold", c_double), ("high_fraction", c_double), ("high_boost", c_double),
+        ("hysteresis_intervals", c_int32), ("min_high_tokens", c_int32), ("scale_bits", c_int32),
+        ("use_packing", c_int32), ("critical_window", c_int32), ("num_protected", c_int32),
+        ("protected_ids", c_int32 * ALLOC_MAX_PROTECTED),
+    ]
+
+
 class SmartKVLibraryError(RuntimeError):
     pass
 
@@ -57,6 +72,19 @@ _SIGNATURES = {
                                             c_int, c_void_p, c_void_p, POINTER(c_void_p), c_void_p]),
     "skv_lse_combine": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "skv_alloc_workspace_bytes": (c_int64, [POINTER(StoreDesc)]),
+    "skv_alloc_bits": (c_int, [POINTER(StoreDesc), POINTER(AllocConfig), c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "skv_repack_plan_workspace_bytes": (c_int64, [POINTER(StoreDesc)]),
+    "skv_repack_plan": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p]),
+    "skv_requant_staging_bytes": (c_int64, [POINTER(StoreDesc), c_int64, c_int]),
+    "skv_requant_repack": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int64, c_void_p, c_void_p]),
+    "skv_repack_meta_staging_bytes": (c_int64, [POINTER(StoreDesc), c_int64]),
+    "skv_repack_meta": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                c_void_p]),
     "skv_importance_update": (c_int, [POINTER(StoreDesc), c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
                                       c_float, c_void_p]),

@@ -629,69 +629,90 @@ struct CombineParams {
   float scale_log2;
 };
 
-// one block per (sequence, KV head) segment
+constexpr int kCombineChunk = 256;
+
+// one block of head_dim threads per (sequence, KV head, head of the group)
 __global__ void lse_combine_kernel(const CombineParams p) {
   const StoreGeom& g = p.g;
   const int D = g.head_dim, G = p.group, Hkv = g.num_kv_heads;
-  const int seg = blockIdx.x, b = seg / Hkv, h = seg - b * Hkv;
-  const int tid = threadIdx.x, NT = blockDim.x;
-  __shared__ float s_cur[8];
+  const int seg = blockIdx.x / G, gq = blockIdx.x - seg * G;
+  const int b = seg / Hkv, h = seg - b * Hkv;
+  const int d = threadIdx.x, warp = d >> 5, lane = d & 31, nwarps = D >> 5;
+  __shared__ float s_red[8];
   const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
   const int nsplit = pv.seg_count[seg] * p.per_run;
   const int r0 = nsplit > 0 ? pv.seg_begin[seg] * p.per_run : 0;
-
-  // ---- current-token logits (full precision), one warp per group row -------------
+  const int pstride = partial_stride(G, D);
+  const float* base = p.partials + (long long)r0 * pstride + gq * (D + 2);
   const bool has_cur = p.cur_k != nullptr && p.cur_v != nullptr;
-  const int warp = tid >> 5, lane = tid & 31, nwarps = NT >> 5;
+  const long long hq = (long long)b * p.num_q_heads + h * G + gq;
+  const long long kv = ((long long)b * Hkv + h) * D + d;
+
+  // ---- current-token logit (full precision) and the maximum over all partials -------
+  float dot = 0.f;
   if (has_cur) {
-    for (int gq = warp; gq < G; gq += nwarps) {
-      const long long qi = ((long long)b * p.num_q_heads + h * G + gq) * D;
-      const long long ki = ((long long)b * Hkv + h) * D;
-      float acc = 0.f;
-      for (int d = lane; d < D; d += 32) {
-        const float q = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[qi + d])
-                                    : static_cast<const float*>(p.query)[qi + d];
-        const float k = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_k)[ki + d])
-                                     : static_cast<const float*>(p.cur_k)[ki + d];
-        acc = fmaf(q, k, acc);
-      }
-      acc = warp_sum(acc);
-      if (lane == 0) s_cur[gq] = acc * p.scale_log2;
-    }
+    const float q = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[hq * D + d])
+                                : static_cast<const float*>(p.query)[hq * D + d];
+    const float k = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_k)[kv])
+                                 : static_cast<const float*>(p.cur_k)[kv];
+    dot = q * k;
+  }
+  float mloc = -INFINITY;
+  for (int k = d; k < nsplit; k += D) mloc = fmaxf(mloc, base[(long long)k * pstride]);
+  dot = warp_sum(dot);
+  mloc = warp_max(mloc);
+  if (lane == 0) {
+    s_red[warp] = dot;
+    s_red[4 + warp] = mloc;
   }
   __syncthreads();
+  float s_cur = 0.f, M = -INFINITY;
+  for (int w = 0; w < nwarps; ++w) {
+    s_cur += s_red[w];
+    M = fmaxf(M, s_red[4 + w]);
+  }
+  s_cur *= p.scale_log2;
+  if (has_cur) M = fmaxf(M, s_cur);
 
-  const int pstride = partial_stride(G, D);
-  for (int i = tid; i < G * D; i += NT) {
-    const int gq = i / D, d = i - gq * D;
-    float M = has_cur ? s_cur[gq] : -INFINITY;
-    for (int k = 0; k < nsplit; ++k) M = fmaxf(M, p.partials[(long long)(r0 + k) * pstride + gq * (D + 2)]);
-    float acc = 0.f, L = 0.f;
-    for (int k = 0; k < nsplit; ++k) {
-      const float* row = p.partials + (long long)(r0 + k) * pstride + gq * (D + 2);
+  // ---- fold the partials (fixed order), kCombineChunk at a time -----------------------------
+  // the weights of a chunk go through shared memory so that the row loads below do not depend
+  // on anything loaded in the same loop and can all be in flight together
+  __shared__ float s_f[kCombineChunk];
+  __shared__ float s_lf[kCombineChunk];
+  float acc = 0.f, L = 0.f;
+  for (int c0 = 0; c0 < nsplit; c0 += kCombineChunk) {
+    const int cn = (nsplit - c0) < kCombineChunk ? (nsplit - c0) : kCombineChunk;
+    __syncthreads();
+    for (int k = d; k < cn; k += D) {
+      const float* row = base + (long long)(c0 + k) * pstride;
       const float mw = row[0];
-      if (mw != -INFINITY) {
-        const float f = ex2f(mw - M);
-        acc += row[2 + d] * f;
-        L += row[1] * f;
-      }
+      const float f = mw == -INFINITY ? 0.f : ex2f(mw - M);
+      s_f[k] = f;
+      s_lf[k] = f == 0.f ? 0.f : row[1] * f;
     }
-    float pc = 0.f;
-    if (has_cur) {
-      pc = ex2f(s_cur[gq] - M);
-      const long long vi = ((long long)b * Hkv + h) * D + d;
-      const float v = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_v)[vi])
-                                   : static_cast<const float*>(p.cur_v)[vi];
-      acc += pc * v;
-      L += pc;
+    __syncthreads();
+    const float* col = base + (long long)c0 * pstride + 2 + d;
+#pragma unroll 8
+    for (int k = 0; k < cn; ++k) {
+      const float f = s_f[k];
+      const float x = col[(long long)k * pstride];  // a partial without keys holds stale bytes: select, not multiply
+      acc += f == 0.f ? 0.f : x * f;
+      L += s_lf[k];
     }
-    const long long hq = (long long)b * p.num_q_heads + h * G + gq;
-    p.out[hq * D + d] = L > 0.f ? acc / L : 0.f;
-    if (d == 0) {
-      if (p.lse_max) p.lse_max[hq] = M;
-      if (p.lse_sum) p.lse_sum[hq] = L;
-      if (p.cur_prob) p.cur_prob[hq] = (has_cur && L > 0.f) ? pc / L : 0.f;
-    }
+  }
+  float pc = 0.f;
+  if (has_cur) {
+    pc = ex2f(s_cur - M);
+    const float v = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_v)[kv])
+                                 : static_cast<const float*>(p.cur_v)[kv];
+    acc = fmaf(pc, v, acc);
+    L += pc;
+  }
+  p.out[hq * D + d] = L > 0.f ? acc / L : 0.f;
+  if (d == 0) {
+    if (p.lse_max) p.lse_max[hq] = M;
+    if (p.lse_sum) p.lse_sum[hq] = L;
+    if (p.cur_prob) p.cur_prob[hq] = (has_cur && L > 0.f) ? pc / L : 0.f;
   }
 }
 
@@ -823,6 +844,7 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const
   const int group = num_q_heads / desc->num_kv_heads;
   if (group < 1 || group > 8) return SKV_ERR_UNSUPPORTED;
   if ((cur_k == nullptr) != (cur_v == nullptr)) return SKV_ERR_INVALID;
+  if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
   CombineParams p;
   p.g = make_geom(*desc);
   p.plan = static_cast<const int*>(plan);
@@ -847,7 +869,7 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const
     if (p.q_is_half && desc->head_dim == 128 && cfg_sel == 1) p.per_run = 11;
     if (p.q_is_half && desc->head_dim == 128 && cfg_sel == 2) p.per_run = 7;
   }
-  lse_combine_kernel<<<desc->num_seqs * desc->num_kv_heads, 256, 0, as_stream(stream)>>>(p);
+  lse_combine_kernel<<<desc->num_seqs * desc->num_kv_heads * group, desc->head_dim, 0, as_stream(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 

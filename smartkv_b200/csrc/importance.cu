@@ -49,7 +49,6 @@ __global__ void importance_update_kernel(const ImportanceParams p) {
   const int b = blockIdx.y, tid = threadIdx.x, Hq = p.num_q_heads;
   __shared__ float s_w[kMaxQHeads];    // head weight / final sum
   __shared__ float s_max[kMaxQHeads];
-  __shared__ float s_mean;
 
   int cnt[kNumBuckets];
   int nkeys = 0;
@@ -58,33 +57,43 @@ __global__ void importance_update_kernel(const ImportanceParams p) {
     cnt[i] = p.counts[b * kNumBuckets + i];
     nkeys += cnt[i];
   }
-  const bool has_cur = p.cur_prob != nullptr && p.cur_slot != nullptr && p.cur_slot[b] >= 0;
+  const int cur_slot = (p.cur_prob != nullptr && p.cur_slot != nullptr) ? p.cur_slot[b] : -1;
+  const bool has_cur = cur_slot >= 0;
   const int total_keys = nkeys + (has_cur ? 1 : 0);
+
+  // most storage indices of a sequence are unused capacity: a block without a live key leaves at once
+  // (block 0 of every sequence stays, it publishes the head-importance EMA)
+  const int s_lo = blockIdx.x * kImpThreads, s_hi = s_lo + kImpThreads;
+  bool block_live = blockIdx.x == 0 || (has_cur && cur_slot >= s_lo && cur_slot < s_hi);
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i)
+    block_live |= cnt[i] > 0 && g.bucket_base[i] < s_hi && g.bucket_base[i] + cnt[i] > s_lo;
+  if (!block_live) return;
 
   // head-importance EMA (cache.py:242-248).  Every softmax row sums to one, so the
   // mean over keys of a head's probabilities is 1 / (number of keys).
   const float* hs_old = p.head_state + ((long long)b * 2 + p.parity) * Hq;
   float* hs_new = p.head_state + ((long long)b * 2 + (p.parity ^ 1)) * Hq;
   const float head_mean = total_keys > 0 ? 1.0f / (float)total_keys : 0.f;
+  float hn = 0.f, lse_l = 0.f, lse_m = 0.f;
   if (tid < Hq) {
-    const float hn = hs_old[tid] * p.head_decay + head_mean * (1.0f - p.head_decay);
+    lse_l = p.lse_sum[(long long)b * Hq + tid];  // issued early: independent of the EMA chain below
+    lse_m = p.lse_max[(long long)b * Hq + tid];
+    hn = hs_old[tid] * p.head_decay + head_mean * (1.0f - p.head_decay);
     s_max[tid] = hn;  // staged, replaced below
     if (blockIdx.x == 0) hs_new[tid] = hn;
   }
   __syncthreads();
-  if (tid == 0) {
+  float my_w = 0.f;
+  if (tid < Hq) {
     float acc = 0.f;
-    for (int h = 0; h < Hq; ++h) acc += s_max[h];
-    s_mean = acc / (float)Hq;
+    for (int h = 0; h < Hq; ++h) acc += s_max[h];  // same order in every thread: one mean per block
+    my_w = hn / (acc / (float)Hq + 1e-6f);
   }
   __syncthreads();
-  float my_w = 0.f;
-  if (tid < Hq) my_w = s_max[tid] / (s_mean + 1e-6f);
-  __syncthreads();
   if (tid < Hq) {
-    const float L = p.lse_sum[(long long)b * Hq + tid];
-    s_w[tid] = L > 0.f ? my_w / L : 0.f;
-    s_max[tid] = p.lse_max[(long long)b * Hq + tid];
+    s_w[tid] = lse_l > 0.f ? my_w / lse_l : 0.f;
+    s_max[tid] = lse_m;
   }
   __syncthreads();
 
@@ -98,9 +107,10 @@ __global__ void importance_update_kernel(const ImportanceParams p) {
   bool write = false;
   if (valid) {
     const float* lg = p.logits + (long long)b * Hq * g.slots + s;
+#pragma unroll 8
     for (int h = 0; h < Hq; ++h) mass += s_w[h] * ex2_approx(lg[(long long)h * g.slots] - s_max[h]);
     write = true;
-  } else if (has_cur && s == p.cur_slot[b]) {
+  } else if (has_cur && s == cur_slot) {
     // the newest token: its probability came out of the combine; it is stored at
     // this storage index when the step's append commits
     for (int h = 0; h < Hq; ++h) {

@@ -1,0 +1,445 @@
+// Requantise / repack after a reallocation.
+//
+// Replaces SmartKVCache._requantize_tokens / _requantize_single / _write_quantized_slot
+// (smartkv/core/cache.py:806-926) and the bucket bookkeeping around them (swap-with-last
+// delete :1121-1161, append :1046-1083): a Python loop over every (layer, changed token).
+//
+// A token whose width changed is dequantised from its stored codes (code * scale, fp32),
+// quantised again at the new width (cache.py:819-844: from the dequantised codes, not from
+// the original values) and moved to the bucket of the new width.  Buckets stay dense: the
+// positions a bucket loses are refilled first by its own rows that now lie beyond the new
+// count, then by the arriving rows, so only changed rows and a few tail rows are touched.
+// Which row of a bucket a token occupies is not observable (attention is a sum over keys).
+//
+// Three steps, every one stream-ordered:
+//   skv_repack_plan     one block per sequence: the list of moves (source -> destination
+//                       storage index), the same for every layer
+//   skv_requant_repack  per layer range: all moved rows -> staging (requantised where the
+//                       width changed), then staging -> destination.  Two kernels, so every
+//                       read of the old layout precedes every write of the new one.
+//   skv_repack_meta     the per-token arrays kept in storage order follow the same moves.
+#include <cub/block/block_scan.cuh>
+
+#include "quant_row.cuh"
+
+namespace skv {
+
+constexpr int kPlanThreads = 1024;
+constexpr int kStageRowBytes = 136;  // 128 packed bytes at most, the fp32 scale at offset 128, padding
+constexpr int kMaxSeqsRepack = 1024;
+
+__device__ __forceinline__ int bucket_of_slot(const StoreGeom& g, int s) {
+  int b = 0;
+#pragma unroll
+  for (int i = 1; i < kNumBuckets; ++i)
+    if (s >= g.bucket_base[i]) b = i;
+  return b;
+}
+
+// ---- the moves ----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kPlanThreads)
+    repack_plan_kernel(StoreGeom g, const int32_t* counts, const uint8_t* new_bits, int32_t* move_src,
+                       int32_t* move_dst, int32_t* n_moves, int32_t* counts_new, int32_t* scratch, int32_t* err) {
+  const int b = blockIdx.x, tid = threadIdx.x, T = g.slots;
+  using Scan = cub::BlockScan<int, kPlanThreads>;
+  __shared__ typename Scan::TempStorage tmp;
+  __shared__ int s_new[kNumBuckets], s_free[kNumBuckets], s_tail[kNumBuckets], s_off[kNumBuckets + 1];
+  __shared__ int s_run[2];
+  const uint8_t* nb = new_bits + (long long)b * T;
+  int32_t* free_pos = scratch + (long long)b * 2 * T;  // [T], bucket w's list at [bucket_base[w] ...)
+  int32_t* tail_src = free_pos + T;                     // [T]
+  int32_t* msrc = move_src + (long long)b * T;
+  int32_t* mdst = move_dst + (long long)b * T;
+  int cnt[kNumBuckets];
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) cnt[i] = counts[b * kNumBuckets + i];
+  if (tid < kNumBuckets) s_new[tid] = 0;
+  __syncthreads();
+
+  // new counts
+  for (int w = 0; w < kNumBuckets; ++w) {
+    for (int pos = tid; pos < cnt[w]; pos += kPlanThreads) {
+      const int nbk = bits_bucket(nb[g.bucket_base[w] + pos]);
+      if (nbk >= 0) atomicAdd(&s_new[nbk], 1);
+      else if (err) atomicExch(err, 4);  // a live token without a width
+    }
+  }
+  __syncthreads();
+  bool over = false;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) over |= s_new[i] > g.cap[i];
+  if (over) {
+    if (tid == 0) {
+      if (err) atomicExch(err, 3);  // a bucket would overflow: nothing moves
+      n_moves[b] = 0;
+      for (int i = 0; i < kNumBuckets; ++i) counts_new[b * kNumBuckets + i] = cnt[i];
+    }
+    return;
+  }
+
+  // per bucket: free positions (ascending) and own rows beyond the new count (ascending)
+  for (int w = 0; w < kNumBuckets; ++w) {
+    const int c_old = cnt[w], c_new = s_new[w], base = g.bucket_base[w], width = bucket_bits(w);
+    const int span = c_old > c_new ? c_old : c_new;
+    if (tid == 0) s_run[0] = s_run[1] = 0;
+    __syncthreads();
+    for (int p0 = 0; p0 < span; p0 += kPlanThreads) {
+      const int pos = p0 + tid;
+      const bool live = pos < c_old;
+      const bool stays = live && nb[base + pos] == width;
+      const int is_free = (pos < c_new && !stays) ? 1 : 0;
+      const int is_tail = (stays && pos >= c_new) ? 1 : 0;
+      int packed = is_free | (is_tail << 16), excl, total;
+      Scan(tmp).ExclusiveSum(packed, excl, total);
+      const int rf = s_run[0] + (excl & 0xffff), rt = s_run[1] + (excl >> 16);
+      if (is_free) free_pos[base + rf] = pos;
+      if (is_tail) tail_src[base + rt] = base + pos;
+      __syncthreads();
+      if (tid == 0) {
+        s_run[0] += total & 0xffff;
+        s_run[1] += total >> 16;
+      }
+      __syncthreads();
+    }
+    if (tid == 0) {
+      s_free[w] = s_run[0];
+      s_tail[w] = s_run[1];
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    int off = 0;
+    for (int w = 0; w < kNumBuckets; ++w) {
+      s_off[w] = off;
+      off += s_free[w];
+    }
+    s_off[kNumBuckets] = off;
+    n_moves[b] = off;
+    for (int i = 0; i < kNumBuckets; ++i) counts_new[b * kNumBuckets + i] = s_new[i];
+  }
+  __syncthreads();
+
+  // arrivals of every bucket in ascending source storage index, after the bucket's tail rows
+  __shared__ int s_arr[kNumBuckets];
+  if (tid < kNumBuckets) s_arr[tid] = 0;
+  __syncthreads();
+  for (int ws = 0; ws < kNumBuckets; ++ws) {
+    const int base = g.bucket_base[ws], width = bucket_bits(ws);
+    for (int p0 = 0; p0 < cnt[ws]; p0 += kPlanThreads) {
+      const int pos = p0 + tid;
+      int to = -1;
+      if (pos < cnt[ws]) {
+        const int nw = nb[base + pos];
+        if (nw != width) to = bits_bucket(nw);
+      }
+      // a chunk can send up to 1024 rows to one bucket: two scans of two 16-bit fields each
+      int pa = (to == 0 ? 1 : 0) | ((to == 1 ? 1 : 0) << 16);
+      int pb = (to == 2 ? 1 : 0) | ((to == 3 ? 1 : 0) << 16);
+      int ea, ta, eb, tb;
+      Scan(tmp).ExclusiveSum(pa, ea, ta);
+      __syncthreads();
+      Scan(tmp).ExclusiveSum(pb, eb, tb);
+      if (to >= 0) {
+        const int rank = to == 0 ? (ea & 0xffff) : to == 1 ? (ea >> 16) : to == 2 ? (eb & 0xffff) : (eb >> 16);
+        msrc[s_off[to] + s_tail[to] + s_arr[to] + rank] = base + pos;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        s_arr[0] += ta & 0xffff;
+        s_arr[1] += ta >> 16;
+        s_arr[2] += tb & 0xffff;
+        s_arr[3] += tb >> 16;
+      }
+      __syncthreads();
+    }
+  }
+  // destinations and the tail sources
+  for (int w = 0; w < kNumBuckets; ++w) {
+    const int base = g.bucket_base[w];
+    if (tid == 0 && s_tail[w] + s_arr[w] != s_free[w] && err) atomicExch(err, 5);  // bookkeeping broken
+    for (int k = tid; k < s_free[w]; k += kPlanThreads) mdst[s_off[w] + k] = base + free_pos[base + k];
+    for (int k = tid; k < s_tail[w]; k += kPlanThreads) msrc[s_off[w] + k] = tail_src[base + k];
+  }
+}
+
+// ---- moving the rows ------------------------------------------------------------------------------------
+struct RowMoveParams {
+  StoreGeom g;
+  uint8_t* store;
+  int layer_begin, layer_end;
+  const int32_t* move_src;
+  const int32_t* move_dst;
+  const int32_t* n_moves;
+  uint8_t* staging;
+  long long staging_rows;
+  int32_t* err;
+};
+
+// prefix of the per-sequence move counts into shared memory; returns the total
+__device__ __forceinline__ int load_move_prefix(const int32_t* n_moves, int B, int* s_prefix) {
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int b = 0; b < B; ++b) {
+      s_prefix[b] = acc;
+      acc += n_moves[b];
+    }
+    s_prefix[B] = acc;
+  }
+  __syncthreads();
+  return s_prefix[B];
+}
+__device__ __forceinline__ int find_seq(const int* s_prefix, int B, int m) {
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (s_prefix[mid] <= m) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// phase 0: source rows -> staging (requantised at the destination width); phase 1: staging -> destination
+template <int EPL, int PHASE>
+__global__ void repack_rows_kernel(const RowMoveParams p) {
+  const StoreGeom& g = p.g;
+  __shared__ int s_prefix[kMaxSeqsRepack + 1];
+  const int total_moves = load_move_prefix(p.n_moves, g.num_seqs, s_prefix);
+  const int Hkv = g.num_kv_heads, nl = p.layer_end - p.layer_begin;
+  const long long jobs = (long long)nl * total_moves * Hkv * 2;
+  if (jobs > p.staging_rows) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && p.err) atomicExch(p.err, 6);  // staging too small: nothing moves
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long job = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); job < jobs; job += nwarps) {
+    const int which = (int)(job & 1);
+    long long r = job >> 1;
+    const int h = (int)(r % Hkv);
+    r /= Hkv;
+    const int m = (int)(r % total_moves);
+    const int layer = p.layer_begin + (int)(r / total_moves);
+    const int b = find_seq(s_prefix, g.num_seqs, m);
+    const int k = m - s_prefix[b];
+    const int src = p.move_src[(long long)b * g.slots + k], dst = p.move_dst[(long long)b * g.slots + k];
+    const int wb_s = bucket_of_slot(g, src), wb_d = bucket_of_slot(g, dst);
+    const int bits_s = bucket_bits(wb_s), bits_d = bucket_bits(wb_d);
+    uint8_t* arena = arena_ptr(g, p.store, layer, b);
+    uint8_t* stage = p.staging + job * kStageRowBytes;
+    if (PHASE == 0) {
+      const long long row = (long long)h * g.cap[wb_s] + (src - g.bucket_base[wb_s]);
+      const uint8_t* rp = arena + (which ? g.v_off[wb_s] : g.k_off[wb_s]) + row * g.row_bytes[wb_s];
+      const float scale = reinterpret_cast<const float*>(arena + g.sc_off[wb_s])[2 * row + which];
+      if (bits_s == bits_d) {
+        const int words = g.row_bytes[wb_s] >> 2;
+        if (lane < words) reinterpret_cast<uint32_t*>(stage)[lane] = reinterpret_cast<const uint32_t*>(rp)[lane];
+        if (lane == 0) *reinterpret_cast<float*>(stage + 128) = scale;
+      } else {
+        int code[EPL];
+        unpack_row<EPL>(rp, bits_s, lane, code);
+        RowVals<EPL> x;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) x.v[i] = __fmul_rn((float)code[i], scale);  // codes.float() * scale
+        int q[EPL];
+        const float ns = quantize_row<EPL>(x, bits_d, q);
+        pack_store_row<EPL>(q, bits_d, stage, lane);
+        if (lane == 0) *reinterpret_cast<float*>(stage + 128) = ns;
+      }
+    } else {
+      const long long row = (long long)h * g.cap[wb_d] + (dst - g.bucket_base[wb_d]);
+      uint8_t* rp = arena + (which ? g.v_off[wb_d] : g.k_off[wb_d]) + row * g.row_bytes[wb_d];
+      const int words = g.row_bytes[wb_d] >> 2;
+      if (lane < words) reinterpret_cast<uint32_t*>(rp)[lane] = reinterpret_cast<const uint32_t*>(stage)[lane];
+      if (lane == 0) reinterpret_cast<float*>(arena + g.sc_off[wb_d])[2 * row + which] = *reinterpret_cast<const float*>(stage + 128);
+    }
+  }
+}
+
+// ---- per-token arrays -----------------------------------------------------------------------------------
+struct MetaParams {
+  StoreGeom g;
+  const int32_t* move_src;
+  const int32_t* move_dst;
+  const int32_t* n_moves;
+  int32_t* counts;
+  const int32_t* counts_new;
+  int32_t* slot_token;
+  double* cumulative;
+  double* rank_pct;
+  int8_t* rank_streak;
+  float* layer_ema;
+  uint8_t* touched;
+  uint8_t* staging;
+  long long staging_moves;
+  int32_t* err;
+};
+
+__host__ __device__ inline long long meta_move_bytes(int num_layers) { return 24 + 8LL * num_layers; }
+
+template <int PHASE>
+__global__ void repack_meta_kernel(const MetaParams p) {
+  const StoreGeom& g = p.g;
+  __shared__ int s_prefix[kMaxSeqsRepack + 1];
+  const int total = load_move_prefix(p.n_moves, g.num_seqs, s_prefix);
+  if (total > p.staging_moves) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && p.err) atomicExch(p.err, 6);
+    return;
+  }
+  const int L = g.num_layers, T = g.slots, B = g.num_seqs;
+  // staging arrays, one entry per move
+  double* st_cum = reinterpret_cast<double*>(p.staging);
+  double* st_pct = st_cum + p.staging_moves;
+  int32_t* st_tok = reinterpret_cast<int32_t*>(st_pct + p.staging_moves);
+  float* st_ema = reinterpret_cast<float*>(st_tok + p.staging_moves);             // [L][moves]
+  uint8_t* st_tch = reinterpret_cast<uint8_t*>(st_ema + (long long)L * p.staging_moves);  // [L][moves]
+  int8_t* st_str = reinterpret_cast<int8_t*>(st_tch + (long long)L * p.staging_moves);
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  for (long long m = (long long)blockIdx.x * blockDim.x + threadIdx.x; m < total; m += nthreads) {
+    const int b = find_seq(s_prefix, B, (int)m);
+    const int k = (int)m - s_prefix[b];
+    const long long si = (long long)b * T + p.move_src[(long long)b * T + k];
+    const long long di = (long long)b * T + p.move_dst[(long long)b * T + k];
+    if (PHASE == 0) {
+      st_cum[m] = p.cumulative[si];
+      st_pct[m] = p.rank_pct[si];
+      st_tok[m] = p.slot_token[si];
+      st_str[m] = p.rank_streak[si];
+      for (int l = 0; l < L; ++l) {
+        st_ema[(long long)l * p.staging_moves + m] = p.layer_ema[(long long)l * B * T + si];
+        st_tch[(long long)l * p.staging_moves + m] = p.touched[(long long)l * B * T + si];
+      }
+    } else {
+      p.cumulative[di] = st_cum[m];
+      p.rank_pct[di] = st_pct[m];
+      p.slot_token[di] = st_tok[m];
+      p.rank_streak[di] = st_str[m];
+      for (int l = 0; l < L; ++l) {
+        p.layer_ema[(long long)l * B * T + di] = st_ema[(long long)l * p.staging_moves + m];
+        p.touched[(long long)l * B * T + di] = st_tch[(long long)l * p.staging_moves + m];
+      }
+    }
+  }
+}
+
+// indices a bucket gave up hold no token any more: a later append must find fresh state there
+__global__ void repack_meta_clear_kernel(const MetaParams p) {
+  const StoreGeom& g = p.g;
+  const int b = blockIdx.y, L = g.num_layers, T = g.slots, B = g.num_seqs;
+  for (int w = 0; w < kNumBuckets; ++w) {
+    const int c_old = p.counts[b * kNumBuckets + w], c_new = p.counts_new[b * kNumBuckets + w];
+    for (int pos = c_new + blockIdx.x * blockDim.x + threadIdx.x; pos < c_old; pos += gridDim.x * blockDim.x) {
+      const long long i = (long long)b * T + g.bucket_base[w] + pos;
+      p.cumulative[i] = 0.0;
+      p.rank_pct[i] = 0.0;
+      p.rank_streak[i] = -1;
+      p.slot_token[i] = -1;
+      for (int l = 0; l < L; ++l) {
+        p.layer_ema[(long long)l * B * T + i] = 0.f;
+        p.touched[(long long)l * B * T + i] = 0;
+      }
+    }
+  }
+}
+__global__ void repack_commit_counts_kernel(int32_t* counts, const int32_t* counts_new, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) counts[i] = counts_new[i];
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" int64_t skv_repack_plan_workspace_bytes(const SkvStoreDesc* desc) {
+  if (!desc || desc->num_seqs <= 0 || desc->slots <= 0) return SKV_ERR_INVALID;
+  return (int64_t)desc->num_seqs * desc->slots * 2 * (int64_t)sizeof(int32_t);
+}
+
+extern "C" int skv_repack_plan(const SkvStoreDesc* desc, const int32_t* counts, const uint8_t* new_bits,
+                               int32_t* move_src, int32_t* move_dst, int32_t* n_moves, int32_t* counts_new,
+                               void* workspace, int32_t* err_flag, void* stream) {
+  if (!desc || !counts || !new_bits || !move_src || !move_dst || !n_moves || !counts_new || !workspace)
+    return SKV_ERR_INVALID;
+  if (desc->num_seqs > kMaxSeqsRepack) return SKV_ERR_UNSUPPORTED;
+  repack_plan_kernel<<<desc->num_seqs, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      make_geom(*desc), counts, new_bits, move_src, move_dst, n_moves, counts_new, static_cast<int32_t*>(workspace),
+      err_flag);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+extern "C" int64_t skv_requant_staging_bytes(const SkvStoreDesc* desc, int64_t max_moves, int num_layers) {
+  if (!desc || max_moves < 0 || num_layers <= 0) return SKV_ERR_INVALID;
+  return max_moves * num_layers * desc->num_kv_heads * 2 * (int64_t)kStageRowBytes;
+}
+
+extern "C" int skv_requant_repack(const SkvStoreDesc* desc, void* store, int layer_begin, int layer_end,
+                                  const int32_t* move_src, const int32_t* move_dst, const int32_t* n_moves,
+                                  void* staging, int64_t staging_bytes, int32_t* err_flag, void* stream) {
+  if (!desc || !store || !move_src || !move_dst || !n_moves || !staging) return SKV_ERR_INVALID;
+  if (layer_begin < 0 || layer_end > desc->num_layers || layer_begin >= layer_end) return SKV_ERR_INVALID;
+  if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
+  if (desc->num_seqs > kMaxSeqsRepack) return SKV_ERR_UNSUPPORTED;
+  RowMoveParams p;
+  p.g = make_geom(*desc);
+  p.store = static_cast<uint8_t*>(store);
+  p.layer_begin = layer_begin;
+  p.layer_end = layer_end;
+  p.move_src = move_src;
+  p.move_dst = move_dst;
+  p.n_moves = n_moves;
+  p.staging = static_cast<uint8_t*>(staging);
+  p.staging_rows = staging_bytes / kStageRowBytes;
+  p.err = err_flag;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = sms * 8, threads = 256;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (desc->head_dim == 128) {
+    repack_rows_kernel<4, 0><<<grid, threads, 0, st>>>(p);
+    repack_rows_kernel<4, 1><<<grid, threads, 0, st>>>(p);
+  } else {
+    repack_rows_kernel<2, 0><<<grid, threads, 0, st>>>(p);
+    repack_rows_kernel<2, 1><<<grid, threads, 0, st>>>(p);
+  }
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+extern "C" int64_t skv_repack_meta_staging_bytes(const SkvStoreDesc* desc, int64_t max_moves) {
+  if (!desc || max_moves < 0) return SKV_ERR_INVALID;
+  return max_moves * meta_move_bytes(desc->num_layers) + 256;
+}
+
+extern "C" int skv_repack_meta(const SkvStoreDesc* desc, const int32_t* move_src, const int32_t* move_dst,
+                               const int32_t* n_moves, int32_t* counts, const int32_t* counts_new,
+                               int32_t* slot_token, double* cumulative, double* rank_pct, int8_t* rank_streak,
+                               float* layer_ema, uint8_t* touched, void* staging, int64_t staging_bytes,
+                               int32_t* err_flag, void* stream) {
+  if (!desc || !move_src || !move_dst || !n_moves || !counts || !counts_new || !slot_token || !cumulative ||
+      !rank_pct || !rank_streak || !layer_ema || !touched || !staging)
+    return SKV_ERR_INVALID;
+  if (desc->num_seqs > kMaxSeqsRepack) return SKV_ERR_UNSUPPORTED;
+  MetaParams p;
+  p.g = make_geom(*desc);
+  p.move_src = move_src;
+  p.move_dst = move_dst;
+  p.n_moves = n_moves;
+  p.counts = counts;
+  p.counts_new = counts_new;
+  p.slot_token = slot_token;
+  p.cumulative = cumulative;
+  p.rank_pct = rank_pct;
+  p.rank_streak = rank_streak;
+  p.layer_ema = layer_ema;
+  p.touched = touched;
+  p.staging = static_cast<uint8_t*>(staging);
+  p.staging_moves = (staging_bytes - 256) / meta_move_bytes(desc->num_layers);
+  p.staging_moves &= ~7LL;  // keeps every staging array 8-byte aligned
+  p.err = err_flag;
+  if (p.staging_moves <= 0) return SKV_ERR_CAPACITY;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  repack_meta_kernel<0><<<296, 256, 0, st>>>(p);
+  repack_meta_kernel<1><<<296, 256, 0, st>>>(p);
+  repack_meta_clear_kernel<<<dim3(8, desc->num_seqs), 256, 0, st>>>(p);
+  repack_commit_counts_kernel<<<(desc->num_seqs * kNumBuckets + 255) / 256, 256, 0, st>>>(counts, counts_new,
+                                                                                        desc->num_seqs * kNumBuckets);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}

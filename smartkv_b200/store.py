@@ -13,6 +13,7 @@ the clone-everything read path (``retrieve_all_quantized``, cache.py:1441-1491).
 from __future__ import annotations
 
 import ctypes
+import math
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -94,7 +95,15 @@ class PackedKVStore:
             self.touched = torch.zeros((num_layers, num_seqs, self.slots), dtype=torch.uint8, device=dev)
             self.head_state = torch.ones((num_seqs, 2, num_q_heads), dtype=torch.float32, device=dev)
         else:
-            self.logits = self.cumulative = self.layer_ema = self.touched = self.head_state = None
+            self.logits = self.head_state = None
+            self.cumulative = torch.zeros((num_seqs, self.slots), dtype=torch.float64, device=dev)
+            self.layer_ema = torch.zeros((num_layers, num_seqs, self.slots), dtype=torch.float32, device=dev)
+            self.touched = torch.zeros((num_layers, num_seqs, self.slots), dtype=torch.uint8, device=dev)
+        # hysteresis record of the allocator (smartkv/core/cache.py:423-450), storage order; streak -1 = none
+        self.rank_pct = torch.zeros((num_seqs, self.slots), dtype=torch.float64, device=dev)
+        self.rank_streak = torch.full((num_seqs, self.slots), -1, dtype=torch.int8, device=dev)
+        self.appended_total = 0  # rows ever appended over all sequences (host-side upper bound of live tokens)
+        self._realloc = None
         self.head_parity = 0
         self._bits_lut = torch.full((9,), -1, dtype=torch.int32, device=dev)
         for bits, b in BITS_TO_BUCKET.items():
@@ -146,6 +155,7 @@ class PackedKVStore:
         self.counts.copy_(new_counts)
         self._plan_valid = False
         self.next_token += n
+        self.appended_total += B * n
         dst_seq = self._seq_ids[:, None].expand(B, n).contiguous().view(-1)
         return dst_seq, bucket.contiguous().view(-1), pos.contiguous().view(-1), storage
 
@@ -165,6 +175,7 @@ class PackedKVStore:
         self.slot_token.scatter_(1, storage.long()[:, None], self.next_token[:, None])
         self.counts.scatter_add_(1, bucket.long()[:, None], torch.ones((self.num_seqs, 1), dtype=torch.int32, device=self.device))
         self.next_token += 1
+        self.appended_total += self.num_seqs
         self._plan_valid = False
 
     # ------------------------------------------------------------------ kernels
@@ -234,6 +245,128 @@ class PackedKVStore:
         """Reads the device error flag (synchronises)."""
         val = ctypes.c_int32(0)
         check(self.lib.skv_read_error_flag(ptr(self.err), ctypes.byref(val), self._stream()), "device error flag")
+
+
+    # ------------------------------------------------------------------ reallocation
+    def make_alloc_config(self, memory_budget: float, available_bits: Sequence[int] = (2, 3, 4, 8),
+                          total_kv_heads: Optional[int] = None, utility_alpha: float = 0.5,
+                          importance_floor: float = 1e-6, hysteresis_rank_threshold: float = 0.05,
+                          hysteresis_intervals: int = 2, high_precision_fraction: float = 0.02,
+                          high_precision_boost: float = 1.5, min_high_precision_tokens: int = 0,
+                          protected: Sequence[int] = (0, 1, 2), critical_window: int = 4,
+                          scale_bits: int = 32) -> "_lib.AllocConfig":
+        """Allocator parameters with the clamping of SmartKVCache.__init__
+        (smartkv/core/cache.py:131-141).  ``total_kv_heads``: KV heads of the whole
+        model when this store holds a shard of them (accounting only)."""
+        c = _lib.AllocConfig()
+        c.num_heads = int(total_kv_heads or self.num_kv_heads)
+        c.head_dim = self.head_dim
+        bits = sorted(int(b) for b in available_bits)
+        c.num_bits = len(bits)
+        alpha = float(utility_alpha) if utility_alpha > 0 else 1.0
+        alpha = min(max(alpha, 0.1), 1.0)
+        for i, b in enumerate(bits):
+            c.bits[i] = b
+            c.util[i] = float(b) if alpha == 1.0 else float(math.pow(b, alpha))
+        c.memory_budget = float(memory_budget)
+        c.importance_floor = float(max(importance_floor, 0.0))
+        c.rank_threshold = float(max(hysteresis_rank_threshold, 0.0))
+        c.hysteresis_intervals = max(int(hysteresis_intervals), 1)
+        c.high_fraction = float(max(0.0, min(high_precision_fraction, 0.5)))
+        c.high_boost = float(max(1.0, high_precision_boost))
+        c.min_high_tokens = int(max(0, min_high_precision_tokens))
+        c.scale_bits = int(scale_bits)
+        c.use_packing = 1
+        c.critical_window = int(critical_window)
+        prot = sorted(set(int(t) for t in protected))
+        if len(prot) > _lib.ALLOC_MAX_PROTECTED:
+            raise ValueError(f"at most {_lib.ALLOC_MAX_PROTECTED} protected token ids")
+        c.num_protected = len(prot)
+        for i, t in enumerate(prot):
+            c.protected_ids[i] = t
+        return c
+
+    def _realloc_buffers(self):
+        if getattr(self, "_realloc", None) is not None:
+            return self._realloc
+        dev, B, T = self.device, self.num_seqs, self.slots
+        d = ctypes.byref(self.desc)
+        r = {
+            "alloc_ws": torch.empty(int(self.lib.skv_alloc_workspace_bytes(d)), dtype=torch.uint8, device=dev),
+            "plan_ws": torch.empty(int(self.lib.skv_repack_plan_workspace_bytes(d)), dtype=torch.uint8, device=dev),
+            "new_bits": torch.zeros((B, T), dtype=torch.uint8, device=dev),
+            "new_counts": torch.zeros((B, NUM_BUCKETS), dtype=torch.int32, device=dev),
+            "counts_new": torch.zeros((B, NUM_BUCKETS), dtype=torch.int32, device=dev),
+            "changed": torch.zeros(B, dtype=torch.int32, device=dev),
+            "move_src": torch.zeros((B, T), dtype=torch.int32, device=dev),
+            "move_dst": torch.zeros((B, T), dtype=torch.int32, device=dev),
+            "n_moves": torch.zeros(B, dtype=torch.int32, device=dev),
+            "staging": None,
+            "meta_staging": None,
+        }
+        self._realloc = r
+        return r
+
+    def allocate_bits(self, cfg, scores: Optional[torch.Tensor] = None, recency: Optional[torch.Tensor] = None):
+        """Runs the allocator on every sequence (skv_alloc_bits).  ``scores``: fp64 [B, slots] in
+        storage order, default the cumulative importance.  Returns (new_bits uint8 [B, slots],
+        new_counts int32 [B, 4], changed int32 [B]) -- device tensors owned by the store."""
+        r = self._realloc_buffers()
+        scores = self.cumulative if scores is None else scores
+        check(self.lib.skv_alloc_bits(ctypes.byref(self.desc), ctypes.byref(cfg), ptr(self.counts), ptr(self.slot_token),
+                                      ptr(scores), ptr(recency), ptr(self.rank_pct), ptr(self.rank_streak),
+                                      ptr(r["new_bits"]), ptr(r["new_counts"]), ptr(r["changed"]), ptr(r["alloc_ws"]),
+                                      self._stream()), "skv_alloc_bits")
+        return r["new_bits"], r["new_counts"], r["changed"]
+
+    def repack(self, new_bits: torch.Tensor, max_moves: Optional[int] = None, staging_budget: int = 1 << 30):
+        """Moves every token to the bucket of its new width (requantising from the stored codes)
+        in all layers and permutes the per-token arrays accordingly.  ``max_moves``: upper bound of
+        the rows that can move over all sequences (default: every token ever appended)."""
+        r = self._realloc_buffers()
+        d = ctypes.byref(self.desc)
+        st = self._stream()
+        check(self.lib.skv_repack_plan(d, ptr(self.counts), ptr(new_bits), ptr(r["move_src"]), ptr(r["move_dst"]),
+                                       ptr(r["n_moves"]), ptr(r["counts_new"]), ptr(r["plan_ws"]), ptr(self.err), st),
+              "skv_repack_plan")
+        if max_moves is None:
+            max_moves = self.appended_total
+        max_moves = max(int(max_moves), 1)
+        per_layer = int(self.lib.skv_requant_staging_bytes(d, max_moves, 1))
+        chunk = max(1, min(self.num_layers, staging_budget // max(per_layer, 1)))
+        need = per_layer * chunk
+        if r["staging"] is None or r["staging"].numel() < need:
+            r["staging"] = torch.empty(need, dtype=torch.uint8, device=self.device)
+        mneed = int(self.lib.skv_repack_meta_staging_bytes(d, max_moves + 8))
+        if r["meta_staging"] is None or r["meta_staging"].numel() < mneed:
+            r["meta_staging"] = torch.empty(mneed, dtype=torch.uint8, device=self.device)
+        for l0 in range(0, self.num_layers, chunk):
+            l1 = min(self.num_layers, l0 + chunk)
+            check(self.lib.skv_requant_repack(d, ptr(self.arena), l0, l1, ptr(r["move_src"]), ptr(r["move_dst"]),
+                                              ptr(r["n_moves"]), ptr(r["staging"]), r["staging"].numel(), ptr(self.err),
+                                              st), "skv_requant_repack")
+        check(self.lib.skv_repack_meta(d, ptr(r["move_src"]), ptr(r["move_dst"]), ptr(r["n_moves"]), ptr(self.counts),
+                                       ptr(r["counts_new"]), ptr(self.slot_token), ptr(self.cumulative),
+                                       ptr(self.rank_pct), ptr(self.rank_streak), ptr(self.layer_ema), ptr(self.touched),
+                                       ptr(r["meta_staging"]), r["meta_staging"].numel(), ptr(self.err), st),
+              "skv_repack_meta")
+        self._plan_valid = False
+
+    def reallocate(self, cfg, max_moves: Optional[int] = None):
+        """allocate_bits + repack: one reallocation of the whole store."""
+        new_bits, _, _ = self.allocate_bits(cfg)
+        self.repack(new_bits, max_moves=max_moves)
+
+    def token_bits(self, seq: int) -> torch.Tensor:
+        """Width of every token of one sequence, indexed by token id (syncs; tests and the API mirror)."""
+        counts = self.counts[seq].tolist()
+        n = sum(counts)
+        out = torch.zeros(max(int(self.next_token[seq]), n), dtype=torch.uint8, device=self.device)
+        for i, c in enumerate(counts):
+            if c:
+                ids = self.slot_token[seq, self.bucket_base[i]: self.bucket_base[i] + c].long()
+                out[ids] = BUCKET_BITS[i]
+        return out
 
     # ------------------------------------------------------------------ read back (tests, API mirror)
     def export_sequence(self, layer: int, seq: int):
