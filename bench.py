@@ -6,9 +6,11 @@ One *step* = one decode step of the Llama-3.1-8B attention shape (32 query heads
 8 KV heads, head_dim 128, fp16 query) over 32 layers, batch 16, KV context 8192:
 per layer the fused packed decode attention (+ current fp token, LSE combine),
 the importance update and the quantize-pack append of the new token.  K/V are
-seeded synthetic N(0,1) with 4 outlier channels per head scaled x8, bit-widths come
-from a Zipf(1.1) importance under memory_budget 0.35 (stand-ins for the reference's
-benchmark inputs, which are synthetic randn as well).
+seeded synthetic N(0,1) with 4 outlier channels per head scaled x8; tokens are stored at
+the default 4 bits, a Zipf(1.1) importance is injected and the device allocator +
+requantise/repack bring the cache to memory_budget 0.35 (stand-ins for the reference's
+benchmark inputs, which are synthetic randn as well).  Every 16th step of the timed
+region ends with a full reallocation (allocator, repack of all layers).
 
 metric  = packed-KV bytes streamed per second (algorithmic bytes: sum over buckets of
           n_b * Hkv * 2 * (row_bytes + 4) per sequence and layer) over the whole step.
@@ -24,7 +26,6 @@ import json
 import os
 import subprocess
 import sys
-import tempfile
 import threading
 import time
 
@@ -60,80 +61,67 @@ def zipf_importance(n, seed, s):
     return (imp / imp.sum()).astype(np.float32)
 
 
-def budget_bits(imp, cfg):
-    """Bit-width per token for the benchmark's initial cache state: greedy marginal-gain fill
-    of the byte budget in importance order (utility bits^0.5, steps 2->3->4->8), first four
-    tokens at 8 bits.  Host-side setup only."""
-    n = imp.size
-    H, D = cfg["num_kv_heads"], cfg["head_dim"]
-    bits_asc = sorted(cfg["available_bits"])
-    elements = 2 * H * D
-    budget_units = (cfg["memory_budget"] * n * elements * 16 - n * 2 * H * 32) / elements  # payload bits / elements
-    bits = np.full(n, bits_asc[0], np.int64)
-    bits[:4] = bits_asc[-1]
-    used = float(bits.sum())
-    items = []
-    for j in range(len(bits_asc) - 1):
-        cur, nxt = bits_asc[j], bits_asc[j + 1]
-        gain = (nxt ** 0.5 - cur ** 0.5) / (nxt - cur)
-        for t in range(4, n):
-            items.append((-float(imp[t]) * gain, t, cur, nxt))
-    items.sort()
-    for _neg, t, cur, nxt in items:
-        if bits[t] != cur:
-            continue
-        if used + (nxt - cur) > budget_units:
-            continue
-        bits[t] = nxt
-        used += nxt - cur
-    return bits
-
-
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason sampler running beside the timed region."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Reads SM clock and throttle reasons through NVML (read-only) every ~2 ms in a thread beside
+    the timed region; falls back to one nvidia-smi query if NVML is not importable."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
-        self.proc = None
-        self.path = None
+        self.samples = []
+        self.mask = 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def _loop(self):
+        nv, h = self._nvml, self._handle
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            import pynvml as nv
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.gpu
+            if visible:
+                ids = [v for v in visible.split(",") if v.strip()]
+                if self.gpu < len(ids) and ids[self.gpu].strip().isdigit():
+                    idx = int(ids[self.gpu])
+            self._handle = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(self._handle, nv.NVML_CLOCK_SM))
+            self._nvml = nv
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
         except Exception:
-            self.proc = None
+            self._nvml = None
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
+        if self._nvml is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            if self.samples:
+                out["sm_mhz"] = float(np.median(self.samples))
+                out["sm_max_mhz"] = self.max_mhz
+                out["samples"] = len(self.samples)
+                out["reasons"] = [nm for nm, bit in self.REASONS if self.mask & bit]
             return out
         try:
-            self.proc.terminate()
-            self.proc.wait(timeout=5)
-            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
-            sm = [float(r[1]) for r in rows if len(r) >= 9]
-            if sm:
-                out["sm_mhz"] = float(np.median(sm))
-                out["sm_max_mhz"] = float(rows[0][2])
-                out["samples"] = len(sm)
-                names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-                for i, nm in enumerate(names):
-                    if any(r[5 + i].strip().lower().startswith("active") for r in rows if len(r) >= 9):
-                        out["reasons"].append(nm)
+            q = "clocks.sm,clocks.max.sm,clocks_event_reasons.active"
+            r = subprocess.run(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                               capture_output=True, text=True, timeout=10).stdout.strip().split(",")
+            out.update(sm_mhz=float(r[0]), sm_max_mhz=float(r[1]), samples=1)
         except Exception:
             pass
-        finally:
-            try:
-                os.unlink(self.path)
-            except Exception:
-                pass
         return out
 
 
@@ -147,8 +135,11 @@ def algorithmic_bytes_per_layer(counts, cfg):
 # ----------------------------------------------------------------------------- our arm
 def run_ours(args):
     import torch
+    import ctypes
+
     import torch.distributed as dist
 
+    from smartkv_b200.sharding import ImportanceSync
     from smartkv_b200.store import PackedKVStore, bucket_capacities
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -167,9 +158,10 @@ def run_ours(args):
     caps = bucket_capacities(N + total_steps, cfg["memory_budget"], D, cfg["available_bits"])
     store = PackedKVStore(L, B, Hkv, D, Hq, caps, device=dev)
 
-    # ---- populate the cache: seeded synthetic K/V, widths from the Zipf importance ----------
-    bits_np = np.stack([budget_bits(zipf_importance(N, 1000 * rank + b, cfg["zipf_s"]), cfg) for b in range(B)])
-    dst = store.plan_bulk(torch.from_numpy(bits_np).to(dev))
+    # ---- populate the cache: seeded synthetic K/V stored at the default 4 bits (cache.py:1214), the
+    # Zipf importance injected the way the reference's kernel benchmark does, then one reallocation
+    bits0 = torch.full((B, N), 4, dtype=torch.int64, device=dev)
+    dst = store.plan_bulk(bits0)
     gen = torch.Generator(device=dev)
     chan = torch.Generator(device="cpu").manual_seed(1234)
     out_k = torch.stack([torch.randperm(D, generator=chan)[:4] for _ in range(Hkv)]).to(dev)
@@ -183,9 +175,25 @@ def run_ours(args):
         v[:, hidx, out_v] *= 8.0
         store.append(layer, k, v, dst[0], dst[1], dst[2])
         del k, v
+    imp = np.stack([zipf_importance(N, b, cfg["zipf_s"]) for b in range(B)])   # the same sequences on every rank
+    store.cumulative.zero_()
+    store.cumulative.scatter_(1, dst[3].view(B, N).long(), torch.from_numpy(imp.astype(np.float64)).to(dev))
+    alloc_cfg = store.make_alloc_config(cfg["memory_budget"], cfg["available_bits"], total_kv_heads=Hkv * world)
+    importance_sync = ImportanceSync(store, dist if world > 1 else None)
+
+    def reallocate():
+        importance_sync()              # KV-head shards: sum the per-shard importance first (no-op on 1 GPU)
+        store.reallocate(alloc_cfg)
+        importance_sync.after_repack()
+
+    reallocate()
     torch.cuda.synchronize()
+    store.check_errors()
     counts0 = store.counts.cpu().numpy()
     hist = counts0.sum(0).tolist()
+    realloc_chunks = -(-L // max(1, min(L, (1 << 30) // max(1, int(store.lib.skv_requant_staging_bytes(
+        ctypes.byref(store.desc), store.appended_total, 1))))))
+    realloc_launches = 15 + (3 if B > 1 else 0) + 2 * realloc_chunks
 
     # ---- per-step inputs (resident) -----------------------------------------------------------
     gen.manual_seed(rank + 99)
@@ -238,7 +246,7 @@ def run_ours(args):
             graph.replay()
         else:
             decode_step(q_stage, k_stage, v_stage)
-        launches[0] += 4 * L
+        launches[0] += 4 * L + 1
 
     def resident_step(i):
         j = i % n_in
@@ -262,7 +270,10 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, n_warm, n_steps, first):
+    realloc_every = cfg["realloc_every"]
+    realloc_events = []
+
+    def timed(fn, n_warm, n_steps, first, with_realloc=True):
         for i in range(n_warm):
             fn(first + i)
         barrier()
@@ -276,6 +287,13 @@ def run_ours(args):
         e0.record()
         for i in range(n_steps):
             fn(first + n_warm + i)
+            if with_realloc and (i + 1) % realloc_every == 0:
+                ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                ev[0].record()
+                reallocate()
+                ev[1].record()
+                realloc_events.append(ev)
+                launches[0] += realloc_launches
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -296,11 +314,12 @@ def run_ours(args):
     launches[0] = 0
     ms, step_bytes, clocks = timed(resident_step, warmup, steps, 0)
     store.check_errors()
-    n_launch = launches[0] - warmup * L * 4
+    n_launch = launches[0] - warmup * (L * 4 + 1)
+    realloc_ms = [a.elapsed_time(b) for a, b in realloc_events]
     # kernel-only time of the attention kernel: the same steps launched un-graphed with a CUDA
     # event pair around every attention launch
     attn_events.clear()
-    ms_k, step_bytes_k, _ = timed(kernel_timing_step, 1, steps, 0)
+    ms_k, step_bytes_k, _ = timed(kernel_timing_step, 1, min(steps, 8), 0, with_realloc=False)
     timed_events = attn_events[L:]
     attn_ms = float(np.mean([a.elapsed_time(b) for a, b in timed_events]))
     per_layer_bytes = step_bytes_k / L / world
@@ -321,7 +340,8 @@ def run_ours(args):
         "config": {"workload": f"BASELINE config 1: Llama-3.1-8B attention shape, {L} layers, batch 16, context 8192, "
                                "budget 0.35, bits [2,3,4,8], fp16 query; one decode step per step",
                    "kv_heads_per_gpu": Hkv, "l2": "inputs larger than L2 (packed cache per step >> 126 MB)",
-                   "bucket_histogram_2_3_4_8": hist, "reallocation": "not in the timed region yet",
+                   "bucket_histogram_2_3_4_8": hist, "reallocation": f"device allocator + requantise/repack of all layers after every {realloc_every}th "
+                                   f"step, inside the timed region ({len(realloc_ms)} in {steps} steps)",
                    "packed_bytes_per_step": int(step_bytes)},
         "decode_tokens_per_s": round(B * world * steps / (ms * 1e-3), 1),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
@@ -331,6 +351,7 @@ def run_ours(args):
                      "algorithmic_bytes_per_launch": int(per_layer_bytes)},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / steps, 4)},
+        "reallocation_ms": round(float(np.mean(realloc_ms)), 3) if realloc_ms else None,
         "gpu_launches": int(n_launch), "cuda_graph": graph is not None,
         "clocks": clocks,
     }
@@ -344,9 +365,11 @@ def run_ours(args):
 
 # ----------------------------------------------------------------------------- CPU baseline
 def cpu_baseline(cfg, budget_s=15.0):
-    """The oracle port of the reference CPU path (streaming attention over int8 codes with the
-    reference's GQA expansion, importance update) timed on this host for one (sequence, layer)
-    at the full context; GB/s counts the same algorithmic packed bytes."""
+    """The oracle port of the reference CPU path timed on this host: for one (sequence, layer) at the
+    full context the streaming attention over int8 codes with the reference's GQA expansion, the
+    importance update and the append-quantize; plus, once, the allocator for one sequence and the
+    requantisation of its changed tokens in one layer.  The step time is scaled to batch x layers
+    (reallocation amortised over realloc_every steps); GB/s counts the same algorithmic packed bytes."""
     from oracle import smartkv_oracle as orc
     try:
         from threadpoolctl import threadpool_info
@@ -356,13 +379,24 @@ def cpu_baseline(cfg, budget_s=15.0):
     Hq, Hkv, D, N = cfg["num_q_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["context"]
     g = Hq // Hkv
     k, v = orc.synth_kv(N, Hkv, D, seed=0)
-    bits = budget_bits(zipf_importance(N, 0, cfg["zipf_s"]), cfg)
-    kq = np.empty(k.shape, np.int8); vq = np.empty(v.shape, np.int8)
-    ks = np.empty(k.shape[:2], np.float32); vs = np.empty(k.shape[:2], np.float32)
-    for w in (2, 3, 4, 8):
+    imp0 = zipf_importance(N, 0, cfg["zipf_s"])
+    acfg = orc.AllocatorConfig(Hkv, D, cfg["memory_budget"], cfg["available_bits"])
+    scores = {t: (float("inf") if t < 4 else float(imp0[t])) for t in range(N)}
+    t0 = time.perf_counter()
+    alloc = orc.solve_allocation(acfg, range(N), scores, {})
+    alloc_s = time.perf_counter() - t0
+    bits = np.array([alloc[t] for t in range(N)], np.int64)
+    # stored at 4 bits, then requantised from the stored codes to the allocated widths (one layer)
+    k4, ks4 = orc.quantize_rows(k, 4)
+    v4, vs4 = orc.quantize_rows(v, 4)
+    kq, vq, ks, vs = k4.copy(), v4.copy(), ks4.copy(), vs4.copy()
+    t0 = time.perf_counter()
+    for w in (2, 3, 8):
         sel = bits == w
-        kq[sel], ks[sel] = orc.quantize_rows(k[sel], w)
-        vq[sel], vs[sel] = orc.quantize_rows(v[sel], w)
+        if sel.any():
+            kq[sel], ks[sel] = orc.requantize_rows(k4[sel], ks4[sel], w)
+            vq[sel], vs[sel] = orc.requantize_rows(v4[sel], vs4[sel], w)
+    requant_s = time.perf_counter() - t0
     rng = np.random.default_rng(0)
     q = rng.standard_normal((1, Hq, 1, D)).astype(np.float32)
     ck = rng.standard_normal((1, Hkv, D)).astype(np.float32)
@@ -387,10 +421,14 @@ def cpu_baseline(cfg, budget_s=15.0):
         if time.perf_counter() - t0 > budget_s or it >= 200:
             break
     dt = (time.perf_counter() - t0) / it
-    return {"value": round(nbytes / dt / 1e9, 4), "unit": "GB/s", "cores": int(threads), "kind": "port",
+    B, L, every = cfg["batch"], cfg["num_layers"], cfg["realloc_every"]
+    step_s = dt * B * L + (alloc_s * B + requant_s * B * L) / every
+    return {"value": round(nbytes * B * L / step_s / 1e9, 4), "unit": "GB/s", "cores": int(threads), "kind": "port",
             "sample": f"1 sequence x 1 layer at context {N} (attention + importance + append-quantize), {it} iterations, "
-                      f"{dt * 1e3:.1f} ms each; the full step is batch {cfg['batch']} x {cfg['num_layers']} layers of this",
-            "ms_per_sequence_layer": round(dt * 1e3, 3)}
+                      f"{dt * 1e3:.1f} ms each; allocator for one sequence {alloc_s * 1e3:.0f} ms and requantisation of "
+                      f"one (sequence, layer) {requant_s * 1e3:.0f} ms, once; step time scaled to batch {B} x {L} "
+                      f"layers with the reallocation amortised over {every} steps",
+            "ms_per_sequence_layer": round(dt * 1e3, 3), "ms_per_step": round(step_s * 1e3, 1)}
 
 
 def run_reference(args):
@@ -407,7 +445,7 @@ def run_reference(args):
         if i >= args.warmup:
             vals.append(base["value"])
     value = float(np.mean(vals))
-    step_ms = base["ms_per_sequence_layer"] * cfg["batch"] * cfg["num_layers"]
+    step_ms = base["ms_per_step"]
     base["value"] = round(value, 4)
     line = {
         "impl": "reference", "metric": "packed_kv_decode_attention_throughput", "value": round(value, 4),
@@ -426,7 +464,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
