@@ -111,6 +111,13 @@ int skv_export_rows(const SkvStoreDesc* desc, const void* store, int layer, int 
                     const int32_t* src_bucket, const int32_t* src_pos, int8_t* k_codes, int8_t* v_codes,
                     float* k_scale, float* v_scale, void* stream);
 
+/* The inverse of skv_export_rows: writes already quantised rows (int8 codes + fp32 scales, the form
+ * the reference's cache hands to its kernels, smartkv/core/cache.py:1441-1491) into the store,
+ * packing them at the width of the destination bucket.  Codes outside that width's range are clamped. */
+int skv_import_rows(const SkvStoreDesc* desc, void* store, int layer, int rows, const int32_t* dst_seq,
+                    const int32_t* dst_bucket, const int32_t* dst_pos, const int8_t* k_codes, const int8_t* v_codes,
+                    const float* k_scale, const float* v_scale, int32_t* err_flag, void* stream);
+
 /* ---- fused packed decode attention --------------------------------------- */
 
 /* Size queries (host only). */
@@ -200,7 +207,7 @@ int skv_importance_update(const SkvStoreDesc* desc, int layer, const int32_t* co
 typedef struct SkvAllocConfig {
   int32_t num_heads;            /* KV heads of the whole model (accounting only) */
   int32_t head_dim;
-  int32_t num_bits;             /* 2..4 widths */
+  int32_t num_bits;             /* 1..4 widths */
   int32_t bits[4];              /* ascending, each in {2,3,4,8} */
   double util[4];               /* bits[i] ** utility_alpha, computed by the host (its libm is the reference's) */
   double memory_budget;

@@ -62,6 +62,8 @@ _SIGNATURES = {
                                          c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_export_rows": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "skv_import_rows": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_attn_num_ctas": (c_int, [c_int]),
     "skv_attn_partials_bytes": (c_int64, [POINTER(StoreDesc), c_int, c_int]),
     "skv_attn_plan_bytes": (c_int64, [POINTER(StoreDesc), c_int]),

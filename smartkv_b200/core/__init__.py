@@ -1,0 +1,2 @@
+"""Mirror of ``smartkv.core``: the cache and the quantiser entry points, over the B200 library."""
+from .cache import SmartKVCache  # noqa: F401

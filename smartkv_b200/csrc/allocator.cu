@@ -628,7 +628,7 @@ extern "C" int skv_alloc_bits(const SkvStoreDesc* desc, const SkvAllocConfig* cf
   if (!desc || !cfg || !counts || !slot_token || !scores || !rank_pct || !rank_streak || !new_bits || !new_counts ||
       !changed || !workspace)
     return SKV_ERR_INVALID;
-  if (cfg->num_bits < 2 || cfg->num_bits > 4 || cfg->num_protected < 0 || cfg->num_protected > SKV_ALLOC_MAX_PROTECTED)
+  if (cfg->num_bits < 1 || cfg->num_bits > 4 || cfg->num_protected < 0 || cfg->num_protected > SKV_ALLOC_MAX_PROTECTED)
     return SKV_ERR_INVALID;
   if (!cfg->use_packing) return SKV_ERR_UNSUPPORTED;  // the store is always packed
   if (desc->num_seqs > 1024) return SKV_ERR_UNSUPPORTED;

@@ -163,6 +163,43 @@ __global__ void export_rows_kernel(StoreGeom g, const uint8_t* store, int layer,
   }
 }
 
+// ---- import rows: int8 codes + scales -> packed rows of the store -----------------------
+template <int EPL>
+__global__ void import_rows_kernel(StoreGeom g, uint8_t* store, int layer, int rows, const int32_t* dst_seq,
+                                   const int32_t* dst_bucket, const int32_t* dst_pos, const int8_t* k_codes,
+                                   const int8_t* v_codes, const float* k_scale, const float* v_scale, int32_t* err) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)rows * g.num_kv_heads * 2;
+  if (warp >= total) return;
+  const int which = (int)(warp & 1);
+  const long long rh = warp >> 1;
+  const int h = (int)(rh % g.num_kv_heads);
+  const int r = (int)(rh / g.num_kv_heads);
+  const int seq = dst_seq[r], bucket = dst_bucket[r], pos = dst_pos[r];
+  if (seq < 0 || seq >= g.num_seqs || bucket < 0 || bucket >= kNumBuckets || pos < 0 || pos >= g.cap[bucket]) {
+    if (lane == 0 && err) atomicExch(err, 2);
+    return;
+  }
+  const int bits = bucket_bits(bucket);
+  const int8_t* in = (which ? v_codes : k_codes) + rh * g.head_dim + lane * EPL;
+  const int lo = -(1 << (bits - 1)), hi = (1 << (bits - 1)) - 1;
+  int code[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int c = in[i];
+    code[i] = c < lo ? lo : (c > hi ? hi : c);  // codes outside the width's range are clamped
+  }
+  uint8_t* arena = arena_ptr(g, store, layer, seq);
+  const long long row_index = (long long)h * g.cap[bucket] + pos;
+  uint8_t* dst = arena + (which ? g.v_off[bucket] : g.k_off[bucket]) + row_index * g.row_bytes[bucket];
+  pack_store_row<EPL>(code, bits, dst, lane);
+  if (lane == 0) {
+    float* sc = reinterpret_cast<float*>(arena + g.sc_off[bucket]);
+    sc[2 * row_index + which] = (which ? v_scale : k_scale)[rh];
+  }
+}
+
 }  // namespace skv
 
 using namespace skv;
@@ -240,5 +277,29 @@ extern "C" int skv_export_rows(const SkvStoreDesc* desc, const void* store, int 
   export_rows_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, as_stream(stream)>>>(
       g, static_cast<const uint8_t*>(store), layer, rows, src_seq, src_bucket, src_pos, k_codes, v_codes, k_scale,
       v_scale);
+  return launch_status();
+}
+
+extern "C" int skv_import_rows(const SkvStoreDesc* desc, void* store, int layer, int rows, const int32_t* dst_seq,
+                               const int32_t* dst_bucket, const int32_t* dst_pos, const int8_t* k_codes,
+                               const int8_t* v_codes, const float* k_scale, const float* v_scale, int32_t* err_flag,
+                               void* stream) {
+  if (!desc || !store || !dst_seq || !dst_bucket || !dst_pos || !k_codes || !v_codes || !k_scale || !v_scale)
+    return SKV_ERR_INVALID;
+  if (layer < 0 || layer >= desc->num_layers || rows < 0) return SKV_ERR_INVALID;
+  if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
+  if (rows == 0) return SKV_OK;
+  const StoreGeom g = make_geom(*desc);
+  const int wpb = 8;
+  const long long warps = (long long)rows * g.num_kv_heads * 2;
+  const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
+  if (desc->head_dim == 128)
+    import_rows_kernel<4><<<grid, wpb * 32, 0, as_stream(stream)>>>(g, static_cast<uint8_t*>(store), layer, rows, dst_seq,
+                                                                    dst_bucket, dst_pos, k_codes, v_codes, k_scale,
+                                                                    v_scale, err_flag);
+  else
+    import_rows_kernel<2><<<grid, wpb * 32, 0, as_stream(stream)>>>(g, static_cast<uint8_t*>(store), layer, rows, dst_seq,
+                                                                    dst_bucket, dst_pos, k_codes, v_codes, k_scale,
+                                                                    v_scale, err_flag);
   return launch_status();
 }
