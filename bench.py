@@ -214,17 +214,17 @@ def run_ours(args):
     launches = [0]
 
     def decode_step(q, k, v, record=False):
-        """One decode step: 4 kernels of this library per layer (attention, combine, importance,
-        append) plus the torch index ops that place / commit the new token."""
+        """One decode step: 2 kernels of this library per layer (attention; combine + append + the
+        previous layer's importance update), the plan kernel, the last layer's importance update, and
+        the torch index ops that place / commit the new token."""
         plan = store.plan_step()
         for layer in range(L):
             ev = None
             if record:
                 ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                 attn_events.append(ev)
-            store.attention(layer, q[layer], k[layer], v[layer], update_importance=True, cur_storage=plan[3],
-                            out=out_dev[layer], kernel_events=ev)
-            store.append(layer, k[layer], v[layer], plan[0], plan[1], plan[2])
+            store.decode_layer(layer, q[layer], k[layer], v[layer], plan, update_importance=True, out=out_dev[layer],
+                               kernel_events=ev)
         store.commit_step(plan)
 
     graph = None
@@ -246,7 +246,7 @@ def run_ours(args):
             graph.replay()
         else:
             decode_step(q_stage, k_stage, v_stage)
-        launches[0] += 4 * L + 1
+        launches[0] += 2 * L + 2
 
     def resident_step(i):
         j = i % n_in
@@ -314,7 +314,7 @@ def run_ours(args):
     launches[0] = 0
     ms, step_bytes, clocks = timed(resident_step, warmup, steps, 0)
     store.check_errors()
-    n_launch = launches[0] - warmup * (L * 4 + 1)
+    n_launch = launches[0] - warmup * (L * 2 + 2)
     realloc_ms = [a.elapsed_time(b) for a, b in realloc_events]
     # kernel-only time of the attention kernel: the same steps launched un-graphed with a CUDA
     # event pair around every attention launch

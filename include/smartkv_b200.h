@@ -124,6 +124,9 @@ int skv_import_rows(const SkvStoreDesc* desc, void* store, int layer, int rows, 
 int skv_attn_num_ctas(int device);                       /* persistent CTAs the kernel launches */
 int64_t skv_attn_partials_bytes(const SkvStoreDesc* desc, int num_q_heads, int num_ctas);
 int64_t skv_attn_plan_bytes(const SkvStoreDesc* desc, int num_ctas);
+/* Partials every run writes (one per consumer warp of the attention launch for that query dtype);
+ * skv_lse_combine folds runs * this many partials per (sequence, KV head). */
+int skv_attn_partials_per_run(const SkvStoreDesc* desc, int query_dtype);
 
 /* Builds the work partition of one decode step: which 16-key tiles of which
  * (sequence, KV head) every persistent CTA streams, balanced by packed bytes.  It
@@ -181,6 +184,28 @@ int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* quer
 int skv_decode_attention_static(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
                                 const void* query, int query_dtype, int num_q_heads, int num_ctas, float* logits,
                                 int32_t* err_flag, void** partials_out, void* stream);
+
+/* ---- everything between two attention kernels in one launch -------------------------------- */
+
+/* skv_lse_combine and the skv_quantize_pack_append of the step's new token (one row per sequence:
+ * cur_k / cur_v, the same tensors the combine step attends to) for `layer`, together with the
+ * skv_importance_update of an EARLIER attention launch, as ONE kernel launch; the three are
+ * independent, so their blocks run side by side.  Same results as the separate calls.
+ *   imp_layer / imp_logits / imp_lse_max / imp_lse_sum / imp_cur_prob: the inputs of the importance
+ *   update, i.e. the logits an earlier skv_decode_attention wrote and the (max, sum, current-token
+ *   probability) an earlier combine wrote for layer imp_layer.  They must not alias this launch's
+ *   lse_max / lse_sum / cur_prob outputs (callers double-buffer them).  imp_logits == NULL skips the
+ *   importance update; dst_seq == NULL skips the append (store may then be NULL).
+ * No counterpart in the reference, which runs these steps as host Python
+ * (smartkv/core/fused_cpu.py:115-167, cache.py:216-279, :1187-1355). */
+int skv_post_attention(const SkvStoreDesc* desc, void* store, int layer, const void* plan, const void* query,
+                       int query_dtype, int num_q_heads, const void* partials, int num_ctas, const void* cur_k,
+                       const void* cur_v, int kv_dtype, float* out, float* lse_max, float* lse_sum, float* cur_prob,
+                       const int32_t* counts, int imp_layer, const float* imp_logits, const float* imp_lse_max,
+                       const float* imp_lse_sum, const float* imp_cur_prob, const int32_t* cur_slot,
+                       float* head_state, int parity, double* cumulative, float* layer_ema, uint8_t* touched,
+                       float decay, float head_decay, const int32_t* dst_seq, const int32_t* dst_bucket,
+                       const int32_t* dst_pos, int32_t* err_flag, void* stream);
 
 /* ---- importance ----------------------------------------------------------- */
 

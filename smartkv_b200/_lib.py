@@ -67,6 +67,12 @@ _SIGNATURES = {
     "skv_attn_num_ctas": (c_int, [c_int]),
     "skv_attn_partials_bytes": (c_int64, [POINTER(StoreDesc), c_int, c_int]),
     "skv_attn_plan_bytes": (c_int64, [POINTER(StoreDesc), c_int]),
+    "skv_attn_partials_per_run": (c_int, [POINTER(StoreDesc), c_int]),
+    "skv_post_attention": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                   c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p]),
     "skv_attn_plan": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p]),
     "skv_decode_attention": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p]),

@@ -24,6 +24,7 @@
 
 #include "attn_frag.cuh"
 #include "attn_sched.cuh"
+#include "post_attention.cuh"
 
 namespace skv {
 
@@ -79,13 +80,6 @@ __device__ __forceinline__ unsigned long long gtimer() {
 #define SKV_TL(slot) do { } while (0)
 #endif
 
-__host__ __device__ inline int partial_stride(int group, int head_dim) { return group * (head_dim + 2); }
-
-__device__ __forceinline__ float ex2f(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return h2_bits(h);
@@ -609,111 +603,9 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
 }
 
 // ---- combine ----------------------------------------------------------------------
-struct CombineParams {
-  StoreGeom g;
-  const int* plan;
-  const void* query;
-  int q_is_half;
-  int num_q_heads;
-  int group;
-  const float* partials;
-  int per_run;  // partials per run = consumer warps of the attention launch
-  int num_ctas;
-  const void* cur_k;
-  const void* cur_v;
-  int kv_is_half;
-  float* out;
-  float* lse_max;
-  float* lse_sum;
-  float* cur_prob;
-  float scale_log2;
-};
-
-constexpr int kCombineChunk = 256;
-
-// one block of head_dim threads per (sequence, KV head, head of the group)
-__global__ void lse_combine_kernel(const CombineParams p) {
-  const StoreGeom& g = p.g;
-  const int D = g.head_dim, G = p.group, Hkv = g.num_kv_heads;
-  const int seg = blockIdx.x / G, gq = blockIdx.x - seg * G;
-  const int b = seg / Hkv, h = seg - b * Hkv;
-  const int d = threadIdx.x, warp = d >> 5, lane = d & 31, nwarps = D >> 5;
-  __shared__ float s_red[8];
-  const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
-  const int nsplit = pv.seg_count[seg] * p.per_run;
-  const int r0 = nsplit > 0 ? pv.seg_begin[seg] * p.per_run : 0;
-  const int pstride = partial_stride(G, D);
-  const float* base = p.partials + (long long)r0 * pstride + gq * (D + 2);
-  const bool has_cur = p.cur_k != nullptr && p.cur_v != nullptr;
-  const long long hq = (long long)b * p.num_q_heads + h * G + gq;
-  const long long kv = ((long long)b * Hkv + h) * D + d;
-
-  // ---- current-token logit (full precision) and the maximum over all partials -------
-  float dot = 0.f;
-  if (has_cur) {
-    const float q = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[hq * D + d])
-                                : static_cast<const float*>(p.query)[hq * D + d];
-    const float k = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_k)[kv])
-                                 : static_cast<const float*>(p.cur_k)[kv];
-    dot = q * k;
-  }
-  float mloc = -INFINITY;
-  for (int k = d; k < nsplit; k += D) mloc = fmaxf(mloc, base[(long long)k * pstride]);
-  dot = warp_sum(dot);
-  mloc = warp_max(mloc);
-  if (lane == 0) {
-    s_red[warp] = dot;
-    s_red[4 + warp] = mloc;
-  }
-  __syncthreads();
-  float s_cur = 0.f, M = -INFINITY;
-  for (int w = 0; w < nwarps; ++w) {
-    s_cur += s_red[w];
-    M = fmaxf(M, s_red[4 + w]);
-  }
-  s_cur *= p.scale_log2;
-  if (has_cur) M = fmaxf(M, s_cur);
-
-  // ---- fold the partials (fixed order), kCombineChunk at a time -----------------------------
-  // the weights of a chunk go through shared memory so that the row loads below do not depend
-  // on anything loaded in the same loop and can all be in flight together
-  __shared__ float s_f[kCombineChunk];
-  __shared__ float s_lf[kCombineChunk];
-  float acc = 0.f, L = 0.f;
-  for (int c0 = 0; c0 < nsplit; c0 += kCombineChunk) {
-    const int cn = (nsplit - c0) < kCombineChunk ? (nsplit - c0) : kCombineChunk;
-    __syncthreads();
-    for (int k = d; k < cn; k += D) {
-      const float* row = base + (long long)(c0 + k) * pstride;
-      const float mw = row[0];
-      const float f = mw == -INFINITY ? 0.f : ex2f(mw - M);
-      s_f[k] = f;
-      s_lf[k] = f == 0.f ? 0.f : row[1] * f;
-    }
-    __syncthreads();
-    const float* col = base + (long long)c0 * pstride + 2 + d;
-#pragma unroll 8
-    for (int k = 0; k < cn; ++k) {
-      const float f = s_f[k];
-      const float x = col[(long long)k * pstride];  // a partial without keys holds stale bytes: select, not multiply
-      acc += f == 0.f ? 0.f : x * f;
-      L += s_lf[k];
-    }
-  }
-  float pc = 0.f;
-  if (has_cur) {
-    pc = ex2f(s_cur - M);
-    const float v = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_v)[kv])
-                                 : static_cast<const float*>(p.cur_v)[kv];
-    acc = fmaf(pc, v, acc);
-    L += pc;
-  }
-  p.out[hq * D + d] = L > 0.f ? acc / L : 0.f;
-  if (d == 0) {
-    if (p.lse_max) p.lse_max[hq] = M;
-    if (p.lse_sum) p.lse_sum[hq] = L;
-    if (p.cur_prob) p.cur_prob[hq] = (has_cur && L > 0.f) ? pc / L : 0.f;
-  }
+__global__ void __launch_bounds__(kPostThreads) lse_combine_kernel(const CombineParams p) {
+  __shared__ CombineShared sh;
+  combine_unit(p, blockIdx.x, sh);
 }
 
 }  // namespace skv
@@ -739,6 +631,15 @@ extern "C" int64_t skv_attn_partials_bytes(const SkvStoreDesc* desc, int num_q_h
   const int group = num_q_heads / desc->num_kv_heads;
   const int64_t runs = (int64_t)num_ctas + (int64_t)desc->num_seqs * desc->num_kv_heads;
   return runs * kMaxPartialsPerRun * partial_stride(group, desc->head_dim) * (int64_t)sizeof(float);
+}
+
+extern "C" int skv_attn_partials_per_run(const SkvStoreDesc* desc, int query_dtype) {
+  if (!desc) return SKV_ERR_INVALID;
+  int n = query_dtype == SKV_DTYPE_F16 ? AttnCfgFast::NCONS : AttnCfgPrecise::NCONS;
+  static const int cfg_sel = getenv("SKV_ATTN_CFG") ? atoi(getenv("SKV_ATTN_CFG")) : 0;
+  if (query_dtype == SKV_DTYPE_F16 && desc->head_dim == 128 && cfg_sel == 1) n = 11;
+  if (query_dtype == SKV_DTYPE_F16 && desc->head_dim == 128 && cfg_sel == 2) n = 7;
+  return n;
 }
 
 extern "C" int64_t skv_attn_plan_bytes(const SkvStoreDesc* desc, int num_ctas) {
@@ -862,14 +763,8 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const
   p.lse_sum = lse_sum;
   p.cur_prob = cur_prob;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)desc->head_dim));
-  // partials per run of the attention launch that produced them (chosen by the query dtype)
-  p.per_run = p.q_is_half ? AttnCfgFast::NCONS : AttnCfgPrecise::NCONS;
-  {
-    static const int cfg_sel = getenv("SKV_ATTN_CFG") ? atoi(getenv("SKV_ATTN_CFG")) : 0;
-    if (p.q_is_half && desc->head_dim == 128 && cfg_sel == 1) p.per_run = 11;
-    if (p.q_is_half && desc->head_dim == 128 && cfg_sel == 2) p.per_run = 7;
-  }
-  lse_combine_kernel<<<desc->num_seqs * desc->num_kv_heads * group, desc->head_dim, 0, as_stream(stream)>>>(p);
+  p.per_run = skv_attn_partials_per_run(desc, query_dtype);
+  lse_combine_kernel<<<combine_units(p.g, group), kPostThreads, 0, as_stream(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 

@@ -1,0 +1,136 @@
+// Everything between two streaming attention kernels in one launch: the LSE combine and the
+// quantise-pack append of this layer, and the importance update of the layer before it (whose
+// combine results are complete by now).  The three are independent, so their blocks run side by
+// side and a decode step costs two launches per layer instead of four.
+#include "post_attention.cuh"
+
+namespace skv {
+
+struct PostParams {
+  CombineParams c;
+  ImportanceParams imp;
+  AppendParams app;
+  int combine_blocks;
+  int imp_chunks;      // importance blocks = imp_chunks * num_seqs (0: no importance update)
+  int append_blocks;   // 8 rows-of-a-head per block (0: no append)
+};
+
+union PostShared {
+  CombineShared c;
+  ImportanceShared i;
+};
+
+template <int EPL>
+__global__ void __launch_bounds__(kPostThreads) post_attention_kernel(const PostParams p) {
+  __shared__ PostShared sh;
+  int blk = blockIdx.x;
+  if (blk < p.combine_blocks) {
+    combine_unit(p.c, blk, sh.c);
+    return;
+  }
+  blk -= p.combine_blocks;
+  const int imp_blocks = p.imp_chunks * p.c.g.num_seqs;
+  if (blk < imp_blocks) {
+    importance_unit(p.imp, blk % p.imp_chunks, blk / p.imp_chunks, sh.i);
+    return;
+  }
+  blk -= imp_blocks;
+  const long long warp = (long long)blk * (kPostThreads / 32) + (threadIdx.x >> 5);
+  if (warp < (long long)p.app.rows * p.app.g.num_kv_heads * 2) append_row<EPL>(p.app, warp, threadIdx.x & 31);
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" int skv_post_attention(const SkvStoreDesc* desc, void* store, int layer, const void* plan,
+                                  const void* query, int query_dtype, int num_q_heads, const void* partials,
+                                  int num_ctas, const void* cur_k, const void* cur_v, int kv_dtype, float* out,
+                                  float* lse_max, float* lse_sum, float* cur_prob, const int32_t* counts,
+                                  int imp_layer, const float* imp_logits, const float* imp_lse_max,
+                                  const float* imp_lse_sum, const float* imp_cur_prob, const int32_t* cur_slot,
+                                  float* head_state, int parity,
+                                  double* cumulative, float* layer_ema, uint8_t* touched, float decay,
+                                  float head_decay, const int32_t* dst_seq, const int32_t* dst_bucket,
+                                  const int32_t* dst_pos, int32_t* err_flag, void* stream) {
+  if (!desc || !plan || !query || !partials || !out) return SKV_ERR_INVALID;
+  if (layer < 0 || layer >= desc->num_layers || num_ctas <= 0) return SKV_ERR_INVALID;
+  if (num_q_heads % desc->num_kv_heads != 0 || num_q_heads > kMaxQHeads) return SKV_ERR_INVALID;
+  const int group = num_q_heads / desc->num_kv_heads;
+  if (group < 1 || group > 8) return SKV_ERR_UNSUPPORTED;
+  if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
+  if ((cur_k == nullptr) != (cur_v == nullptr)) return SKV_ERR_INVALID;
+  const bool with_importance = imp_logits != nullptr;
+  if (with_importance && (!counts || !head_state || !cumulative || !layer_ema || !touched || !imp_lse_max ||
+                          !imp_lse_sum || imp_layer < 0 || imp_layer >= desc->num_layers))
+    return SKV_ERR_INVALID;
+  if (with_importance && (imp_lse_max == lse_max || imp_lse_sum == lse_sum || (imp_cur_prob && imp_cur_prob == cur_prob)))
+    return SKV_ERR_INVALID;  // the importance step reads an earlier launch's results, not this launch's
+  if (with_importance && parity != 0 && parity != 1) return SKV_ERR_INVALID;
+  const bool with_append = dst_seq != nullptr;
+  if (with_append && (!store || !dst_bucket || !dst_pos || !cur_k)) return SKV_ERR_INVALID;
+
+  PostParams p = {};
+  CombineParams& c = p.c;
+  c.g = make_geom(*desc);
+  c.plan = static_cast<const int*>(plan);
+  c.query = query;
+  c.q_is_half = query_dtype == SKV_DTYPE_F16;
+  c.num_q_heads = num_q_heads;
+  c.group = group;
+  c.partials = static_cast<const float*>(partials);
+  c.per_run = skv_attn_partials_per_run(desc, query_dtype);
+  c.num_ctas = num_ctas;
+  c.cur_k = cur_k;
+  c.cur_v = cur_v;
+  c.kv_is_half = kv_dtype == SKV_DTYPE_F16;
+  c.out = out;
+  c.lse_max = lse_max;
+  c.lse_sum = lse_sum;
+  c.cur_prob = cur_prob;
+  c.scale_log2 = (float)(1.4426950408889634 / sqrt((double)desc->head_dim));
+  p.combine_blocks = combine_units(c.g, group);
+  if (with_importance) {
+    ImportanceParams& i = p.imp;
+    i.g = c.g;
+    i.layer = imp_layer;
+    i.counts = counts;
+    i.num_q_heads = num_q_heads;
+    i.logits = imp_logits;
+    i.lse_max = imp_lse_max;
+    i.lse_sum = imp_lse_sum;
+    i.cur_prob = imp_cur_prob;
+    i.cur_slot = cur_slot;
+    i.head_state = head_state;
+    i.parity = parity;
+    i.cumulative = cumulative;
+    i.layer_ema = layer_ema;
+    i.touched = touched;
+    i.decay = decay;
+    i.head_decay = head_decay;
+    p.imp_chunks = (desc->slots + kPostThreads - 1) / kPostThreads;
+  }
+  if (with_append) {
+    AppendParams& a = p.app;
+    a.g = c.g;
+    a.store = static_cast<uint8_t*>(store);
+    a.layer = layer;
+    a.k = cur_k;
+    a.v = cur_v;
+    a.dtype = kv_dtype;
+    a.rows = desc->num_seqs;
+    a.dst_seq = dst_seq;
+    a.dst_bucket = dst_bucket;
+    a.dst_pos = dst_pos;
+    a.err = err_flag;
+    const long long warps = (long long)a.rows * desc->num_kv_heads * 2;
+    p.append_blocks = (int)((warps + kPostThreads / 32 - 1) / (kPostThreads / 32));
+  }
+  const int grid = p.combine_blocks + p.imp_chunks * desc->num_seqs + p.append_blocks;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (desc->head_dim == 128)
+    post_attention_kernel<4><<<grid, kPostThreads, 0, st>>>(p);
+  else
+    post_attention_kernel<2><<<grid, kPostThreads, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}

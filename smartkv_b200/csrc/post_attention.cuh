@@ -1,0 +1,316 @@
+// Block-level bodies of the three steps that follow the streaming attention kernel of a layer:
+//   combine     fold the split-KV partials of a (sequence, KV head), add the current token in full
+//               precision, normalise (smartkv/core/fused_cpu.py:115-137)
+//   importance  per-key attention mass -> cumulative importance + per-layer EMA
+//               (smartkv/core/cache.py:232-264, smartkv/core/importance.py:44-101)
+//   append      quantise + pack the step's new token into the store (smartkv/core/cache.py:1187-1355)
+// The importance step of a layer needs what that layer's combine step produced, but nothing stops
+// it from running one launch later: post_attention.cu runs the combine and the append of layer l
+// side by side with the importance step of the layer before it.  The stand-alone entry points run
+// the same bodies from their own kernels.
+#pragma once
+
+#include "attn_sched.cuh"
+#include "quant_row.cuh"
+
+namespace skv {
+
+constexpr int kPostThreads = 256;
+constexpr int kCombineChunk = 256;
+constexpr int kMaxQHeads = 128;
+
+__host__ __device__ inline int partial_stride(int group, int head_dim) { return group * (head_dim + 2); }
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---- combine ----------------------------------------------------------------------------------------
+struct CombineParams {
+  StoreGeom g;
+  const int* plan;
+  const void* query;
+  int q_is_half;
+  int num_q_heads;
+  int group;
+  const float* partials;
+  int per_run;  // partials per run = consumer warps of the attention launch
+  int num_ctas;
+  const void* cur_k;
+  const void* cur_v;
+  int kv_is_half;
+  float* out;
+  float* lse_max;
+  float* lse_sum;
+  float* cur_prob;
+  float scale_log2;
+};
+
+__host__ __device__ inline int combine_heads_per_block(int head_dim) { return kPostThreads / head_dim; }
+__host__ __device__ inline int combine_units(const StoreGeom& g, int group) {
+  const int hpb = combine_heads_per_block(g.head_dim);
+  return g.num_seqs * g.num_kv_heads * ((group + hpb - 1) / hpb);
+}
+
+struct CombineShared {
+  float red[kPostThreads / 32][2];
+  float f[kPostThreads / 64][kCombineChunk];   // per head of the block
+  float lf[kPostThreads / 64][kCombineChunk];
+};
+
+// The scaled logit of the current token for one query head: q . k * scale, reduced over the D threads
+// of the head in a fixed shape (warp tree, then the warps of the head in order).
+// `sub` = head slot inside the block, `d` = thread's element.
+__device__ __forceinline__ float head_dot(float prod, int sub, int d, int D, float (*red)[2], int slot) {
+  const float s = warp_sum(prod);
+  const int warp_in_head = d >> 5, lane = d & 31, wph = D >> 5;
+  if (lane == 0) red[sub * wph + warp_in_head][slot] = s;
+  __syncthreads();
+  float acc = 0.f;
+  for (int w = 0; w < wph; ++w) acc += red[sub * wph + w][slot];
+  return acc;
+}
+
+// One unit = up to kPostThreads / D query heads of one (sequence, KV head); blockDim.x == kPostThreads.
+__device__ __forceinline__ void combine_unit(const CombineParams& p, int unit, CombineShared& sh) {
+  const StoreGeom& g = p.g;
+  const int D = g.head_dim, G = p.group, Hkv = g.num_kv_heads;
+  const int hpb = combine_heads_per_block(D), groups = (G + hpb - 1) / hpb;
+  const int seg = unit / groups, hg = unit - seg * groups;
+  const int b = seg / Hkv, h = seg - b * Hkv;
+  const int tid = threadIdx.x, sub = tid / D, d = tid - sub * D;
+  const int gq = hg * hpb + sub;
+  const bool valid = gq < G;
+  const int gqc = valid ? gq : G - 1;  // threads of a missing head go through the motions of the last one
+  const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
+  const int nsplit = pv.seg_count[seg] * p.per_run;
+  const int r0 = nsplit > 0 ? pv.seg_begin[seg] * p.per_run : 0;
+  const int pstride = partial_stride(G, D);
+  const float* base = p.partials + (long long)r0 * pstride + gqc * (D + 2);
+  const bool has_cur = p.cur_k != nullptr && p.cur_v != nullptr;
+  const long long hq = (long long)b * p.num_q_heads + h * G + gqc;
+  const long long kv = ((long long)b * Hkv + h) * D + d;
+
+  float prod = 0.f;
+  if (has_cur) {
+    const float q = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[hq * D + d])
+                                : static_cast<const float*>(p.query)[hq * D + d];
+    const float k = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_k)[kv])
+                                 : static_cast<const float*>(p.cur_k)[kv];
+    prod = q * k;
+  }
+  float mloc = -INFINITY;
+  for (int k = d; k < nsplit; k += D) mloc = fmaxf(mloc, base[(long long)k * pstride]);
+  const float s_cur = head_dot(prod, sub, d, D, sh.red, 0) * p.scale_log2;
+  {
+    const float m = warp_max(mloc);
+    const int wph = D >> 5;
+    if ((d & 31) == 0) sh.red[sub * wph + (d >> 5)][1] = m;
+    __syncthreads();
+    mloc = -INFINITY;
+    for (int w = 0; w < wph; ++w) mloc = fmaxf(mloc, sh.red[sub * wph + w][1]);
+  }
+  float M = mloc;
+  if (has_cur) M = fmaxf(M, s_cur);
+
+  // fold the partials in a fixed order, kCombineChunk at a time; the weights of a chunk go through
+  // shared memory so that the row loads do not depend on anything loaded in the same loop
+  float acc = 0.f, L = 0.f;
+  for (int c0 = 0; c0 < nsplit; c0 += kCombineChunk) {
+    const int cn = (nsplit - c0) < kCombineChunk ? (nsplit - c0) : kCombineChunk;
+    __syncthreads();
+    for (int k = d; k < cn; k += D) {
+      const float* row = base + (long long)(c0 + k) * pstride;
+      const float mw = row[0];
+      const float f = mw == -INFINITY ? 0.f : ex2f(mw - M);
+      sh.f[sub][k] = f;
+      sh.lf[sub][k] = f == 0.f ? 0.f : row[1] * f;
+    }
+    __syncthreads();
+    const float* col = base + (long long)c0 * pstride + 2 + d;
+#pragma unroll 8
+    for (int k = 0; k < cn; ++k) {
+      const float f = sh.f[sub][k];
+      const float x = col[(long long)k * pstride];  // a partial without keys holds stale bytes: select, not multiply
+      acc += f == 0.f ? 0.f : x * f;
+      L += sh.lf[sub][k];
+    }
+  }
+  float pc = 0.f;
+  if (has_cur) {
+    pc = ex2f(s_cur - M);
+    const float v = p.kv_is_half ? __half2float(static_cast<const __half*>(p.cur_v)[kv])
+                                 : static_cast<const float*>(p.cur_v)[kv];
+    acc = fmaf(pc, v, acc);
+    L += pc;
+  }
+  if (!valid) return;
+  p.out[hq * D + d] = L > 0.f ? acc / L : 0.f;
+  if (d == 0) {
+    if (p.lse_max) p.lse_max[hq] = M;
+    if (p.lse_sum) p.lse_sum[hq] = L;
+    if (p.cur_prob) p.cur_prob[hq] = (has_cur && L > 0.f) ? pc / L : 0.f;
+  }
+}
+
+// ---- importance ---------------------------------------------------------------------------------------
+struct ImportanceParams {
+  StoreGeom g;
+  int layer;
+  const int32_t* counts;
+  int num_q_heads;
+  const float* logits;
+  const float* lse_max;
+  const float* lse_sum;
+  const float* cur_prob;
+  const int32_t* cur_slot;
+  float* head_state;
+  int parity;
+  double* cumulative;
+  float* layer_ema;
+  uint8_t* touched;
+  float decay;
+  float head_decay;
+};
+
+struct ImportanceShared {
+  float w[kMaxQHeads];      // head weight / final sum
+  float mx[kMaxQHeads];     // final max
+  float cprob[kMaxQHeads];  // pc (unnormalised probability of the current token)
+};
+
+// One unit = 256 consecutive storage indices of one sequence; blockDim.x == kPostThreads.
+__device__ __forceinline__ void importance_unit(const ImportanceParams& p, int chunk, int b, ImportanceShared& sh) {
+  const StoreGeom& g = p.g;
+  const int tid = threadIdx.x, Hq = p.num_q_heads;
+  int cnt[kNumBuckets];
+  int nkeys = 0;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) {
+    cnt[i] = p.counts[b * kNumBuckets + i];
+    nkeys += cnt[i];
+  }
+  const int cur_slot = (p.cur_prob != nullptr && p.cur_slot != nullptr) ? p.cur_slot[b] : -1;
+  const bool has_cur = cur_slot >= 0;
+  const int total_keys = nkeys + (has_cur ? 1 : 0);
+
+  // most storage indices of a sequence are unused capacity: a block without a live key leaves at once
+  // (chunk 0 of every sequence stays, it publishes the head-importance EMA)
+  const int s_lo = chunk * kPostThreads, s_hi = s_lo + kPostThreads;
+  bool block_live = chunk == 0 || (has_cur && cur_slot >= s_lo && cur_slot < s_hi);
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i)
+    block_live |= cnt[i] > 0 && g.bucket_base[i] < s_hi && g.bucket_base[i] + cnt[i] > s_lo;
+  if (!block_live) return;
+
+  // final (max, sum) of every query head and the probability of the current token, as the combine
+  // step of this layer left them (issued early: independent of the EMA chain below)
+  float lse_l = 0.f, lse_m = 0.f, pcur = 0.f;
+  if (tid < Hq) {
+    lse_l = p.lse_sum[(long long)b * Hq + tid];
+    lse_m = p.lse_max[(long long)b * Hq + tid];
+    pcur = has_cur ? p.cur_prob[(long long)b * Hq + tid] * lse_l : 0.f;
+  }
+
+  // head-importance EMA (cache.py:242-248).  Every softmax row sums to one, so the
+  // mean over keys of a head's probabilities is 1 / (number of keys).
+  const float* hs_old = p.head_state + ((long long)b * 2 + p.parity) * Hq;
+  float* hs_new = p.head_state + ((long long)b * 2 + (p.parity ^ 1)) * Hq;
+  const float head_mean = total_keys > 0 ? 1.0f / (float)total_keys : 0.f;
+  float hn = 0.f;
+  if (tid < Hq) {
+    hn = hs_old[tid] * p.head_decay + head_mean * (1.0f - p.head_decay);
+    sh.mx[tid] = hn;  // staged, replaced below
+    if (chunk == 0) hs_new[tid] = hn;
+  }
+  __syncthreads();
+  float my_w = 0.f;
+  if (tid < Hq) {
+    float acc = 0.f;
+    for (int h = 0; h < Hq; ++h) acc += sh.mx[h];  // same order in every thread: one mean per block
+    my_w = hn / (acc / (float)Hq + 1e-6f);
+  }
+  __syncthreads();
+  if (tid < Hq) {
+    sh.w[tid] = lse_l > 0.f ? my_w / lse_l : 0.f;
+    sh.mx[tid] = lse_m;
+    sh.cprob[tid] = pcur;
+  }
+  __syncthreads();
+
+  const int s = s_lo + tid;  // storage index
+  bool valid = false;
+  if (s < g.slots) {
+#pragma unroll
+    for (int i = 0; i < kNumBuckets; ++i) valid |= (s >= g.bucket_base[i] && s < g.bucket_base[i] + cnt[i]);
+  }
+  float mass = 0.f;
+  bool write = false;
+  if (valid) {
+    const float* lg = p.logits + (long long)b * Hq * g.slots + s;
+#pragma unroll 8
+    for (int h = 0; h < Hq; ++h) mass += sh.w[h] * ex2f(lg[(long long)h * g.slots] - sh.mx[h]);
+    write = true;
+  } else if (has_cur && s == cur_slot) {
+    // the newest token: it is stored at this storage index when the step's append commits
+    for (int h = 0; h < Hq; ++h) mass += sh.w[h] * sh.cprob[h];
+    write = true;
+  }
+  if (write) {
+    const long long ci = (long long)b * g.slots + s;
+    p.cumulative[ci] += (double)mass;
+    const long long li = ((long long)p.layer * g.num_seqs + b) * g.slots + s;
+    if (p.touched[li]) {
+      p.layer_ema[li] = p.decay * p.layer_ema[li] + (1.0f - p.decay) * mass;
+    } else {
+      p.layer_ema[li] = mass;
+      p.touched[li] = 1;
+    }
+  }
+}
+
+// ---- append ---------------------------------------------------------------------------------------------
+struct AppendParams {
+  StoreGeom g;
+  uint8_t* store;
+  int layer;
+  const void* k;
+  const void* v;
+  int dtype;
+  int rows;
+  const int32_t* dst_seq;
+  const int32_t* dst_bucket;
+  const int32_t* dst_pos;
+  int32_t* err;
+};
+
+// One warp quantises and packs one row (one of K / V of one KV head of one new token).
+template <int EPL>
+__device__ __forceinline__ void append_row(const AppendParams& p, long long warp, int lane) {
+  const StoreGeom& g = p.g;
+  const int which = (int)(warp & 1);  // 0 = K, 1 = V
+  const long long rh = warp >> 1;
+  const int h = (int)(rh % g.num_kv_heads);
+  const int r = (int)(rh / g.num_kv_heads);
+  const int seq = p.dst_seq[r], bucket = p.dst_bucket[r], pos = p.dst_pos[r];
+  if (seq < 0 || seq >= g.num_seqs || bucket < 0 || bucket >= kNumBuckets || pos < 0 || pos >= g.cap[bucket]) {
+    if (lane == 0 && p.err) atomicExch(p.err, 2);
+    return;
+  }
+  const int bits = bucket_bits(bucket);
+  RowVals<EPL> x = load_row<EPL>(which ? p.v : p.k, p.dtype, rh, lane);
+  int code[EPL];
+  const float scale = quantize_row<EPL>(x, bits, code);
+  uint8_t* arena = arena_ptr(g, p.store, p.layer, seq);
+  const long long row_index = (long long)h * g.cap[bucket] + pos;
+  uint8_t* dst = arena + (which ? g.v_off[bucket] : g.k_off[bucket]) + row_index * g.row_bytes[bucket];
+  pack_store_row<EPL>(code, bits, dst, lane);
+  if (lane == 0) {
+    float* sc = reinterpret_cast<float*>(arena + g.sc_off[bucket]);
+    sc[2 * row_index + which] = scale;
+  }
+}
+
+}  // namespace skv

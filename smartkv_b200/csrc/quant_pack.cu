@@ -6,40 +6,17 @@
 // code = clamp(rint(x / scale)) with round-half-even.  No fast-math anywhere in
 // this file: codes and scales are bit-exact with the CPU path.
 // Packed format: smartkv/csrc/bit_packing.cu:20-43, 69-95, 128-151.
-#include "quant_row.cuh"
+#include "post_attention.cuh"
 
 namespace skv {
 
 // ---- append into the store ----------------------------------------------------
 template <int EPL>
-__global__ void quantize_pack_append_kernel(StoreGeom g, uint8_t* store, int layer, const void* k, const void* v,
-                                            int dtype, int rows, const int32_t* dst_seq, const int32_t* dst_bucket,
-                                            const int32_t* dst_pos, int32_t* err) {
+__global__ void quantize_pack_append_kernel(const AppendParams p) {
   const int lane = threadIdx.x & 31;
   const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long total = (long long)rows * g.num_kv_heads * 2;
-  if (warp >= total) return;
-  const int which = (int)(warp & 1);  // 0 = K, 1 = V
-  const long long rh = warp >> 1;
-  const int h = (int)(rh % g.num_kv_heads);
-  const int r = (int)(rh / g.num_kv_heads);
-  const int seq = dst_seq[r], bucket = dst_bucket[r], pos = dst_pos[r];
-  if (seq < 0 || seq >= g.num_seqs || bucket < 0 || bucket >= kNumBuckets || pos < 0 || pos >= g.cap[bucket]) {
-    if (lane == 0 && err) atomicExch(err, 2);
-    return;
-  }
-  const int bits = bucket_bits(bucket);
-  RowVals<EPL> x = load_row<EPL>(which ? v : k, dtype, rh, lane);
-  int code[EPL];
-  const float scale = quantize_row<EPL>(x, bits, code);
-  uint8_t* arena = arena_ptr(g, store, layer, seq);
-  const long long row_index = (long long)h * g.cap[bucket] + pos;
-  uint8_t* dst = arena + (which ? g.v_off[bucket] : g.k_off[bucket]) + row_index * g.row_bytes[bucket];
-  pack_store_row<EPL>(code, bits, dst, lane);
-  if (lane == 0) {
-    float* sc = reinterpret_cast<float*>(arena + g.sc_off[bucket]);
-    sc[2 * row_index + which] = scale;
-  }
+  if (warp >= (long long)p.rows * p.g.num_kv_heads * 2) return;
+  append_row<EPL>(p, warp, lane);
 }
 
 // ---- plain quantise (parity helper) --------------------------------------------
@@ -251,16 +228,25 @@ extern "C" int skv_quantize_pack_append(const SkvStoreDesc* desc, void* store, i
   if (input_dtype != SKV_DTYPE_F32 && input_dtype != SKV_DTYPE_F16) return SKV_ERR_INVALID;
   if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
   if (rows == 0) return SKV_OK;
-  StoreGeom g = make_geom(*desc);
+  AppendParams p;
+  p.g = make_geom(*desc);
+  p.store = static_cast<uint8_t*>(store);
+  p.layer = layer;
+  p.k = k;
+  p.v = v;
+  p.dtype = input_dtype;
+  p.rows = rows;
+  p.dst_seq = dst_seq;
+  p.dst_bucket = dst_bucket;
+  p.dst_pos = dst_pos;
+  p.err = nullptr;
   const int wpb = 8;
-  const long long warps = (long long)rows * g.num_kv_heads * 2;
+  const long long warps = (long long)rows * p.g.num_kv_heads * 2;
   const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
   if (desc->head_dim == 128)
-    quantize_pack_append_kernel<4><<<grid, wpb * 32, 0, as_stream(stream)>>>(
-        g, static_cast<uint8_t*>(store), layer, k, v, input_dtype, rows, dst_seq, dst_bucket, dst_pos, nullptr);
+    quantize_pack_append_kernel<4><<<grid, wpb * 32, 0, as_stream(stream)>>>(p);
   else
-    quantize_pack_append_kernel<2><<<grid, wpb * 32, 0, as_stream(stream)>>>(
-        g, static_cast<uint8_t*>(store), layer, k, v, input_dtype, rows, dst_seq, dst_bucket, dst_pos, nullptr);
+    quantize_pack_append_kernel<2><<<grid, wpb * 32, 0, as_stream(stream)>>>(p);
   return launch_status();
 }
 

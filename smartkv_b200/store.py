@@ -171,6 +171,9 @@ class PackedKVStore:
         return self._seq_ids, bucket, pos, storage
 
     def commit_step(self, plan):
+        self.flush_importance()          # reads the counts as they stood during the step
+        if getattr(self, "_pipe", None) is not None:
+            self._pipe["next"] = 0       # every step starts on the same buffer set (CUDA graph replays rely on it)
         _seq, bucket, _pos, storage = plan
         self.slot_token.scatter_(1, storage.long()[:, None], self.next_token[:, None])
         self.counts.scatter_add_(1, bucket.long()[:, None], torch.ones((self.num_seqs, 1), dtype=torch.int32, device=self.device))
@@ -201,6 +204,7 @@ class PackedKVStore:
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
         st = self._stream()
+        self.flush_importance()
         if not self._plan_valid:
             self.build_plan()
         if kernel_events is not None:
@@ -232,6 +236,86 @@ class PackedKVStore:
                   "skv_importance_update")
             self.head_parity ^= 1
         return out
+
+    def decode_layer(self, layer: int, query: torch.Tensor, cur_k: torch.Tensor, cur_v: torch.Tensor, step_plan,
+                     update_importance: bool = True, out: Optional[torch.Tensor] = None,
+                     kernel_events=None) -> torch.Tensor:
+        """One layer of a decode step in two launches: the streaming attention kernel, then one kernel
+        with this layer's combine, the append of the new token (``step_plan`` from plan_step) and the
+        importance update of the PREVIOUS decode_layer call (skv_post_attention).  The last layer's
+        importance update is flushed by commit_step / flush_importance.  Same results as
+        attention(...) followed by append(...)."""
+        q = query.contiguous()
+        assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
+        want_logits = update_importance and self.track_importance
+        st = self._stream()
+        if not self._plan_valid:
+            self.build_plan()
+        pipe = self._pipe_buffers()
+        cur = pipe["next"]
+        bufs = pipe["bufs"][cur]
+        if kernel_events is not None:
+            kernel_events[0].record()
+        check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q),
+                                            self._dtype_code(q), self.num_q_heads, ptr(self.partials), self.num_ctas,
+                                            ptr(bufs["logits"]) if want_logits else None, ptr(self.err), st),
+              "skv_decode_attention")
+        if kernel_events is not None:
+            kernel_events[1].record()
+        out = self.out if out is None else out
+        cur_k = cur_k.contiguous()
+        cur_v = cur_v.contiguous()
+        dst_seq, dst_bucket, dst_pos, storage = step_plan
+        pend = pipe["pending"]
+        pb = pipe["bufs"][pend["buf"]] if pend is not None else None
+        check(self.lib.skv_post_attention(
+            ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q), self._dtype_code(q),
+            self.num_q_heads, ptr(self.partials), self.num_ctas, ptr(cur_k), ptr(cur_v), self._dtype_code(cur_k),
+            ptr(out), ptr(bufs["lse_max"]), ptr(bufs["lse_sum"]), ptr(bufs["cur_prob"]), ptr(self.counts),
+            pend["layer"] if pend is not None else 0, ptr(pb["logits"]) if pend is not None else None,
+            ptr(pb["lse_max"]) if pend is not None else None, ptr(pb["lse_sum"]) if pend is not None else None,
+            ptr(pb["cur_prob"]) if pend is not None else None, ptr(pend["storage"]) if pend is not None else None,
+            ptr(self.head_state), self.head_parity, ptr(self.cumulative), ptr(self.layer_ema), ptr(self.touched),
+            self.decay, self.head_decay, ptr(dst_seq), ptr(dst_bucket), ptr(dst_pos), ptr(self.err), st),
+            "skv_post_attention")
+        if pend is not None:
+            self.head_parity ^= 1
+        pipe["pending"] = {"layer": layer, "buf": cur, "storage": storage} if want_logits else None
+        pipe["next"] = cur ^ 1
+        self.lse_max, self.lse_sum, self.cur_prob = bufs["lse_max"], bufs["lse_sum"], bufs["cur_prob"]
+        return out
+
+    def _pipe_buffers(self):
+        """Two sets of (logits, max, sum, current-token probability): the importance update of a layer runs
+        one launch after its attention, while the next layer's attention already writes the other set."""
+        if getattr(self, "_pipe", None) is None:
+            dev, B, Hq = self.device, self.num_seqs, self.num_q_heads
+            bufs = []
+            for i in range(2):
+                bufs.append({
+                    "logits": (self.logits if i == 0 else torch.empty_like(self.logits)) if self.track_importance else None,
+                    "lse_max": torch.empty((B, Hq), dtype=torch.float32, device=dev),
+                    "lse_sum": torch.empty((B, Hq), dtype=torch.float32, device=dev),
+                    "cur_prob": torch.empty((B, Hq), dtype=torch.float32, device=dev),
+                })
+            self._pipe = {"bufs": bufs, "next": 0, "pending": None}
+        return self._pipe
+
+    def flush_importance(self):
+        """Runs the importance update still owed by the last decode_layer call (no-op otherwise)."""
+        pipe = getattr(self, "_pipe", None)
+        if pipe is None or pipe["pending"] is None:
+            return
+        pend = pipe["pending"]
+        pb = pipe["bufs"][pend["buf"]]
+        check(self.lib.skv_importance_update(ctypes.byref(self.desc), pend["layer"], ptr(self.counts), self.num_q_heads,
+                                             ptr(pb["logits"]), ptr(pb["lse_max"]), ptr(pb["lse_sum"]),
+                                             ptr(pb["cur_prob"]), ptr(pend["storage"]), ptr(self.head_state),
+                                             self.head_parity, ptr(self.cumulative), ptr(self.layer_ema),
+                                             ptr(self.touched), self.decay, self.head_decay, self._stream()),
+              "skv_importance_update")
+        self.head_parity ^= 1
+        pipe["pending"] = None
 
     def build_plan(self):
         """(Re)build the attention work partition from the live bucket counts.  Needed once
@@ -311,6 +395,7 @@ class PackedKVStore:
         """Runs the allocator on every sequence (skv_alloc_bits).  ``scores``: fp64 [B, slots] in
         storage order, default the cumulative importance.  Returns (new_bits uint8 [B, slots],
         new_counts int32 [B, 4], changed int32 [B]) -- device tensors owned by the store."""
+        self.flush_importance()
         r = self._realloc_buffers()
         scores = self.cumulative if scores is None else scores
         check(self.lib.skv_alloc_bits(ctypes.byref(self.desc), ctypes.byref(cfg), ptr(self.counts), ptr(self.slot_token),
