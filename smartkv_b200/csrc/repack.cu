@@ -197,59 +197,92 @@ __device__ __forceinline__ int find_seq(const int* s_prefix, int B, int m) {
   return lo;
 }
 
-// phase 0: source rows -> staging (requantised at the destination width); phase 1: staging -> destination
+// Reads this lane's EPL codes out of a packed row through aligned 32-bit loads (rows are at least
+// 16 bytes and 4-byte aligned; a lane's field of EPL*bits <= 32 bits spans at most two words).
+template <int EPL>
+__device__ __forceinline__ void unpack_row_words(const uint8_t* src, int bits, int lane, int (&code)[EPL]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(src);
+  const int bitpos = lane * EPL * bits, wi = bitpos >> 5, sh = bitpos & 31, nbits = EPL * bits;
+  const int nwords = nbits;  // 32 lanes * nbits / 32
+  uint32_t lo = w[wi];
+  uint32_t hi = (sh + nbits > 32 && wi + 1 < nwords) ? w[wi + 1] : 0u;
+  const uint32_t field = __funnelshift_r(lo, hi, sh);
+  if (bits == 8) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) code[i] = (int)(int8_t)((field >> (8 * i)) & 0xffu);
+  } else {
+    const uint32_t fm = (1u << bits) - 1u;
+    const int off = 1 << (bits - 1);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) code[i] = (int)((field >> (bits * i)) & fm) - off;
+  }
+}
+
+// phase 0: source rows -> staging (requantised at the destination width); phase 1: staging -> destination.
+// One warp takes one move and walks its rows (layers of the call x KV heads x {K, V}).
 template <int EPL, int PHASE>
 __global__ void repack_rows_kernel(const RowMoveParams p) {
   const StoreGeom& g = p.g;
   __shared__ int s_prefix[kMaxSeqsRepack + 1];
   const int total_moves = load_move_prefix(p.n_moves, g.num_seqs, s_prefix);
   const int Hkv = g.num_kv_heads, nl = p.layer_end - p.layer_begin;
-  const long long jobs = (long long)nl * total_moves * Hkv * 2;
-  if (jobs > p.staging_rows) {
+  const int rows_per_move = nl * Hkv * 2;
+  if ((long long)total_moves * rows_per_move > p.staging_rows) {
     if (threadIdx.x == 0 && blockIdx.x == 0 && p.err) atomicExch(p.err, 6);  // staging too small: nothing moves
     return;
   }
   const int lane = threadIdx.x & 31;
-  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long job = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); job < jobs; job += nwarps) {
-    const int which = (int)(job & 1);
-    long long r = job >> 1;
-    const int h = (int)(r % Hkv);
-    r /= Hkv;
-    const int m = (int)(r % total_moves);
-    const int layer = p.layer_begin + (int)(r / total_moves);
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  for (int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); m < total_moves; m += nwarps) {
     const int b = find_seq(s_prefix, g.num_seqs, m);
     const int k = m - s_prefix[b];
     const int src = p.move_src[(long long)b * g.slots + k], dst = p.move_dst[(long long)b * g.slots + k];
     const int wb_s = bucket_of_slot(g, src), wb_d = bucket_of_slot(g, dst);
     const int bits_s = bucket_bits(wb_s), bits_d = bucket_bits(wb_d);
-    uint8_t* arena = arena_ptr(g, p.store, layer, b);
-    uint8_t* stage = p.staging + job * kStageRowBytes;
-    if (PHASE == 0) {
-      const long long row = (long long)h * g.cap[wb_s] + (src - g.bucket_base[wb_s]);
-      const uint8_t* rp = arena + (which ? g.v_off[wb_s] : g.k_off[wb_s]) + row * g.row_bytes[wb_s];
-      const float scale = reinterpret_cast<const float*>(arena + g.sc_off[wb_s])[2 * row + which];
-      if (bits_s == bits_d) {
-        const int words = g.row_bytes[wb_s] >> 2;
-        if (lane < words) reinterpret_cast<uint32_t*>(stage)[lane] = reinterpret_cast<const uint32_t*>(rp)[lane];
-        if (lane == 0) *reinterpret_cast<float*>(stage + 128) = scale;
-      } else {
-        int code[EPL];
-        unpack_row<EPL>(rp, bits_s, lane, code);
-        RowVals<EPL> x;
+    const int rb_s = g.row_bytes[wb_s], rb_d = g.row_bytes[wb_d];
+    const int pos_s = src - g.bucket_base[wb_s], pos_d = dst - g.bucket_base[wb_d];
+    uint8_t* stage = p.staging + (long long)m * rows_per_move * kStageRowBytes;
+    for (int li = 0; li < nl; ++li) {
+      uint8_t* arena = arena_ptr(g, p.store, p.layer_begin + li, b);
+      if (PHASE == 0) {
+        const float* scales = reinterpret_cast<const float*>(arena + g.sc_off[wb_s]);
+        for (int h = 0; h < Hkv; ++h) {
+          const long long row = (long long)h * g.cap[wb_s] + pos_s;
+          const float2 sc = reinterpret_cast<const float2*>(scales)[row];
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) x.v[i] = __fmul_rn((float)code[i], scale);  // codes.float() * scale
-        int q[EPL];
-        const float ns = quantize_row<EPL>(x, bits_d, q);
-        pack_store_row<EPL>(q, bits_d, stage, lane);
-        if (lane == 0) *reinterpret_cast<float*>(stage + 128) = ns;
+          for (int which = 0; which < 2; ++which) {
+            const uint8_t* rp = arena + (which ? g.v_off[wb_s] : g.k_off[wb_s]) + row * rb_s;
+            uint8_t* st = stage + ((li * Hkv + h) * 2 + which) * kStageRowBytes;
+            const float scale = which ? sc.y : sc.x;
+            if (bits_s == bits_d) {
+              if (lane < (rb_s >> 2)) reinterpret_cast<uint32_t*>(st)[lane] = reinterpret_cast<const uint32_t*>(rp)[lane];
+              if (lane == 0) *reinterpret_cast<float*>(st + 128) = scale;
+            } else {
+              int code[EPL];
+              unpack_row_words<EPL>(rp, bits_s, lane, code);
+              RowVals<EPL> x;
+#pragma unroll
+              for (int i = 0; i < EPL; ++i) x.v[i] = __fmul_rn((float)code[i], scale);  // codes.float() * scale
+              int q[EPL];
+              const float ns = quantize_row<EPL>(x, bits_d, q);
+              pack_store_row<EPL>(q, bits_d, st, lane);
+              if (lane == 0) *reinterpret_cast<float*>(st + 128) = ns;
+            }
+          }
+        }
+      } else {
+        float* scales = reinterpret_cast<float*>(arena + g.sc_off[wb_d]);
+        for (int h = 0; h < Hkv; ++h) {
+          const long long row = (long long)h * g.cap[wb_d] + pos_d;
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            uint8_t* rp = arena + (which ? g.v_off[wb_d] : g.k_off[wb_d]) + row * rb_d;
+            const uint8_t* st = stage + ((li * Hkv + h) * 2 + which) * kStageRowBytes;
+            if (lane < (rb_d >> 2)) reinterpret_cast<uint32_t*>(rp)[lane] = reinterpret_cast<const uint32_t*>(st)[lane];
+            if (lane == 0) scales[2 * row + which] = *reinterpret_cast<const float*>(st + 128);
+          }
+        }
       }
-    } else {
-      const long long row = (long long)h * g.cap[wb_d] + (dst - g.bucket_base[wb_d]);
-      uint8_t* rp = arena + (which ? g.v_off[wb_d] : g.k_off[wb_d]) + row * g.row_bytes[wb_d];
-      const int words = g.row_bytes[wb_d] >> 2;
-      if (lane < words) reinterpret_cast<uint32_t*>(rp)[lane] = reinterpret_cast<const uint32_t*>(stage)[lane];
-      if (lane == 0) reinterpret_cast<float*>(arena + g.sc_off[wb_d])[2 * row + which] = *reinterpret_cast<const float*>(stage + 128);
     }
   }
 }
