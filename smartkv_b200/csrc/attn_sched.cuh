@@ -1,12 +1,14 @@
 // Work partition of the fused decode attention: which 16-key tiles of which
 // (sequence, KV head) segment a persistent CTA owns.
 //
-// Every segment is a byte string: for each bucket in turn, ceil(count/16) tiles of
-// tile_bytes(bucket) = 16 * (2*row_bytes + 8) bytes (packed K rows, V rows and a
-// float2 of scales per key).  All heads of a sequence have the same length W[b].
+// Every segment is a string of cost units: for each bucket in turn, ceil(count/16) tiles of
+// tile_cost(bucket) = tile_bytes(bucket) + a fixed term, tile_bytes = 16 * (2*row_bytes + 8)
+// (packed K rows, V rows and a float2 of scales per key).  The fixed term stands for the
+// per-tile arithmetic, which is the same for every width: narrow tiles are bound by it, 8-bit
+// tiles by their bytes.  All heads of a sequence have the same length W[b].
 // The global string concatenates the segments in (sequence, head) order; CTA c
-// owns the tiles whose first byte lies in [ceil(c*T/C), ceil((c+1)*T/C)), i.e. the
-// CTAs are balanced by bytes and never share a tile.  A maximal piece of one
+// owns the tiles whose first unit lies in [ceil(c*T/C), ceil((c+1)*T/C)), i.e. the
+// CTAs are balanced by estimated time and never share a tile.  A maximal piece of one
 // segment owned by one CTA is a *run*; runs are numbered in byte order, which is
 // both (CTA, segment) order and (segment, CTA) order, so a CTA's runs and a
 // segment's runs are each consecutive.  The partition depends only on the bucket
@@ -22,14 +24,20 @@ __host__ __device__ constexpr int tile_bytes_for(int head_dim, int bits) {
   return 16 * (2 * row_bytes_for(head_dim, bits) + 8);
 }
 
+// fixed cost of a tile in byte-equivalents (time of its arithmetic x the per-SM share of the bandwidth)
+constexpr int kTileFixedCost = 3072;
+__host__ __device__ constexpr int tile_cost_for(int head_dim, int bits, int fixed) {
+  return tile_bytes_for(head_dim, bits) + fixed;
+}
+
 struct SegLayout {
   int cnt[kNumBuckets];          // live keys per bucket
   int nt[kNumBuckets];           // tiles per bucket
-  long long start[kNumBuckets];  // first byte of the bucket inside the segment
-  long long bytes;               // W: bytes of one segment of this sequence
+  long long start[kNumBuckets];  // first cost unit of the bucket inside the segment
+  long long bytes;               // W: cost units of one segment of this sequence
 };
 
-__host__ __device__ inline SegLayout seg_layout(const int32_t* counts4, int head_dim) {
+__host__ __device__ inline SegLayout seg_layout(const int32_t* counts4, int head_dim, int fixed = kTileFixedCost) {
   SegLayout s;
   long long off = 0;
 #pragma unroll
@@ -37,7 +45,7 @@ __host__ __device__ inline SegLayout seg_layout(const int32_t* counts4, int head
     s.cnt[i] = counts4[i];
     s.nt[i] = (counts4[i] + 15) >> 4;
     s.start[i] = off;
-    off += (long long)s.nt[i] * tile_bytes_for(head_dim, bucket_bits(i));
+    off += (long long)s.nt[i] * tile_cost_for(head_dim, bucket_bits(i), fixed);
   }
   s.bytes = off;
   return s;
@@ -47,14 +55,15 @@ __host__ __device__ inline long long cta_range_begin(long long total, int c, int
   return (total * c + num_ctas - 1) / num_ctas;
 }
 
-// Tiles [ka, kb) of every bucket whose first byte lies in the segment-local range [lo, hi).
+// Tiles [ka, kb) of every bucket whose first unit lies in the segment-local range [lo, hi).
 // Returns the number of tiles.
 __host__ __device__ inline int seg_tiles_in_range(const SegLayout& s, int head_dim, long long lo, long long hi,
-                                                  int (&ka)[kNumBuckets], int (&kb)[kNumBuckets]) {
+                                                  int (&ka)[kNumBuckets], int (&kb)[kNumBuckets],
+                                                  int fixed = kTileFixedCost) {
   int total = 0;
 #pragma unroll
   for (int i = 0; i < kNumBuckets; ++i) {
-    const long long tb = tile_bytes_for(head_dim, bucket_bits(i));
+    const long long tb = tile_cost_for(head_dim, bucket_bits(i), fixed);
     long long a = lo - s.start[i], b = hi - s.start[i];
     a = a <= 0 ? 0 : (a + tb - 1) / tb;
     b = b <= 0 ? 0 : (b + tb - 1) / tb;
@@ -83,17 +92,20 @@ static_assert(sizeof(RunDesc) == 64, "RunDesc is one 64-byte record");
 //   seg_begin[nseg]      first run of every segment (undefined when seg_count is 0)
 //   seg_count[nseg]      runs of every segment
 //   (padding to 16 words)  RunDesc runs[C + nseg]
+//   RunDesc first[C]     copy of every CTA's first run, so that a CTA reaches it with one load
+//                        instead of two dependent ones (cta_begin, then runs[])
 struct PlanView {
   int* header;
   int* cta_begin;
   int* seg_begin;
   int* seg_count;
   RunDesc* runs;
+  RunDesc* first;
 };
 __host__ __device__ inline long long plan_words(int num_ctas, int nseg) {
   long long head = 4 + (num_ctas + 1) + 2LL * nseg;
   head = (head + 15) / 16 * 16;
-  return head + 16LL * (num_ctas + nseg);
+  return head + 16LL * (num_ctas + nseg) + 16LL * num_ctas;
 }
 __host__ __device__ inline PlanView plan_view(int* base, int num_ctas, int nseg) {
   PlanView v;
@@ -104,6 +116,7 @@ __host__ __device__ inline PlanView plan_view(int* base, int num_ctas, int nseg)
   long long head = 4 + (num_ctas + 1) + 2LL * nseg;
   head = (head + 15) / 16 * 16;
   v.runs = reinterpret_cast<RunDesc*>(base + head);
+  v.first = v.runs + (num_ctas + nseg);
   return v;
 }
 

@@ -37,8 +37,8 @@ template <int NCONS_, int STAGES_, int STAGE_BYTES_>
 struct AttnCfg {
   static constexpr int NCONS = NCONS_, STAGES = STAGES_, STAGE_BYTES = STAGE_BYTES_;
 };
-constexpr int kMaxPartialsPerRun = 15;  // consumer warps of the widest configuration
-using AttnCfgFast = AttnCfg<15, 3, 63360>;     // fp16 queries: 16 warps x 128 registers; 15 8-bit tiles per stage
+constexpr int kMaxPartialsPerRun = 11;  // consumer warps of the widest configuration
+using AttnCfgFast = AttnCfg<11, 3, 63360>;  // 11 consumer warps x 168 registers beat 15 x 128 (no remat of constants)     // fp16 queries: 16 warps x 128 registers; 15 8-bit tiles per stage
 using AttnCfgPrecise = AttnCfg<7, 3, 42240>;   // fp32 queries (hi/lo split): 8 warps, more registers per thread
 
 // tiles per block for a bit-width: as many 16-key tiles as fit one stage
@@ -76,8 +76,13 @@ __device__ __forceinline__ unsigned long long gtimer() {
   do {                                                                                            \
     if (p.timeline != nullptr && (threadIdx.x == 0) && (slot) < 16) p.timeline[blockIdx.x * 16 + (slot)] = gtimer(); \
   } while (0)
+#define SKV_TLP(slot)                                                                             \
+  do {                                                                                            \
+    if (p.timeline != nullptr && lane == 0 && (slot) < 16) p.timeline[blockIdx.x * 16 + (slot)] = gtimer(); \
+  } while (0)
 #else
 #define SKV_TL(slot) do { } while (0)
+#define SKV_TLP(slot) do { } while (0)
 #endif
 
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
@@ -89,13 +94,14 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 // ---- plan: the byte-balanced partition, built once per decode step --------------------
-__global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int32_t* counts, int C, int* plan_base) {
+__global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int32_t* counts, int C, int* plan_base,
+                                                         int fixed) {
   __shared__ long long cumw[kMaxSeqs + 1];
   __shared__ int nruns_of[kMaxCtas + 1];
   const int tid = threadIdx.x, NT = blockDim.x;
   const int B = g.num_seqs, Hkv = g.num_kv_heads, D = g.head_dim, nseg = B * Hkv;
   PlanView pv = plan_view(plan_base, C, nseg);
-  for (int b = tid; b < B; b += NT) cumw[b + 1] = seg_layout(counts + b * kNumBuckets, D).bytes;
+  for (int b = tid; b < B; b += NT) cumw[b + 1] = seg_layout(counts + b * kNumBuckets, D, fixed).bytes;
   for (int s = tid; s < nseg; s += NT) {
     pv.seg_begin[s] = 0x7fffffff;
     pv.seg_count[s] = 0;
@@ -124,14 +130,14 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int3
         if (cumw[mid] * Hkv <= y) lo = mid; else hi = mid;
       }
       b = lo;
-      const SegLayout sl = seg_layout(counts + b * kNumBuckets, D);
+      const SegLayout sl = seg_layout(counts + b * kNumBuckets, D, fixed);
       const long long seq_first = cumw[b] * Hkv;
       const int h = (int)((y - seq_first) / sl.bytes);
       const long long seg_off = seq_first + (long long)h * sl.bytes;
       const long long seg_end = seg_off + sl.bytes;
       const long long y_next = seg_end < y_end ? seg_end : y_end;
       int ka[kNumBuckets], kb[kNumBuckets];
-      if (seg_tiles_in_range(sl, D, y - seg_off, y_next - seg_off, ka, kb) > 0) {
+      if (seg_tiles_in_range(sl, D, y - seg_off, y_next - seg_off, ka, kb, fixed) > 0) {
         if (out != nullptr) {
           RunDesc r;
           r.seq = b;
@@ -170,8 +176,10 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int3
   }
   __syncthreads();
   for (int c = tid; c <= C; c += NT) pv.cta_begin[c] = nruns_of[c];
-  for (int c = tid; c < C; c += NT)
+  for (int c = tid; c < C; c += NT) {
     if (total > 0) walk(c, pv.runs, nruns_of[c]);
+    if (nruns_of[c + 1] > nruns_of[c]) pv.first[c] = pv.runs[nruns_of[c]];  // written by this thread just above
+  }
 }
 
 // Online-softmax state of one lane: query head g = lane >> 2 (the 4 lanes of a head share m).
@@ -361,6 +369,62 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
+// The query rows of one head of a run: fp16 copy (plus a residual row in the precise mode) and
+// radix-128 int8 limbs with their row sums.  One warp per call.
+template <int D, bool PRECISE>
+__device__ __forceinline__ void prep_query_head(QSlot<D, PRECISE>& slot, const AttnParams& p, int seq, int head,
+                                                int G, int gq, int lane) {
+  constexpr int NL = QSlot<D, PRECISE>::NLIMB;
+  constexpr int EPL = D / 32;  // query elements per lane and head
+  const long long q_off = ((long long)seq * p.num_q_heads + (long long)head * G) * D;
+  float q[EPL];
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const long long idx = q_off + (long long)gq * D + lane * EPL + e;
+    q[e] = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[idx])
+                       : static_cast<const float*>(p.query)[idx];
+    amax = fmaxf(amax, fabsf(q[e]));
+  }
+  amax = warp_max(amax);
+  float range = 127.f;
+#pragma unroll
+  for (int l = 1; l < NL; ++l) range *= 128.f;
+  const float step = amax > 0.f ? amax / range : 1.f;
+  const float inv = 1.f / step;
+  int sum[NL];
+#pragma unroll
+  for (int l = 0; l < NL; ++l) sum[l] = 0;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const int d_idx = lane * EPL + e;
+    const __half qh = __float2half_rn(q[e]);
+    slot.qh[gq][d_idx] = qh;
+    if (PRECISE) slot.qh[gq + 8][d_idx] = __float2half_rn(q[e] - __half2float(qh));
+    float rem = fminf(fmaxf(rintf(q[e] * inv), -range), range);  // integer in [-range, range]
+#pragma unroll
+    for (int l = NL - 1; l >= 1; --l) {
+      const float hi = rintf(rem * (1.f / 128.f));
+      const int low = (int)(rem - hi * 128.f);  // in [-64, 64]
+      slot.limb[l][gq][d_idx] = (int8_t)low;
+      sum[l] += low;
+      rem = hi;
+    }
+    slot.limb[0][gq][d_idx] = (int8_t)(int)rem;
+    sum[0] += (int)rem;
+  }
+#pragma unroll
+  for (int l = 0; l < NL; ++l) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], off);
+  }
+  if (lane == 0) {
+    slot.sq[gq] = step;
+    slot.sumA[gq] = 128 * sum[0] + sum[1];
+    slot.sumB[gq] = NL == 3 ? sum[NL - 1] : 0;
+  }
+}
+
 template <int D, bool PRECISE, class CFG>
 __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(const AttnParams p) {
   constexpr int NCONS = CFG::NCONS, STAGES = CFG::STAGES, STAGE_BYTES = CFG::STAGE_BYTES;
@@ -445,71 +509,44 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       }
       return true;
     };
-    for (int r = run_begin; r < run_end; ++r) {
-      const RunDesc d = pv.runs[r];
-      int ci = 0, ct0 = -1;
-      // the first run's copies start before its query is prepared (nothing else is in flight yet)
-      if (r == run_begin && !issue_blocks(d, ci, ct0, STAGES)) break;
-      if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err)) break;
+    // Publishes the query slot of run r: its descriptor and, except for the CTA's first run (whose
+    // rows the consumer warps prepare themselves, one head each, while the first copies are in
+    // flight), the query rows.
+    auto publish_query = [&](int r, const RunDesc& d) -> bool {
+      if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err)) return false;
       Slot& slot = qslots[qi];
       if (lane == 0) slot.desc = d;
-      // ---- the query rows of this group: fp16 copy and radix-128 int8 limbs --------------
-      const long long q_off = ((long long)d.seq * p.num_q_heads + (long long)d.head * G) * D;
-      for (int gq = 0; gq < G; ++gq) {
-        float q[EPL];
-        float amax = 0.f;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          const long long idx = q_off + (long long)gq * D + lane * EPL + e;
-          q[e] = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[idx])
-                             : static_cast<const float*>(p.query)[idx];
-          amax = fmaxf(amax, fabsf(q[e]));
-        }
-        amax = warp_max(amax);
-        float range = 127.f;
-#pragma unroll
-        for (int l = 1; l < NL; ++l) range *= 128.f;
-        const float step = amax > 0.f ? amax / range : 1.f;
-        const float inv = 1.f / step;
-        int sum[NL];
-#pragma unroll
-        for (int l = 0; l < NL; ++l) sum[l] = 0;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          const int d_idx = lane * EPL + e;
-          const __half qh = __float2half_rn(q[e]);
-          slot.qh[gq][d_idx] = qh;
-          if (PRECISE) slot.qh[gq + 8][d_idx] = __float2half_rn(q[e] - __half2float(qh));
-          float rem = fminf(fmaxf(rintf(q[e] * inv), -range), range);  // integer in [-range, range]
-#pragma unroll
-          for (int l = NL - 1; l >= 1; --l) {
-            const float hi = rintf(rem * (1.f / 128.f));
-            const int low = (int)(rem - hi * 128.f);  // in [-64, 64]
-            slot.limb[l][gq][d_idx] = (int8_t)low;
-            sum[l] += low;
-            rem = hi;
-          }
-          slot.limb[0][gq][d_idx] = (int8_t)(int)rem;
-          sum[0] += (int)rem;
-        }
-#pragma unroll
-        for (int l = 0; l < NL; ++l) {
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], off);
-        }
-        if (lane == 0) {
-          slot.sq[gq] = step;
-          slot.sumA[gq] = 128 * sum[0] + sum[1];
-          slot.sumB[gq] = NL == 3 ? sum[NL - 1] : 0;
-        }
+      if (r != run_begin) {
+        for (int gq = 0; gq < G; ++gq) prep_query_head<D, PRECISE>(slot, p, d.seq, d.head, G, gq, lane);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&qfull[qi]);
-      if (!issue_blocks(d, ci, ct0, 1 << 30)) break;
       if (++qi == kQBufs) {
         qi = 0;
         qepar ^= 1u;
       }
+      return true;
+    };
+    RunDesc d = pv.first[blockIdx.x];  // meaningful when the CTA has a run
+    bool ok = run_begin < run_end;
+    for (int r = run_begin; ok && r < run_end; ++r) {
+      int ci = 0, ct0 = -1;
+      // the first blocks of a run go out first; then, while they are in flight, the query slot of
+      // the NEXT run is published, so that no consumer ever waits for query rows at a run boundary
+      ok = issue_blocks(d, ci, ct0, STAGES);
+      if (r == run_begin) {
+        SKV_TLP(10);
+        ok = ok && publish_query(r, d);
+        SKV_TLP(11);
+      }
+      RunDesc dn = d;
+      if (ok && r + 1 < run_end) {
+        dn = pv.runs[r + 1];
+        ok = publish_query(r + 1, dn);
+      }
+      ok = ok && issue_blocks(d, ci, ct0, 1 << 30);
+      SKV_TLP(12 + (r - run_begin));
+      d = dn;
     }
     return;
   }
@@ -523,6 +560,10 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     SKV_TL(2 + 4 * (r - run_begin));
     const Slot& slot = qslots[qi];  // stays valid until this warp arrives on qempty below
     const RunDesc& d = slot.desc;
+    if (r == run_begin) {
+      for (int gq = warp; gq < G; gq += NCONS) prep_query_head<D, PRECISE>(qslots[qi], p, d.seq, d.head, G, gq, lane);
+      named_bar_sync(1, NCONS * 32);
+    }
     const int b = d.seq, h = d.head;
 
     LaneState st;
@@ -636,9 +677,6 @@ extern "C" int64_t skv_attn_partials_bytes(const SkvStoreDesc* desc, int num_q_h
 extern "C" int skv_attn_partials_per_run(const SkvStoreDesc* desc, int query_dtype) {
   if (!desc) return SKV_ERR_INVALID;
   int n = query_dtype == SKV_DTYPE_F16 ? AttnCfgFast::NCONS : AttnCfgPrecise::NCONS;
-  static const int cfg_sel = getenv("SKV_ATTN_CFG") ? atoi(getenv("SKV_ATTN_CFG")) : 0;
-  if (query_dtype == SKV_DTYPE_F16 && desc->head_dim == 128 && cfg_sel == 1) n = 11;
-  if (query_dtype == SKV_DTYPE_F16 && desc->head_dim == 128 && cfg_sel == 2) n = 7;
   return n;
 }
 
@@ -652,7 +690,8 @@ extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, in
   if (!desc || !counts || !plan) return SKV_ERR_INVALID;
   if (num_ctas <= 0 || num_ctas > kMaxCtas || desc->num_seqs > kMaxSeqs) return SKV_ERR_UNSUPPORTED;
   if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
-  attn_plan_kernel<<<1, 1024, 0, as_stream(stream)>>>(make_geom(*desc), counts, num_ctas, static_cast<int*>(plan));
+  attn_plan_kernel<<<1, 1024, 0, as_stream(stream)>>>(make_geom(*desc), counts, num_ctas, static_cast<int*>(plan),
+                                                      kTileFixedCost);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 
@@ -695,6 +734,8 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
   p.logits = logits;
   p.err = err_flag;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)desc->head_dim));
+  // timing probe, off unless SKV_ATTN_DEBUG is set: 1 = stream only (no arithmetic), 2 = arithmetic only
+  // (no copies), 3 = neither; results are meaningless in these modes
   static const int debug_mode = getenv("SKV_ATTN_DEBUG") ? atoi(getenv("SKV_ATTN_DEBUG")) : 0;
   p.debug_mode = debug_mode;
 #ifdef SKV_TIMELINE
@@ -713,7 +754,7 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
       for (int c = 0; c < num_ctas; ++c) if (host_tl[c * 16] && host_tl[c * 16] < t0) t0 = host_tl[c * 16];
       for (int c = 0; c < num_ctas; c += 13) {
         fprintf(stderr, "cta %3d:", c);
-        for (int k = 0; k < 12; ++k) fprintf(stderr, " %6lld", host_tl[c * 16 + k] ? (long long)(host_tl[c * 16 + k] - t0) : -1LL);
+        for (int k = 0; k < 14; ++k) fprintf(stderr, " %6lld", host_tl[c * 16 + k] ? (long long)(host_tl[c * 16 + k] - t0) : -1LL);
         fprintf(stderr, "\n");
       }
       unsigned long long tmax = 0;
@@ -723,12 +764,7 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
     }
   }
 #endif
-  static const int no_logits = getenv("SKV_ATTN_NOLOGITS") ? atoi(getenv("SKV_ATTN_NOLOGITS")) : 0;
-  if (no_logits) p.logits = nullptr;
   const bool precise = !p.q_is_half;
-  static const int cfg_sel = getenv("SKV_ATTN_CFG") ? atoi(getenv("SKV_ATTN_CFG")) : 0;
-  if (desc->head_dim == 128 && !precise && cfg_sel == 1) return launch_attn<128, false, AttnCfg<11, 3, 63360>>(p, as_stream(stream));
-  if (desc->head_dim == 128 && !precise && cfg_sel == 2) return launch_attn<128, false, AttnCfg<7, 3, 63360>>(p, as_stream(stream));
   if (desc->head_dim == 128)
     return precise ? launch_attn<128, true, AttnCfgPrecise>(p, as_stream(stream))
                    : launch_attn<128, false, AttnCfgFast>(p, as_stream(stream));
