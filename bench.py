@@ -38,6 +38,8 @@ if ROOT not in sys.path:
 CFG = dict(num_layers=32, num_q_heads=32, num_kv_heads=8, head_dim=128, batch=16, context=8192,
            memory_budget=0.35, available_bits=(2, 3, 4, 8), zipf_s=1.1, realloc_every=16)
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes one attention launch of this workload moved under ncu (188.50 MB read + 13.94 MB written)
+ATTN_DRAM_TRAFFIC_PER_LAUNCH = 202_440_000
 
 
 def measured_peak():
@@ -345,7 +347,10 @@ def run_ours(args):
                    "packed_bytes_per_step": int(step_bytes)},
         "decode_tokens_per_s": round(B * world * steps / (ms * 1e-3), 1),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
+                     "frac": round(achieved / peak, 4), "traffic": ATTN_DRAM_TRAFFIC_PER_LAUNCH,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
+                                       "profiles/decode_attn_kernel_config1_shape_2layers.md",
+                     "peak_source": peak_kind,
                      "kernel": "decode_attn_kernel", "kernel_ms": round(attn_ms, 4),
                      "timing": "CUDA event pair around every launch, un-graphed pass of the same steps",
                      "algorithmic_bytes_per_launch": int(per_layer_bytes)},
