@@ -182,6 +182,11 @@ def run_ours(args):
     store.cumulative.scatter_(1, dst[3].view(B, N).long(), torch.from_numpy(imp.astype(np.float64)).to(dev))
     alloc_cfg = store.make_alloc_config(cfg["memory_budget"], cfg["available_bits"], total_kv_heads=Hkv * world)
     importance_sync = ImportanceSync(store, dist if world > 1 else None)
+    if world > 1:
+        # first use of the communicator (connection set-up) happens here, not inside the timed region
+        warm = torch.zeros(1024, dtype=torch.float64, device=dev)
+        dist.all_reduce(warm)
+        torch.cuda.synchronize()
 
     def reallocate():
         importance_sync()              # KV-head shards: sum the per-shard importance first (no-op on 1 GPU)
