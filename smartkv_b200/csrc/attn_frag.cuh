@@ -1,30 +1,34 @@
-// Register-level unpack of packed K/V rows straight into mma.sync m16n8k16
-// fragments, for the fused decode-attention kernel.
+// Register-level unpack of packed K/V rows straight into mma.sync fragments, for the fused
+// decode-attention kernel.
 //
-// One 16-key tile (one KV head) sits in shared memory as 16 packed K rows,
-// row_bytes apart, and 16 packed V rows.  lane = 4*g + t.  Keys are the M
-// dimension of both products and the (up to 8) query heads of the GQA group
-// are the N dimension, so nothing of the 16x8 tile is padding:
+// One 16-key tile (one KV head) sits in shared memory as 16 packed K rows, row_bytes apart, and
+// 16 packed V rows.  lane = 4*g + t.
 //
-//  S^T[16 keys x 8 heads] = K (A operand, 16 x D)  x  Q^T (B operand, D x 8)
-//     Lane (g,t) supplies keys g and g+8, and of each the D/4 consecutive
-//     elements [t*D/4, (t+1)*D/4) -- its "K slice"; the B fragment is head g,
-//     same slice.  The order in which a slice's elements are fed to the k-steps
-//     is free as long as Q uses the same order, so each bit-width uses whichever
-//     order its cheapest bit extraction produces (kelem<BITS>() records it and
-//     the Q fragments are gathered through it).
+//  S[8 heads x 16 keys] = Q (A operand, rows = heads)  x  K^T (B operand, two n-tiles of 8 keys)
+//     2-, 4- and 8-bit keys: integer product, mma.sync.m16n8k32.s8.(u8|s8) on the stored
+//     (offset-binary) codes.  The query row of a head is split into two radix-128 int8 limbs; rows
+//     0..7 of the A operand hold limb 0 of the 8 heads, rows 8..15 limb 1, so one MMA yields both
+//     partial products and the score is 128 * c[row g] + c[row g+8].  The constant that the offset
+//     of the stored codes adds (2^(w-1) * sum of the limb) is folded into the accumulator's initial
+//     value.  3-bit keys: fp16 product, m16n8k16, rows 8..15 carry the fp16 residual of the query
+//     in the precise mode.
+//     Lane (g,t) supplies, for the B operand, key g (and g+8 for the second n-tile) and of it a
+//     "K slice" of D/4 elements.  The order in which a slice's elements are fed to the k-steps is
+//     free as long as Q uses the same order, so each bit-width uses whichever order its cheapest bit
+//     extraction produces (kelem<BITS>() / kelem_i8<BITS>() record it and the Q fragments are
+//     gathered through it).
+//     The accumulator of lane (g,t) holds head g, keys 2t, 2t+1 (and 2t+8, 2t+9): exactly the
+//     B-fragment layout of the next product, so nothing is transposed or shuffled in between.
 //
-//  O^T[D x 8 heads] = V^T (A operand, D x 16 keys)  x  P^T (B operand, 16 keys x 8)
-//     For m-tile j lane (g,t) supplies rows d = g*D/8 + 2j and d+1 for the key
-//     pairs (2t,2t+1) and (2t+8,2t+9); a half2 therefore pairs the SAME element
-//     of two different rows, which a byte permute of the two rows' words gives
-//     for free, in natural element order.  P^T comes from the S^T accumulator
-//     layout through movmatrix (8x8 b16 transpose).
+//  O^T[D x 8 heads] = V^T (A operand, D x 16 keys)  x  P^T (B operand, 16 keys x 8 heads)
+//     For m-tile j lane (g,t) supplies rows d = g*D/8 + 2j and d+1 for the key pairs (2t,2t+1) and
+//     (2t+8,2t+9); a half2 therefore pairs the SAME element of two different rows, which a byte
+//     permute of the two rows' words gives for free, in natural element order.
 //
-// Sub-byte fields become fp16 through the 0x6400 trick: OR a field that sits
-// at bit p (p+width <= 10) of a 16-bit lane into the mantissa of 1024.0, then
-// one HFMA2 computes (1024 + f*2^p) * 2^-p - (1024*2^-p + 2^(w-1)) = f - 2^(w-1)
-// exactly.  The two lanes of a register may use different p.
+// Sub-byte fields become fp16 through the 0x6400 trick: OR a field that sits at bit p
+// (p+width <= 10) of a 16-bit lane into the mantissa of 1024.0, then one HFMA2 computes
+// (1024 + f*2^p) * 2^-p - (1024*2^-p + 2^(w-1)) = f - 2^(w-1) exactly.  The two lanes of a
+// register may use different p.
 #pragma once
 
 #include "common.cuh"

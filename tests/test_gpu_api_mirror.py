@@ -253,3 +253,39 @@ def test_llama_wrapper_generates_and_tracks_the_dense_model():
     stats = wrapped.get_smartkv_stats()
     assert stats["realloc_count"] >= 1 and stats["memory_ratio_true"] <= 0.4 + 1e-6
     assert wrapped.smartkv_cache.store.counts.sum().item() == 24 + 39
+
+
+def test_tinyllama_shape_fused_decode_matches_dequantised_path():
+    """BASELINE config 2 scaled down in depth only: TinyLlama-1.1B attention shape (hidden 2048, 32 query /
+    4 KV heads, head_dim 64, vocab 32000), random N(0, 0.02) fp16 weights, 512 random prompt ids, budget 0.5.
+    The fused decode path (packed kernels, current token in full precision) and the dequantise-then-attend
+    path over the same cache must give the same next-token logits."""
+    transformers = pytest.importorskip("transformers")
+    from smartkv_b200 import LlamaSmartKV, SmartKVConfig
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=4,
+                                   num_attention_heads=32, num_key_value_heads=4, max_position_embeddings=2048,
+                                   initializer_range=0.02, bos_token_id=1, eos_token_id=2)
+    model = transformers.LlamaForCausalLM(cfg).cuda().half().eval()
+    ids = torch.randint(3, 32000, (1, 512), device="cuda")
+    wrapped = LlamaSmartKV(model, SmartKVConfig(enabled=True, memory_budget=0.5, device="cuda"))
+    steps = []
+    for fused in (True, False):
+        wrapped.reset_cache()
+        wrapped.set_use_fused_gpu(fused)
+        with torch.no_grad():
+            wrapped(ids[:, :-1])
+            logits = wrapped(ids[:, -1:]).logits[0, -1].float()
+        steps.append(logits)
+        stats = wrapped.get_smartkv_stats()
+        assert stats["num_tokens"] == 512 and stats["memory_ratio_true"] <= 0.5 + 1e-6
+        dist_ = stats["precision_distribution"]
+        assert sum(dist_.values()) == 512 and sum(1 for c in dist_.values() if c > 0) >= 2     # mixed widths
+    assert torch.allclose(steps[0], steps[1], atol=2e-2, rtol=2e-2), float((steps[0] - steps[1]).abs().max())
+    assert int(steps[0].argmax()) == int(steps[1].argmax())
+    wrapped.set_use_fused_gpu(True)
+    wrapped.reset_cache()
+    with torch.no_grad():
+        out = wrapped.generate(ids, max_new_tokens=24, do_sample=False)
+    assert out.shape == (1, 512 + 24)
+    assert wrapped.smartkv_cache.store.counts.sum().item() == 512 + 23
