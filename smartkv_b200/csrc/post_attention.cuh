@@ -101,8 +101,23 @@ __device__ __forceinline__ void combine_unit(const CombineParams& p, int unit, C
                                  : static_cast<const float*>(p.cur_k)[kv];
     prod = q * k;
   }
+  // (max, sum) headers of this thread's share of the partials: one 8-byte load each, kept in registers
+  // when the segment has at most kCombineChunk partials (the usual case), so that the chain of
+  // dependent loads is plan -> headers -> rows and nothing more
+  constexpr int kHdrRegs = kCombineChunk / 64;  // D >= 64
+  const bool small = nsplit <= kCombineChunk;
+  float2 hdr[kHdrRegs];
   float mloc = -INFINITY;
-  for (int k = d; k < nsplit; k += D) mloc = fmaxf(mloc, base[(long long)k * pstride]);
+  if (small) {
+#pragma unroll
+    for (int j = 0; j < kHdrRegs; ++j) {
+      const int k = d + j * D;
+      hdr[j] = k < nsplit ? *reinterpret_cast<const float2*>(base + (long long)k * pstride) : make_float2(-INFINITY, 0.f);
+      mloc = fmaxf(mloc, hdr[j].x);
+    }
+  } else {
+    for (int k = d; k < nsplit; k += D) mloc = fmaxf(mloc, base[(long long)k * pstride]);
+  }
   const float s_cur = head_dot(prod, sub, d, D, sh.red, 0) * p.scale_log2;
   {
     const float m = warp_max(mloc);
@@ -121,16 +136,28 @@ __device__ __forceinline__ void combine_unit(const CombineParams& p, int unit, C
   for (int c0 = 0; c0 < nsplit; c0 += kCombineChunk) {
     const int cn = (nsplit - c0) < kCombineChunk ? (nsplit - c0) : kCombineChunk;
     __syncthreads();
-    for (int k = d; k < cn; k += D) {
-      const float* row = base + (long long)(c0 + k) * pstride;
-      const float mw = row[0];
-      const float f = mw == -INFINITY ? 0.f : ex2f(mw - M);
-      sh.f[sub][k] = f;
-      sh.lf[sub][k] = f == 0.f ? 0.f : row[1] * f;
+    if (small) {
+#pragma unroll
+      for (int j = 0; j < kHdrRegs; ++j) {
+        const int k = d + j * D;
+        if (k < cn) {
+          const float f = hdr[j].x == -INFINITY ? 0.f : ex2f(hdr[j].x - M);
+          sh.f[sub][k] = f;
+          sh.lf[sub][k] = f == 0.f ? 0.f : hdr[j].y * f;
+        }
+      }
+    } else {
+      for (int k = d; k < cn; k += D) {
+        const float* row = base + (long long)(c0 + k) * pstride;
+        const float mw = row[0];
+        const float f = mw == -INFINITY ? 0.f : ex2f(mw - M);
+        sh.f[sub][k] = f;
+        sh.lf[sub][k] = f == 0.f ? 0.f : row[1] * f;
+      }
     }
     __syncthreads();
     const float* col = base + (long long)c0 * pstride + 2 + d;
-#pragma unroll 8
+#pragma unroll 16
     for (int k = 0; k < cn; ++k) {
       const float f = sh.f[sub][k];
       const float x = col[(long long)k * pstride];  // a partial without keys holds stale bytes: select, not multiply
@@ -247,23 +274,31 @@ __device__ __forceinline__ void importance_unit(const ImportanceParams& p, int c
     for (int i = 0; i < kNumBuckets; ++i) valid |= (s >= g.bucket_base[i] && s < g.bucket_base[i] + cnt[i]);
   }
   float mass = 0.f;
-  bool write = false;
+  const bool is_cur = !valid && has_cur && s == cur_slot;
+  const bool write = valid || is_cur;
+  const long long ci = (long long)b * g.slots + s;
+  const long long li = ((long long)p.layer * g.num_seqs + b) * g.slots + s;
+  // the state this thread updates is fetched before the logits so that the two latencies overlap
+  double cum = 0.0;
+  float ema = 0.f;
+  uint8_t seen = 0;
+  if (write) {
+    cum = p.cumulative[ci];
+    ema = p.layer_ema[li];
+    seen = p.touched[li];
+  }
   if (valid) {
     const float* lg = p.logits + (long long)b * Hq * g.slots + s;
-#pragma unroll 8
+#pragma unroll 16
     for (int h = 0; h < Hq; ++h) mass += sh.w[h] * ex2f(lg[(long long)h * g.slots] - sh.mx[h]);
-    write = true;
-  } else if (has_cur && s == cur_slot) {
+  } else if (is_cur) {
     // the newest token: it is stored at this storage index when the step's append commits
     for (int h = 0; h < Hq; ++h) mass += sh.w[h] * sh.cprob[h];
-    write = true;
   }
   if (write) {
-    const long long ci = (long long)b * g.slots + s;
-    p.cumulative[ci] += (double)mass;
-    const long long li = ((long long)p.layer * g.num_seqs + b) * g.slots + s;
-    if (p.touched[li]) {
-      p.layer_ema[li] = p.decay * p.layer_ema[li] + (1.0f - p.decay) * mass;
+    p.cumulative[ci] = cum + (double)mass;
+    if (seen) {
+      p.layer_ema[li] = p.decay * ema + (1.0f - p.decay) * mass;
     } else {
       p.layer_ema[li] = mass;
       p.touched[li] = 1;
