@@ -196,6 +196,8 @@ int skv_decode_attention_static(const SkvStoreDesc* desc, const void* store, int
  *   probability) an earlier combine wrote for layer imp_layer.  They must not alias this launch's
  *   lse_max / lse_sum / cur_prob outputs (callers double-buffer them).  imp_logits == NULL skips the
  *   importance update; dst_seq == NULL skips the append (store may then be NULL).
+ *   max_seq_tokens: an upper bound of the cached tokens of any sequence if the caller knows one (the
+ *   importance blocks are then launched for that many storage indices only), 0 otherwise.
  * No counterpart in the reference, which runs these steps as host Python
  * (smartkv/core/fused_cpu.py:115-167, cache.py:216-279, :1187-1355). */
 int skv_post_attention(const SkvStoreDesc* desc, void* store, int layer, const void* plan, const void* query,
@@ -205,7 +207,7 @@ int skv_post_attention(const SkvStoreDesc* desc, void* store, int layer, const v
                        const float* imp_lse_sum, const float* imp_cur_prob, const int32_t* cur_slot,
                        float* head_state, int parity, double* cumulative, float* layer_ema, uint8_t* touched,
                        float decay, float head_decay, const int32_t* dst_seq, const int32_t* dst_bucket,
-                       const int32_t* dst_pos, int32_t* err_flag, void* stream);
+                       const int32_t* dst_pos, int max_seq_tokens, int32_t* err_flag, void* stream);
 
 /* ---- importance ----------------------------------------------------------- */
 

@@ -72,7 +72,7 @@ _SIGNATURES = {
                                    c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                    c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p,
-                                   c_void_p, c_void_p]),
+                                   c_int, c_void_p, c_void_p]),
     "skv_attn_plan": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p]),
     "skv_decode_attention": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p]),

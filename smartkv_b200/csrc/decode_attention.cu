@@ -474,6 +474,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     int stg = 0, qi = 0;
     uint32_t epar = 1, qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
     const int kbt[kNumBuckets] = {KBT0, KBT1, KBT2, KBT3};
+    const uint64_t stream_policy = l2_evict_first_policy();  // the cache is read once per step
     constexpr int NL = Slot::NLIMB;
     constexpr int EPL = D / 32;  // query elements per lane and head
     // issues up to `limit` further blocks of run d, resuming at (bucket ci, tile ct0)
@@ -495,9 +496,9 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
             const uint32_t kbytes = (uint32_t)(n16 * pd), sbytes = (uint32_t)(n16 * 8);
             fence_proxy_async();
             mbar_expect_tx(&full[stg], 2 * kbytes + sbytes);
-            bulk_g2s(sb, arena + g.k_off[ci] + row * pd, kbytes, &full[stg]);
-            bulk_g2s(sb + kbkeys * pd, arena + g.v_off[ci] + row * pd, kbytes, &full[stg]);
-            bulk_g2s(sb + 2 * kbkeys * pd, arena + g.sc_off[ci] + row * 8, sbytes, &full[stg]);
+            bulk_g2s_hint(sb, arena + g.k_off[ci] + row * pd, kbytes, &full[stg], stream_policy);
+            bulk_g2s_hint(sb + kbkeys * pd, arena + g.v_off[ci] + row * pd, kbytes, &full[stg], stream_policy);
+            bulk_g2s_hint(sb + 2 * kbkeys * pd, arena + g.sc_off[ci] + row * 8, sbytes, &full[stg], stream_policy);
           } else if (lane == 0) {
             mbar_arrive(&full[stg]);
           }

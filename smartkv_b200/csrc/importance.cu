@@ -18,7 +18,7 @@ namespace skv {
 // grid = (ceil(slots / 256), num_seqs)
 __global__ void __launch_bounds__(kPostThreads) importance_update_kernel(const ImportanceParams p) {
   __shared__ ImportanceShared sh;
-  importance_unit(p, blockIdx.x, blockIdx.y, sh);
+  importance_unit(p, blockIdx.x, blockIdx.y, blockIdx.x == 0, sh);
 }
 
 }  // namespace skv

@@ -12,6 +12,7 @@ struct PostParams {
   AppendParams app;
   int combine_blocks;
   int imp_chunks;      // importance blocks = imp_chunks * num_seqs (0: no importance update)
+  int imp_compact;     // 1: block j of a sequence takes that sequence's j-th live chunk
   int append_blocks;   // 8 rows-of-a-head per block (0: no append)
 };
 
@@ -31,7 +32,10 @@ __global__ void __launch_bounds__(kPostThreads) post_attention_kernel(const Post
   blk -= p.combine_blocks;
   const int imp_blocks = p.imp_chunks * p.c.g.num_seqs;
   if (blk < imp_blocks) {
-    importance_unit(p.imp, blk % p.imp_chunks, blk / p.imp_chunks, sh.i);
+    const int b = blk / p.imp_chunks, j = blk - b * p.imp_chunks;
+    // a compact grid walks the live chunks only; the full grid visits every chunk
+    const int chunk = p.imp_compact ? live_chunk(p.c.g, p.imp.counts + b * kNumBuckets, j) : j;
+    if (chunk >= 0) importance_unit(p.imp, chunk, b, j == 0, sh.i);
     return;
   }
   blk -= imp_blocks;
@@ -52,7 +56,7 @@ extern "C" int skv_post_attention(const SkvStoreDesc* desc, void* store, int lay
                                   float* head_state, int parity,
                                   double* cumulative, float* layer_ema, uint8_t* touched, float decay,
                                   float head_decay, const int32_t* dst_seq, const int32_t* dst_bucket,
-                                  const int32_t* dst_pos, int32_t* err_flag, void* stream) {
+                                  const int32_t* dst_pos, int max_seq_tokens, int32_t* err_flag, void* stream) {
   if (!desc || !plan || !query || !partials || !out) return SKV_ERR_INVALID;
   if (layer < 0 || layer >= desc->num_layers || num_ctas <= 0) return SKV_ERR_INVALID;
   if (num_q_heads % desc->num_kv_heads != 0 || num_q_heads > kMaxQHeads) return SKV_ERR_INVALID;
@@ -109,6 +113,14 @@ extern "C" int skv_post_attention(const SkvStoreDesc* desc, void* store, int lay
     i.decay = decay;
     i.head_decay = head_decay;
     p.imp_chunks = (desc->slots + kPostThreads - 1) / kPostThreads;
+    if (max_seq_tokens > 0) {
+      // live chunks of a sequence: its tokens spread over the buckets, every bucket may begin and end inside a chunk
+      const int compact = (max_seq_tokens + 1 + kPostThreads - 1) / kPostThreads + 2 * kNumBuckets + 2;
+      if (compact < p.imp_chunks) {
+        p.imp_chunks = compact;
+        p.imp_compact = 1;
+      }
+    }
   }
   if (with_append) {
     AppendParams& a = p.app;

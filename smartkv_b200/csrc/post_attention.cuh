@@ -208,8 +208,34 @@ struct ImportanceShared {
   float cprob[kMaxQHeads];  // pc (unnormalised probability of the current token)
 };
 
+// Maps the j-th *live* chunk of sequence b (chunks of kPostThreads storage indices that hold a cached
+// key or the slot the current token will take) to its chunk index; -1 when j is past the last one.
+// Buckets lie at increasing storage indices, so their chunk ranges are increasing and only neighbours can
+// share a chunk.  j == 0 always maps to a chunk (chunk 0 if nothing is live): that block publishes the
+// head-importance EMA.
+__device__ __forceinline__ int live_chunk(const StoreGeom& g, const int32_t* counts4, int j) {
+  int prev_last = -1, seen = 0;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) {
+    const int cnt = counts4[i] + 1;  // + the slot a token appended this step would take
+    if (g.cap[i] == 0) continue;
+    int first = g.bucket_base[i] / kPostThreads;
+    const int last = (g.bucket_base[i] + cnt - 1) / kPostThreads;
+    if (first <= prev_last) first = prev_last + 1;
+    if (last >= first) {
+      const int n = last - first + 1;
+      if (j < seen + n) return first + (j - seen);
+      seen += n;
+      prev_last = last;
+    }
+  }
+  return (j == 0 && seen == 0) ? 0 : -1;
+}
+
 // One unit = 256 consecutive storage indices of one sequence; blockDim.x == kPostThreads.
-__device__ __forceinline__ void importance_unit(const ImportanceParams& p, int chunk, int b, ImportanceShared& sh) {
+// `publish` marks the one block per sequence that writes the new head-importance EMA.
+__device__ __forceinline__ void importance_unit(const ImportanceParams& p, int chunk, int b, bool publish,
+                                                ImportanceShared& sh) {
   const StoreGeom& g = p.g;
   const int tid = threadIdx.x, Hq = p.num_q_heads;
   int cnt[kNumBuckets];
@@ -224,9 +250,9 @@ __device__ __forceinline__ void importance_unit(const ImportanceParams& p, int c
   const int total_keys = nkeys + (has_cur ? 1 : 0);
 
   // most storage indices of a sequence are unused capacity: a block without a live key leaves at once
-  // (chunk 0 of every sequence stays, it publishes the head-importance EMA)
+  // (the publishing block of every sequence stays)
   const int s_lo = chunk * kPostThreads, s_hi = s_lo + kPostThreads;
-  bool block_live = chunk == 0 || (has_cur && cur_slot >= s_lo && cur_slot < s_hi);
+  bool block_live = publish || (has_cur && cur_slot >= s_lo && cur_slot < s_hi);
 #pragma unroll
   for (int i = 0; i < kNumBuckets; ++i)
     block_live |= cnt[i] > 0 && g.bucket_base[i] < s_hi && g.bucket_base[i] + cnt[i] > s_lo;
@@ -250,7 +276,7 @@ __device__ __forceinline__ void importance_unit(const ImportanceParams& p, int c
   if (tid < Hq) {
     hn = hs_old[tid] * p.head_decay + head_mean * (1.0f - p.head_decay);
     sh.mx[tid] = hn;  // staged, replaced below
-    if (chunk == 0) hs_new[tid] = hn;
+    if (publish) hs_new[tid] = hn;
   }
   __syncthreads();
   float my_w = 0.f;

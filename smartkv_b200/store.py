@@ -103,6 +103,7 @@ class PackedKVStore:
         self.rank_pct = torch.zeros((num_seqs, self.slots), dtype=torch.float64, device=dev)
         self.rank_streak = torch.full((num_seqs, self.slots), -1, dtype=torch.int8, device=dev)
         self.appended_total = 0  # rows ever appended over all sequences (host-side upper bound of live tokens)
+        self.max_seq_tokens = 0  # upper bound of the cached tokens of any one sequence (host side)
         self._realloc = None
         self.head_parity = 0
         self._bits_lut = torch.full((9,), -1, dtype=torch.int32, device=dev)
@@ -156,6 +157,7 @@ class PackedKVStore:
         self._plan_valid = False
         self.next_token += n
         self.appended_total += B * n
+        self.max_seq_tokens += n
         dst_seq = self._seq_ids[:, None].expand(B, n).contiguous().view(-1)
         return dst_seq, bucket.contiguous().view(-1), pos.contiguous().view(-1), storage
 
@@ -179,6 +181,7 @@ class PackedKVStore:
         self.counts.scatter_add_(1, bucket.long()[:, None], torch.ones((self.num_seqs, 1), dtype=torch.int32, device=self.device))
         self.next_token += 1
         self.appended_total += self.num_seqs
+        self.max_seq_tokens += 1
         self._plan_valid = False
 
     # ------------------------------------------------------------------ kernels
@@ -276,8 +279,8 @@ class PackedKVStore:
             ptr(pb["lse_max"]) if pend is not None else None, ptr(pb["lse_sum"]) if pend is not None else None,
             ptr(pb["cur_prob"]) if pend is not None else None, ptr(pend["storage"]) if pend is not None else None,
             ptr(self.head_state), self.head_parity, ptr(self.cumulative), ptr(self.layer_ema), ptr(self.touched),
-            self.decay, self.head_decay, ptr(dst_seq), ptr(dst_bucket), ptr(dst_pos), ptr(self.err), st),
-            "skv_post_attention")
+            self.decay, self.head_decay, ptr(dst_seq), ptr(dst_bucket), ptr(dst_pos), self.max_seq_tokens,
+            ptr(self.err), st), "skv_post_attention")
         if pend is not None:
             self.head_parity ^= 1
         pipe["pending"] = {"layer": layer, "buf": cur, "storage": storage} if want_logits else None
