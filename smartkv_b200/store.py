@@ -175,7 +175,8 @@ class PackedKVStore:
     def commit_step(self, plan):
         self.flush_importance()          # reads the counts as they stood during the step
         if getattr(self, "_pipe", None) is not None:
-            self._pipe["next"] = 0       # every step starts on the same buffer set (CUDA graph replays rely on it)
+            self._pipe["calls"] = 0      # every step starts on the same buffer set (CUDA graph replays rely on it)
+            self._pipe["post_events"] = []
         _seq, bucket, _pos, storage = plan
         self.slot_token.scatter_(1, storage.long()[:, None], self.next_token[:, None])
         self.counts.scatter_add_(1, bucket.long()[:, None], torch.ones((self.num_seqs, 1), dtype=torch.int32, device=self.device))
@@ -242,25 +243,35 @@ class PackedKVStore:
 
     def decode_layer(self, layer: int, query: torch.Tensor, cur_k: torch.Tensor, cur_v: torch.Tensor, step_plan,
                      update_importance: bool = True, out: Optional[torch.Tensor] = None,
-                     kernel_events=None) -> torch.Tensor:
+                     kernel_events=None, overlap: bool = False) -> torch.Tensor:
         """One layer of a decode step in two launches: the streaming attention kernel, then one kernel
         with this layer's combine, the append of the new token (``step_plan`` from plan_step) and the
         importance update of the PREVIOUS decode_layer call (skv_post_attention).  The last layer's
         importance update is flushed by commit_step / flush_importance.  Same results as
-        attention(...) followed by append(...)."""
+        attention(...) followed by append(...).
+
+        ``overlap``: the second launch goes to a side stream, so that it runs while the NEXT layer's attention
+        kernel is already starting (it fills the SMs that kernel's CTAs leave early); the attention kernel of
+        call m then only waits for the side work of call m-2 (partials are double, logits triple buffered).
+        The outputs of such a call are ready after join() / commit_step()."""
         q = query.contiguous()
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
-        st = self._stream()
         if not self._plan_valid:
             self.build_plan()
         pipe = self._pipe_buffers()
-        cur = pipe["next"]
-        bufs = pipe["bufs"][cur]
+        m = pipe["calls"]
+        lslot, pslot = m % 3, (m % 2 if overlap else 0)
+        bufs = pipe["bufs"][lslot]
+        partials = pipe["partials"][pslot]
+        main = torch.cuda.current_stream(self.device)
+        if overlap and len(pipe["post_events"]) >= 2:
+            main.wait_event(pipe["post_events"][-2])      # the buffers this call reuses are free again
+        st = self._stream()
         if kernel_events is not None:
             kernel_events[0].record()
         check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q),
-                                            self._dtype_code(q), self.num_q_heads, ptr(self.partials), self.num_ctas,
+                                            self._dtype_code(q), self.num_q_heads, ptr(partials), self.num_ctas,
                                             ptr(bufs["logits"]) if want_logits else None, ptr(self.err), st),
               "skv_decode_attention")
         if kernel_events is not None:
@@ -271,45 +282,74 @@ class PackedKVStore:
         dst_seq, dst_bucket, dst_pos, storage = step_plan
         pend = pipe["pending"]
         pb = pipe["bufs"][pend["buf"]] if pend is not None else None
-        check(self.lib.skv_post_attention(
-            ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q), self._dtype_code(q),
-            self.num_q_heads, ptr(self.partials), self.num_ctas, ptr(cur_k), ptr(cur_v), self._dtype_code(cur_k),
-            ptr(out), ptr(bufs["lse_max"]), ptr(bufs["lse_sum"]), ptr(bufs["cur_prob"]), ptr(self.counts),
-            pend["layer"] if pend is not None else 0, ptr(pb["logits"]) if pend is not None else None,
-            ptr(pb["lse_max"]) if pend is not None else None, ptr(pb["lse_sum"]) if pend is not None else None,
-            ptr(pb["cur_prob"]) if pend is not None else None, ptr(pend["storage"]) if pend is not None else None,
-            ptr(self.head_state), self.head_parity, ptr(self.cumulative), ptr(self.layer_ema), ptr(self.touched),
-            self.decay, self.head_decay, ptr(dst_seq), ptr(dst_bucket), ptr(dst_pos), self.max_seq_tokens,
-            ptr(self.err), st), "skv_post_attention")
+
+        def post(stream_ptr):
+            check(self.lib.skv_post_attention(
+                ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q), self._dtype_code(q),
+                self.num_q_heads, ptr(partials), self.num_ctas, ptr(cur_k), ptr(cur_v), self._dtype_code(cur_k),
+                ptr(out), ptr(bufs["lse_max"]), ptr(bufs["lse_sum"]), ptr(bufs["cur_prob"]), ptr(self.counts),
+                pend["layer"] if pend is not None else 0, ptr(pb["logits"]) if pend is not None else None,
+                ptr(pb["lse_max"]) if pend is not None else None, ptr(pb["lse_sum"]) if pend is not None else None,
+                ptr(pb["cur_prob"]) if pend is not None else None, ptr(pend["storage"]) if pend is not None else None,
+                ptr(self.head_state), self.head_parity, ptr(self.cumulative), ptr(self.layer_ema), ptr(self.touched),
+                self.decay, self.head_decay, ptr(dst_seq), ptr(dst_bucket), ptr(dst_pos), self.max_seq_tokens,
+                ptr(self.err), stream_ptr), "skv_post_attention")
+
+        if overlap:
+            side = pipe["side"]
+            done = torch.cuda.Event()
+            done.record(main)
+            side.wait_event(done)
+            with torch.cuda.stream(side):
+                post(self._stream())
+                ev = torch.cuda.Event()
+                ev.record(side)
+            pipe["post_events"].append(ev)
+            pipe["forked"] = True
+        else:
+            post(st)
         if pend is not None:
             self.head_parity ^= 1
-        pipe["pending"] = {"layer": layer, "buf": cur, "storage": storage} if want_logits else None
-        pipe["next"] = cur ^ 1
+        pipe["pending"] = {"layer": layer, "buf": lslot, "storage": storage} if want_logits else None
+        pipe["calls"] = m + 1
         self.lse_max, self.lse_sum, self.cur_prob = bufs["lse_max"], bufs["lse_sum"], bufs["cur_prob"]
         return out
 
     def _pipe_buffers(self):
-        """Two sets of (logits, max, sum, current-token probability): the importance update of a layer runs
-        one launch after its attention, while the next layer's attention already writes the other set."""
+        """Three sets of (logits, max, sum, current-token probability) and two of partials: the importance
+        update of a layer runs one launch after its attention, and with ``overlap`` that launch may still be
+        running while the next layer's attention kernel writes the following set."""
         if getattr(self, "_pipe", None) is None:
             dev, B, Hq = self.device, self.num_seqs, self.num_q_heads
             bufs = []
-            for i in range(2):
+            for i in range(3):
                 bufs.append({
                     "logits": (self.logits if i == 0 else torch.empty_like(self.logits)) if self.track_importance else None,
                     "lse_max": torch.empty((B, Hq), dtype=torch.float32, device=dev),
                     "lse_sum": torch.empty((B, Hq), dtype=torch.float32, device=dev),
                     "cur_prob": torch.empty((B, Hq), dtype=torch.float32, device=dev),
                 })
-            self._pipe = {"bufs": bufs, "next": 0, "pending": None}
+            self._pipe = {"bufs": bufs, "partials": [self.partials, torch.empty_like(self.partials)], "calls": 0,
+                          "pending": None, "side": torch.cuda.Stream(device=dev), "post_events": [], "forked": False}
         return self._pipe
+
+    def join(self):
+        """Makes the current stream wait for side-stream work of decode_layer(overlap=True) calls."""
+        pipe = getattr(self, "_pipe", None)
+        if pipe is None or not pipe["forked"]:
+            return
+        torch.cuda.current_stream(self.device).wait_event(pipe["post_events"][-1])
+        pipe["forked"] = False
 
     def flush_importance(self):
         """Runs the importance update still owed by the last decode_layer call (no-op otherwise)."""
         pipe = getattr(self, "_pipe", None)
-        if pipe is None or pipe["pending"] is None:
+        if pipe is None:
             return
+        self.join()
         pend = pipe["pending"]
+        if pend is None:
+            return
         pb = pipe["bufs"][pend["buf"]]
         check(self.lib.skv_importance_update(ctypes.byref(self.desc), pend["layer"], ptr(self.counts), self.num_q_heads,
                                              ptr(pb["logits"]), ptr(pb["lse_max"]), ptr(pb["lse_sum"]),

@@ -17,7 +17,7 @@ def _pair(B, hq, hkv, d, n, L, seed):
     for l in range(L):
         k, v = orc.synth_kv(B * n, hkv, d, seed=seed * 10 + l)
         kvs.append((k.reshape(B, n, hkv, d), v.reshape(B, n, hkv, d)))
-    for _ in range(2):
+    for _ in range(3):
         s = make_store(L, B, hkv, d, hq, n + 8)
         fill_store(s, kvs, bits)
         stores.append(s)
@@ -28,9 +28,10 @@ def _pair(B, hq, hkv, d, n, L, seed):
                                               (4, 4, 64, np.float16)])
 def test_fused_post_attention_equals_separate_calls(hq, hkv, d, q_dtype):
     B, n, L = 3, 700, 2
-    (a, b), rng = _pair(B, hq, hkv, d, n, L, seed=hq + d)
+    (a, b, c), rng = _pair(B, hq, hkv, d, n, L, seed=hq + d)
     for step in range(3):
-        plan_a, plan_b = a.plan_step(), b.plan_step()
+        plan_a, plan_b, plan_c = a.plan_step(), b.plan_step(), c.plan_step()
+        outs_a, outs_c = [], [torch.empty((B, hq, d), dtype=torch.float32, device="cuda") for _ in range(L)]
         for l in range(L):
             q = torch.from_numpy(rng.standard_normal((B, hq, d)).astype(q_dtype)).cuda()
             ck = torch.from_numpy(rng.standard_normal((B, hkv, d)).astype(np.float32)).cuda()
@@ -38,22 +39,30 @@ def test_fused_post_attention_equals_separate_calls(hq, hkv, d, q_dtype):
             out_a = a.attention(l, q, ck, cv, update_importance=True, cur_storage=plan_a[3]).clone()
             a.append(l, ck, cv, plan_a[0], plan_a[1], plan_a[2])
             out_b = b.decode_layer(l, q, ck, cv, plan_b, update_importance=True).clone()
+            # third store: the post-attention launch on a side stream, overlapping the next layer's attention
+            c.decode_layer(l, q, ck, cv, plan_c, update_importance=True, out=outs_c[l], overlap=True)
+            outs_a.append(out_a)
             assert torch.equal(out_a, out_b), (step, l)
             assert torch.equal(a.lse_max, b.lse_max) and torch.equal(a.lse_sum, b.lse_sum)
             assert torch.equal(a.cur_prob, b.cur_prob)
         a.commit_step(plan_a)
         b.commit_step(plan_b)
-        a.check_errors(); b.check_errors()
-        assert torch.equal(a.counts, b.counts)
+        c.commit_step(plan_c)
+        a.check_errors(); b.check_errors(); c.check_errors()
+        for l in range(L):
+            assert torch.equal(outs_a[l], outs_c[l]), (step, l, "overlap")
+        assert torch.equal(a.cumulative, c.cumulative) or torch.allclose(a.cumulative, c.cumulative, rtol=1e-6, atol=1e-12)
+        assert torch.allclose(a.layer_ema, c.layer_ema, rtol=1e-5, atol=1e-9) and torch.equal(a.touched, c.touched)
+        assert torch.equal(a.counts, b.counts) and torch.equal(a.counts, c.counts)
         assert torch.allclose(a.cumulative, b.cumulative, rtol=1e-6, atol=1e-12)
         assert torch.allclose(a.layer_ema, b.layer_ema, rtol=1e-5, atol=1e-9)
         assert torch.equal(a.touched, b.touched)
         assert torch.allclose(a.head_state, b.head_state, rtol=1e-6)
-    assert torch.equal(a.arena, b.arena)            # the appended rows are byte-identical
+    assert torch.equal(a.arena, b.arena) and torch.equal(a.arena, c.arena)   # the appended rows are byte-identical
 
 
 def test_fused_post_attention_without_importance_or_append():
-    (a, b), rng = _pair(2, 8, 2, 128, 300, 1, seed=3)
+    (a, b, _), rng = _pair(2, 8, 2, 128, 300, 1, seed=3)
     q = torch.from_numpy(rng.standard_normal((2, 8, 128)).astype(np.float16)).cuda()
     ck = torch.from_numpy(rng.standard_normal((2, 2, 128)).astype(np.float32)).cuda()
     cv = torch.from_numpy(rng.standard_normal((2, 2, 128)).astype(np.float32)).cuda()
