@@ -462,8 +462,11 @@ def run_reference(args):
         "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(step_ms, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic (seeded N(0,1) K/V, 4 outlier channels x8 per head, Zipf(1.1) importance)",
-        "config": {"workload": "BASELINE config 1 shape; each step a bounded sample: one (sequence, layer) at the full "
-                               "context on the host cores, ms_per_step scaled by batch x layers"},
+        "config": {"workload": f"BASELINE config 1: Llama-3.1-8B attention shape, {cfg['num_layers']} layers, batch 16, "
+                               "context 8192, budget 0.35, bits [2,3,4,8], fp16 query; one decode step per step",
+                   "sample": "each step is a bounded sample of that workload on the host cores: one (sequence, layer) at "
+                             "the full context, one allocator call and one requantisation; ms_per_step and value are "
+                             "scaled to batch x layers with the reallocation amortised over 16 steps"},
         "cpu_baseline": base,
         "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": round(time.perf_counter() - t0, 1),
