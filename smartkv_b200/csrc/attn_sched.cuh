@@ -2,10 +2,11 @@
 // (sequence, KV head) segment a persistent CTA owns.
 //
 // Every segment is a string of cost units: for each bucket in turn, ceil(count/16) tiles of
-// tile_cost(bucket) = tile_bytes(bucket) + a fixed term, tile_bytes = 16 * (2*row_bytes + 8)
-// (packed K rows, V rows and a float2 of scales per key).  The fixed term stands for the
-// per-tile arithmetic, which is the same for every width: narrow tiles are bound by it, 8-bit
-// tiles by their bytes.  All heads of a sequence have the same length W[b].
+// tile_cost(bucket), the time one CTA needs per tile of that width (measured with every token at
+// that width: narrow tiles are bound by their arithmetic, 8-bit tiles by their bytes; 3-bit tiles
+// pay for the fp16 score path).  tile_bytes = 16 * (2*row_bytes + 8) (packed K rows, V rows and a
+// float2 of scales per key) is what a tile occupies in a stage.  All heads of a sequence have the
+// same length W[b].
 // The global string concatenates the segments in (sequence, head) order; CTA c
 // owns the tiles whose first unit lies in [ceil(c*T/C), ceil((c+1)*T/C)), i.e. the
 // CTAs are balanced by estimated time and never share a tile.  A maximal piece of one
@@ -24,10 +25,11 @@ __host__ __device__ constexpr int tile_bytes_for(int head_dim, int bits) {
   return 16 * (2 * row_bytes_for(head_dim, bits) + 8);
 }
 
-// fixed cost of a tile in byte-equivalents (time of its arithmetic x the per-SM share of the bandwidth)
-constexpr int kTileFixedCost = 3072;
+// nanoseconds one CTA spends per tile of each width at head_dim 128 (B200, all tokens at one width:
+// 48.5 / 57.7 / 49.7 / 64.5 us per launch of 65,536 tiles on 148 CTAs); only the ratios matter
+constexpr int kTileFixedCost = 0;  // kept for the plan kernel's signature
 __host__ __device__ constexpr int tile_cost_for(int head_dim, int bits, int fixed) {
-  return tile_bytes_for(head_dim, bits) + fixed;
+  return (bits == 2 ? 110 : bits == 3 ? 130 : bits == 4 ? 112 : 146) + fixed + 0 * head_dim;
 }
 
 struct SegLayout {

@@ -369,59 +369,72 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
-// The query rows of one head of a run: fp16 copy (plus a residual row in the precise mode) and
-// radix-128 int8 limbs with their row sums.  One warp per call.
+// The query rows of a run: fp16 copy (plus a residual row in the precise mode) and radix-128 int8
+// limbs with their row sums.  One warp per call, heads [gq0, gq1) (at most 8); every head's elements are
+// fetched before any is processed, so the call costs one round trip to memory, not one per head.
 template <int D, bool PRECISE>
-__device__ __forceinline__ void prep_query_head(QSlot<D, PRECISE>& slot, const AttnParams& p, int seq, int head,
-                                                int G, int gq, int lane) {
+__device__ __forceinline__ void prep_query_heads(QSlot<D, PRECISE>& slot, const AttnParams& p, int seq, int head,
+                                                 int G, int gq0, int gq1, int lane) {
   constexpr int NL = QSlot<D, PRECISE>::NLIMB;
   constexpr int EPL = D / 32;  // query elements per lane and head
   const long long q_off = ((long long)seq * p.num_q_heads + (long long)head * G) * D;
-  float q[EPL];
-  float amax = 0.f;
+  float q[8][EPL];
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) {
-    const long long idx = q_off + (long long)gq * D + lane * EPL + e;
-    q[e] = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[idx])
-                       : static_cast<const float*>(p.query)[idx];
-    amax = fmaxf(amax, fabsf(q[e]));
-  }
-  amax = warp_max(amax);
-  float range = 127.f;
+  for (int i = 0; i < 8; ++i) {
+    const int gq = gq0 + i;
+    if (gq < gq1) {
 #pragma unroll
-  for (int l = 1; l < NL; ++l) range *= 128.f;
-  const float step = amax > 0.f ? amax / range : 1.f;
-  const float inv = 1.f / step;
-  int sum[NL];
-#pragma unroll
-  for (int l = 0; l < NL; ++l) sum[l] = 0;
-#pragma unroll
-  for (int e = 0; e < EPL; ++e) {
-    const int d_idx = lane * EPL + e;
-    const __half qh = __float2half_rn(q[e]);
-    slot.qh[gq][d_idx] = qh;
-    if (PRECISE) slot.qh[gq + 8][d_idx] = __float2half_rn(q[e] - __half2float(qh));
-    float rem = fminf(fmaxf(rintf(q[e] * inv), -range), range);  // integer in [-range, range]
-#pragma unroll
-    for (int l = NL - 1; l >= 1; --l) {
-      const float hi = rintf(rem * (1.f / 128.f));
-      const int low = (int)(rem - hi * 128.f);  // in [-64, 64]
-      slot.limb[l][gq][d_idx] = (int8_t)low;
-      sum[l] += low;
-      rem = hi;
+      for (int e = 0; e < EPL; ++e) {
+        const long long idx = q_off + (long long)gq * D + lane * EPL + e;
+        q[i][e] = p.q_is_half ? __half2float(static_cast<const __half*>(p.query)[idx])
+                              : static_cast<const float*>(p.query)[idx];
+      }
     }
-    slot.limb[0][gq][d_idx] = (int8_t)(int)rem;
-    sum[0] += (int)rem;
   }
 #pragma unroll
-  for (int l = 0; l < NL; ++l) {
+  for (int i = 0; i < 8; ++i) {
+    const int gq = gq0 + i;
+    if (gq >= gq1) break;
+    float amax = 0.f;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], off);
-  }
-  if (lane == 0) {
-    slot.sq[gq] = step;
-    slot.sumA[gq] = 128 * sum[0] + sum[1];
-    slot.sumB[gq] = NL == 3 ? sum[NL - 1] : 0;
+    for (int e = 0; e < EPL; ++e) amax = fmaxf(amax, fabsf(q[i][e]));
+    amax = warp_max(amax);
+    float range = 127.f;
+#pragma unroll
+    for (int l = 1; l < NL; ++l) range *= 128.f;
+    const float step = amax > 0.f ? amax / range : 1.f;
+    const float inv = 1.f / step;
+    int sum[NL];
+#pragma unroll
+    for (int l = 0; l < NL; ++l) sum[l] = 0;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const int d_idx = lane * EPL + e;
+      const __half qh = __float2half_rn(q[i][e]);
+      slot.qh[gq][d_idx] = qh;
+      if (PRECISE) slot.qh[gq + 8][d_idx] = __float2half_rn(q[i][e] - __half2float(qh));
+      float rem = fminf(fmaxf(rintf(q[i][e] * inv), -range), range);  // integer in [-range, range]
+#pragma unroll
+      for (int l = NL - 1; l >= 1; --l) {
+        const float hi = rintf(rem * (1.f / 128.f));
+        const int low = (int)(rem - hi * 128.f);  // in [-64, 64]
+        slot.limb[l][gq][d_idx] = (int8_t)low;
+        sum[l] += low;
+        rem = hi;
+      }
+      slot.limb[0][gq][d_idx] = (int8_t)(int)rem;
+      sum[0] += (int)rem;
+    }
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sum[l] += __shfl_xor_sync(0xffffffffu, sum[l], off);
+    }
+    if (lane == 0) {
+      slot.sq[gq] = step;
+      slot.sumA[gq] = 128 * sum[0] + sum[1];
+      slot.sumB[gq] = NL == 3 ? sum[NL - 1] : 0;
+    }
   }
 }
 
@@ -518,7 +531,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       Slot& slot = qslots[qi];
       if (lane == 0) slot.desc = d;
       if (r != run_begin) {
-        for (int gq = 0; gq < G; ++gq) prep_query_head<D, PRECISE>(slot, p, d.seq, d.head, G, gq, lane);
+        prep_query_heads<D, PRECISE>(slot, p, d.seq, d.head, G, 0, G, lane);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&qfull[qi]);
@@ -562,7 +575,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     const Slot& slot = qslots[qi];  // stays valid until this warp arrives on qempty below
     const RunDesc& d = slot.desc;
     if (r == run_begin) {
-      for (int gq = warp; gq < G; gq += NCONS) prep_query_head<D, PRECISE>(qslots[qi], p, d.seq, d.head, G, gq, lane);
+      for (int gq = warp; gq < G; gq += NCONS) prep_query_heads<D, PRECISE>(qslots[qi], p, d.seq, d.head, G, gq, gq + 1, lane);
       named_bar_sync(1, NCONS * 32);
     }
     const int b = d.seq, h = d.head;
