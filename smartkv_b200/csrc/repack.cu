@@ -218,6 +218,86 @@ __device__ __forceinline__ void unpack_row_words(const uint8_t* src, int bits, i
   }
 }
 
+// ---- head_dim 128: half a warp per row, 8 consecutive elements per lane --------------------------------
+// The K row and the V row of one (token, head) are handled by the two halves of a warp at once, which
+// halves the per-row cost of everything that is not per element (reductions, address arithmetic, packing).
+
+// this lane's 8 codes (elements 8*l16 .. 8*l16+7) of a packed 128-element row
+__device__ __forceinline__ void unpack8(const uint8_t* src, int bits, int l16, int (&code)[8]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(src);
+  const int bitpos = l16 * 8 * bits, wi = bitpos >> 5, sh = bitpos & 31, nwords = 4 * bits;  // 128*bits/32
+  const uint32_t w0 = w[wi];
+  const uint32_t w1 = wi + 1 < nwords ? w[wi + 1] : 0u;
+  // a lane's field is 8 * bits wide: 64 bits = two aligned words at 8 bits (sh == 0), else at most 32 bits
+  const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = w1;
+  if (bits == 8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      code[i] = (int)(int8_t)((lo >> (8 * i)) & 0xffu);
+      code[4 + i] = (int)(int8_t)((hi >> (8 * i)) & 0xffu);
+    }
+  } else {
+    const uint32_t fm = (1u << bits) - 1u;
+    const int off = 1 << (bits - 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) code[i] = (int)((lo >> (bits * i)) & fm) - off;  // 8 * bits <= 32
+  }
+}
+
+// packs this lane's 8 codes and stores the half-warp's 128-element row at dst (4-byte aligned)
+__device__ __forceinline__ void pack8_store(const int (&code)[8], int bits, uint8_t* dst, int l16) {
+  uint32_t* out = reinterpret_cast<uint32_t*>(dst);
+  if (bits == 8) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo |= ((uint32_t)code[i] & 0xffu) << (8 * i);
+      hi |= ((uint32_t)code[4 + i] & 0xffu) << (8 * i);
+    }
+    out[2 * l16] = lo;
+    out[2 * l16 + 1] = hi;
+    return;
+  }
+  const int off = 1 << (bits - 1);
+  const uint32_t fm = (1u << bits) - 1u;
+  uint32_t f = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f |= (((uint32_t)(code[i] + off)) & fm) << (bits * i);  // 16, 24 or 32 bits
+  const uint32_t n = __shfl_down_sync(0xffffffffu, f, 1);  // the next lane's field (same half for the lanes that use it)
+  if (bits == 4) {
+    out[l16] = f;
+  } else if (bits == 2) {
+    if ((l16 & 1) == 0) out[l16 >> 1] = f | (n << 16);
+  } else {  // 3 bits: four 24-bit fields make three words
+    const int r = l16 & 3;
+    const uint32_t word = r == 0 ? (f | (n << 24)) : r == 1 ? ((f >> 8) | (n << 16)) : ((f >> 16) | (n << 8));
+    if (r < 3) out[3 * (l16 >> 2) + r] = word;
+  }
+}
+
+// dequantise (code * scale) and quantise again at `bits`; returns the new scale (all 16 lanes of the row)
+__device__ __forceinline__ float requant8(const int (&code)[8], float scale, int bits, int (&q)[8]) {
+  float x[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    x[i] = __fmul_rn((float)code[i], scale);  // codes.float() * scale
+    amax = fmaxf(amax, fabsf(x[i]));
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // stays inside the half
+  const int hi = (1 << (bits - 1)) - 1, lo = -(1 << (bits - 1));
+  float ns = __fdiv_rn(amax, (float)(hi > 1 ? hi : 1));
+  if (ns == 0.f) ns = 1.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float v = rintf(__fdiv_rn(x[i], ns));
+    v = fminf(fmaxf(v, (float)lo), (float)hi);
+    q[i] = (int)v;
+  }
+  return ns;
+}
+
 // phase 0: source rows -> staging (requantised at the destination width); phase 1: staging -> destination.
 // One warp takes one move and walks its rows (layers of the call x KV heads x {K, V}).
 template <int EPL, int PHASE>
@@ -246,6 +326,29 @@ __global__ void repack_rows_kernel(const RowMoveParams p) {
       uint8_t* arena = arena_ptr(g, p.store, p.layer_begin + li, b);
       if (PHASE == 0) {
         const float* scales = reinterpret_cast<const float*>(arena + g.sc_off[wb_s]);
+        if constexpr (EPL == 4) {
+          // head_dim 128: lanes 0..15 take the K row, lanes 16..31 the V row of the same (token, head)
+          const int which = lane >> 4, l16 = lane & 15;
+          for (int h = 0; h < Hkv; ++h) {
+            const long long row = (long long)h * g.cap[wb_s] + pos_s;
+            const float2 sc = reinterpret_cast<const float2*>(scales)[row];
+            const uint8_t* rp = arena + (which ? g.v_off[wb_s] : g.k_off[wb_s]) + row * rb_s;
+            uint8_t* st = stage + ((li * Hkv + h) * 2 + which) * kStageRowBytes;
+            const float scale = which ? sc.y : sc.x;
+            if (bits_s == bits_d) {
+              const int words = rb_s >> 2;  // 8, 12, 16 or 32
+              if (l16 < words) reinterpret_cast<uint32_t*>(st)[l16] = reinterpret_cast<const uint32_t*>(rp)[l16];
+              if (l16 + 16 < words) reinterpret_cast<uint32_t*>(st)[l16 + 16] = reinterpret_cast<const uint32_t*>(rp)[l16 + 16];
+              if (l16 == 0) *reinterpret_cast<float*>(st + 128) = scale;
+            } else {
+              int code[8], q[8];
+              unpack8(rp, bits_s, l16, code);
+              const float ns = requant8(code, scale, bits_d, q);
+              pack8_store(q, bits_d, st, l16);
+              if (l16 == 0) *reinterpret_cast<float*>(st + 128) = ns;
+            }
+          }
+        } else {
         for (int h = 0; h < Hkv; ++h) {
           const long long row = (long long)h * g.cap[wb_s] + pos_s;
           const float2 sc = reinterpret_cast<const float2*>(scales)[row];
@@ -269,6 +372,7 @@ __global__ void repack_rows_kernel(const RowMoveParams p) {
               if (lane == 0) *reinterpret_cast<float*>(st + 128) = ns;
             }
           }
+        }
         }
       } else {
         float* scales = reinterpret_cast<float*>(arena + g.sc_off[wb_d]);

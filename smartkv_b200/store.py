@@ -49,6 +49,47 @@ def bucket_capacities(max_tokens: int, memory_budget: Optional[float] = None, he
     return tuple(caps)
 
 
+def make_alloc_config(num_kv_heads: int, head_dim: int, memory_budget: float,
+                      available_bits: Sequence[int] = (2, 3, 4, 8), utility_alpha: float = 0.5,
+                      importance_floor: float = 1e-6, hysteresis_rank_threshold: float = 0.05,
+                      hysteresis_intervals: int = 2, high_precision_fraction: float = 0.02,
+                      high_precision_boost: float = 1.5, min_high_precision_tokens: int = 0,
+                      protected: Sequence[int] = (0, 1, 2), critical_window: int = 4,
+                      scale_bits: int = 32) -> "_lib.AllocConfig":
+    """SkvAllocConfig with the clamping of SmartKVCache.__init__ (smartkv/core/cache.py:94-97,
+    131-144) and of _solve_allocation (alpha to [0.1, 1], :390).  ``num_kv_heads``: KV heads of the
+    whole model (accounting only).  bits ** alpha is computed here, with the host's libm."""
+    c = _lib.AllocConfig()
+    c.num_heads = int(num_kv_heads)
+    c.head_dim = int(head_dim)
+    bits = sorted(int(b) for b in available_bits)
+    if not 1 <= len(bits) <= 4 or any(b not in BITS_TO_BUCKET for b in bits) or len(set(bits)) != len(bits):
+        raise ValueError(f"available_bits must be 1 to 4 distinct widths out of 2, 3, 4, 8; got {list(available_bits)}")
+    c.num_bits = len(bits)
+    alpha = float(utility_alpha) if utility_alpha > 0 else 1.0
+    alpha = min(max(alpha, 0.1), 1.0)
+    for i, b in enumerate(bits):
+        c.bits[i] = b
+        c.util[i] = float(b) if alpha == 1.0 else float(math.pow(b, alpha))
+    c.memory_budget = float(memory_budget)
+    c.importance_floor = float(max(importance_floor, 0.0))
+    c.rank_threshold = float(max(hysteresis_rank_threshold, 0.0))
+    c.hysteresis_intervals = max(int(hysteresis_intervals), 1)
+    c.high_fraction = float(max(0.0, min(high_precision_fraction, 0.5)))
+    c.high_boost = float(max(1.0, high_precision_boost))
+    c.min_high_tokens = int(max(0, min_high_precision_tokens))
+    c.scale_bits = int(scale_bits)
+    c.use_packing = 1
+    c.critical_window = int(critical_window)
+    prot = sorted(set(int(t) for t in protected))
+    if len(prot) > _lib.ALLOC_MAX_PROTECTED:
+        raise ValueError(f"at most {_lib.ALLOC_MAX_PROTECTED} protected token ids")
+    c.num_protected = len(prot)
+    for i, t in enumerate(prot):
+        c.protected_ids[i] = t
+    return c
+
+
 class PackedKVStore:
     def __init__(self, num_layers: int, num_seqs: int, num_kv_heads: int, head_dim: int, num_q_heads: int,
                  caps: Sequence[int], device="cuda", decay: float = 0.9, head_decay: float = 0.9,
@@ -376,42 +417,11 @@ class PackedKVStore:
 
     # ------------------------------------------------------------------ reallocation
     def make_alloc_config(self, memory_budget: float, available_bits: Sequence[int] = (2, 3, 4, 8),
-                          total_kv_heads: Optional[int] = None, utility_alpha: float = 0.5,
-                          importance_floor: float = 1e-6, hysteresis_rank_threshold: float = 0.05,
-                          hysteresis_intervals: int = 2, high_precision_fraction: float = 0.02,
-                          high_precision_boost: float = 1.5, min_high_precision_tokens: int = 0,
-                          protected: Sequence[int] = (0, 1, 2), critical_window: int = 4,
-                          scale_bits: int = 32) -> "_lib.AllocConfig":
-        """Allocator parameters with the clamping of SmartKVCache.__init__
-        (smartkv/core/cache.py:131-141).  ``total_kv_heads``: KV heads of the whole
-        model when this store holds a shard of them (accounting only)."""
-        c = _lib.AllocConfig()
-        c.num_heads = int(total_kv_heads or self.num_kv_heads)
-        c.head_dim = self.head_dim
-        bits = sorted(int(b) for b in available_bits)
-        c.num_bits = len(bits)
-        alpha = float(utility_alpha) if utility_alpha > 0 else 1.0
-        alpha = min(max(alpha, 0.1), 1.0)
-        for i, b in enumerate(bits):
-            c.bits[i] = b
-            c.util[i] = float(b) if alpha == 1.0 else float(math.pow(b, alpha))
-        c.memory_budget = float(memory_budget)
-        c.importance_floor = float(max(importance_floor, 0.0))
-        c.rank_threshold = float(max(hysteresis_rank_threshold, 0.0))
-        c.hysteresis_intervals = max(int(hysteresis_intervals), 1)
-        c.high_fraction = float(max(0.0, min(high_precision_fraction, 0.5)))
-        c.high_boost = float(max(1.0, high_precision_boost))
-        c.min_high_tokens = int(max(0, min_high_precision_tokens))
-        c.scale_bits = int(scale_bits)
-        c.use_packing = 1
-        c.critical_window = int(critical_window)
-        prot = sorted(set(int(t) for t in protected))
-        if len(prot) > _lib.ALLOC_MAX_PROTECTED:
-            raise ValueError(f"at most {_lib.ALLOC_MAX_PROTECTED} protected token ids")
-        c.num_protected = len(prot)
-        for i, t in enumerate(prot):
-            c.protected_ids[i] = t
-        return c
+                          total_kv_heads: Optional[int] = None, **kw) -> "_lib.AllocConfig":
+        """Allocator parameters for this store (see make_alloc_config at module level).  ``total_kv_heads``:
+        KV heads of the whole model when this store holds a shard of them (accounting only)."""
+        return make_alloc_config(int(total_kv_heads or self.num_kv_heads), self.head_dim, memory_budget,
+                                 available_bits, **kw)
 
     def _realloc_buffers(self):
         if getattr(self, "_realloc", None) is not None:

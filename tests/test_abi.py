@@ -79,3 +79,31 @@ def test_bucket_capacities():
     caps = bucket_capacities(8192, 0.35)
     assert all(c % 128 == 0 for c in caps)
     assert caps[0] >= 8192 and caps[3] < 8192 and caps[3] >= int(0.35 * 16 * 8192 / 8)
+
+
+def test_alloc_config_clamps_like_the_reference():
+    import math
+
+    from oracle import smartkv_oracle as orc
+    from smartkv_b200.store import make_alloc_config
+    c = make_alloc_config(8, 128, 0.35, (8, 2, 4, 3), utility_alpha=0.05, importance_floor=-1.0,
+                          hysteresis_rank_threshold=-3.0, hysteresis_intervals=0, high_precision_fraction=0.9,
+                          high_precision_boost=0.2, min_high_precision_tokens=-4, protected=(2, 0, 1, 1))
+    o = orc.AllocatorConfig(8, 128, 0.35, (8, 2, 4, 3), utility_alpha=0.05, importance_floor=-1.0,
+                            hysteresis_rank_threshold=-3.0, hysteresis_intervals=0, high_precision_fraction=0.9,
+                            high_precision_boost=0.2, min_high_precision_tokens=-4)
+    assert list(c.bits)[:c.num_bits] == o.available_bits == [2, 3, 4, 8]
+    alpha = min(max(o.utility_alpha, 0.1), 1.0)
+    assert [c.util[i] for i in range(4)] == [math.pow(b, alpha) for b in (2, 3, 4, 8)]
+    assert (c.importance_floor, c.rank_threshold, c.hysteresis_intervals) == (
+        o.importance_floor, o.hysteresis_rank_threshold, o.hysteresis_intervals)
+    assert (c.high_fraction, c.high_boost, c.min_high_tokens) == (
+        o.high_precision_fraction, o.high_precision_boost, o.min_high_precision_tokens)
+    assert c.num_protected == 3 and list(c.protected_ids)[:3] == [0, 1, 2] and c.use_packing == 1
+    lin = make_alloc_config(4, 64, 0.5, (2, 4, 8), utility_alpha=0.0)        # alpha <= 0 means linear utility
+    assert [lin.util[i] for i in range(3)] == [2.0, 4.0, 8.0]
+    import pytest
+    with pytest.raises(ValueError):
+        make_alloc_config(4, 64, 0.5, (2, 5))
+    with pytest.raises(ValueError):
+        make_alloc_config(4, 64, 0.5, (2, 4), protected=range(40))
