@@ -38,8 +38,8 @@ if ROOT not in sys.path:
 CFG = dict(num_layers=32, num_q_heads=32, num_kv_heads=8, head_dim=128, batch=16, context=8192,
            memory_budget=0.35, available_bits=(2, 3, 4, 8), zipf_s=1.1, realloc_every=16)
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes one attention launch of this workload moved under ncu (188.50 MB read + 13.94 MB written)
-ATTN_DRAM_TRAFFIC_PER_LAUNCH = 202_440_000
+# DRAM bytes one attention launch of this workload moved under ncu (188.44 MB read + 6.96 MB written)
+ATTN_DRAM_TRAFFIC_PER_LAUNCH = 195_400_000
 
 
 def measured_peak():
@@ -362,6 +362,7 @@ def run_ours(args):
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / steps, 4)},
         "reallocation_ms": round(float(np.mean(realloc_ms)), 3) if realloc_ms else None,
+        "reallocation_moved_tokens": int(store._realloc["n_moves"].sum()) if realloc_ms else None,   # last one
         "gpu_launches": int(n_launch), "cuda_graph": graph is not None,
         "clocks": clocks,
     }
