@@ -222,8 +222,8 @@ def run_ours(args):
 
     def decode_step(q, k, v, record=False):
         """One decode step: 2 kernels of this library per layer (attention; combine + append + the
-        previous layer's importance update), the plan kernel, the last layer's importance update, and
-        the torch index ops that place / commit the new token."""
+        previous layer's importance update), the attention plan kernel, the last layer's importance update and
+        the two kernels that place and commit the new token."""
         plan = store.plan_step()
         for layer in range(L):
             ev = None
@@ -253,7 +253,7 @@ def run_ours(args):
             graph.replay()
         else:
             decode_step(q_stage, k_stage, v_stage)
-        launches[0] += 2 * L + 2
+        launches[0] += 2 * L + 4
 
     def resident_step(i):
         j = i % n_in
@@ -321,7 +321,7 @@ def run_ours(args):
     launches[0] = 0
     ms, step_bytes, clocks = timed(resident_step, warmup, steps, 0)
     store.check_errors()
-    n_launch = launches[0] - warmup * (L * 2 + 2)
+    n_launch = launches[0] - warmup * (L * 2 + 4)
     realloc_ms = [a.elapsed_time(b) for a, b in realloc_events]
     # kernel-only time of the attention kernel: the same steps launched un-graphed with a CUDA
     # event pair around every attention launch

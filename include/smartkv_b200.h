@@ -103,6 +103,18 @@ int skv_quantize_pack_append(const SkvStoreDesc* desc, void* store, int layer, c
                              int input_dtype, int rows, const int32_t* dst_seq, const int32_t* dst_bucket,
                              const int32_t* dst_pos, void* stream);
 
+/* Bookkeeping of one decode step, the per-token part of quantize_and_store_batch
+ * (smartkv/core/cache.py:1214, :1319-1339, :1355) for one new token per sequence.
+ * skv_step_plan: where each sequence's token goes: bucket of bits[b] (uint8 [num_seqs]; NULL = the
+ * default 4 bits), position = the bucket's live count.  Outputs int32 [num_seqs] each; dst_storage
+ * is the storage index.  *err_flag = 3 if a bucket is full.
+ * skv_step_commit: after every layer appended the token: records its id (next_token[b]) at that
+ * storage index, counts[b][bucket] += 1, next_token[b] += 1. */
+int skv_step_plan(const SkvStoreDesc* desc, const int32_t* counts, const uint8_t* bits, int32_t* dst_seq,
+                  int32_t* dst_bucket, int32_t* dst_pos, int32_t* dst_storage, int32_t* err_flag, void* stream);
+int skv_step_commit(const SkvStoreDesc* desc, int32_t* counts, int32_t* slot_token, int32_t* next_token,
+                    const int32_t* dst_bucket, const int32_t* dst_storage, void* stream);
+
 /* Reads rows back out of the store as int8 codes + fp32 scales (the dequantising
  * read side of cache.py:1493-1543 / get_bucket_views :671-744).  Row r is read
  * from (src_seq[r], src_bucket[r], src_pos[r]); outputs [rows][num_kv_heads][head_dim]
@@ -110,6 +122,13 @@ int skv_quantize_pack_append(const SkvStoreDesc* desc, void* store, int layer, c
 int skv_export_rows(const SkvStoreDesc* desc, const void* store, int layer, int rows, const int32_t* src_seq,
                     const int32_t* src_bucket, const int32_t* src_pos, int8_t* k_codes, int8_t* v_codes,
                     float* k_scale, float* v_scale, void* stream);
+
+/* The dequantising read of SmartKVCache.retrieve / retrieve_all (smartkv/core/cache.py:1357-1439,
+ * :1493-1543): rows of the store as values, code * scale in fp32, written as fp32 or fp16
+ * [rows][num_kv_heads][head_dim]. */
+int skv_dequant_rows(const SkvStoreDesc* desc, const void* store, int layer, int rows, const int32_t* src_seq,
+                     const int32_t* src_bucket, const int32_t* src_pos, int out_dtype, void* k_out, void* v_out,
+                     void* stream);
 
 /* The inverse of skv_export_rows: writes already quantised rows (int8 codes + fp32 scales, the form
  * the reference's cache hands to its kernels, smartkv/core/cache.py:1441-1491) into the store,

@@ -60,8 +60,13 @@ _SIGNATURES = {
     "skv_unpack": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "skv_quantize_pack_append": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                          c_void_p, c_void_p, c_void_p, c_void_p]),
+    "skv_step_plan": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p]),
+    "skv_step_commit": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_export_rows": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "skv_dequant_rows": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_void_p]),
     "skv_import_rows": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_attn_num_ctas": (c_int, [c_int]),

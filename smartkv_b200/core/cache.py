@@ -304,6 +304,21 @@ class SmartKVCache:
                                          ptr(kc), ptr(vc), ptr(ks), ptr(vs), st._stream()), "skv_export_rows")
         return kc, vc, ks, vs
 
+    def _values_of(self, layer_idx: int, ids: List[int]):
+        """Dequantised (keys, values) fp32 [n, num_heads, head_dim] of the given tokens of one layer."""
+        n = len(ids)
+        dev = self._dev
+        keys = torch.empty((n, self.num_heads, self.head_dim), dtype=torch.float32, device=dev)
+        values = torch.empty_like(keys)
+        if n:
+            seq = torch.zeros(n, dtype=torch.int32, device=dev)
+            bk = torch.tensor([self._slot[t][0] for t in ids], dtype=torch.int32, device=dev)
+            pos = torch.tensor([self._slot[t][1] for t in ids], dtype=torch.int32, device=dev)
+            st = self.store
+            check(st.lib.skv_dequant_rows(ctypes.byref(st.desc), ptr(st.arena), layer_idx, n, ptr(seq), ptr(bk), ptr(pos),
+                                          _lib.DTYPE_F32, ptr(keys), ptr(values), st._stream()), "skv_dequant_rows")
+        return keys, values
+
     def _select(self, layer_idx: int, token_ids: Optional[Sequence[int]]) -> List[int]:
         have = self._layer_tokens[layer_idx]
         if token_ids is None:
@@ -314,8 +329,8 @@ class SmartKVCache:
         """Dequantised (key, value) [num_heads, head_dim]; KeyError if the layer does not hold the token."""
         if int(token_id) not in self._layer_tokens[layer_idx]:
             raise KeyError(f"Token {token_id} not found in cache for layer {layer_idx}")
-        kc, vc, ks, vs = self._rows_of(layer_idx, [int(token_id)])
-        return kc[0].float() * ks[0][:, None], vc[0].float() * vs[0][:, None]
+        keys, values = self._values_of(layer_idx, [int(token_id)])
+        return keys[0], values[0]
 
     def retrieve_all(self, layer_idx: int, token_ids: Optional[List[int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Dequantised keys, values [n, num_heads, head_dim] (ascending token id, or the order asked for)."""
@@ -323,8 +338,7 @@ class SmartKVCache:
         if not ids:
             empty = torch.empty(0, self.num_heads, self.head_dim, device=self._dev)
             return empty, empty.clone()
-        kc, vc, ks, vs = self._rows_of(layer_idx, ids)
-        return kc.float() * ks[..., None], vc.float() * vs[..., None]
+        return self._values_of(layer_idx, ids)
 
     def retrieve_all_quantized(self, layer_idx: int, token_ids: Optional[List[int]] = None) -> Dict[str, torch.Tensor]:
         """Codes and scales as the reference hands them to its kernels (cache.py:1441-1491)."""

@@ -55,3 +55,54 @@ extern "C" int skv_read_error_flag(int32_t* err_flag, int32_t* host_value, void*
   if (cudaStreamSynchronize(st) != cudaSuccess) return SKV_ERR_CUDA;
   return *host_value == 0 ? SKV_OK : SKV_ERR_TIMEOUT;
 }
+
+// ---- placement of the token every sequence appends in a decode step ----------------------------
+namespace skv {
+
+__global__ void step_plan_kernel(StoreGeom g, const int32_t* counts, const uint8_t* bits, int32_t* dst_seq,
+                                 int32_t* dst_bucket, int32_t* dst_pos, int32_t* dst_storage, int32_t* err) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= g.num_seqs) return;
+  int bucket = bits ? bits_bucket(bits[b]) : bits_bucket(4);  // unseen tokens enter at 4 bits (cache.py:1214)
+  if (bucket < 0) {
+    if (err) atomicExch(err, 4);
+    bucket = bits_bucket(4);
+  }
+  const int pos = counts[b * kNumBuckets + bucket];
+  if (pos >= g.cap[bucket] && err) atomicExch(err, 3);  // the bucket is full: the append kernel will refuse the row
+  dst_seq[b] = b;
+  dst_bucket[b] = bucket;
+  dst_pos[b] = pos;
+  dst_storage[b] = g.bucket_base[bucket] + pos;
+}
+
+__global__ void step_commit_kernel(StoreGeom g, int32_t* counts, int32_t* slot_token, int32_t* next_token,
+                                   const int32_t* dst_bucket, const int32_t* dst_storage) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= g.num_seqs) return;
+  const int bucket = dst_bucket[b], s = dst_storage[b];
+  if (bucket < 0 || bucket >= kNumBuckets || s < 0 || s >= g.slots) return;
+  if (s - g.bucket_base[bucket] >= g.cap[bucket]) return;  // was refused
+  slot_token[(long long)b * g.slots + s] = next_token[b];
+  counts[b * kNumBuckets + bucket] += 1;
+  next_token[b] += 1;
+}
+
+}  // namespace skv
+
+extern "C" int skv_step_plan(const SkvStoreDesc* desc, const int32_t* counts, const uint8_t* bits, int32_t* dst_seq,
+                             int32_t* dst_bucket, int32_t* dst_pos, int32_t* dst_storage, int32_t* err_flag,
+                             void* stream) {
+  if (!desc || !counts || !dst_seq || !dst_bucket || !dst_pos || !dst_storage) return SKV_ERR_INVALID;
+  skv::step_plan_kernel<<<(desc->num_seqs + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      skv::make_geom(*desc), counts, bits, dst_seq, dst_bucket, dst_pos, dst_storage, err_flag);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+extern "C" int skv_step_commit(const SkvStoreDesc* desc, int32_t* counts, int32_t* slot_token, int32_t* next_token,
+                               const int32_t* dst_bucket, const int32_t* dst_storage, void* stream) {
+  if (!desc || !counts || !slot_token || !next_token || !dst_bucket || !dst_storage) return SKV_ERR_INVALID;
+  skv::step_commit_kernel<<<(desc->num_seqs + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      skv::make_geom(*desc), counts, slot_token, next_token, dst_bucket, dst_storage);
+  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}

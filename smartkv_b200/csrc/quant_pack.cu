@@ -140,6 +140,41 @@ __global__ void export_rows_kernel(StoreGeom g, const uint8_t* store, int layer,
   }
 }
 
+// ---- dequantising read: rows of the store as fp32 / fp16 values ------------------------------
+template <typename OutT>
+__global__ void dequant_rows_kernel(StoreGeom g, const uint8_t* store, int layer, int rows, const int32_t* src_seq,
+                                    const int32_t* src_bucket, const int32_t* src_pos, OutT* k_out, OutT* v_out) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)rows * g.num_kv_heads * 2;
+  if (warp >= total) return;
+  const int which = (int)(warp & 1);
+  const long long rh = warp >> 1;
+  const int h = (int)(rh % g.num_kv_heads);
+  const int r = (int)(rh / g.num_kv_heads);
+  const int seq = src_seq[r], bucket = src_bucket[r], pos = src_pos[r];
+  if (seq < 0 || seq >= g.num_seqs || bucket < 0 || bucket >= kNumBuckets || pos < 0 || pos >= g.cap[bucket]) return;
+  const int bits = bucket_bits(bucket);
+  const uint8_t* arena = arena_ptr(g, store, layer, seq);
+  const long long row_index = (long long)h * g.cap[bucket] + pos;
+  const uint8_t* src = arena + (which ? g.v_off[bucket] : g.k_off[bucket]) + row_index * g.row_bytes[bucket];
+  const float scale = reinterpret_cast<const float*>(arena + g.sc_off[bucket])[2 * row_index + which];
+  OutT* out = (which ? v_out : k_out) + rh * g.head_dim;
+  const uint32_t fm = (1u << bits) - 1u;
+  for (int d = lane; d < g.head_dim; d += 32) {
+    int c;
+    if (bits == 8) {
+      c = (int8_t)src[d];
+    } else {
+      const int bitpos = d * bits, byte = bitpos >> 3, sh = bitpos & 7;
+      uint32_t win = src[byte];
+      if (sh + bits > 8) win |= (uint32_t)src[byte + 1] << 8;
+      c = (int)((win >> sh) & fm) - (1 << (bits - 1));
+    }
+    out[d] = (OutT)__fmul_rn((float)c, scale);  // code.float() * scale, as the reference dequantises (cache.py:1493-1543)
+  }
+}
+
 // ---- import rows: int8 codes + scales -> packed rows of the store -----------------------
 template <int EPL>
 __global__ void import_rows_kernel(StoreGeom g, uint8_t* store, int layer, int rows, const int32_t* dst_seq,
@@ -287,5 +322,27 @@ extern "C" int skv_import_rows(const SkvStoreDesc* desc, void* store, int layer,
     import_rows_kernel<2><<<grid, wpb * 32, 0, as_stream(stream)>>>(g, static_cast<uint8_t*>(store), layer, rows, dst_seq,
                                                                     dst_bucket, dst_pos, k_codes, v_codes, k_scale,
                                                                     v_scale, err_flag);
+  return launch_status();
+}
+
+extern "C" int skv_dequant_rows(const SkvStoreDesc* desc, const void* store, int layer, int rows,
+                                const int32_t* src_seq, const int32_t* src_bucket, const int32_t* src_pos,
+                                int out_dtype, void* k_out, void* v_out, void* stream) {
+  if (!desc || !store || !src_seq || !src_bucket || !src_pos || !k_out || !v_out) return SKV_ERR_INVALID;
+  if (layer < 0 || layer >= desc->num_layers || rows < 0) return SKV_ERR_INVALID;
+  if (out_dtype != SKV_DTYPE_F32 && out_dtype != SKV_DTYPE_F16) return SKV_ERR_INVALID;
+  if (rows == 0) return SKV_OK;
+  const StoreGeom g = make_geom(*desc);
+  const int wpb = 8;
+  const long long warps = (long long)rows * g.num_kv_heads * 2;
+  const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
+  if (out_dtype == SKV_DTYPE_F32)
+    dequant_rows_kernel<float><<<grid, wpb * 32, 0, as_stream(stream)>>>(
+        g, static_cast<const uint8_t*>(store), layer, rows, src_seq, src_bucket, src_pos, static_cast<float*>(k_out),
+        static_cast<float*>(v_out));
+  else
+    dequant_rows_kernel<__half><<<grid, wpb * 32, 0, as_stream(stream)>>>(
+        g, static_cast<const uint8_t*>(store), layer, rows, src_seq, src_bucket, src_pos, static_cast<__half*>(k_out),
+        static_cast<__half*>(v_out));
   return launch_status();
 }

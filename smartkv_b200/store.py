@@ -203,15 +203,16 @@ class PackedKVStore:
         return dst_seq, bucket.contiguous().view(-1), pos.contiguous().view(-1), storage
 
     def plan_step(self, bits: Optional[torch.Tensor] = None):
-        """Destination of the token each sequence appends this decode step
-        (same bucket position in every layer); does not commit."""
-        if bits is None:
-            bucket = torch.full((self.num_seqs,), BITS_TO_BUCKET[4], dtype=torch.int32, device=self.device)
-        else:
-            bucket = self._bits_lut[bits.long()]
-        pos = self.counts.gather(1, bucket.long()[:, None])[:, 0].contiguous()
-        storage = (self._base_t[bucket.long()] + pos).to(torch.int32)
-        return self._seq_ids, bucket, pos, storage
+        """Destination of the token each sequence appends this decode step (same bucket position in every
+        layer); does not commit.  Returns (dst_seq, dst_bucket, dst_pos, storage), int32 [num_seqs] each,
+        in buffers the store reuses every step."""
+        if getattr(self, "_step_bufs", None) is None:
+            self._step_bufs = tuple(torch.zeros(self.num_seqs, dtype=torch.int32, device=self.device) for _ in range(4))
+        seq, bucket, pos, storage = self._step_bufs
+        b8 = None if bits is None else bits.to(torch.uint8).contiguous()
+        check(self.lib.skv_step_plan(ctypes.byref(self.desc), ptr(self.counts), ptr(b8), ptr(seq), ptr(bucket), ptr(pos),
+                                     ptr(storage), ptr(self.err), self._stream()), "skv_step_plan")
+        return seq, bucket, pos, storage
 
     def commit_step(self, plan):
         self.flush_importance()          # reads the counts as they stood during the step
@@ -219,9 +220,9 @@ class PackedKVStore:
             self._pipe["calls"] = 0      # every step starts on the same buffer set (CUDA graph replays rely on it)
             self._pipe["post_events"] = []
         _seq, bucket, _pos, storage = plan
-        self.slot_token.scatter_(1, storage.long()[:, None], self.next_token[:, None])
-        self.counts.scatter_add_(1, bucket.long()[:, None], torch.ones((self.num_seqs, 1), dtype=torch.int32, device=self.device))
-        self.next_token += 1
+        check(self.lib.skv_step_commit(ctypes.byref(self.desc), ptr(self.counts), ptr(self.slot_token),
+                                       ptr(self.next_token), ptr(bucket), ptr(storage), self._stream()),
+              "skv_step_commit")
         self.appended_total += self.num_seqs
         self.max_seq_tokens += 1
         self._plan_valid = False
