@@ -711,13 +711,15 @@ extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, in
 
 template <int D, bool PRECISE, class CFG>
 static int launch_attn(AttnParams& p, cudaStream_t st) {
-  static bool configured = false;  // per template instance
+  static bool configured[64] = {};  // per template instance and device: the attribute belongs to the device's context
   const size_t smem = attn_smem_bytes<D, CFG, PRECISE>();
-  if (!configured) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SKV_ERR_CUDA;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     if (cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE, CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return SKV_ERR_CUDA;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   decode_attn_kernel<D, PRECISE, CFG><<<p.num_ctas, (CFG::NCONS + 1) * 32, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;

@@ -289,3 +289,37 @@ def test_tinyllama_shape_fused_decode_matches_dequantised_path():
         out = wrapped.generate(ids, max_new_tokens=24, do_sample=False)
     assert out.shape == (1, 512 + 24)
     assert wrapped.smartkv_cache.store.counts.sum().item() == 512 + 23
+
+
+def test_cache_grows_past_its_initial_capacity():
+    from smartkv_b200 import SmartKVCache
+    L, H, d = 2, 2, 64
+    cache = SmartKVCache(num_layers=L, num_heads=H, head_dim=d, memory_budget=0.5, max_tokens=100)
+    cap0 = cache.store.caps[2]
+    n = 3 * cap0 + 17                      # forces two doublings of the 4-bit bucket
+    kv = [orc.synth_kv(n, H, d, seed=60 + l) for l in range(L)]
+    cache.token_counter = 1
+    step = 50
+    for lo in range(0, n, step):
+        hi = min(n, lo + step)
+        for l in range(L):
+            cache.quantize_and_store_batch(l, list(range(lo, hi)), torch.from_numpy(kv[l][0][lo:hi]).cuda(),
+                                           torch.from_numpy(kv[l][1][lo:hi]).cuda())
+    assert cache.store.caps[2] > cap0 and len(cache) == n and cache.store.counts.sum().item() == n
+    for l in range(L):
+        keys, values = cache.retrieve_all(l)
+        q4, s4 = orc.quantize_rows(kv[l][0], 4)
+        assert np.array_equal(keys.cpu().numpy(), orc.dequantize_rows(q4, s4)), l
+        q4, s4 = orc.quantize_rows(kv[l][1], 4)
+        assert np.array_equal(values.cpu().numpy(), orc.dequantize_rows(q4, s4)), l
+    # attention over the grown store
+    rng = np.random.default_rng(2)
+    q = rng.standard_normal((H, d)).astype(np.float32)
+    ck = rng.standard_normal((H, d)).astype(np.float32)
+    cv = rng.standard_normal((H, d)).astype(np.float32)
+    out = cache.fused_decode_attention(0, torch.from_numpy(q).cuda(), torch.from_numpy(ck).cuda(),
+                                       torch.from_numpy(cv).cuda(), token_id=n, update_importance=False)
+    kq, ks = orc.quantize_rows(kv[0][0], 4)
+    vq, vs = orc.quantize_rows(kv[0][1], 4)
+    ref, _ = orc.streaming_attention(q[None, :, None, :], kq, ks, vq, vs, tile_size=512, current_k=ck[None], current_v=cv[None])
+    assert_close(out.cpu().numpy(), ref[0, :, 0], what="attention after growth")
