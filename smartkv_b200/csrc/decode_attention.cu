@@ -716,13 +716,21 @@ static int launch_attn(AttnParams& p, cudaStream_t st) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return SKV_ERR_CUDA;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    if (cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE, CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
+    const cudaError_t rc = cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE, CFG>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (rc != cudaSuccess) {
+      fprintf(stderr, "skv_decode_attention: cannot reserve %zu bytes of shared memory: %s\n", smem, cudaGetErrorString(rc));
       return SKV_ERR_CUDA;
+    }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   decode_attn_kernel<D, PRECISE, CFG><<<p.num_ctas, (CFG::NCONS + 1) * 32, smem, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+  const cudaError_t rc = cudaGetLastError();
+  if (rc != cudaSuccess) {
+    fprintf(stderr, "skv_decode_attention: launch failed: %s\n", cudaGetErrorString(rc));
+    return SKV_ERR_CUDA;
+  }
+  return SKV_OK;
 }
 
 extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
