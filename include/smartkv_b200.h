@@ -148,7 +148,7 @@ int64_t skv_attn_plan_bytes(const SkvStoreDesc* desc, int num_ctas);
 int skv_attn_partials_per_run(const SkvStoreDesc* desc, int query_dtype);
 
 /* Builds the work partition of one decode step: which 16-key tiles of which
- * (sequence, KV head) every persistent CTA streams, balanced by packed bytes.  It
+ * (sequence, KV head) every persistent CTA streams, balanced by estimated time.  It
  * depends only on the bucket counts, which are the same for every layer of the
  * step, so one call serves all layers.  No counterpart in the reference (its kernel
  * walks one head per CTA, smartkv/csrc/quantized_attention.cu:679-777).
@@ -161,9 +161,10 @@ int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, int num_ctas,
  * and the CPU streaming path (smartkv/core/fused_cpu.py:7-167) for q_len == 1.
  *
  * Streams the packed buckets of `layer` for every sequence, split-KV over
- * persistent CTAs as laid out by `plan`, and writes one partial (max, sum, out)
- * triple per run into `partials`; if `logits` is not NULL it also writes the scaled
- * logit (log2 units) of every cached key, logits[seq][q_head][storage index].
+ * persistent CTAs as laid out by `plan`, and writes partial (max, sum, out) triples into
+ * `partials`: skv_attn_partials_per_run() of them per run (one per consumer warp); if `logits`
+ * is not NULL it also writes the scaled logit (log2 units) of every cached key,
+ * logits[seq][q_head][storage index].
  *   query    [num_seqs][num_q_heads][head_dim] fp32 or fp16
  * num_q_heads must be a multiple of num_kv_heads with group size <= 8.
  * err_flag: device int32, set non-zero if a bounded wait inside the kernel gave up. */
@@ -175,7 +176,9 @@ int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer,
  * (smartkv/core/fused_cpu.py:115-137; wrapper call smartkv/models/llama_smartkv.py:264-305),
  * and normalises.  cur_k/cur_v [num_seqs][num_kv_heads][head_dim] (may be NULL: no
  * current token).  out fp32 [num_seqs][num_q_heads][head_dim]; lse_max / lse_sum fp32
- * [num_seqs][num_q_heads] (final max in log2 units, final sum); cur_prob fp32
+ * [num_seqs][num_q_heads]: the reference point m (log2 units; the kernels raise their running
+ * maximum lazily, so m may lie below the true maximum) and the sum of 2^(logit - m), i.e.
+ * lse_max + log2(lse_sum) is the log-sum-exp; cur_prob fp32
  * [num_seqs][num_q_heads] = probability of the current token (may be NULL). */
 int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
                     int num_q_heads, const void* partials, int num_ctas, const void* cur_k, const void* cur_v,
