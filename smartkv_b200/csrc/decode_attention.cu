@@ -1,17 +1,17 @@
 // Fused packed-KV decode attention for sm_100a (q_len == 1, GQA group <= 8).
 //
 // Persistent CTAs (one per SM).  The packed buckets of every (sequence, KV head)
-// segment form one byte string of 16-key tiles; the global string is split evenly
-// -- i.e. by bytes -- over the CTAs (attn_sched.cuh) by a tiny plan kernel that runs
+// segment form one string of 16-key tiles; the global string is split into ranges of
+// equal estimated time over the CTAs (attn_sched.cuh) by a tiny plan kernel that runs
 // once per decode step.  A CTA streams its runs through a ring of shared-memory
-// stages: one producer warp issues bulk async copies (TMA 1-D: packed K rows,
-// packed V rows, scales, and the query rows of the group), the consumer warps take
-// the tiles of a block round-robin, unpack the codes in registers straight into
-// tensor-core fragments (attn_frag.cuh), keep an online softmax and accumulate P.V
-// in registers.  Full/empty mbarriers order producer and consumers; every wait is
-// bounded.  At the end of a run the consumers merge their (max, sum, out) through
-// shared memory and write one partial per run; skv_lse_combine merges the partials
-// of a segment, adds the full-precision current token and normalises.
+// stages: one producer warp issues bulk async copies (TMA 1-D, L2 evict-first: packed
+// K rows, packed V rows, scales) and publishes the query rows of each run (fp16 copy
+// and int8 limbs), the consumer warps take the tiles of a block round-robin, unpack
+// the codes in registers straight into tensor-core fragments (attn_frag.cuh), keep an
+// online softmax and accumulate P.V in registers.  Full/empty mbarriers order producer
+// and consumers; every wait is bounded.  At the end of a run every consumer warp writes
+// its own (max, sum, out) partial; the combine step (post_attention.cuh) folds the
+// partials of a segment, adds the full-precision current token and normalises.
 //
 // Replaces smartkv/csrc/quantized_attention.cu:460-828 (per-bucket kernel, one
 // CTA per head walking the whole context) and the host LSE combine in
