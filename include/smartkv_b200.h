@@ -341,8 +341,9 @@ int skv_debug_tile_products(int head_dim, int bits, const uint8_t* k_rows, const
                             const void* q_half, const void* p_half, float* scores, float* out, void* stream);
 
 /* Integer scores of one 16-key tile through the int8 tensor-core path the attention kernel
- * uses for 2-, 4- and 8-bit rows: scores int32 [8][16] = sum_d q[h][d] * u[key][d], q int8
- * [8][head_dim], u = the stored code (offset-binary for 2/4-bit rows, two's complement for 8-bit). */
+ * uses for 2-, 4- and 8-bit rows and, at head_dim 128, for 3-bit rows: scores int32 [8][16] =
+ * sum_d q[h][d] * u[key][d], q int8 [8][head_dim], u = the stored code (offset-binary below 8 bits,
+ * two's complement for 8-bit). */
 int skv_debug_tile_scores_i8(int head_dim, int bits, const uint8_t* k_rows, const int8_t* q_int8, int32_t* scores,
                              void* stream);
 

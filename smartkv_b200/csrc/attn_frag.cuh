@@ -5,13 +5,13 @@
 // 16 packed V rows.  lane = 4*g + t.
 //
 //  S[8 heads x 16 keys] = Q (A operand, rows = heads)  x  K^T (B operand, two n-tiles of 8 keys)
-//     2-, 4- and 8-bit keys: integer product, mma.sync.m16n8k32.s8.(u8|s8) on the stored
+//     2-, 4-, 8-bit keys and (head_dim 128) 3-bit keys: integer product, mma.sync.m16n8k32.s8.(u8|s8) on the stored
 //     (offset-binary) codes.  The query row of a head is split into two radix-128 int8 limbs; rows
 //     0..7 of the A operand hold limb 0 of the 8 heads, rows 8..15 limb 1, so one MMA yields both
 //     partial products and the score is 128 * c[row g] + c[row g+8].  The constant that the offset
 //     of the stored codes adds (2^(w-1) * sum of the limb) is folded into the accumulator's initial
-//     value.  3-bit keys: fp16 product, m16n8k16, rows 8..15 carry the fp16 residual of the query
-//     in the precise mode.
+//     value.  3-bit keys at head_dim 64: fp16 product, m16n8k16, rows 8..15 carry the fp16
+//     residual of the query in the precise mode.
 //     Lane (g,t) supplies, for the B operand, key g (and g+8 for the second n-tile) and of it a
 //     "K slice" of D/4 elements.  The order in which a slice's elements are fed to the k-steps is
 //     free as long as Q uses the same order, so each bit-width uses whichever order its cheapest bit
@@ -318,6 +318,7 @@ template <int BITS>
 __host__ __device__ constexpr int kelem_i8(int s, int r, int j) {
   if (BITS == 8) return 8 * s + 4 * r + j;
   if (BITS == 4) return 8 * s + 2 * j + r;          // word s: even nibbles -> r = 0, odd -> r = 1
+  if (BITS == 3) return (2 * s + r) + 8 * j;        // register 2s+r: field 2s+r of each of the four 24-bit groups
   return 16 * (s / 2) + 4 * j + 2 * (s % 2) + r;    // 2-bit: word s/2, shift index 2*(s%2)+r
 }
 
@@ -341,8 +342,29 @@ __device__ __forceinline__ void mma_i8_16832(int (&d)[4], const uint32_t (&a)[4]
 template <int D, int BITS>
 __device__ __forceinline__ void unpack_kslice_i8(const uint32_t (&w)[SliceWords<D, BITS>::K], uint32_t* o) {
   constexpr int NW = SliceWords<D, BITS>::K;
-  static_assert(BITS == 8 || BITS == 4 || BITS == 2, "3-bit rows use the fp16 path");
-  if constexpr (BITS == 8) {
+  static_assert(BITS != 3 || D == 128, "3-bit rows of head_dim 64 use the fp16 path");
+  if constexpr (BITS == 3) {
+    // 32 fields of 3 bits in 12 bytes (four 24-bit groups).  Field i0 of every group sits at the same
+    // offset inside its byte, 3 bytes apart, so one byte gather + shift + mask yields the register of
+    // a field class (bytes = groups).  Classes 2 and 5 straddle a byte boundary: they are taken from the
+    // slice shifted right by 6 bits, where they do not.
+    constexpr uint32_t m = 0x07070707u;
+    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+    const uint32_t g0 = prmt(prmt(w0, w1, 0x0630), w2, 0x5210);  // bytes 0, 3, 6, 9
+    const uint32_t g1 = prmt(prmt(w0, w1, 0x0741), w2, 0x6210);  // bytes 1, 4, 7, 10
+    const uint32_t g2 = prmt(prmt(w0, w1, 0x0052), w2, 0x7410);  // bytes 2, 5, 8, 11
+    const uint32_t s0 = __funnelshift_r(w0, w1, 6), s1 = __funnelshift_r(w1, w2, 6), s2 = w2 >> 6;
+    const uint32_t h0 = prmt(prmt(s0, s1, 0x0630), s2, 0x5210);
+    const uint32_t h1 = prmt(prmt(s0, s1, 0x0741), s2, 0x6210);
+    o[0] = g0 & m;
+    o[1] = (g0 >> 3) & m;
+    o[2] = h0 & m;
+    o[3] = (g1 >> 1) & m;
+    o[4] = (g1 >> 4) & m;
+    o[5] = (h1 >> 1) & m;
+    o[6] = (g2 >> 2) & m;
+    o[7] = (g2 >> 5) & m;
+  } else if constexpr (BITS == 8) {
 #pragma unroll
     for (int i = 0; i < NW; ++i) o[i] = w[i];
   } else if constexpr (BITS == 4) {

@@ -4,7 +4,7 @@
 // Every segment is a string of cost units: for each bucket in turn, ceil(count/16) tiles of
 // tile_cost(bucket), the time one CTA needs per tile of that width (measured with every token at
 // that width: narrow tiles are bound by their arithmetic, 8-bit tiles by their bytes; 3-bit tiles
-// pay for the fp16 score path).  tile_bytes = 16 * (2*row_bytes + 8) (packed K rows, V rows and a
+// pay for the costlier field extraction).  tile_bytes = 16 * (2*row_bytes + 8) (packed K rows, V rows and a
 // float2 of scales per key) is what a tile occupies in a stage.  All heads of a sequence have the
 // same length W[b].
 // The global string concatenates the segments in (sequence, head) order; CTA c
@@ -26,10 +26,10 @@ __host__ __device__ constexpr int tile_bytes_for(int head_dim, int bits) {
 }
 
 // nanoseconds one CTA spends per tile of each width at head_dim 128 (B200, all tokens at one width:
-// 48.5 / 57.7 / 49.7 / 64.5 us per launch of 65,536 tiles on 148 CTAs); only the ratios matter
+// 46.5 / 51.6 / 48.9 / 63.3 us per launch of 65,536 tiles on 148 CTAs); only the ratios matter
 constexpr int kTileFixedCost = 0;  // kept for the plan kernel's signature
 __host__ __device__ constexpr int tile_cost_for(int head_dim, int bits, int fixed) {
-  return (bits == 2 ? 110 : bits == 3 ? 130 : bits == 4 ? 112 : 146) + fixed + 0 * head_dim;
+  return (bits == 2 ? 105 : bits == 3 ? 116 : bits == 4 ? 110 : 143) + fixed + 0 * head_dim;
 }
 
 struct SegLayout {

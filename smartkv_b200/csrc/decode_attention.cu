@@ -209,7 +209,7 @@ struct QSlot {
 // Query of one run as a lane sees it, specialised per bit-width of the keys it meets.
 template <int D, int BITS, bool PRECISE>
 struct QFrags {
-  static constexpr bool INT8 = BITS != 3;
+  static constexpr bool INT8 = BITS != 3 || D == 128;  // 3-bit rows of head_dim 64 keep the fp16 score path
   uint32_t qa[INT8 ? D / 32 : D / 16][4];   // A fragments: int8 limbs 0/1, or fp16 query/residual
   uint32_t qa2[(INT8 && PRECISE) ? D / 32 : 1][4];  // precise mode: limb 2
   float sq;     // limb step of head g
@@ -998,6 +998,7 @@ extern "C" int skv_debug_tile_scores_i8(int head_dim, int bits, const uint8_t* k
   cudaStream_t st = as_stream(stream);
   if (head_dim == 128) {
     if (bits == 2) debug_tile_i8_kernel<128, 2><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
+    else if (bits == 3) debug_tile_i8_kernel<128, 3><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
     else if (bits == 4) debug_tile_i8_kernel<128, 4><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
     else if (bits == 8) debug_tile_i8_kernel<128, 8><<<1, 32, 0, st>>>(k_rows, q_int8, scores);
     else return SKV_ERR_INVALID;

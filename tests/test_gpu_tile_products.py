@@ -37,10 +37,9 @@ def test_tile_products_exact(d, bits):
         assert np.array_equal(out.cpu().numpy().astype(np.float64), want_o), (d, bits, "out")
 
 
-@pytest.mark.parametrize("d", [64, 128])
-@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("d,bits", [(64, 2), (64, 4), (64, 8), (128, 2), (128, 3), (128, 4), (128, 8)])
 def test_tile_scores_int8_exact(d, bits):
-    """The int8 tensor-core path used for 2/4/8-bit keys: exact int32 dot products."""
+    """The int8 tensor-core path used for 2/4/8-bit keys (and 3-bit keys at head_dim 128): exact int32 dot products."""
     from smartkv_b200 import _lib as L
     lo, hi = orc.code_range(bits)
     for seed in range(3):
