@@ -353,15 +353,22 @@ __device__ __forceinline__ void append_row(const AppendParams& p, long long warp
   const StoreGeom& g = p.g;
   const int which = (int)(warp & 1);  // 0 = K, 1 = V
   const long long rh = warp >> 1;
-  const int h = (int)(rh % g.num_kv_heads);
-  const int r = (int)(rh / g.num_kv_heads);
+  int h, r;
+  if (rh >> 31) {  // 64-bit division is a long subroutine: only where the row count needs it
+    h = (int)(rh % g.num_kv_heads);
+    r = (int)(rh / g.num_kv_heads);
+  } else {
+    r = (int)rh / g.num_kv_heads;
+    h = (int)rh - r * g.num_kv_heads;
+  }
+  // the row's values do not depend on where it goes: both loads are in flight together
+  RowVals<EPL> x = load_row<EPL>(which ? p.v : p.k, p.dtype, rh, lane);
   const int seq = p.dst_seq[r], bucket = p.dst_bucket[r], pos = p.dst_pos[r];
   if (seq < 0 || seq >= g.num_seqs || bucket < 0 || bucket >= kNumBuckets || pos < 0 || pos >= g.cap[bucket]) {
     if (lane == 0 && p.err) atomicExch(p.err, 2);
     return;
   }
   const int bits = bucket_bits(bucket);
-  RowVals<EPL> x = load_row<EPL>(which ? p.v : p.k, p.dtype, rh, lane);
   int code[EPL];
   const float scale = quantize_row<EPL>(x, bits, code);
   uint8_t* arena = arena_ptr(g, p.store, p.layer, seq);

@@ -41,6 +41,60 @@ __device__ __forceinline__ RowVals<EPL> load_row(const void* base, int dtype, lo
   return r;
 }
 
+// ---- the quantiser's arithmetic without a division or a conversion per element ----------------------------
+// The reference computes scale = amax / levels and q = clamp(round_half_even(x / scale)) in IEEE single
+// precision.  A division is a subroutine of tens of instructions and every int<->float conversion goes
+// through the quarter-rate pipe, which made the kernels that quantise issue-bound; both are avoided here
+// without changing a bit of the result.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// amax / levels, correctly rounded (levels = 2^(bits-1) - 1, at least 1): the product with the rounded
+// reciprocal, corrected once through the exact remainder (two fused multiply-adds), is the correctly rounded
+// quotient for every normal amax (checked over all 2^23 significands for 3, 7 and 127).
+__device__ __forceinline__ float scale_of(float amax, int levels) {
+  const float d = levels >= 127 ? 127.f : levels >= 7 ? 7.f : levels >= 3 ? 3.f : 1.f;
+  if (!(amax >= 1e-30f && amax <= 1e30f)) return __fdiv_rn(amax, d);
+  const float y = levels >= 127 ? (1.f / 127.f) : levels >= 7 ? (1.f / 7.f) : levels >= 3 ? (1.f / 3.f) : 1.f;
+  const float q0 = __fmul_rn(amax, y);
+  const float r = __fmaf_rn(-q0, d, amax);
+  return __fmaf_rn(r, y, q0);
+}
+
+// q_i = clamp(rint(x_i / s), lo, hi) for N values that are NaN or satisfy |x_i| <= levels * s with
+// s = max|x| / levels, levels <= 127 (what both callers pass: s comes from the same values).
+// t = x * (1/s approx) differs from the rounded quotient by less than 7e-5 for |t| <= 256, so rint(t) is
+// rint(x / s) unless t lies within that distance of a half-integer; rint itself is the add of 1.5 * 2^23,
+// whose significand then holds the integer.  A lane that meets a near-tie, a NaN or a scale outside the
+// normal range redoes its values with the division.
+template <int N>
+__device__ __forceinline__ void quantize_vals(const float (&x)[N], float s, int lo, int hi, int (&q)[N]) {
+  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23 = 0x4B400000
+  bool exact = !(s >= 1e-30f && s <= 1e30f);
+  if (!exact) {
+    const float r = rcp_approx(s);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const float t = __fmul_rn(x[i], r);
+      const float m = __fadd_rn(t, kMagic);
+      const float d = __fsub_rn(t, __fsub_rn(m, kMagic));
+      exact |= !(fabsf(d) < 0.5f - 1.25e-4f);  // also true for a NaN
+      q[i] = __float_as_int(m) - 0x4B400000;   // |t| <= levels * (1 + 2^-22): already inside [lo, hi]
+    }
+  }
+  if (exact) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      float v = rintf(__fdiv_rn(x[i], s));
+      v = fminf(fmaxf(v, (float)lo), (float)hi);
+      q[i] = (int)v;
+    }
+  }
+}
+
 // Quantise one row held across a warp.  Returns this lane's EPL codes and the row scale.
 template <int EPL>
 __device__ __forceinline__ float quantize_row(const RowVals<EPL>& x, int bits, int (&code)[EPL]) {
@@ -49,14 +103,9 @@ __device__ __forceinline__ float quantize_row(const RowVals<EPL>& x, int bits, i
   for (int i = 0; i < EPL; ++i) amax = fmaxf(amax, fabsf(x.v[i]));
   amax = warp_max(amax);
   const int hi = (1 << (bits - 1)) - 1, lo = -(1 << (bits - 1));
-  float scale = __fdiv_rn(amax, (float)(hi > 1 ? hi : 1));
+  float scale = scale_of(amax, hi);
   if (scale == 0.f) scale = 1.f;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    float q = rintf(__fdiv_rn(x.v[i], scale));
-    q = fminf(fmaxf(q, (float)lo), (float)hi);
-    code[i] = (int)q;
-  }
+  quantize_vals<EPL>(x.v, scale, lo, hi, code);
   return scale;
 }
 

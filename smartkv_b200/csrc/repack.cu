@@ -197,50 +197,26 @@ __device__ __forceinline__ int find_seq(const int* s_prefix, int B, int m) {
   return lo;
 }
 
-// Reads this lane's EPL codes out of a packed row through aligned 32-bit loads (rows are at least
-// 16 bytes and 4-byte aligned; a lane's field of EPL*bits <= 32 bits spans at most two words).
-template <int EPL>
-__device__ __forceinline__ void unpack_row_words(const uint8_t* src, int bits, int lane, int (&code)[EPL]) {
-  const uint32_t* w = reinterpret_cast<const uint32_t*>(src);
-  const int bitpos = lane * EPL * bits, wi = bitpos >> 5, sh = bitpos & 31, nbits = EPL * bits;
-  const int nwords = nbits;  // 32 lanes * nbits / 32
-  uint32_t lo = w[wi];
-  uint32_t hi = (sh + nbits > 32 && wi + 1 < nwords) ? w[wi + 1] : 0u;
-  const uint32_t field = __funnelshift_r(lo, hi, sh);
-  if (bits == 8) {
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) code[i] = (int)(int8_t)((field >> (8 * i)) & 0xffu);
-  } else {
-    const uint32_t fm = (1u << bits) - 1u;
-    const int off = 1 << (bits - 1);
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) code[i] = (int)((field >> (bits * i)) & fm) - off;
-  }
-}
-
 // ---- head_dim 128: half a warp per row, 8 consecutive elements per lane --------------------------------
 // The K row and the V row of one (token, head) are handled by the two halves of a warp at once, which
 // halves the per-row cost of everything that is not per element (reductions, address arithmetic, packing).
 
-// this lane's 8 codes (elements 8*l16 .. 8*l16+7) of a packed 128-element row
-__device__ __forceinline__ void unpack8(const uint8_t* src, int bits, int l16, int (&code)[8]) {
-  const uint32_t* w = reinterpret_cast<const uint32_t*>(src);
-  const int bitpos = l16 * 8 * bits, wi = bitpos >> 5, sh = bitpos & 31, nwords = 4 * bits;  // 128*bits/32
-  const uint32_t w0 = w[wi];
-  const uint32_t w1 = wi + 1 < nwords ? w[wi + 1] : 0u;
+// this lane's 8 values code * scale (elements 8*l16 .. 8*l16+7) of a packed 128-element row, from the two
+// aligned words (w0 at word bitpos/32, w1 the next one or 0 past the row's end) that hold the lane's field.
+// The code goes into the significand of 2^23 and the offset comes off in the same subtraction, so no
+// int->float conversion is needed; 8-bit rows hold two's complement, which flipping the top bit turns
+// into the offset form of the other widths.
+__device__ __forceinline__ void dequant8(uint32_t w0, uint32_t w1, int l16, int bits, float scale, float (&x)[8]) {
+  const int sh = (l16 * 8 * bits) & 31;
   // a lane's field is 8 * bits wide: 64 bits = two aligned words at 8 bits (sh == 0), else at most 32 bits
   const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = w1;
-  if (bits == 8) {
+  const uint32_t fm = (1u << bits) - 1u, flip = bits == 8 ? 0x80u : 0u;
+  const float bias = bits == 8 ? 8388736.f : bits == 4 ? 8388616.f : bits == 3 ? 8388612.f : 8388610.f;  // 2^23 + 2^(bits-1)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      code[i] = (int)(int8_t)((lo >> (8 * i)) & 0xffu);
-      code[4 + i] = (int)(int8_t)((hi >> (8 * i)) & 0xffu);
-    }
-  } else {
-    const uint32_t fm = (1u << bits) - 1u;
-    const int off = 1 << (bits - 1);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) code[i] = (int)((lo >> (bits * i)) & fm) - off;  // 8 * bits <= 32
+  for (int i = 0; i < 8; ++i) {
+    const int at = bits * i;
+    const uint32_t u = (((at >= 32 ? hi : lo) >> (at & 31)) ^ flip) & fm;
+    x[i] = __fmul_rn(__fsub_rn(__uint_as_float(u | 0x4B000000u), bias), scale);  // codes.float() * scale
   }
 }
 
@@ -275,117 +251,209 @@ __device__ __forceinline__ void pack8_store(const int (&code)[8], int bits, uint
   }
 }
 
-// dequantise (code * scale) and quantise again at `bits`; returns the new scale (all 16 lanes of the row)
-__device__ __forceinline__ float requant8(const int (&code)[8], float scale, int bits, int (&q)[8]) {
-  float x[8];
+// quantises the half-warp's row x again at `bits`; returns the new scale (all 16 lanes of the row)
+__device__ __forceinline__ float requant8(const float (&x)[8], int bits, int (&q)[8]) {
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    x[i] = __fmul_rn((float)code[i], scale);  // codes.float() * scale
-    amax = fmaxf(amax, fabsf(x[i]));
-  }
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // stays inside the half
   const int hi = (1 << (bits - 1)) - 1, lo = -(1 << (bits - 1));
-  float ns = __fdiv_rn(amax, (float)(hi > 1 ? hi : 1));
+  float ns = scale_of(amax, hi);
   if (ns == 0.f) ns = 1.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float v = rintf(__fdiv_rn(x[i], ns));
-    v = fminf(fmaxf(v, (float)lo), (float)hi);
-    q[i] = (int)v;
-  }
+  quantize_vals<8>(x, ns, lo, hi, q);
   return ns;
 }
 
+// head_dim 64: the same with 4 consecutive elements per lane
+__device__ __forceinline__ float requant4(const int (&code)[4], float scale, int bits, int (&q)[4]) {
+  float x[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[i] = __fmul_rn((float)code[i], scale);
+    amax = fmaxf(amax, fabsf(x[i]));
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const int hi = (1 << (bits - 1)) - 1, lo = -(1 << (bits - 1));
+  float ns = scale_of(amax, hi);
+  if (ns == 0.f) ns = 1.f;
+  quantize_vals<4>(x, ns, lo, hi, q);
+  return ns;
+}
+
+// packs the half-warp's 64-element row (4 codes per lane) and stores its 2 * bits words at dst
+__device__ __forceinline__ void pack4_store(const int (&code)[4], int bits, uint8_t* dst, int l16) {
+  const int wb = 4 * bits;  // bits this lane contributes: 8, 12, 16 or 32
+  uint32_t mine = 0;
+  if (bits == 8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mine |= ((uint32_t)code[i] & 0xffu) << (8 * i);
+  } else {
+    const int off = 1 << (bits - 1);
+    const uint32_t fm = (1u << bits) - 1u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mine |= (((uint32_t)(code[i] + off)) & fm) << (bits * i);
+  }
+  // lane l16 assembles word l16 of the row from the (at most four) lanes whose fields overlap it
+  const int base_lane = (threadIdx.x & 16), first = (32 * l16) / wb;
+  uint32_t word = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int sl = first + i;
+    const uint32_t f = __shfl_sync(0xffffffffu, mine, base_lane + (sl & 15));
+    const int pos = sl * wb - 32 * l16;
+    if (sl < 16 && pos < 32 && pos + wb > 0) word |= pos >= 0 ? (f << pos) : (f >> (-pos));
+  }
+  if (l16 < 2 * bits) reinterpret_cast<uint32_t*>(dst)[l16] = word;
+}
+
 // phase 0: source rows -> staging (requantised at the destination width); phase 1: staging -> destination.
-// One warp takes one move and walks its rows (layers of the call x KV heads x {K, V}).
+// Staging holds one row per (layer, KV head, K|V, move), moves innermost.
+//
+// A row is a separate memory transaction of 32..128 bytes.  Two things keep the memory system busy with
+// such small pieces: a warp takes kRowBatch consecutive moves of one (layer, KV head) and issues all their
+// loads before it does anything with them; and because consecutive moves mostly have consecutive source
+// and destination positions (the planner lists them in ascending order), the warps of a block touch
+// neighbouring rows, scales and staging rows at about the same time, so that the 4- and 8-byte scale
+// accesses and the short rows of neighbouring tokens share sectors and DRAM pages.
+// Half a warp per row: the K row in lanes 0..15, the V row of the same (token, head) in lanes 16..31.
+constexpr int kRowBatch = 4;
+
+struct MoveInfo {
+  int src, dst, seq;
+};
+
 template <int EPL, int PHASE>
-__global__ void repack_rows_kernel(const RowMoveParams p) {
+__global__ void __launch_bounds__(256) repack_rows_kernel(const RowMoveParams p) {
   const StoreGeom& g = p.g;
   __shared__ int s_prefix[kMaxSeqsRepack + 1];
   const int total_moves = load_move_prefix(p.n_moves, g.num_seqs, s_prefix);
   const int Hkv = g.num_kv_heads, nl = p.layer_end - p.layer_begin;
-  const int rows_per_move = nl * Hkv * 2;
-  if ((long long)total_moves * rows_per_move > p.staging_rows) {
+  if ((long long)total_moves * nl * Hkv * 2 > p.staging_rows) {
     if (threadIdx.x == 0 && blockIdx.x == 0 && p.err) atomicExch(p.err, 6);  // staging too small: nothing moves
     return;
   }
   const int lane = threadIdx.x & 31;
-  const int nwarps = gridDim.x * (blockDim.x >> 5);
-  for (int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); m < total_moves; m += nwarps) {
-    const int b = find_seq(s_prefix, g.num_seqs, m);
-    const int k = m - s_prefix[b];
-    const int src = p.move_src[(long long)b * g.slots + k], dst = p.move_dst[(long long)b * g.slots + k];
-    const int wb_s = bucket_of_slot(g, src), wb_d = bucket_of_slot(g, dst);
-    const int bits_s = bucket_bits(wb_s), bits_d = bucket_bits(wb_d);
-    const int rb_s = g.row_bytes[wb_s], rb_d = g.row_bytes[wb_d];
-    const int pos_s = src - g.bucket_base[wb_s], pos_d = dst - g.bucket_base[wb_d];
-    uint8_t* stage = p.staging + (long long)m * rows_per_move * kStageRowBytes;
-    for (int li = 0; li < nl; ++li) {
-      uint8_t* arena = arena_ptr(g, p.store, p.layer_begin + li, b);
-      if (PHASE == 0) {
-        const float* scales = reinterpret_cast<const float*>(arena + g.sc_off[wb_s]);
-        if constexpr (EPL == 4) {
-          // head_dim 128: lanes 0..15 take the K row, lanes 16..31 the V row of the same (token, head)
-          const int which = lane >> 4, l16 = lane & 15;
-          for (int h = 0; h < Hkv; ++h) {
-            const long long row = (long long)h * g.cap[wb_s] + pos_s;
-            const float2 sc = reinterpret_cast<const float2*>(scales)[row];
-            const uint8_t* rp = arena + (which ? g.v_off[wb_s] : g.k_off[wb_s]) + row * rb_s;
-            uint8_t* st = stage + ((li * Hkv + h) * 2 + which) * kStageRowBytes;
-            const float scale = which ? sc.y : sc.x;
-            if (bits_s == bits_d) {
-              const int words = rb_s >> 2;  // 8, 12, 16 or 32
-              if (l16 < words) reinterpret_cast<uint32_t*>(st)[l16] = reinterpret_cast<const uint32_t*>(rp)[l16];
-              if (l16 + 16 < words) reinterpret_cast<uint32_t*>(st)[l16 + 16] = reinterpret_cast<const uint32_t*>(rp)[l16 + 16];
-              if (l16 == 0) *reinterpret_cast<float*>(st + 128) = scale;
-            } else {
-              int code[8], q[8];
-              unpack8(rp, bits_s, l16, code);
-              const float ns = requant8(code, scale, bits_d, q);
-              pack8_store(q, bits_d, st, l16);
-              if (l16 == 0) *reinterpret_cast<float*>(st + 128) = ns;
-            }
-          }
+  const int which = lane >> 4, l16 = lane & 15;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const int groups = (total_moves + kRowBatch - 1) / kRowBatch;
+  const long long items = (long long)groups * nl * Hkv;
+  for (long long it = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); it < items; it += nwarps) {
+    int lh, grp;
+    if (items >> 31) {  // 64-bit division is a long subroutine: only where the item count needs it
+      lh = (int)(it / groups);
+      grp = (int)(it - (long long)lh * groups);
+    } else {
+      lh = (int)it / groups;
+      grp = (int)it - lh * groups;
+    }
+    const int li = lh / Hkv, h = lh - li * Hkv;
+    const int m0 = grp * kRowBatch;
+    // lanes 0..kRowBatch-1 look one move up each
+    MoveInfo mine{-1, -1, 0};
+    if (lane < kRowBatch && m0 + lane < total_moves) {
+      mine.seq = find_seq(s_prefix, g.num_seqs, m0 + lane);
+      const long long at = (long long)mine.seq * g.slots + (m0 + lane - s_prefix[mine.seq]);
+      mine.src = p.move_src[at];
+      mine.dst = p.move_dst[at];
+    }
+    // rows of (layer li, head h, K|V): staging row index = ((lh * 2 + which) * total_moves + move)
+    uint8_t* stage = p.staging + (((long long)lh * 2 + which) * total_moves + m0) * kStageRowBytes;
+    uint32_t w0[kRowBatch], w1[kRowBatch];
+    float sc[kRowBatch];
+    if (PHASE == 0) {
+#pragma unroll
+      for (int u = 0; u < kRowBatch; ++u) {
+        const int src = __shfl_sync(0xffffffffu, mine.src, u), seq = __shfl_sync(0xffffffffu, mine.seq, u);
+        const int dst = __shfl_sync(0xffffffffu, mine.dst, u);
+        w0[u] = w1[u] = 0u;
+        sc[u] = 0.f;
+        if (src < 0) continue;
+        const int wb_s = bucket_of_slot(g, src), bits_s = bucket_bits(wb_s), rb_s = g.row_bytes[wb_s];
+        const uint8_t* arena = arena_ptr(g, p.store, p.layer_begin + li, seq);
+        const long long row = (long long)h * g.cap[wb_s] + (src - g.bucket_base[wb_s]);
+        const uint32_t* rp =
+            reinterpret_cast<const uint32_t*>(arena + (which ? g.v_off[wb_s] : g.k_off[wb_s]) + row * rb_s);
+        const float2 t = reinterpret_cast<const float2*>(arena + g.sc_off[wb_s])[row];
+        sc[u] = which ? t.y : t.x;
+        if (bucket_of_slot(g, dst) == wb_s || EPL != 4) {
+          // the row only changes place (up to 32 words, two per lane), or head_dim 64: whole-row words
+          const int words = rb_s >> 2;
+          if (l16 < words) w0[u] = rp[l16];
+          if (l16 + 16 < words) w1[u] = rp[l16 + 16];
         } else {
-        for (int h = 0; h < Hkv; ++h) {
-          const long long row = (long long)h * g.cap[wb_s] + pos_s;
-          const float2 sc = reinterpret_cast<const float2*>(scales)[row];
+          // head_dim 128: 8 consecutive elements per lane lie in at most two aligned words
+          const int wi = (l16 * 8 * bits_s) >> 5;
+          w0[u] = rp[wi];
+          if (wi + 1 < 4 * bits_s) w1[u] = rp[wi + 1];
+        }
+      }
 #pragma unroll
-          for (int which = 0; which < 2; ++which) {
-            const uint8_t* rp = arena + (which ? g.v_off[wb_s] : g.k_off[wb_s]) + row * rb_s;
-            uint8_t* st = stage + ((li * Hkv + h) * 2 + which) * kStageRowBytes;
-            const float scale = which ? sc.y : sc.x;
-            if (bits_s == bits_d) {
-              if (lane < (rb_s >> 2)) reinterpret_cast<uint32_t*>(st)[lane] = reinterpret_cast<const uint32_t*>(rp)[lane];
-              if (lane == 0) *reinterpret_cast<float*>(st + 128) = scale;
-            } else {
-              int code[EPL];
-              unpack_row_words<EPL>(rp, bits_s, lane, code);
-              RowVals<EPL> x;
+      for (int u = 0; u < kRowBatch; ++u) {
+        const int src = __shfl_sync(0xffffffffu, mine.src, u), dst = __shfl_sync(0xffffffffu, mine.dst, u);
+        if (src < 0) continue;  // the same for the whole warp: the shuffles below see every lane
+        const int wb_s = bucket_of_slot(g, src), wb_d = bucket_of_slot(g, dst);
+        const int bits_s = bucket_bits(wb_s), bits_d = bucket_bits(wb_d);
+        uint8_t* st = stage + u * kStageRowBytes;
+        if (wb_s == wb_d) {
+          const int words = g.row_bytes[wb_s] >> 2;
+          if (l16 < words) reinterpret_cast<uint32_t*>(st)[l16] = w0[u];
+          if (l16 + 16 < words) reinterpret_cast<uint32_t*>(st)[l16 + 16] = w1[u];
+          if (l16 == 0) *reinterpret_cast<float*>(st + 128) = sc[u];
+        } else if constexpr (EPL == 4) {
+          float x[8];
+          int q[8];
+          dequant8(w0[u], w1[u], l16, bits_s, sc[u], x);
+          const float ns = requant8(x, bits_d, q);
+          pack8_store(q, bits_d, st, l16);
+          if (l16 == 0) *reinterpret_cast<float*>(st + 128) = ns;
+        } else {
+          // head_dim 64: 4 consecutive elements per lane, out of the row's words held by the half-warp
+          const int bitpos = l16 * 4 * bits_s, wi = bitpos >> 5, sh = bitpos & 31;
+          const int base_lane = lane & 16;
+          const uint32_t lo = __shfl_sync(0xffffffffu, w0[u], base_lane + (wi & 15));
+          const uint32_t hi = __shfl_sync(0xffffffffu, w0[u], base_lane + ((wi + 1) & 15));
+          const uint32_t field = __funnelshift_r(lo, hi, sh);
+          int code[4], q[4];
+          if (bits_s == 8) {
 #pragma unroll
-              for (int i = 0; i < EPL; ++i) x.v[i] = __fmul_rn((float)code[i], scale);  // codes.float() * scale
-              int q[EPL];
-              const float ns = quantize_row<EPL>(x, bits_d, q);
-              pack_store_row<EPL>(q, bits_d, st, lane);
-              if (lane == 0) *reinterpret_cast<float*>(st + 128) = ns;
-            }
+            for (int i = 0; i < 4; ++i) code[i] = (int)(int8_t)((field >> (8 * i)) & 0xffu);
+          } else {
+            const uint32_t fm = (1u << bits_s) - 1u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) code[i] = (int)((field >> (bits_s * i)) & fm) - (1 << (bits_s - 1));
           }
+          const float ns = requant4(code, sc[u], bits_d, q);
+          pack4_store(q, bits_d, st, l16);
+          if (l16 == 0) *reinterpret_cast<float*>(st + 128) = ns;
         }
-        }
-      } else {
-        float* scales = reinterpret_cast<float*>(arena + g.sc_off[wb_d]);
-        for (int h = 0; h < Hkv; ++h) {
-          const long long row = (long long)h * g.cap[wb_d] + pos_d;
+      }
+    } else {
 #pragma unroll
-          for (int which = 0; which < 2; ++which) {
-            uint8_t* rp = arena + (which ? g.v_off[wb_d] : g.k_off[wb_d]) + row * rb_d;
-            const uint8_t* st = stage + ((li * Hkv + h) * 2 + which) * kStageRowBytes;
-            if (lane < (rb_d >> 2)) reinterpret_cast<uint32_t*>(rp)[lane] = reinterpret_cast<const uint32_t*>(st)[lane];
-            if (lane == 0) scales[2 * row + which] = *reinterpret_cast<const float*>(st + 128);
-          }
-        }
+      for (int u = 0; u < kRowBatch; ++u) {
+        const int dst = __shfl_sync(0xffffffffu, mine.dst, u);
+        w0[u] = w1[u] = 0u;
+        sc[u] = 0.f;
+        if (dst < 0) continue;
+        const int words = g.row_bytes[bucket_of_slot(g, dst)] >> 2;
+        const uint32_t* st = reinterpret_cast<const uint32_t*>(stage + u * kStageRowBytes);
+        if (l16 < words) w0[u] = st[l16];
+        if (l16 + 16 < words) w1[u] = st[l16 + 16];
+        if (l16 == 0) sc[u] = reinterpret_cast<const float*>(st)[32];
+      }
+#pragma unroll
+      for (int u = 0; u < kRowBatch; ++u) {
+        const int dst = __shfl_sync(0xffffffffu, mine.dst, u), seq = __shfl_sync(0xffffffffu, mine.seq, u);
+        if (dst < 0) continue;
+        const int wb_d = bucket_of_slot(g, dst), rb_d = g.row_bytes[wb_d], words = rb_d >> 2;
+        uint8_t* arena = arena_ptr(g, p.store, p.layer_begin + li, seq);
+        const long long row = (long long)h * g.cap[wb_d] + (dst - g.bucket_base[wb_d]);
+        uint32_t* rp = reinterpret_cast<uint32_t*>(arena + (which ? g.v_off[wb_d] : g.k_off[wb_d]) + row * rb_d);
+        if (l16 < words) rp[l16] = w0[u];
+        if (l16 + 16 < words) rp[l16 + 16] = w1[u];
+        if (l16 == 0) reinterpret_cast<float*>(arena + g.sc_off[wb_d])[2 * row + which] = sc[u];
       }
     }
   }
