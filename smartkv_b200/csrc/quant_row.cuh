@@ -124,18 +124,35 @@ __device__ __forceinline__ void pack_store_row(const int (&code)[EPL], int bits,
 #pragma unroll
     for (int i = 0; i < EPL; ++i) mine |= (((uint32_t)(code[i] + off)) & fm) << (bits * i);
   }
-  // output word `lane` covers row bits [32*lane, 32*lane+32): gather the lanes that overlap it
-  const int nwords = wbits;  // 32 lanes * wbits bits / 32
-  const int first = (32 * lane) / wbits;
-  uint32_t word = 0;
-  const int max_src = 32 / wbits + 2;
-  for (int j = 0; j < max_src; ++j) {
-    int src = first + j;
-    uint32_t v = __shfl_sync(0xffffffffu, mine, src & 31);
-    int pos = src * wbits - 32 * lane;  // bit position of that lane's field inside my word
-    if (src < 32 && pos < 32 && pos + wbits > 0) word |= (pos >= 0) ? (v << pos) : (v >> (-pos));
+  // Neighbouring lanes' fields are joined by doubling (shuffle down, shift, or) until the lanes that
+  // lead a group hold whole words; no step depends on a division by the field width.
+  uint32_t* out = reinterpret_cast<uint32_t*>(dst);
+  if (bits == 3) {
+    // 3*EPL-bit fields -> 24-bit fields in every S-th lane; four of those make three words
+    constexpr int S = 8 / EPL;
+    int w = 3 * EPL;
+#pragma unroll
+    for (int st = 1; st < S; st <<= 1) {
+      mine |= __shfl_down_sync(0xffffffffu, mine, st) << w;
+      w <<= 1;
+    }
+    const uint32_t n = __shfl_down_sync(0xffffffffu, mine, S);  // the next 24-bit field
+    const int r = (lane / S) & 3;
+    const uint32_t word = r == 0 ? (mine | (n << 24)) : r == 1 ? ((mine >> 8) | (n << 16)) : ((mine >> 16) | (n << 8));
+    if ((lane & (S - 1)) == 0 && r < 3) out[3 * (lane / (4 * S)) + r] = word;
+  } else {
+    // field widths 4, 8, 16 or 32 bits: log2(32 / wbits) doubling steps (the width is the same for the whole warp)
+    int w = wbits, lg = 0;
+#pragma unroll
+    for (int st = 1; st < 8; st <<= 1) {
+      if (w < 32) {
+        mine |= __shfl_down_sync(0xffffffffu, mine, st) << w;
+        w <<= 1;
+        ++lg;
+      }
+    }
+    if ((lane & ((1 << lg) - 1)) == 0) out[lane >> lg] = mine;
   }
-  if (lane < nwords) reinterpret_cast<uint32_t*>(dst)[lane] = word;
 }
 
 // Reads this lane's EPL codes (element index = lane*EPL + i) out of a packed row.

@@ -52,6 +52,34 @@ def test_quantize_random_vs_oracle(bits, d):
     assert np.array_equal(s.view(np.uint32), so.view(np.uint32))
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+@pytest.mark.parametrize("d", [64, 128])
+def test_quantize_near_ties_and_extreme_scales(bits, d):
+    """Values whose quotient x / scale sits on or next to a half-integer, and rows whose scale is
+    tiny, huge or subnormal: the kernel's reciprocal-multiply shortcut must fall back to the IEEE
+    division exactly where the two could round differently."""
+    rng = np.random.default_rng(900 + bits + d)
+    levels = max(2 ** (bits - 1) - 1, 1)
+    rows = []
+    for amax in (1.0, 3.0, 0.7310585, 127.0, 1e-3, 6.1e-5, 2.5e7, 1e-33, 1e33, 3e-39, 1e-44):
+        amax = np.float32(amax)
+        s = np.float32(amax / np.float32(levels))
+        for _ in range(24):
+            k = rng.integers(-levels, levels, size=d).astype(np.float32)
+            delta = rng.choice([0.0, 1e-7, -1e-7, 1e-6, -1e-6, 3e-5, -3e-5, 1.2e-4, -1.2e-4, 1.3e-4, -1.3e-4, 4e-4],
+                               size=d).astype(np.float32)
+            x = ((k + np.float32(0.5) + delta) * s).astype(np.float32)
+            x = np.clip(x, -amax, amax)
+            x[rng.integers(0, d)] = amax * rng.choice([-1.0, 1.0])   # pins the row's absolute maximum
+            rows.append(x.astype(np.float32))
+    x = np.stack(rows)
+    q, s = _quantize_gpu(x, bits)
+    with np.errstate(all="ignore"):
+        qo, so = orc.quantize_rows(x, bits)
+    assert np.array_equal(s.view(np.uint32), so.view(np.uint32))
+    assert np.array_equal(q, qo)
+
+
 def test_quantize_fp16_input():
     rng = np.random.default_rng(3)
     x = rng.standard_normal((300, 128)).astype(np.float16)
