@@ -38,7 +38,7 @@ struct AttnCfg {
   static constexpr int NCONS = NCONS_, STAGES = STAGES_, STAGE_BYTES = STAGE_BYTES_;
 };
 constexpr int kMaxPartialsPerRun = 11;  // consumer warps of the widest configuration
-using AttnCfgFast = AttnCfg<11, 3, 63360>;  // 11 consumer warps x 168 registers beat 15 x 128 (no remat of constants)     // fp16 queries: 16 warps x 128 registers; 15 8-bit tiles per stage
+using AttnCfgFast = AttnCfg<11, 3, 63360>;  // fp16 queries: 11 consumer warps x 145 registers (12 were no faster, 13 and 15 at 128 registers slower); 15 8-bit tiles per stage
 using AttnCfgPrecise = AttnCfg<7, 3, 42240>;   // fp32 queries (hi/lo split): 8 warps, more registers per thread
 
 // tiles per block for a bit-width: as many 16-key tiles as fit one stage
