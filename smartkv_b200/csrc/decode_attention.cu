@@ -491,6 +491,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     int stg = 0, qi = 0;
     uint32_t epar = 1, qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
     const int kbt[kNumBuckets] = {KBT0, KBT1, KBT2, KBT3};
+    bool first_block = true;
     const uint64_t stream_policy = l2_evict_first_policy();  // the cache is read once per step
     constexpr int NL = Slot::NLIMB;
     constexpr int EPL = D / 32;  // query elements per lane and head
@@ -500,11 +501,14 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       for (; ci < kNumBuckets; ++ci, ct0 = -1) {
         if (ct0 < 0) ct0 = d.ka[ci];
         const int pd = g.row_bytes[ci], kbkeys = kbt[ci] * 16;
-        for (; ct0 < d.kb[ci]; ct0 += kbt[ci]) {
+        for (int step = 0; ct0 < d.kb[ci]; ct0 += step) {
           if (limit-- <= 0) return true;
+          // the CTA's very first block is short (one tile per consumer warp), so that it arrives early
+          step = (first_block && kbt[ci] > NCONS) ? NCONS : kbt[ci];
+          first_block = false;
           if (!wait_or_abort(&empty[stg], epar, abort_flag, p.err)) return false;
           if (lane == 0 && p.debug_mode < 2) {
-            const int ntl = (d.kb[ci] - ct0) < kbt[ci] ? (d.kb[ci] - ct0) : kbt[ci];
+            const int ntl = (d.kb[ci] - ct0) < step ? (d.kb[ci] - ct0) : step;
             const int key0 = ct0 * 16;
             const int nkeys = (d.cnt[ci] - key0) < ntl * 16 ? (d.cnt[ci] - key0) : ntl * 16;
             const int n16 = (nkeys + 15) & ~15;
@@ -573,6 +577,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
   int stg = 0, qi = 0;
   uint32_t fpar = 0, qfpar = 0;
   bool aborted = false;
+  bool first_block = true;  // the CTA's first block holds one tile per consumer warp
   for (int r = run_begin; r < run_end; ++r) {
     if (!aborted && !wait_or_abort(&qfull[qi], qfpar, abort_flag, p.err)) aborted = true;
     SKV_TL(2 + 4 * (r - run_begin));
@@ -602,8 +607,10 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       if (d.ka[bucket] >= d.kb[bucket]) return;
       QFrags<D, BITS, PRECISE> qf;
       load_qfrags<D, BITS, PRECISE>(slot, lane, qf);
-      for (int t0 = d.ka[bucket]; t0 < d.kb[bucket]; t0 += KBT) {
-        const int ntl = (d.kb[bucket] - t0) < KBT ? (d.kb[bucket] - t0) : KBT;
+      for (int t0 = d.ka[bucket], step = 0; t0 < d.kb[bucket]; t0 += step) {
+        step = (first_block && KBT > NCONS) ? NCONS : KBT;  // as the producer issued it
+        first_block = false;
+        const int ntl = (d.kb[bucket] - t0) < step ? (d.kb[bucket] - t0) : step;
         const int key0 = t0 * 16;
         const int nkeys = (d.cnt[bucket] - key0) < ntl * 16 ? (d.cnt[bucket] - key0) : ntl * 16;
         if (!aborted && !wait_or_abort(&full[stg], fpar, abort_flag, p.err)) aborted = true;
