@@ -185,13 +185,24 @@ def run_ours(args):
     importance_sync = ImportanceSync(store, dist if world > 1 else None)
     if world > 1:
         # first use of the communicator (connection set-up) happens here, not inside the timed region
-        warm = torch.zeros(1024, dtype=torch.float64, device=dev)
+        # (with a buffer of the size the importance sync exchanges: the first all-reduce of a size costs ms)
+        warm = torch.zeros_like(store.cumulative)
+        dist.all_reduce(warm)
         dist.all_reduce(warm)
         torch.cuda.synchronize()
 
+    sync_events = []
+
     def reallocate():
         importance_sync()              # KV-head shards: sum the per-shard importance first (no-op on 1 GPU)
-        store.reallocate(alloc_cfg)
+        if world > 1:                  # when the all-reduce was through (it waits for the slowest rank)
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            sync_events.append(e)
+        if args.no_graph:
+            store.reallocate(alloc_cfg)
+        else:
+            store.reallocate_graphed(alloc_cfg)
         importance_sync.after_repack()
 
     reallocate()
@@ -200,7 +211,7 @@ def run_ours(args):
     counts0 = store.counts.cpu().numpy()
     hist = counts0.sum(0).tolist()
     realloc_chunks = -(-L // max(1, min(L, (1 << 30) // max(1, int(store.lib.skv_requant_staging_bytes(
-        ctypes.byref(store.desc), store.appended_total, 1))))))
+        ctypes.byref(store.desc), store.appended_total if args.no_graph else store.num_seqs * store.slots, 1))))))
     realloc_launches = 15 + (3 if B > 1 else 0) + 2 * realloc_chunks
 
     # ---- per-step inputs (resident) -----------------------------------------------------------
@@ -332,6 +343,8 @@ def run_ours(args):
 
     realloc_every = cfg["realloc_every"]
     realloc_events = []
+    moved_log = torch.zeros(256, dtype=torch.int64, device=dev)  # tokens moved by every timed reallocation
+    rank_ms = {}
 
     def timed(fn, n_warm, n_steps, first, with_realloc=True):
         for i in range(n_warm):
@@ -352,6 +365,8 @@ def run_ours(args):
                 ev[0].record()
                 reallocate()
                 ev[1].record()
+                if len(realloc_events) < moved_log.numel():
+                    moved_log[len(realloc_events)].copy_(store._realloc["n_moves"].sum())
                 realloc_events.append(ev)
                 launches[0] += realloc_launches
         e1.record()
@@ -364,8 +379,10 @@ def run_ours(args):
         step_bytes = L * (per_layer[0] + per_layer[1]) / 2.0
         if world > 1:
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+            every = [torch.zeros_like(t) for _ in range(world)]
+            dist.all_gather(every, t)
+            rank_ms[fn.__name__] = [round(float(x.item()) / n_steps, 4) for x in every]
+            ms = max(float(x.item()) for x in every)
             bt = torch.tensor([step_bytes], device=dev, dtype=torch.float64)
             dist.all_reduce(bt, op=dist.ReduceOp.SUM)
             step_bytes = float(bt.item())
@@ -422,6 +439,11 @@ def run_ours(args):
                 "copies": "per layer on two copy streams inside the step's CUDA graph" if e2e_graphs else "around the step"},
         "reallocation_ms": round(float(np.mean(realloc_ms)), 3) if realloc_ms else None,
         "reallocation_moved_tokens": int(store._realloc["n_moves"].sum()) if realloc_ms else None,   # last one
+        "reallocation_detail": [[round(m, 3), int(n)] for m, n in
+                                zip(realloc_ms + realloc_ms_e2e, moved_log[:len(realloc_ms) + len(realloc_ms_e2e)].tolist())],
+        "ms_per_step_by_rank": rank_ms or None,
+        "reallocation_wait_for_ranks_ms": ([round(a[0].elapsed_time(b), 3) for a, b in zip(realloc_events, sync_events[1:])]
+                                           if sync_events else None),
         "gpu_launches": int(n_launch), "cuda_graph": graph is not None,
         "clocks": clocks,
     }

@@ -496,6 +496,25 @@ class PackedKVStore:
         new_bits, _, _ = self.allocate_bits(cfg)
         self.repack(new_bits, max_moves=max_moves)
 
+    def reallocate_graphed(self, cfg):
+        """reallocate() as one CUDA graph launch: a reallocation is about 70 small launches, and issuing them
+        one by one costs more than running them once the allocation has settled.  The first call runs eagerly
+        (it sizes every buffer for the store's whole capacity, so that the captured launches stay valid as the
+        cache grows) and captures the graph; later calls replay it.  ``cfg`` must be the same at every call."""
+        self.flush_importance()
+        cap_moves = self.num_seqs * self.slots
+        if getattr(self, "_realloc_graph", None) is None:
+            self.reallocate(cfg, max_moves=cap_moves)
+            self._realloc_cfg = cfg  # the graph's kernels hold a copy of it; keeps the object alive all the same
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.reallocate(cfg, max_moves=cap_moves)
+            self._realloc_graph = graph
+            return
+        self._realloc_graph.replay()
+        self._plan_valid = False
+
     def token_bits(self, seq: int) -> torch.Tensor:
         """Width of every token of one sequence, indexed by token id (syncs; tests and the API mirror)."""
         counts = self.counts[seq].tolist()
