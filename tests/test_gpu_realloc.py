@@ -225,3 +225,34 @@ def test_repack_keeps_per_token_state_and_attention():
             assert np.array_equal(ksc.cpu().numpy(), ks) and np.array_equal(vsc.cpu().numpy(), vs)
             ref, _ = oracle_attention(q[b], kq, vq, ks, vs, hq // hkv)
             assert_close(out[b], ref, what=f"attention after repack l{l} b{b}")
+
+
+def test_reallocate_graphed_equals_eager():
+    """reallocate_graphed (first call eager + capture, later calls one graph launch) leaves the store in
+    exactly the state reallocate() does, also when the importance changes between the calls."""
+    rng = np.random.default_rng(11)
+    B, hq, hkv, d, n, L = 2, 8, 2, 128, 700, 2
+    stores = [make_store(L, B, hkv, d, hq, n) for _ in range(2)]
+    kvs = []
+    for l in range(L):
+        k, v = orc.synth_kv(B * n, hkv, d, seed=300 + l)
+        kvs.append((k.reshape(B, n, hkv, d), v.reshape(B, n, hkv, d)))
+    bits0 = rng.choice((2, 3, 4, 8), size=(B, n))
+    for s in stores:
+        fill_store(s, kvs, bits0)
+    cfgs = [s.make_alloc_config(0.35) for s in stores]
+    for rnd in range(3):
+        imps = [_random_importance(rng, n, (b + rnd) % 3) for b in range(B)]
+        for s in stores:
+            for b in range(B):
+                _scatter_scores(s, b, imps[b])
+        stores[0].reallocate(cfgs[0])
+        stores[1].reallocate_graphed(cfgs[1])     # round 0: eager + capture; rounds 1, 2: replay
+        for s in stores:
+            s.check_errors()
+        a, g = stores
+        assert torch.equal(a.counts, g.counts) and torch.equal(a.slot_token, g.slot_token), rnd
+        assert torch.equal(a.arena, g.arena), rnd
+        assert torch.equal(a.cumulative, g.cumulative) and torch.equal(a.rank_streak, g.rank_streak), rnd
+    q = torch.from_numpy(rng.standard_normal((B, hq, d)).astype(np.float32)).cuda()
+    assert torch.equal(stores[0].attention(0, q), stores[1].attention(0, q))
