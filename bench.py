@@ -155,6 +155,13 @@ def run_ours(args):
     cfg = dict(CFG)
     if args.layers:
         cfg["num_layers"] = args.layers      # profiler captures only: fewer layers = less device memory
+    # other shapes with the same kernels and settings (e.g. one long sequence); not the contract's workload
+    if args.batch:
+        cfg["batch"] = args.batch
+    if args.context:
+        cfg["context"] = args.context
+    if args.budget:
+        cfg["memory_budget"] = args.budget
     L, Hq, Hkv, D, B, N = (cfg[k] for k in ("num_layers", "num_q_heads", "num_kv_heads", "head_dim", "batch", "context"))
     steps, warmup = args.steps, args.warmup
     total_steps = steps * 3 + warmup * 2 + 8
@@ -418,15 +425,15 @@ def run_ours(args):
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma, f32 accumulate",
         "data": "synthetic (seeded N(0,1) K/V, 4 outlier channels x8 per head, Zipf(1.1) importance)",
-        "config": {"workload": f"BASELINE config 1: Llama-3.1-8B attention shape, {L} layers, batch 16, context 8192, "
-                               "budget 0.35, bits [2,3,4,8], fp16 query; one decode step per step",
+        "config": {"workload": f"BASELINE config 1: Llama-3.1-8B attention shape, {L} layers, batch {B}, context {N}, "
+                               f"budget {cfg['memory_budget']}, bits [2,3,4,8], fp16 query; one decode step per step",
                    "kv_heads_per_gpu": Hkv, "l2": "inputs larger than L2 (packed cache per step >> 126 MB)",
                    "bucket_histogram_2_3_4_8": hist, "reallocation": f"device allocator + requantise/repack of all layers after every {realloc_every}th "
                                    f"step, inside the timed region ({len(realloc_ms)} in {steps} steps)",
                    "packed_bytes_per_step": int(step_bytes)},
         "decode_tokens_per_s": round(B * world * steps / (ms * 1e-3), 1),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": ATTN_DRAM_TRAFFIC_PER_LAUNCH,
+                     "frac": round(achieved / peak, 4), "traffic": ATTN_DRAM_TRAFFIC_PER_LAUNCH if not (args.batch or args.context or args.budget) else None,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
                                        "profiles/decode_attn_kernel_config1_shape_2layers.md",
                      "peak_source": peak_kind,
@@ -565,6 +572,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--batch", type=int, default=0, help="other batch than the contract's 16 (extra measurements only)")
+    ap.add_argument("--context", type=int, default=0, help="other context than the contract's 8192 (extra measurements only)")
+    ap.add_argument("--budget", type=float, default=0.0, help="other memory budget than the contract's 0.35")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the layer count (profiler captures of a small case only; not a bench line)")
     args = ap.parse_args()
