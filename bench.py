@@ -41,6 +41,8 @@ CFG = dict(num_layers=32, num_q_heads=32, num_kv_heads=8, head_dim=128, batch=16
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes one attention launch of this workload moved under ncu (188.44 MB read + 6.96 MB written)
 ATTN_DRAM_TRAFFIC_PER_LAUNCH = 195_400_000
+# staging of the graphed reallocation: 4 GiB lets one pair of row-move launches cover 14 of the 32 layers
+REALLOC_STAGING_BYTES = 4 << 30
 
 
 def measured_peak():
@@ -209,7 +211,7 @@ def run_ours(args):
         if args.no_graph:
             store.reallocate(alloc_cfg)
         else:
-            store.reallocate_graphed(alloc_cfg)
+            store.reallocate_graphed(alloc_cfg, staging_budget=REALLOC_STAGING_BYTES)
         importance_sync.after_repack()
 
     reallocate()
@@ -217,7 +219,7 @@ def run_ours(args):
     store.check_errors()
     counts0 = store.counts.cpu().numpy()
     hist = counts0.sum(0).tolist()
-    realloc_chunks = -(-L // max(1, min(L, (1 << 30) // max(1, int(store.lib.skv_requant_staging_bytes(
+    realloc_chunks = -(-L // max(1, min(L, ((1 << 30) if args.no_graph else REALLOC_STAGING_BYTES) // max(1, int(store.lib.skv_requant_staging_bytes(
         ctypes.byref(store.desc), store.appended_total if args.no_graph else store.num_seqs * store.slots, 1))))))
     realloc_launches = 15 + (3 if B > 1 else 0) + 2 * realloc_chunks
 

@@ -177,13 +177,16 @@ struct RowMoveParams {
 
 // prefix of the per-sequence move counts into shared memory; returns the total
 __device__ __forceinline__ int load_move_prefix(const int32_t* n_moves, int B, int* s_prefix) {
+  // all counts are fetched at once (one round trip to memory), then one thread adds them up
+  for (int b = threadIdx.x; b < B; b += blockDim.x) s_prefix[b + 1] = n_moves[b];
+  __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0;
+    s_prefix[0] = 0;
     for (int b = 0; b < B; ++b) {
-      s_prefix[b] = acc;
-      acc += n_moves[b];
+      acc += s_prefix[b + 1];
+      s_prefix[b + 1] = acc;
     }
-    s_prefix[B] = acc;
   }
   __syncthreads();
   return s_prefix[B];

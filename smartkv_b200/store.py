@@ -491,25 +491,27 @@ class PackedKVStore:
               "skv_repack_meta")
         self._plan_valid = False
 
-    def reallocate(self, cfg, max_moves: Optional[int] = None):
+    def reallocate(self, cfg, max_moves: Optional[int] = None, staging_budget: int = 1 << 30):
         """allocate_bits + repack: one reallocation of the whole store."""
         new_bits, _, _ = self.allocate_bits(cfg)
-        self.repack(new_bits, max_moves=max_moves)
+        self.repack(new_bits, max_moves=max_moves, staging_budget=staging_budget)
 
-    def reallocate_graphed(self, cfg):
+    def reallocate_graphed(self, cfg, staging_budget: int = 1 << 30):
         """reallocate() as one CUDA graph launch: a reallocation is about 70 small launches, and issuing them
         one by one costs more than running them once the allocation has settled.  The first call runs eagerly
         (it sizes every buffer for the store's whole capacity, so that the captured launches stay valid as the
-        cache grows) and captures the graph; later calls replay it.  ``cfg`` must be the same at every call."""
+        cache grows) and captures the graph; later calls replay it.  ``cfg`` must be the same at every call.
+        ``staging_budget`` bytes of staging decide how many layers one pair of row-move launches covers: every
+        pair costs tens of microseconds however few rows move, so a larger budget makes a quiet reallocation cheaper."""
         self.flush_importance()
         cap_moves = self.num_seqs * self.slots
         if getattr(self, "_realloc_graph", None) is None:
-            self.reallocate(cfg, max_moves=cap_moves)
+            self.reallocate(cfg, max_moves=cap_moves, staging_budget=staging_budget)
             self._realloc_cfg = cfg  # the graph's kernels hold a copy of it; keeps the object alive all the same
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                self.reallocate(cfg, max_moves=cap_moves)
+                self.reallocate(cfg, max_moves=cap_moves, staging_budget=staging_budget)
             self._realloc_graph = graph
             return
         self._realloc_graph.replay()
