@@ -241,18 +241,18 @@ def test_reallocate_graphed_equals_eager():
     for s in stores:
         fill_store(s, kvs, bits0)
     cfgs = [s.make_alloc_config(0.35) for s in stores]
-    for rnd in range(3):
-        imps = [_random_importance(rng, n, (b + rnd) % 3) for b in range(B)]
+    for it in range(3):
+        imps = [_random_importance(rng, n, (b + it) % 3) for b in range(B)]
         for s in stores:
             for b in range(B):
                 _scatter_scores(s, b, imps[b])
         stores[0].reallocate(cfgs[0])
-        stores[1].reallocate_graphed(cfgs[1])     # round 0: eager + capture; rounds 1, 2: replay
+        stores[1].reallocate_graphed(cfgs[1])     # first pass: eager + capture; later passes: replay
         for s in stores:
             s.check_errors()
         a, g = stores
-        assert torch.equal(a.counts, g.counts) and torch.equal(a.slot_token, g.slot_token), rnd
-        assert torch.equal(a.arena, g.arena), rnd
-        assert torch.equal(a.cumulative, g.cumulative) and torch.equal(a.rank_streak, g.rank_streak), rnd
+        assert torch.equal(a.counts, g.counts) and torch.equal(a.slot_token, g.slot_token), it
+        assert torch.equal(a.arena, g.arena), it
+        assert torch.equal(a.cumulative, g.cumulative) and torch.equal(a.rank_streak, g.rank_streak), it
     q = torch.from_numpy(rng.standard_normal((B, hq, d)).astype(np.float32)).cuda()
     assert torch.equal(stores[0].attention(0, q), stores[1].attention(0, q))
