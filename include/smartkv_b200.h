@@ -147,11 +147,11 @@ int64_t skv_attn_plan_bytes(const SkvStoreDesc* desc, int num_ctas);
  * skv_lse_combine folds runs * this many partials per (sequence, KV head). */
 int skv_attn_partials_per_run(const SkvStoreDesc* desc, int query_dtype);
 
-/* Builds the work partition of one decode step: which 16-key tiles of which
- * (sequence, KV head) every persistent CTA streams, balanced by estimated time.  It
- * depends only on the bucket counts, which are the same for every layer of the
- * step, so one call serves all layers.  No counterpart in the reference (its kernel
- * walks one head per CTA, smartkv/csrc/quantized_attention.cu:679-777).
+/* Builds the work partition of one decode step: which tiles of which (sequence, KV head) every
+ * persistent CTA streams, balanced by estimated time (tiles of 128 keys where the tensor-memory
+ * kernel serves the shape, of 16 keys otherwise).  It depends only on the bucket counts, which are
+ * the same for every layer of the step, so one call serves all layers.  No counterpart in the
+ * reference (its kernel walks one head per CTA, smartkv/csrc/quantized_attention.cu:679-777).
  *   counts int32 [num_seqs][4] live tokens per bucket (device); plan: device buffer
  *   of skv_attn_plan_bytes() bytes. */
 int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, int num_ctas, void* plan, void* stream);
@@ -162,15 +162,40 @@ int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, int num_ctas,
  *
  * Streams the packed buckets of `layer` for every sequence, split-KV over
  * persistent CTAs as laid out by `plan`, and writes partial (max, sum, out) triples into
- * `partials`: skv_attn_partials_per_run() of them per run (one per consumer warp); if `logits`
+ * `partials`: skv_attn_partials_per_run() of them per run; if `logits`
  * is not NULL it also writes the scaled logit (log2 units) of every cached key,
  * logits[seq][q_head][storage index].
  *   query    [num_seqs][num_q_heads][head_dim] fp32 or fp16
  * num_q_heads must be a multiple of num_kv_heads with group size <= 8.
+ * Two kernels serve the call.  head_dim 128 with fp16 queries runs on the tcgen05 tensor cores with the
+ * keys as the M operand, accumulators in tensor memory and the 8-bit rows landed by tiled TMA loads;
+ * every other shape runs the mma.sync fragment kernel.  Both read the same store and the same plan.
  * err_flag: device int32, set non-zero if a bounded wait inside the kernel gave up. */
 int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
                          const void* query, int query_dtype, int num_q_heads, void* partials, int num_ctas,
                          float* logits, int32_t* err_flag, void* stream);
+
+/* skv_decode_attention with the additive attention mask the reference's kernels take
+ * (smartkv/csrc/quantized_attention.cu:213-216, 570-575: mask indexed by the key's global slot).
+ *   mask fp32 [num_seqs][mask_stride], natural-log units, indexed by TOKEN ID (position in the
+ *   sequence); slot_token int32 [num_seqs][slots] gives the token id of every storage index.
+ *   mask == NULL: no mask (slot_token may then be NULL).  The mask value of the step's current token is
+ *   an argument of the combine step (skv_lse_combine_masked). */
+int skv_decode_attention_masked(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
+                                const void* query, int query_dtype, int num_q_heads, void* partials, int num_ctas,
+                                float* logits, const float* mask, int64_t mask_stride, const int32_t* slot_token,
+                                int32_t* err_flag, void* stream);
+
+/* Kernel selection for skv_decode_attention: 0 = automatic (default), 1 = always the mma.sync fragment
+ * kernel, 2 = the tensor-memory kernel wherever it applies.  Process-wide; plans and partials built
+ * under one setting must be consumed under the same setting.  No counterpart in the reference. */
+int skv_set_attention_path(int path);
+int skv_get_attention_path(void);
+
+/* Limit of every bounded device-side wait of the attention kernels, in polls of about 50 ns (default
+ * 2^24, about one second).  When a wait runs out the kernel sets *err_flag and returns; nothing faults.
+ * No counterpart in the reference. */
+int skv_set_wait_limit(unsigned polls);
 
 /* Combines the partials with the newest token, which takes part in full precision
  * (smartkv/core/fused_cpu.py:115-137; wrapper call smartkv/models/llama_smartkv.py:264-305),

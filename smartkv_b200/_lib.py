@@ -81,6 +81,11 @@ _SIGNATURES = {
     "skv_attn_plan": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p]),
     "skv_decode_attention": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "skv_decode_attention_masked": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                            c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "skv_set_attention_path": (c_int, [c_int]),
+    "skv_get_attention_path": (c_int, []),
+    "skv_set_wait_limit": (c_int, [ctypes.c_uint]),
     "skv_decode_attention_static": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                             c_int, c_void_p, c_void_p, POINTER(c_void_p), c_void_p]),
     "skv_lse_combine": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,

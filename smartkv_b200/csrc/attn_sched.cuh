@@ -1,12 +1,14 @@
-// Work partition of the fused decode attention: which 16-key tiles of which
-// (sequence, KV head) segment a persistent CTA owns.
+// Work partition of the fused decode attention: which tiles of which (sequence, KV head) segment a
+// persistent CTA owns.
 //
-// Every segment is a string of cost units: for each bucket in turn, ceil(count/16) tiles of
-// tile_cost(bucket), the time one CTA needs per tile of that width (measured with every token at
-// that width: narrow tiles are bound by their arithmetic, 8-bit tiles by their bytes; 3-bit tiles
-// pay for the costlier field extraction).  tile_bytes = 16 * (2*row_bytes + 8) (packed K rows, V rows and a
-// float2 of scales per key) is what a tile occupies in a stage.  All heads of a sequence have the
-// same length W[b].
+// Two kernels consume a plan and each has its own cost model (`model`):
+//   model 0  mma.sync fragment kernel: tiles of 16 keys; the cost of a tile is the time one CTA needs
+//            for it (measured with every token at that width: narrow tiles are bound by their
+//            arithmetic, 8-bit tiles by their bytes)
+//   model 1  tensor-memory (tcgen05) kernel: tiles of 128 keys = one MMA block; the cost is the block's
+//            bytes plus a fixed term for the per-block arithmetic and hand-offs
+// Every segment is a string of cost units: for each bucket in turn, ceil(count / tile_keys) tiles of
+// tile_cost(bucket).  All heads of a sequence have the same length W[b].
 // The global string concatenates the segments in (sequence, head) order; CTA c
 // owns the tiles whose first unit lies in [ceil(c*T/C), ceil((c+1)*T/C)), i.e. the
 // CTAs are balanced by estimated time and never share a tile.  A maximal piece of one
@@ -25,11 +27,17 @@ __host__ __device__ constexpr int tile_bytes_for(int head_dim, int bits) {
   return 16 * (2 * row_bytes_for(head_dim, bits) + 8);
 }
 
-// nanoseconds one CTA spends per tile of each width at head_dim 128 (B200, all tokens at one width:
-// 46.5 / 51.6 / 48.9 / 63.3 us per launch of 65,536 tiles on 148 CTAs); only the ratios matter
-constexpr int kTileFixedCost = 0;  // kept for the plan kernel's signature
-__host__ __device__ constexpr int tile_cost_for(int head_dim, int bits, int fixed) {
-  return (bits == 2 ? 105 : bits == 3 ? 116 : bits == 4 ? 110 : 143) + fixed + 0 * head_dim;
+constexpr int kPlanModelFrag = 0;  // 16-key tiles, mma.sync fragment kernel
+constexpr int kPlanModelTc = 1;    // 128-key tiles, tensor-memory kernel
+__host__ __device__ constexpr int plan_tile_keys(int model) { return model == kPlanModelTc ? 128 : 16; }
+
+// Relative cost of one tile.  Model 0: nanoseconds one CTA spends per 16-key tile of each width at
+// head_dim 128 (B200, all tokens at one width: 46.5 / 51.6 / 48.9 / 63.3 us per launch of 65,536 tiles
+// on 148 CTAs).  Model 1: the block's bytes in units of 256 B plus a fixed per-block term.  Only the
+// ratios matter.
+__host__ __device__ constexpr int tile_cost_for(int head_dim, int bits, int model) {
+  if (model == kPlanModelTc) return 128 * (2 * row_bytes_for(head_dim, bits) + 8) / 256 + 24;
+  return bits == 2 ? 105 : bits == 3 ? 116 : bits == 4 ? 110 : 143;
 }
 
 struct SegLayout {
@@ -39,15 +47,16 @@ struct SegLayout {
   long long bytes;               // W: cost units of one segment of this sequence
 };
 
-__host__ __device__ inline SegLayout seg_layout(const int32_t* counts4, int head_dim, int fixed = kTileFixedCost) {
+__host__ __device__ inline SegLayout seg_layout(const int32_t* counts4, int head_dim, int model) {
   SegLayout s;
   long long off = 0;
+  const int tk = plan_tile_keys(model);
 #pragma unroll
   for (int i = 0; i < kNumBuckets; ++i) {
     s.cnt[i] = counts4[i];
-    s.nt[i] = (counts4[i] + 15) >> 4;
+    s.nt[i] = (counts4[i] + tk - 1) / tk;
     s.start[i] = off;
-    off += (long long)s.nt[i] * tile_cost_for(head_dim, bucket_bits(i), fixed);
+    off += (long long)s.nt[i] * tile_cost_for(head_dim, bucket_bits(i), model);
   }
   s.bytes = off;
   return s;
@@ -60,12 +69,11 @@ __host__ __device__ inline long long cta_range_begin(long long total, int c, int
 // Tiles [ka, kb) of every bucket whose first unit lies in the segment-local range [lo, hi).
 // Returns the number of tiles.
 __host__ __device__ inline int seg_tiles_in_range(const SegLayout& s, int head_dim, long long lo, long long hi,
-                                                  int (&ka)[kNumBuckets], int (&kb)[kNumBuckets],
-                                                  int fixed = kTileFixedCost) {
+                                                  int (&ka)[kNumBuckets], int (&kb)[kNumBuckets], int model) {
   int total = 0;
 #pragma unroll
   for (int i = 0; i < kNumBuckets; ++i) {
-    const long long tb = tile_cost_for(head_dim, bucket_bits(i), fixed);
+    const long long tb = tile_cost_for(head_dim, bucket_bits(i), model);
     long long a = lo - s.start[i], b = hi - s.start[i];
     a = a <= 0 ? 0 : (a + tb - 1) / tb;
     b = b <= 0 ? 0 : (b + tb - 1) / tb;
@@ -78,7 +86,8 @@ __host__ __device__ inline int seg_tiles_in_range(const SegLayout& s, int head_d
   return total;
 }
 
-// One run: the tiles [ka, kb) of each bucket of segment (seq, head) that one CTA streams.
+// One run: the tiles [ka, kb) of each bucket of segment (seq, head) that one CTA streams, in units of the
+// plan's tile size (header word 3).
 struct __align__(16) RunDesc {
   int seq, head;
   int ka[kNumBuckets];
@@ -89,7 +98,7 @@ struct __align__(16) RunDesc {
 static_assert(sizeof(RunDesc) == 64, "RunDesc is one 64-byte record");
 
 // Plan buffer (int32 words):
-//   [0] number of runs  [1] number of CTAs  [2] number of segments  [3] reserved
+//   [0] number of runs  [1] number of CTAs  [2] number of segments  [3] keys per tile (16 or 128)
 //   cta_begin[C + 1]     first run of every CTA
 //   seg_begin[nseg]      first run of every segment (undefined when seg_count is 0)
 //   seg_count[nseg]      runs of every segment

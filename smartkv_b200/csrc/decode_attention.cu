@@ -17,19 +17,18 @@
 // CTA per head walking the whole context) and the host LSE combine in
 // smartkv/kernels/__init__.py:350-371; numerics follow the CPU streaming path
 // smartkv/core/fused_cpu.py:70-113 (dequantise, q.k/sqrt(d), online softmax).
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
 #include "attn_frag.cuh"
-#include "attn_sched.cuh"
+#include "attn_params.cuh"
 #include "post_attention.cuh"
 
 namespace skv {
 
-constexpr int kMaxSeqs = 1024;
-constexpr int kMaxCtas = 1024;
 constexpr int kQBufs = 4;        // query / run-descriptor ring (the producer runs at most STAGES blocks ahead)
 
 // Shape of the persistent CTA: NCONS consumer warps + 1 producer warp share STAGES stages.
@@ -46,62 +45,20 @@ __host__ __device__ constexpr int block_tiles(int stage_bytes, int head_dim, int
   return stage_bytes / tile_bytes_for(head_dim, bits);
 }
 
-struct AttnParams {
-  StoreGeom g;
-  const uint8_t* store;
-  int layer;
-  const int* plan;
-  const void* query;
-  int q_is_half;
-  int num_q_heads;
-  int group;
-  float* partials;
-  int num_ctas;
-  float* logits;
-  int32_t* err;
-  float scale_log2;
-  int debug_mode;  // 0 = normal; timing probes: 1 = stream only (no math), 2 = math only (no copies), 3 = neither
-#ifdef SKV_TIMELINE
-  unsigned long long* timeline;  // [num_ctas][16] globaltimer samples (debug builds only)
-#endif
-};
-
-#ifdef SKV_TIMELINE
-__device__ __forceinline__ unsigned long long gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define SKV_TL(slot)                                                                              \
-  do {                                                                                            \
-    if (p.timeline != nullptr && (threadIdx.x == 0) && (slot) < 16) p.timeline[blockIdx.x * 16 + (slot)] = gtimer(); \
-  } while (0)
-#define SKV_TLP(slot)                                                                             \
-  do {                                                                                            \
-    if (p.timeline != nullptr && lane == 0 && (slot) < 16) p.timeline[blockIdx.x * 16 + (slot)] = gtimer(); \
-  } while (0)
-#else
-#define SKV_TL(slot) do { } while (0)
-#define SKV_TLP(slot) do { } while (0)
-#endif
-
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return h2_bits(h);
 }
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
 
 // ---- plan: the byte-balanced partition, built once per decode step --------------------
 __global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int32_t* counts, int C, int* plan_base,
-                                                         int fixed) {
+                                                         int model) {
   __shared__ long long cumw[kMaxSeqs + 1];
   __shared__ int nruns_of[kMaxCtas + 1];
   const int tid = threadIdx.x, NT = blockDim.x;
   const int B = g.num_seqs, Hkv = g.num_kv_heads, D = g.head_dim, nseg = B * Hkv;
   PlanView pv = plan_view(plan_base, C, nseg);
-  for (int b = tid; b < B; b += NT) cumw[b + 1] = seg_layout(counts + b * kNumBuckets, D, fixed).bytes;
+  for (int b = tid; b < B; b += NT) cumw[b + 1] = seg_layout(counts + b * kNumBuckets, D, model).bytes;
   for (int s = tid; s < nseg; s += NT) {
     pv.seg_begin[s] = 0x7fffffff;
     pv.seg_count[s] = 0;
@@ -130,14 +87,14 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int3
         if (cumw[mid] * Hkv <= y) lo = mid; else hi = mid;
       }
       b = lo;
-      const SegLayout sl = seg_layout(counts + b * kNumBuckets, D, fixed);
+      const SegLayout sl = seg_layout(counts + b * kNumBuckets, D, model);
       const long long seq_first = cumw[b] * Hkv;
       const int h = (int)((y - seq_first) / sl.bytes);
       const long long seg_off = seq_first + (long long)h * sl.bytes;
       const long long seg_end = seg_off + sl.bytes;
       const long long y_next = seg_end < y_end ? seg_end : y_end;
       int ka[kNumBuckets], kb[kNumBuckets];
-      if (seg_tiles_in_range(sl, D, y - seg_off, y_next - seg_off, ka, kb, fixed) > 0) {
+      if (seg_tiles_in_range(sl, D, y - seg_off, y_next - seg_off, ka, kb, model) > 0) {
         if (out != nullptr) {
           RunDesc r;
           r.seq = b;
@@ -172,7 +129,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(StoreGeom g, const int3
     pv.header[0] = acc;
     pv.header[1] = C;
     pv.header[2] = nseg;
-    pv.header[3] = 0;
+    pv.header[3] = plan_tile_keys(model);
   }
   __syncthreads();
   for (int c = tid; c <= C; c += NT) pv.cta_begin[c] = nruns_of[c];
@@ -356,23 +313,6 @@ __device__ __forceinline__ void process_block(const uint8_t* sb, int nkeys, int 
   }
 }
 
-// Bounded mbarrier wait that also gives up as soon as another thread of the CTA has given up.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                              int32_t* err) {
-  // Polls the phase with a short sleep in between: a warp suspended inside mbarrier.try_wait resumed
-  // noticeably later after the phase completed (4 % of the kernel's time on the mixed workload), and
-  // the sleep keeps a waiting warp out of the issue slots.  2^24 polls of at least 50 ns bound the wait
-  // to about a second.
-  for (uint32_t i = 0; i < (1u << 24); ++i) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
-    __nanosleep(50);
-  }
-  *abort_flag = 1;
-  atomicExch(err, 1);
-  return false;
-}
-
 // The query rows of a run: fp16 copy (plus a residual row in the precise mode) and radix-128 int8
 // limbs with their row sums.  One warp per call, heads [gq0, gq1) (at most 8); every head's elements are
 // fetched before any is processed, so the call costs one round trip to memory, not one per head.
@@ -454,7 +394,6 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
   const StoreGeom& g = p.g;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.group, Hkv = g.num_kv_heads;
-  SKV_TL(0);
 
   uint8_t* stages = smem;                                                          // [STAGES][STAGE_BYTES]
   Slot* qslots = reinterpret_cast<Slot*>(smem + STAGES * STAGE_BYTES);             // [kQBufs]
@@ -484,7 +423,6 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
 
   const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
   const int run_begin = pv.cta_begin[blockIdx.x], run_end = pv.cta_begin[blockIdx.x + 1];
-  SKV_TL(1);
 
   if (warp == NCONS) {
     // ================================ producer warp ================================
@@ -506,8 +444,8 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
           // the CTA's very first block is short (one tile per consumer warp), so that it arrives early
           step = (first_block && kbt[ci] > NCONS) ? NCONS : kbt[ci];
           first_block = false;
-          if (!wait_or_abort(&empty[stg], epar, abort_flag, p.err)) return false;
-          if (lane == 0 && p.debug_mode < 2) {
+          if (!wait_or_abort(&empty[stg], epar, abort_flag, p.err, p.wait_polls)) return false;
+          if (lane == 0) {
             const int ntl = (d.kb[ci] - ct0) < step ? (d.kb[ci] - ct0) : step;
             const int key0 = ct0 * 16;
             const int nkeys = (d.cnt[ci] - key0) < ntl * 16 ? (d.cnt[ci] - key0) : ntl * 16;
@@ -520,8 +458,6 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
             bulk_g2s_hint(sb, arena + g.k_off[ci] + row * pd, kbytes, &full[stg], stream_policy);
             bulk_g2s_hint(sb + kbkeys * pd, arena + g.v_off[ci] + row * pd, kbytes, &full[stg], stream_policy);
             bulk_g2s_hint(sb + 2 * kbkeys * pd, arena + g.sc_off[ci] + row * 8, sbytes, &full[stg], stream_policy);
-          } else if (lane == 0) {
-            mbar_arrive(&full[stg]);
           }
           if (++stg == STAGES) {
             stg = 0;
@@ -535,7 +471,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     // rows the consumer warps prepare themselves, one head each, while the first copies are in
     // flight), the query rows.
     auto publish_query = [&](int r, const RunDesc& d) -> bool {
-      if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err)) return false;
+      if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err, p.wait_polls)) return false;
       Slot& slot = qslots[qi];
       if (lane == 0) slot.desc = d;
       if (r != run_begin) {
@@ -549,7 +485,20 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       }
       return true;
     };
-    RunDesc d = pv.first[blockIdx.x];  // meaningful when the CTA has a run
+    // a plan cut in 128-key tiles (built for the tensor-memory kernel) is read in 16-key tiles here
+    const int tile_mul = pv.header[3] == 128 ? 8 : 1;
+    auto in_16_key_tiles = [&](RunDesc x) {
+      if (tile_mul != 1) {
+#pragma unroll
+        for (int i = 0; i < kNumBuckets; ++i) {
+          const int nt = (x.cnt[i] + 15) >> 4;
+          x.ka[i] = x.ka[i] * tile_mul < nt ? x.ka[i] * tile_mul : nt;
+          x.kb[i] = x.kb[i] * tile_mul < nt ? x.kb[i] * tile_mul : nt;
+        }
+      }
+      return x;
+    };
+    RunDesc d = in_16_key_tiles(pv.first[blockIdx.x]);  // meaningful when the CTA has a run
     bool ok = run_begin < run_end;
     for (int r = run_begin; ok && r < run_end; ++r) {
       int ci = 0, ct0 = -1;
@@ -557,17 +506,14 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       // the NEXT run is published, so that no consumer ever waits for query rows at a run boundary
       ok = issue_blocks(d, ci, ct0, STAGES);
       if (r == run_begin) {
-        SKV_TLP(10);
         ok = ok && publish_query(r, d);
-        SKV_TLP(11);
       }
       RunDesc dn = d;
       if (ok && r + 1 < run_end) {
-        dn = pv.runs[r + 1];
+        dn = in_16_key_tiles(pv.runs[r + 1]);
         ok = publish_query(r + 1, dn);
       }
       ok = ok && issue_blocks(d, ci, ct0, 1 << 30);
-      SKV_TLP(12 + (r - run_begin));
       d = dn;
     }
     return;
@@ -579,8 +525,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
   bool aborted = false;
   bool first_block = true;  // the CTA's first block holds one tile per consumer warp
   for (int r = run_begin; r < run_end; ++r) {
-    if (!aborted && !wait_or_abort(&qfull[qi], qfpar, abort_flag, p.err)) aborted = true;
-    SKV_TL(2 + 4 * (r - run_begin));
+    if (!aborted && !wait_or_abort(&qfull[qi], qfpar, abort_flag, p.err, p.wait_polls)) aborted = true;
     const Slot& slot = qslots[qi];  // stays valid until this warp arrives on qempty below
     const RunDesc& d = slot.desc;
     if (r == run_begin) {
@@ -613,10 +558,10 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
         const int ntl = (d.kb[bucket] - t0) < step ? (d.kb[bucket] - t0) : step;
         const int key0 = t0 * 16;
         const int nkeys = (d.cnt[bucket] - key0) < ntl * 16 ? (d.cnt[bucket] - key0) : ntl * 16;
-        if (!aborted && !wait_or_abort(&full[stg], fpar, abort_flag, p.err)) aborted = true;
+        if (!aborted && !wait_or_abort(&full[stg], fpar, abort_flag, p.err, p.wait_polls)) aborted = true;
         int first = warp - tile_base;
         if (first < 0) first += NCONS;
-        if (!aborted && first < ntl && p.debug_mode != 1 && p.debug_mode != 3) {
+        if (!aborted && first < ntl) {
           float* lrow = lbase != nullptr ? lbase + g.bucket_base[bucket] + key0 : nullptr;
           process_block<D, BITS, PRECISE, KBT * 16, NCONS>(stages + (long long)stg * STAGE_BYTES, nkeys, first, lane,
                                                            qf, st, o, p.scale_log2, write_logits, lrow);
@@ -637,7 +582,6 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
 
     // ---- every consumer warp writes its own partial (max, sum, out) of this run -------------------
     // (no cross-warp merge: skv_lse_combine folds the NCONS partials of a run like any others)
-    SKV_TL(3 + 4 * (r - run_begin));
     __syncwarp();
     if (lane == 0) mbar_arrive(&qempty[qi]);  // query rows and descriptor are no longer needed
     {
@@ -660,7 +604,6 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
         }
       }
     }
-    SKV_TL(4 + 4 * (r - run_begin));
     if (++qi == kQBufs) {
       qi = 0;
       qfpar ^= 1u;
@@ -686,6 +629,27 @@ static size_t attn_smem_bytes() {
          (2 * CFG::STAGES + 2 * kQBufs) * sizeof(uint64_t) + 64;
 }
 
+// ---- which kernel serves a launch -----------------------------------------------------------------
+// 0 = automatic (tensor-memory kernel where it applies: head_dim 128, fp16 queries), 1 = always the
+// mma.sync fragment kernel, 2 = tensor-memory kernel wherever it applies (same as 0 today).
+static std::atomic<int> g_attn_path{0};
+
+extern "C" int skv_set_attention_path(int path) {
+  if (path < 0 || path > 2) return SKV_ERR_INVALID;
+  g_attn_path.store(path);
+  return SKV_OK;
+}
+extern "C" int skv_get_attention_path(void) { return g_attn_path.load(); }
+
+static bool use_tc_path(const SkvStoreDesc* desc, int query_dtype) {
+  return g_attn_path.load() != 1 && desc->head_dim == 128 && query_dtype == SKV_DTYPE_F16;
+}
+// The plan is shared by every launch of a step; its tile size follows the kernel that head_dim selects
+// for fp16 queries (the fragment kernel reads either tile size).
+static int plan_model_for(const SkvStoreDesc* desc) {
+  return (g_attn_path.load() != 1 && desc->head_dim == 128) ? kPlanModelTc : kPlanModelFrag;
+}
+
 extern "C" int skv_attn_num_ctas(int device) {
   int sms = 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return SKV_ERR_CUDA;
@@ -701,6 +665,7 @@ extern "C" int64_t skv_attn_partials_bytes(const SkvStoreDesc* desc, int num_q_h
 
 extern "C" int skv_attn_partials_per_run(const SkvStoreDesc* desc, int query_dtype) {
   if (!desc) return SKV_ERR_INVALID;
+  if (use_tc_path(desc, query_dtype)) return attn_tc_partials_per_run();
   int n = query_dtype == SKV_DTYPE_F16 ? AttnCfgFast::NCONS : AttnCfgPrecise::NCONS;
   return n;
 }
@@ -716,7 +681,7 @@ extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, in
   if (num_ctas <= 0 || num_ctas > kMaxCtas || desc->num_seqs > kMaxSeqs) return SKV_ERR_UNSUPPORTED;
   if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
   attn_plan_kernel<<<1, 1024, 0, as_stream(stream)>>>(make_geom(*desc), counts, num_ctas, static_cast<int*>(plan),
-                                                      kTileFixedCost);
+                                                      plan_model_for(desc));
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 
@@ -744,9 +709,18 @@ static int launch_attn(AttnParams& p, cudaStream_t st) {
   return SKV_OK;
 }
 
-extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
-                                    const void* query, int query_dtype, int num_q_heads, void* partials,
-                                    int num_ctas, float* logits, int32_t* err_flag, void* stream) {
+// Limit of every bounded device-side wait, in polls of about 50 ns (default 2^24, about a second).
+static std::atomic<unsigned> g_wait_polls{1u << 24};
+extern "C" int skv_set_wait_limit(unsigned polls) {
+  if (polls == 0) return SKV_ERR_INVALID;
+  g_wait_polls.store(polls);
+  return SKV_OK;
+}
+
+extern "C" int skv_decode_attention_masked(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
+                                           const void* query, int query_dtype, int num_q_heads, void* partials,
+                                           int num_ctas, float* logits, const float* mask, int64_t mask_stride,
+                                           const int32_t* slot_token, int32_t* err_flag, void* stream) {
   if (!desc || !store || !plan || !query || !partials || !err_flag) return SKV_ERR_INVALID;
   if (layer < 0 || layer >= desc->num_layers || num_ctas <= 0 || num_ctas > kMaxCtas) return SKV_ERR_INVALID;
   if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
@@ -755,6 +729,7 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
   const int group = num_q_heads / desc->num_kv_heads;
   if (group < 1 || group > 8) return SKV_ERR_UNSUPPORTED;
   if (query_dtype != SKV_DTYPE_F32 && query_dtype != SKV_DTYPE_F16) return SKV_ERR_INVALID;
+  if (mask != nullptr && (slot_token == nullptr || mask_stride <= 0)) return SKV_ERR_INVALID;
   AttnParams p;
   p.g = make_geom(*desc);
   p.store = static_cast<const uint8_t*>(store);
@@ -767,44 +742,26 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
   p.partials = static_cast<float*>(partials);
   p.num_ctas = num_ctas;
   p.logits = logits;
+  p.mask = mask;
+  p.slot_token = slot_token;
+  p.mask_stride = mask_stride;
   p.err = err_flag;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)desc->head_dim));
-  // timing probe, off unless SKV_ATTN_DEBUG is set: 1 = stream only (no arithmetic), 2 = arithmetic only
-  // (no copies), 3 = neither; results are meaningless in these modes
-  static const int debug_mode = getenv("SKV_ATTN_DEBUG") ? atoi(getenv("SKV_ATTN_DEBUG")) : 0;
-  p.debug_mode = debug_mode;
-#ifdef SKV_TIMELINE
-  {
-    static unsigned long long* tl = nullptr;
-    static unsigned long long host_tl[kMaxCtas * 16];
-    if (tl == nullptr) {
-      cudaMalloc(&tl, sizeof(host_tl));
-      cudaMemset(tl, 0, sizeof(host_tl));
-    }
-    p.timeline = tl;
-    if (getenv("SKV_ATTN_TL_DUMP") && layer == 1) {  // dump what the previous launch recorded
-      cudaDeviceSynchronize();
-      cudaMemcpy(host_tl, tl, sizeof(host_tl), cudaMemcpyDeviceToHost);
-      unsigned long long t0 = ~0ull;
-      for (int c = 0; c < num_ctas; ++c) if (host_tl[c * 16] && host_tl[c * 16] < t0) t0 = host_tl[c * 16];
-      for (int c = 0; c < num_ctas; c += 13) {
-        fprintf(stderr, "cta %3d:", c);
-        for (int k = 0; k < 14; ++k) fprintf(stderr, " %6lld", host_tl[c * 16 + k] ? (long long)(host_tl[c * 16 + k] - t0) : -1LL);
-        fprintf(stderr, "\n");
-      }
-      unsigned long long tmax = 0;
-      for (int i = 0; i < num_ctas * 16; ++i) if (host_tl[i] > tmax) tmax = host_tl[i];
-      fprintf(stderr, "span %lld ns\n", (long long)(tmax - t0));
-      cudaMemset(tl, 0, sizeof(host_tl));
-    }
-  }
-#endif
+  p.wait_polls = g_wait_polls.load();
+  if (use_tc_path(desc, query_dtype)) return launch_attn_tc(p, *desc, as_stream(stream));
   const bool precise = !p.q_is_half;
   if (desc->head_dim == 128)
     return precise ? launch_attn<128, true, AttnCfgPrecise>(p, as_stream(stream))
                    : launch_attn<128, false, AttnCfgFast>(p, as_stream(stream));
   return precise ? launch_attn<64, true, AttnCfgPrecise>(p, as_stream(stream))
                  : launch_attn<64, false, AttnCfgFast>(p, as_stream(stream));
+}
+
+extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
+                                    const void* query, int query_dtype, int num_q_heads, void* partials,
+                                    int num_ctas, float* logits, int32_t* err_flag, void* stream) {
+  return skv_decode_attention_masked(desc, store, layer, plan, query, query_dtype, num_q_heads, partials, num_ctas,
+                                     logits, nullptr, 0, nullptr, err_flag, stream);
 }
 
 extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
