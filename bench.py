@@ -154,6 +154,8 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    from smartkv_b200 import _lib as skv_lib
+    skv_lib.lib().skv_set_attention_path(1 if args.attn_kernel == "fragment" else 0)
     cfg = dict(CFG)
     if args.layers:
         cfg["num_layers"] = args.layers      # profiler captures only: fewer layers = less device memory
@@ -579,6 +581,8 @@ def main():
     ap.add_argument("--budget", type=float, default=0.0, help="other memory budget than the contract's 0.35")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the layer count (profiler captures of a small case only; not a bench line)")
+    ap.add_argument("--attn-kernel", default="auto", choices=["auto", "fragment"],
+                    help="auto: tensor-memory (tcgen05) kernel where it applies; fragment: the mma.sync kernel everywhere")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

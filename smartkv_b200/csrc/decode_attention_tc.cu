@@ -7,10 +7,10 @@
 //                       K is the int8 code matrix, K-major, 128-byte rows in the 128-byte swizzle.  Rows of
 //                       the 8-bit bucket are exactly that, so a tiled TMA load (cp.async.bulk.tensor, 3-D map
 //                       over the arena, SWIZZLE_128B, no multicast) lands them ready for the MMA and no CUDA core
-//                       ever touches an 8-bit code.  2/3/4-bit rows arrive packed (1-D bulk copies) and one
-//                       warpgroup spreads their fields to bytes (offset-binary, unsigned operand) into the
-//                       same tile.  The query rows are two radix-128 int8 limbs per head (columns h and
-//                       GP + h), stored once per run in the element order each width's unpacker produces.
+//                       ever touches an 8-bit code.  2/3/4-bit rows arrive packed (1-D bulk copies) and a
+//                       warpgroup spreads their fields to bytes into the same tile.  The query rows are two
+//                       radix-128 int8 limbs per head, stored once per run in the element order each width's
+//                       unpacker produces.
 //   softmax           one thread per key: tcgen05.ld of its row of S, scale by the key's K scale, block
 //                       maximum per head (redux.sync + one exchange through shared memory), probabilities
 //                       relative to the block maximum times the key's V scale (relative to the block's largest)
@@ -20,12 +20,16 @@
 //                       block's scale into fp32 registers (the rescale of an online softmax happens there, never in
 //                       tensor memory).
 //
-// Persistent CTAs (one per SM) walk the runs of the step's plan (attn_sched.cuh, 128-key tiles): a producer
-// warp streams blocks into a ring of shared-memory slots; two warpgroups take the blocks alternately,
-// each software-pipelined over its own blocks (unpack + score MMA of block j+1, softmax + PV MMA of block j,
-// epilogue of block j-1), so the MMA latencies hide behind the other phases.  Every wait is bounded (attn_params.cuh).
-// At the end of a run each warpgroup writes one partial (max, sum, out[128]) per query head; the combine step
-// (post_attention.cuh) folds the partials of a segment.
+// Persistent CTAs (one per SM) walk the runs of the step's plan (attn_sched.cuh, 128-key tiles).  Warp roles:
+//   producer      streams blocks into a ring of shared-memory slots (and asks L2 for the blocks after them),
+//                 prepares the query limbs of the next run
+//   score issuer  one thread issues the K.Q MMAs as tiles become ready
+//   PV issuer     one thread issues the V.P MMAs as probabilities become ready; its commit frees the slot
+//   warpgroups    take the blocks round-robin; each unpacks its narrow blocks, turns scores into probabilities
+//                 and drains the P.V accumulators, software-pipelined over its own blocks
+// so a single thread's MMA issue time and every MMA latency stay off the warpgroups' critical path.  All
+// hand-offs are mbarriers; every wait is bounded (attn_params.cuh).  At the end of a run each warpgroup writes
+// one partial (max, sum, out[128]) per query head; the combine step (post_attention.cuh) folds a segment's partials.
 //
 // Replaces smartkv/csrc/quantized_attention.cu:460-828 (per-bucket kernel, one CTA per head) and the host LSE
 // combine in smartkv/kernels/__init__.py:350-371; numerics follow the CPU streaming path
@@ -43,47 +47,62 @@ namespace skv {
 constexpr int kTcKeys = 128;                         // keys per block
 constexpr int kTcTile = 16384;                       // one int8 tile: 128 rows x 128 B
 constexpr int kTcSlotBytes = 2 * kTcTile + 1024;     // K tile | V tile | 128 x (K scale, V scale)
-constexpr int kTcWgs = 2;                            // warpgroups that consume blocks
 constexpr int kTcQBufs = 2;                          // query ring (runs in flight)
-constexpr int kTcThreads = (kTcWgs * 4 + 1) * 32;    // + the producer warp
-constexpr int kTcQTile = 16 * 128;                   // 16 limb rows x 128 B, swizzled like a K tile
+constexpr int kTcPartialsPerRun = 4;                 // partial slots per run (one per warpgroup; unused ones are marked empty)
+constexpr int kTcPrefetch = 6;                       // blocks the producer asks L2 for ahead of its copies
 // Fixed-point unit of P: the largest probability-times-V-scale of a block maps to 2^24 - 256, so that no
 // rounding in the chain can reach 2^24 (whose three low bytes would read as zero).
 constexpr float kTcPOne = 16776960.f;
 
+#ifdef SKV_PROBES
+// timing probes of an instrumented build (never compiled into the product library)
+constexpr int kTlCtas = 8, kTlBlocks = 40, kTlWgs = 4;
+__device__ long long g_tc_timeline[kTlCtas][kTlWgs][kTlBlocks][16];
+#define TCP(blk, i)                                                                                          \
+  do {                                                                                                       \
+    if (wt == 0 && (blk).jj < kTlBlocks && blockIdx.x % 18 == 0 && blockIdx.x / 18 < kTlCtas)                \
+      g_tc_timeline[blockIdx.x / 18][wg][(blk).jj][i] = clock64();                                          \
+  } while (0)
+#else
+#define TCP(blk, i) do { } while (0)
+#endif
+
 template <int GP>
 struct TcCfg {
+  static constexpr int WGS = GP <= 4 ? 4 : 3;              // warpgroups that consume blocks
   static constexpr int NS = GP <= 4 ? 6 : 5;               // ring slots
   static constexpr int PN = GP <= 4 ? 16 : 32;             // bytes of one P row = N of the PV MMA (3 limbs x GP, padded)
-  static constexpr int PBYTES = kTcKeys * PN;              // one P buffer
+  static constexpr int PBYTES = kTcKeys * PN;              // the P buffer of a warpgroup
   static constexpr int SCOLS = 16;                         // N of the score MMA (2 limbs x GP, padded)
-  static constexpr int WG_COLS = 2 * SCOLS + 2 * PN;       // tensor-memory columns of one warpgroup (double buffered)
-  static constexpr int TMEM_COLS = GP <= 4 ? 128 : 256;    // power of two >= kTcWgs * WG_COLS
-  static_assert(kTcWgs * WG_COLS <= TMEM_COLS, "tensor memory budget");
+  static constexpr int WG_COLS = 2 * SCOLS + PN;           // tensor-memory columns of one warpgroup: S twice, O once
+  static constexpr int TMEM_COLS = 256;                    // power of two >= WGS * WG_COLS
+  static constexpr int QROWS = GP <= 4 ? 8 : 16;           // limb rows of one element order: GP high limbs, GP low limbs
+  static constexpr int QSTRIDE = QROWS * 128;              // bytes between two element orders
+  static constexpr int QBUF = 4 * QSTRIDE + (16 - QROWS) * 128;  // the MMA reads 16 rows whatever QROWS is
+  static constexpr int THREADS = (WGS * 4 + 3) * 32;       // + producer, score issuer, PV issuer
+  static_assert(WGS * WG_COLS <= TMEM_COLS, "tensor memory budget");
 };
 
 struct TcQMeta {
   float qs[8];   // limb step of head g times 1/sqrt(d) * log2(e)
   int sumA[8];   // 128 * sum(limb 0) + sum(limb 1): what the offset of unsigned codes adds per unit of offset
-  RunDesc desc;
 };
 
 template <int GP>
 struct TcMeta {
-  uint64_t full[8], empty[8];
+  uint64_t full[8], uready[8], empty[8];
   uint64_t qfull[kTcQBufs], qempty[kTcQBufs];
-  uint64_t sbar[kTcWgs][2], obar[kTcWgs][2];
-  uint64_t drain[kTcWgs];
+  uint64_t sbar[4][2], sdone[4][2], pready[4], obar[4];
+  uint64_t drain[2];
   uint32_t tmem_base;
   int abort_flag;
-  uint32_t red[kTcWgs][4][12];          // per warp: GP block maxima (order keys) + the largest V scale
-  uint32_t wsum[kTcWgs][2][4][8];       // per warp: sum of the fixed-point P of every head (unsigned-code blocks)
+  alignas(16) uint32_t red[4][4][12];  // per warpgroup and warp: GP block maxima (order keys) + the largest V scale
   TcQMeta q[kTcQBufs];
 };
 
 template <int GP>
 constexpr size_t tc_smem_bytes() {
-  return (size_t)TcCfg<GP>::NS * kTcSlotBytes + (size_t)kTcQBufs * 4 * kTcQTile + (size_t)kTcWgs * 2 * TcCfg<GP>::PBYTES +
+  return (size_t)TcCfg<GP>::NS * kTcSlotBytes + (size_t)kTcQBufs * TcCfg<GP>::QBUF + (size_t)TcCfg<GP>::WGS * TcCfg<GP>::PBYTES +
          sizeof(TcMeta<GP>) + 1024;  // + slack to align the base to 1024 B
 }
 
@@ -92,13 +111,13 @@ constexpr size_t tc_smem_bytes() {
 // whatever the cheapest field extraction of that width yields.  The query limbs are stored in the same order
 // (a dot product does not care) and the output rows are put back in order once per run.
 __host__ __device__ constexpr int tc_perm(int bucket, int i) {
-  return bucket == 0   ? (i & ~15) + ((i >> 2) & 3) + 4 * (i & 3)    // 2-bit: word s, shift j, byte b -> 16s + j + 4b
+  return bucket == 0   ? (i & ~15) + 8 * ((i >> 3) & 1) + 2 * (i & 3) + ((i >> 2) & 1)  // 2-bit: word k of 4, byte b -> 8(k/2) + 2b + k%2
          : bucket == 1 ? (i & ~31) + 8 * (i & 3) + ((i >> 2) & 7)    // 3-bit: field class f, group g -> 8g + f
          : bucket == 2 ? (i & ~7) + 2 * (i & 3) + ((i >> 2) & 1)     // 4-bit: word s, low/high nibble e, byte j -> 8s + 2j + e
                        : i;                                          // 8-bit: as stored
 }
 __host__ __device__ constexpr int tc_perm_inv(int bucket, int d) {
-  return bucket == 0   ? (d & ~15) + 4 * (d & 3) + ((d >> 2) & 3)
+  return bucket == 0   ? (d & ~15) + 8 * ((d >> 3) & 1) + 4 * (d & 1) + ((d >> 1) & 3)
          : bucket == 1 ? (d & ~31) + 4 * (d & 7) + ((d >> 3) & 3)
          : bucket == 2 ? (d & ~7) + 4 * (d & 1) + ((d >> 1) & 3)
                        : d;
@@ -106,14 +125,23 @@ __host__ __device__ constexpr int tc_perm_inv(int bucket, int d) {
 // byte offset of (row, byte position) inside a 128-byte-swizzled tile whose base is 1024-byte aligned
 __host__ __device__ constexpr int tc_swz(int row, int pos) { return row * 128 + ((((pos >> 4) ^ (row & 7))) << 4) + (pos & 15); }
 
-// ---- unpack: packed rows of a narrow bucket -> int8 tile (unsigned codes) -------------------------------
+// Which operands are signed bytes after the unpack.  V tiles always are (so that P.V needs no offset term);
+// K tiles of the 3- and 4-bit buckets keep the stored offset-binary code, whose share of the score,
+// offset * sum(query limbs), is a per-head constant.
+__host__ __device__ constexpr int tc_k_signed(int bucket) { return bucket == 0 || bucket == 3; }
+__host__ __device__ constexpr int tc_k_offset(int bucket) { return bucket == 1 ? 4 : bucket == 2 ? 8 : 0; }
+
+// ---- unpack: packed rows of a narrow bucket -> int8 tile -------------------------------------------
 // All loads of the warpgroup complete before the first store (the tiles overlay the packed bytes).
 // `wt` = thread index inside the warpgroup, `bar` = the warpgroup's named barrier.
 __device__ __forceinline__ void tc_store_chunk(uint8_t* tile, int row, int oc, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   *reinterpret_cast<uint4*>(tile + row * 128 + ((oc ^ (row & 7)) << 4)) = make_uint4(a, b, c, d);
 }
+// bytes u (0 <= u < 128) -> signed bytes u - off, four at a time
+__device__ __forceinline__ uint32_t tc_sub4(uint32_t x_or_80, uint32_t off4) { return (x_or_80 - off4) ^ 0x80808080u; }
 
 // 2-bit: 128 rows x 32 B = 256 chunks of 16 B per tile; thread wt takes chunks wt and wt + 128 of K and of V.
+// Four crumbs at a time go through a byte permute used as a look-up table (0,1,2,3 -> -2,-1,0,1).
 __device__ __forceinline__ void tc_unpack2(uint8_t* slot, int wt, int bar) {
   uint4 kin[2], vin[2];
 #pragma unroll
@@ -122,6 +150,7 @@ __device__ __forceinline__ void tc_unpack2(uint8_t* slot, int wt, int bar) {
     vin[n] = *reinterpret_cast<const uint4*>(slot + kTcTile + (wt + 128 * n) * 16);
   }
   named_bar_sync(bar, 128);
+  constexpr uint32_t lut = 0x0100fffeu;
 #pragma unroll
   for (int which = 0; which < 2; ++which) {
 #pragma unroll
@@ -131,8 +160,8 @@ __device__ __forceinline__ void tc_unpack2(uint8_t* slot, int wt, int bar) {
       const uint32_t w[4] = {in.x, in.y, in.z, in.w};
 #pragma unroll
       for (int s = 0; s < 4; ++s)
-        tc_store_chunk(slot + which * kTcTile, row, 4 * hf + s, w[s] & 0x03030303u, (w[s] >> 2) & 0x03030303u,
-                       (w[s] >> 4) & 0x03030303u, (w[s] >> 6) & 0x03030303u);
+        tc_store_chunk(slot + which * kTcTile, row, 4 * hf + s, prmt(lut, 0u, w[s] & 0x3333u), prmt(lut, 0u, (w[s] >> 2) & 0x3333u),
+                       prmt(lut, 0u, (w[s] >> 16) & 0x3333u), prmt(lut, 0u, (w[s] >> 18) & 0x3333u));
     }
   }
 }
@@ -146,16 +175,22 @@ __device__ __forceinline__ void tc_unpack4(uint8_t* slot, int wt, int bar) {
     vin[n] = *reinterpret_cast<const uint4*>(slot + kTcTile + (wt + 128 * n) * 16);
   }
   named_bar_sync(bar, 128);
+  constexpr uint32_t m = 0x0f0f0f0fu, hi = 0x80808080u, off = 0x08080808u;
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
+  for (int n = 0; n < 4; ++n) {
+    const uint4 in = kin[n];
+    const int c = wt + 128 * n, row = c >> 2, q = c & 3;
+    tc_store_chunk(slot, row, 2 * q, in.x & m, (in.x >> 4) & m, in.y & m, (in.y >> 4) & m);
+    tc_store_chunk(slot, row, 2 * q + 1, in.z & m, (in.z >> 4) & m, in.w & m, (in.w >> 4) & m);
+  }
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const uint4 in = which ? vin[n] : kin[n];
-      const int c = wt + 128 * n, row = c >> 2, q = c & 3;
-      constexpr uint32_t m = 0x0f0f0f0fu;
-      tc_store_chunk(slot + which * kTcTile, row, 2 * q, in.x & m, (in.x >> 4) & m, in.y & m, (in.y >> 4) & m);
-      tc_store_chunk(slot + which * kTcTile, row, 2 * q + 1, in.z & m, (in.z >> 4) & m, in.w & m, (in.w >> 4) & m);
-    }
+  for (int n = 0; n < 4; ++n) {
+    const uint4 in = vin[n];
+    const int c = wt + 128 * n, row = c >> 2, q = c & 3;
+    tc_store_chunk(slot + kTcTile, row, 2 * q, tc_sub4(lop_and_or(in.x, m, hi), off), tc_sub4(lop_and_or(in.x >> 4, m, hi), off),
+                   tc_sub4(lop_and_or(in.y, m, hi), off), tc_sub4(lop_and_or(in.y >> 4, m, hi), off));
+    tc_store_chunk(slot + kTcTile, row, 2 * q + 1, tc_sub4(lop_and_or(in.z, m, hi), off), tc_sub4(lop_and_or(in.z >> 4, m, hi), off),
+                   tc_sub4(lop_and_or(in.w, m, hi), off), tc_sub4(lop_and_or(in.w >> 4, m, hi), off));
   }
 }
 
@@ -171,20 +206,27 @@ __device__ __forceinline__ void tc_unpack3(uint8_t* slot, int wt, int bar) {
   }
   named_bar_sync(bar, 128);
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
+  for (int a = 0; a < 4; ++a) {
+    const uint32_t w[3] = {kin[3 * a], kin[3 * a + 1], kin[3 * a + 2]};
+    uint32_t o[8];
+    unpack_kslice_i8<128, 3>(w, o);
+    tc_store_chunk(slot, wt, 2 * a, o[0], o[1], o[2], o[3]);
+    tc_store_chunk(slot, wt, 2 * a + 1, o[4], o[5], o[6], o[7]);
+  }
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const uint32_t* in = which ? vin : kin;
-      const uint32_t w[3] = {in[3 * a], in[3 * a + 1], in[3 * a + 2]};
-      uint32_t o[8];
-      unpack_kslice_i8<128, 3>(w, o);
-      tc_store_chunk(slot + which * kTcTile, wt, 2 * a, o[0], o[1], o[2], o[3]);
-      tc_store_chunk(slot + which * kTcTile, wt, 2 * a + 1, o[4], o[5], o[6], o[7]);
-    }
+  for (int a = 0; a < 4; ++a) {
+    const uint32_t w[3] = {vin[3 * a], vin[3 * a + 1], vin[3 * a + 2]};
+    uint32_t o[8];
+    unpack_kslice_i8<128, 3>(w, o);
+    constexpr uint32_t hi = 0x80808080u, off = 0x04040404u;
+#pragma unroll
+    for (int f = 0; f < 8; ++f) o[f] = tc_sub4(o[f] | hi, off);
+    tc_store_chunk(slot + kTcTile, wt, 2 * a, o[0], o[1], o[2], o[3]);
+    tc_store_chunk(slot + kTcTile, wt, 2 * a + 1, o[4], o[5], o[6], o[7]);
   }
 }
 
-// ---- block cursor: the blocks of a run in the order producer and consumers both follow ------------------
+// ---- block cursor: the blocks of a run in the order every role follows -------------------------------
 struct TcCursor {
   int ci, t;
 };
@@ -199,11 +241,16 @@ __device__ __forceinline__ TcCursor tc_cursor_begin(const RunDesc& d) {
   tc_cursor_skip(d, c);
   return c;
 }
+__device__ __forceinline__ void tc_cursor_next(const RunDesc& d, TcCursor& c) {
+  ++c.t;
+  tc_cursor_skip(d, c);
+}
 
 // ---- query limbs of a run, in the four element orders (one warp) ---------------------------------------------
 template <int GP>
-__device__ __forceinline__ void tc_prep_query(uint8_t* qtiles, TcQMeta& meta, const AttnParams& p, int seq, int head, int G,
+__device__ __forceinline__ void tc_prep_query(uint8_t* qbuf, TcQMeta& meta, const AttnParams& p, int seq, int head, int G,
                                               int lane) {
+  constexpr int QSTRIDE = TcCfg<GP>::QSTRIDE;
   const long long q_off = ((long long)seq * p.num_q_heads + (long long)head * G) * 128;
   float q[GP][4];
 #pragma unroll
@@ -234,8 +281,8 @@ __device__ __forceinline__ void tc_prep_query(uint8_t* qtiles, TcQMeta& meta, co
 #pragma unroll
       for (int c = 0; c < kNumBuckets; ++c) {
         const int pos = tc_perm_inv(c, d);
-        qtiles[c * kTcQTile + tc_swz(h, pos)] = (uint8_t)(int8_t)(int)hi;
-        qtiles[c * kTcQTile + tc_swz(GP + h, pos)] = (uint8_t)(int8_t)lo;
+        qbuf[c * QSTRIDE + tc_swz(h, pos)] = (uint8_t)(int8_t)(int)hi;
+        qbuf[c * QSTRIDE + tc_swz(GP + h, pos)] = (uint8_t)(int8_t)lo;
       }
     }
 #pragma unroll
@@ -251,41 +298,45 @@ __device__ __forceinline__ void tc_prep_query(uint8_t* qtiles, TcQMeta& meta, co
 }
 
 template <int GP>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     decode_attn_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   using Cfg = TcCfg<GP>;
-  constexpr int NS = Cfg::NS, PN = Cfg::PN;
+  constexpr int NS = Cfg::NS, PN = Cfg::PN, WGS = Cfg::WGS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* slots = smem;                                               // [NS][kTcSlotBytes]
-  uint8_t* qtiles = slots + (size_t)NS * kTcSlotBytes;                 // [kTcQBufs][4][kTcQTile]
-  uint8_t* pbufs = qtiles + (size_t)kTcQBufs * 4 * kTcQTile;           // [kTcWgs][2][PBYTES]
-  TcMeta<GP>& mt = *reinterpret_cast<TcMeta<GP>*>(pbufs + (size_t)kTcWgs * 2 * Cfg::PBYTES);
+  uint8_t* slots = smem;                                        // [NS][kTcSlotBytes]
+  uint8_t* qbufs = slots + (size_t)NS * kTcSlotBytes;           // [kTcQBufs][QBUF]
+  uint8_t* pbufs = qbufs + (size_t)kTcQBufs * Cfg::QBUF;        // [WGS][PBYTES]
+  TcMeta<GP>& mt = *reinterpret_cast<TcMeta<GP>*>(pbufs + (size_t)WGS * Cfg::PBYTES);
   const StoreGeom& g = p.g;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.group, Hkv = g.num_kv_heads;
   volatile int* abort_flag = &mt.abort_flag;
 
   {  // limb rows of heads that do not exist stay zero
-    uint32_t* z = reinterpret_cast<uint32_t*>(qtiles);
-    for (int i = tid; i < kTcQBufs * 4 * kTcQTile / 4; i += kTcThreads) z[i] = 0u;
+    uint32_t* z = reinterpret_cast<uint32_t*>(qbufs);
+    for (int i = tid; i < kTcQBufs * Cfg::QBUF / 4; i += Cfg::THREADS) z[i] = 0u;
   }
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&mt.full[s], 1);
+      mbar_init(&mt.uready[s], 128);
       mbar_init(&mt.empty[s], 1);
     }
     for (int s = 0; s < kTcQBufs; ++s) {
       mbar_init(&mt.qfull[s], 1);
-      mbar_init(&mt.qempty[s], kTcWgs);
+      mbar_init(&mt.qempty[s], WGS);
     }
-    for (int w = 0; w < kTcWgs; ++w) {
+    for (int w = 0; w < WGS; ++w) {
       mbar_init(&mt.sbar[w][0], 1);
       mbar_init(&mt.sbar[w][1], 1);
-      mbar_init(&mt.obar[w][0], 1);
-      mbar_init(&mt.obar[w][1], 1);
-      mbar_init(&mt.drain[w], 1);
+      mbar_init(&mt.sdone[w][0], 128);
+      mbar_init(&mt.sdone[w][1], 128);
+      mbar_init(&mt.pready[w], 128);
+      mbar_init(&mt.obar[w], 1);
     }
+    mbar_init(&mt.drain[0], 1);
+    mbar_init(&mt.drain[1], 1);
     mt.abort_flag = 0;
     for (int q = 0; q < kTcQBufs; ++q)
       for (int h = 0; h < 8; ++h) {
@@ -305,17 +356,45 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   const int run_begin = pv.cta_begin[blockIdx.x], run_end = pv.cta_begin[blockIdx.x + 1];
   const unsigned polls = p.wait_polls;
 
-  if (warp == kTcWgs * 4) {
+  if (warp == WGS * 4) {
     // ================================ producer warp ================================
     int gi = 0, qi = 0;
     uint32_t qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
     bool ok = run_begin < run_end;
     const uint64_t stream_policy = l2_evict_first_policy();  // the cache is read once per step
+    // L2 prefetch stream: runs kTcPrefetch blocks ahead of the copies, across run boundaries
+    int pf_run = run_begin, pf_count = 0;
+    RunDesc pf_d = pv.first[blockIdx.x];
+    TcCursor pf_c = ok ? tc_cursor_begin(pf_d) : TcCursor{kNumBuckets, 0};
+    auto prefetch_to = [&](int upto) {
+      while (pf_count < upto) {
+        if (pf_c.ci >= kNumBuckets) {
+          if (pf_run + 1 >= run_end) return;
+          ++pf_run;
+          pf_d = pv.runs[pf_run];
+          pf_c = tc_cursor_begin(pf_d);
+          continue;
+        }
+        if (lane == 0) {
+          const int ci = pf_c.ci, key0 = pf_c.t * kTcKeys;
+          const int nkeys = (pf_d.cnt[ci] - key0) < kTcKeys ? (pf_d.cnt[ci] - key0) : kTcKeys;
+          const int n16 = (nkeys + 15) & ~15, pd = g.row_bytes[ci];
+          const uint8_t* arena = arena_ptr(g, p.store, p.layer, pf_d.seq);
+          const long long row = (long long)pf_d.head * g.cap[ci] + key0;
+          bulk_prefetch_l2(arena + g.k_off[ci] + row * pd, (uint32_t)(n16 * pd));
+          bulk_prefetch_l2(arena + g.v_off[ci] + row * pd, (uint32_t)(n16 * pd));
+          bulk_prefetch_l2(arena + g.sc_off[ci] + row * 8, (uint32_t)(n16 * 8));
+        }
+        ++pf_count;
+        tc_cursor_next(pf_d, pf_c);
+      }
+    };
     // issues up to `limit` further blocks of run d, resuming at cursor c
     auto issue_blocks = [&](const RunDesc& d, TcCursor& c, int limit) -> bool {
       const uint8_t* arena = arena_ptr(g, p.store, p.layer, d.seq);
       while (c.ci < kNumBuckets) {
         if (limit-- <= 0) return true;
+        prefetch_to(gi + 1 + kTcPrefetch);
         const int slot = gi % NS;
         if (!wait_or_abort(&mt.empty[slot], ((gi / NS) & 1) ^ 1u, abort_flag, p.err, polls)) return false;
         if (lane == 0) {
@@ -340,15 +419,13 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           bulk_g2s_hint(sb + 2 * kTcTile, arena + g.sc_off[ci] + row * 8, sbytes, &mt.full[slot], stream_policy);
         }
         ++gi;
-        ++c.t;
-        tc_cursor_skip(d, c);
+        tc_cursor_next(d, c);
       }
       return true;
     };
     auto publish_query = [&](const RunDesc& d) -> bool {
       if (!wait_or_abort(&mt.qempty[qi], qepar, abort_flag, p.err, polls)) return false;
-      if (lane == 0) mt.q[qi].desc = d;
-      tc_prep_query<GP>(qtiles + (size_t)qi * 4 * kTcQTile, mt.q[qi], p, d.seq, d.head, G, lane);
+      tc_prep_query<GP>(qbufs + (size_t)qi * Cfg::QBUF, mt.q[qi], p, d.seq, d.head, G, lane);
       fence_proxy_async();  // the MMA reads the limb rows through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(&mt.qfull[qi]);
@@ -362,7 +439,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     for (int r = run_begin; ok && r < run_end; ++r) {
       TcCursor c = tc_cursor_begin(d);
       // the first blocks of a run go out first; while they are in flight the query of the NEXT run is
-      // published, so that no consumer waits for query rows at a run boundary
+      // published, so that nobody waits for query rows at a run boundary
       ok = issue_blocks(d, c, NS);
       if (r == run_begin) ok = ok && publish_query(d);
       RunDesc dn = d;
@@ -373,26 +450,91 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       ok = ok && issue_blocks(d, c, 1 << 30);
       d = dn;
     }
+  } else if (warp == WGS * 4 + 1) {
+    // ================================ score issuer ================================
+    // K.Q of block i as soon as its tile is ready and the S buffer it writes has been read
+    if (lane == 0) {
+      int i = 0, qi = 0;
+      uint32_t qfpar = 0, umask = 0;
+      bool ok = true;
+      for (int r = run_begin; ok && r < run_end; ++r) {
+        const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
+        ok = wait_or_abort(&mt.qfull[qi], qfpar, abort_flag, p.err, polls);
+        const uint32_t qa0 = smem_u32(qbufs + (size_t)qi * Cfg::QBUF);
+        for (TcCursor c = tc_cursor_begin(d); ok && c.ci < kNumBuckets; tc_cursor_next(d, c), ++i) {
+          const int w = i % WGS, j = i / WGS, slot = i % NS, sbuf = j & 1;
+          ok = wait_or_abort(&mt.sdone[w][sbuf], ((j >> 1) & 1) ^ 1u, abort_flag, p.err, polls);
+          if (!ok) break;
+          if (c.ci == 3) {
+            ok = wait_or_abort(&mt.full[slot], (i / NS) & 1, abort_flag, p.err, polls);
+          } else {
+            ok = wait_or_abort(&mt.uready[slot], (umask >> slot) & 1u, abort_flag, p.err, polls);
+            umask ^= 1u << slot;
+          }
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t idesc = idesc_i8(tc_k_signed(c.ci), 1, 0, 0, 128, Cfg::SCOLS);
+          const uint32_t ka = smem_u32(slots + (size_t)slot * kTcSlotBytes), qa = qa0 + c.ci * Cfg::QSTRIDE;
+          const uint32_t dcol = tmem_base + (uint32_t)(w * Cfg::WG_COLS + sbuf * Cfg::SCOLS);
+#pragma unroll
+          for (int s = 0; s < 4; ++s)
+            mma_i8_ss(dcol, smem_desc(ka + 32 * s, 1, 64, 2), smem_desc(qa + 32 * s, 1, 64, 2), idesc, s > 0);
+          mma_commit(&mt.sbar[w][sbuf]);
+        }
+        if (++qi == kTcQBufs) {
+          qi = 0;
+          qfpar ^= 1u;
+        }
+      }
+      mma_commit(&mt.drain[0]);
+      wait_or_abort(&mt.drain[0], 0, abort_flag, p.err, polls);
+    }
+    __syncwarp();
+  } else if (warp == WGS * 4 + 2) {
+    // ================================ PV issuer ================================
+    if (lane == 0) {
+      int i = 0;
+      bool ok = true;
+      const uint32_t idesc = idesc_i8(1, 0, 1, 1, 128, PN);
+      for (int r = run_begin; ok && r < run_end; ++r) {
+        const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
+        for (TcCursor c = tc_cursor_begin(d); ok && c.ci < kNumBuckets; tc_cursor_next(d, c), ++i) {
+          const int w = i % WGS, j = i / WGS, slot = i % NS;
+          ok = wait_or_abort(&mt.pready[w], j & 1, abort_flag, p.err, polls);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t va = smem_u32(slots + (size_t)slot * kTcSlotBytes + kTcTile), pa = smem_u32(pbufs + (size_t)w * Cfg::PBYTES);
+          const uint32_t dcol = tmem_base + (uint32_t)(w * Cfg::WG_COLS + 2 * Cfg::SCOLS);
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4)
+            mma_i8_ss(dcol, smem_desc(va + 4096 * s4, 64, 64, 2), smem_desc(pa + 512 * s4, 8, kTcKeys, 0), idesc, s4 > 0);
+          mma_commit(&mt.obar[w]);
+          mma_commit(&mt.empty[slot]);  // the slot goes back to the producer when the tile has been read
+        }
+      }
+      mma_commit(&mt.drain[1]);
+      wait_or_abort(&mt.drain[1], 0, abort_flag, p.err, polls);
+    }
+    __syncwarp();
   } else {
     // ================================== consumer warpgroups ==================================
     const int wg = warp >> 2, wt = tid & 127, wq = warp & 3;  // wq: this warp's lane quarter of tensor memory
     const int bar = 1 + wg;
     const uint32_t tm_wg = tmem_base + (uint32_t)(wg * Cfg::WG_COLS) + ((uint32_t)(wq * 32) << 16);
-    uint8_t* pbuf_wg = pbufs + (size_t)wg * 2 * Cfg::PBYTES;
-    int gi = 0, j = 0, qi = 0;
+    uint8_t* pbuf = pbufs + (size_t)wg * Cfg::PBYTES;
+    int gi = 0, qi = 0;
     uint32_t qfpar = 0;
     bool aborted = false;
 
     struct Blk {
-      int ci, key0, nkeys, slot, buf;
-      uint32_t fpar, bpar;
+      int ci, key0, nkeys, slot, jj;
+      uint32_t fpar;
       bool valid;
     };
 
     for (int r = run_begin; r < run_end; ++r) {
+      const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
       if (!aborted && !wait_or_abort(&mt.qfull[qi], qfpar, abort_flag, p.err, polls)) aborted = true;
-      const RunDesc d = mt.q[qi].desc;
-      const uint8_t* qt = qtiles + (size_t)qi * 4 * kTcQTile;
       float qs[GP];
       int sumA[GP];
 #pragma unroll
@@ -417,81 +559,77 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         Blk k{};
         k.valid = false;
         while (cur_c.ci < kNumBuckets) {
-          const bool take = (gi % kTcWgs) == wg;
+          const bool take = (gi % WGS) == wg;
           if (take) {
             k.ci = cur_c.ci;
             k.key0 = cur_c.t * kTcKeys;
             k.nkeys = (d.cnt[k.ci] - k.key0) < kTcKeys ? (d.cnt[k.ci] - k.key0) : kTcKeys;
             k.slot = gi % NS;
             k.fpar = (gi / NS) & 1;
-            k.buf = j & 1;
-            k.bpar = (j >> 1) & 1;
+            k.jj = gi / WGS;
             k.valid = true;
-            ++j;
           }
           ++gi;
-          ++cur_c.t;
-          tc_cursor_skip(d, cur_c);
+          tc_cursor_next(d, cur_c);
           if (take) break;
         }
         return k;
       };
 
-      // ---- phase A: data of the block present, narrow rows spread to bytes, score MMA issued ----
-      auto phase_a = [&](const Blk& k) {
+      // ---- unpack: narrow rows spread to bytes, tile handed to the score issuer ----
+      auto phase_u = [&](const Blk& k) {
+        if (k.ci == 3) return;  // 8-bit rows are MMA operands as they land
         uint8_t* sb = slots + (size_t)k.slot * kTcSlotBytes;
+        TCP(k, 0);
         if (!aborted && !wait_or_abort(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
-        if (k.ci != 3) {
-          if (k.ci == 0) tc_unpack2(sb, wt, bar);
-          else if (k.ci == 1) tc_unpack3(sb, wt, bar);
-          else tc_unpack4(sb, wt, bar);
-          fence_proxy_async();
-          tc_fence_before();
-          named_bar_sync(bar, 128);
-        }
-        if (wt == 0) {
-          tc_fence_after();
-          const uint32_t idesc = idesc_i8(k.ci == 3, 1, 0, 0, 128, Cfg::SCOLS);
-          const uint32_t ka = smem_u32(sb), qa = smem_u32(qt + k.ci * kTcQTile);
-#pragma unroll
-          for (int s = 0; s < 4; ++s)
-            mma_i8_ss(tmem_base + (uint32_t)(wg * Cfg::WG_COLS + k.buf * Cfg::SCOLS), smem_desc(ka + 32 * s, 1, 64, 2),
-                      smem_desc(qa + 32 * s, 1, 64, 2), idesc, s > 0);
-          mma_commit(&mt.sbar[wg][k.buf]);
-        }
+        TCP(k, 1);
+        if (k.ci == 0) tc_unpack2(sb, wt, bar);
+        else if (k.ci == 1) tc_unpack3(sb, wt, bar);
+        else tc_unpack4(sb, wt, bar);
+        fence_proxy_async();
+        mbar_arrive(&mt.uready[k.slot]);
+        TCP(k, 2);
       };
 
-      // what phase C needs from phase B of the same block
+      // what the epilogue needs from the softmax of the same block
       struct Pend {
         float mb[GP];
         float vsmax;
-        Blk k;
+        int ci, jj;
       };
+      float x[GP], vs_cur = 0.f;  // scores of this thread's key (log2 units), its V scale
 
-      // ---- phase B: scores -> probabilities (24-bit fixed point), PV MMA issued -----------------------
-      auto phase_b = [&](const Blk& k, Pend& pe) {
+      // ---- scores: S out of tensor memory, scaled; block maxima exchanged ---------------------------
+      auto phase_b1 = [&](const Blk& k, Pend& pe) {
         uint8_t* sb = slots + (size_t)k.slot * kTcSlotBytes;
-        if (!aborted && !wait_or_abort(&mt.sbar[wg][k.buf], k.bpar, abort_flag, p.err, polls)) aborted = true;
+        const int sbuf = k.jj & 1;
+        TCP(k, 4);
+        if (!aborted && !wait_or_abort(&mt.sbar[wg][sbuf], (k.jj >> 1) & 1, abort_flag, p.err, polls)) aborted = true;
+        TCP(k, 5);
         tc_fence_after();
         uint32_t s[2 * GP];
         if constexpr (GP <= 4) {
           uint32_t t8[8];
-          tmem_ld8(tm_wg + (uint32_t)(k.buf * Cfg::SCOLS), t8);
+          tmem_ld8(tm_wg + (uint32_t)(sbuf * Cfg::SCOLS), t8);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 8; ++i) s[i] = t8[i];
         } else {
           uint32_t t16[16];
-          tmem_ld16(tm_wg + (uint32_t)(k.buf * Cfg::SCOLS), t16);
+          tmem_ld16(tm_wg + (uint32_t)(sbuf * Cfg::SCOLS), t16);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) s[i] = t16[i];
         }
+        tc_fence_before();
+        mbar_arrive(&mt.sdone[wg][sbuf]);  // the score issuer may overwrite this S buffer
+        TCP(k, 6);
+        if (k.ci == 3 && !aborted && !wait_or_abort(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
         const float2 sc = *reinterpret_cast<const float2*>(sb + 2 * kTcTile + wt * 8);
         const bool valid = wt < k.nkeys;
-        const float ks = valid ? sc.x : 0.f, vs = valid ? sc.y : 0.f;
-        const int off = k.ci == 3 ? 0 : (1 << (bucket_bits(k.ci) - 1));
-        float x[GP];
+        const float ks = valid ? sc.x : 0.f;
+        vs_cur = valid ? sc.y : 0.f;
+        const int off = tc_k_offset(k.ci);
         float madd = 0.f;
         if (p.mask != nullptr && valid) {
           const int tok = p.slot_token[(long long)b * g.slots + g.bucket_base[k.ci] + k.key0 + wt];
@@ -512,29 +650,41 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         uint32_t rk[GP];
 #pragma unroll
         for (int h = 0; h < GP; ++h) rk[h] = redux_max_u32(float_order_key(x[h]));
-        const uint32_t rv = redux_max_u32(__float_as_uint(vs));
+        const uint32_t rv = redux_max_u32(__float_as_uint(vs_cur));
         if (lane == 0) {
 #pragma unroll
-          for (int h = 0; h < GP; ++h) mt.red[wg][wq][h] = rk[h];
+          for (int h = 0; h < GP; h += 4)
+            *reinterpret_cast<uint4*>(&mt.red[wg][wq][h]) = make_uint4(rk[h], rk[h + 1], rk[h + 2], rk[h + 3]);
           mt.red[wg][wq][GP] = rv;
         }
         named_bar_sync(bar, 128);
-        float vsmax;
+        TCP(k, 7);
         {
           uint32_t a = mt.red[wg][0][GP], c2 = mt.red[wg][1][GP], c3 = mt.red[wg][2][GP], c4 = mt.red[wg][3][GP];
           a = a > c2 ? a : c2;
           c3 = c3 > c4 ? c3 : c4;
-          vsmax = __uint_as_float(a > c3 ? a : c3);
+          pe.vsmax = __uint_as_float(a > c3 ? a : c3);
         }
-        const float vnorm = vsmax > 0.f ? kTcPOne / vsmax : 0.f;
+#pragma unroll
+        for (int h = 0; h < GP; h += 4) {
+          const uint4 r0 = *reinterpret_cast<const uint4*>(&mt.red[wg][0][h]), r1 = *reinterpret_cast<const uint4*>(&mt.red[wg][1][h]);
+          const uint4 r2 = *reinterpret_cast<const uint4*>(&mt.red[wg][2][h]), r3 = *reinterpret_cast<const uint4*>(&mt.red[wg][3][h]);
+          pe.mb[h] = float_from_order_key(max(max(r0.x, r1.x), max(r2.x, r3.x)));
+          pe.mb[h + 1] = float_from_order_key(max(max(r0.y, r1.y), max(r2.y, r3.y)));
+          pe.mb[h + 2] = float_from_order_key(max(max(r0.z, r1.z), max(r2.z, r3.z)));
+          pe.mb[h + 3] = float_from_order_key(max(max(r0.w, r1.w), max(r2.w, r3.w)));
+        }
+        pe.ci = k.ci;
+        pe.jj = k.jj;
+      };
+
+      // ---- probabilities: running state updated, P row written, handed to the PV issuer --------------------
+      auto phase_b2 = [&](const Blk& k, const Pend& pe) {
+        const float vnorm = pe.vsmax > 0.f ? kTcPOne / pe.vsmax : 0.f;
         uint32_t wfix[GP];
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
-          uint32_t a = mt.red[wg][0][h], c2 = mt.red[wg][1][h], c3 = mt.red[wg][2][h], c4 = mt.red[wg][3][h];
-          a = a > c2 ? a : c2;
-          c3 = c3 > c4 ? c3 : c4;
-          const float mb = float_from_order_key(a > c3 ? a : c3);
-          pe.mb[h] = mb;
+          const float mb = pe.mb[h];
           const float mn = fmaxf(m_run[h], mb);
           if (mn != m_run[h]) {  // uniform over the warpgroup: every thread holds the same state
             const float alpha = ex2f(m_run[h] - mn);
@@ -545,17 +695,14 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           }
           const float pb = ex2f(x[h] - mb);  // in [0, 1]; 0 for rows past the end
           l_run[h] = fmaf(pb, ex2f(mb - mn), l_run[h]);
-          wfix[h] = __float2uint_rn(pb * (vs * vnorm));
+          wfix[h] = __float2uint_rn(pb * (vs_cur * vnorm));
         }
-        pe.vsmax = vsmax;
-        pe.k = k;
         // P row of this key: byte h of limb word l = limb l of head h (most significant limb first)
-        uint8_t* prow = pbuf_wg + (size_t)k.buf * Cfg::PBYTES;
         if constexpr (GP <= 4) {
           const uint32_t lo01 = prmt(wfix[0], wfix[1], 0x5410), lo23 = prmt(wfix[2], wfix[3], 0x5410);  // bytes 0,1 of each
           const uint32_t hi01 = prmt(wfix[0], wfix[1], 0x0062), hi23 = prmt(wfix[2], wfix[3], 0x0062);  // byte 2 of each
           const uint32_t l0 = prmt(lo01, lo23, 0x6420), l1 = prmt(lo01, lo23, 0x7531), l2 = prmt(hi01, hi23, 0x5410);
-          *reinterpret_cast<uint4*>(prow + wt * 16) = make_uint4(l2, l1, l0, 0u);
+          *reinterpret_cast<uint4*>(pbuf + wt * 16) = make_uint4(l2, l1, l0, 0u);
         } else {
           uint32_t l0[2], l1[2], l2[2];
 #pragma unroll
@@ -567,48 +714,32 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             l2[q4] = prmt(hi01, hi23, 0x5410);
           }
           // columns 0..15 (limbs 2 and 1) form the first 16-byte panel, columns 16..31 (limb 0, zeros) the second
-          *reinterpret_cast<uint4*>(prow + wt * 16) = make_uint4(l2[0], l2[1], l1[0], l1[1]);
-          *reinterpret_cast<uint4*>(prow + kTcKeys * 16 + wt * 16) = make_uint4(l0[0], l0[1], 0u, 0u);
-        }
-        if (k.ci != 3) {  // unsigned codes: the offset's share of the product is offset * sum of P
-#pragma unroll
-          for (int h = 0; h < GP; ++h) {
-            const uint32_t sum = redux_add_u32(wfix[h]);
-            if (lane == 0) mt.wsum[wg][k.buf][wq][h] = sum;
-          }
+          *reinterpret_cast<uint4*>(pbuf + wt * 16) = make_uint4(l2[0], l2[1], l1[0], l1[1]);
+          *reinterpret_cast<uint4*>(pbuf + kTcKeys * 16 + wt * 16) = make_uint4(l0[0], l0[1], 0u, 0u);
         }
         fence_proxy_async();
         tc_fence_before();
-        named_bar_sync(bar, 128);
-        if (wt == 0) {
-          tc_fence_after();
-          const uint32_t idesc = idesc_i8(k.ci == 3, 0, 1, 1, 128, PN);
-          const uint32_t va = smem_u32(sb + kTcTile), pa = smem_u32(prow);
-#pragma unroll
-          for (int s4 = 0; s4 < 4; ++s4)
-            mma_i8_ss(tmem_base + (uint32_t)(wg * Cfg::WG_COLS + 2 * Cfg::SCOLS + k.buf * PN), smem_desc(va + 4096 * s4, 64, 64, 2),
-                      smem_desc(pa + 512 * s4, 8, kTcKeys, 0), idesc, s4 > 0);
-          mma_commit(&mt.obar[wg][k.buf]);
-          mma_commit(&mt.empty[k.slot]);  // the slot goes back to the producer when the tile has been read
-        }
+        mbar_arrive(&mt.pready[wg]);
+        TCP(k, 8);
       };
 
-      // ---- phase C: the block's P.V out of tensor memory into the fp32 accumulators ---------------
+      // ---- epilogue: the block's P.V out of tensor memory into the fp32 accumulators ---------------
       auto phase_c = [&](const Pend& pe) {
-        const Blk& k = pe.k;
-        if (!aborted && !wait_or_abort(&mt.obar[wg][k.buf], k.bpar, abort_flag, p.err, polls)) aborted = true;
+        TCP(pe, 11);
+        if (!aborted && !wait_or_abort(&mt.obar[wg], pe.jj & 1, abort_flag, p.err, polls)) aborted = true;
+        TCP(pe, 12);
         tc_fence_after();
         uint32_t acc[PN];
         if constexpr (GP <= 4) {
           uint32_t t16[16];
-          tmem_ld16(tm_wg + (uint32_t)(2 * Cfg::SCOLS + k.buf * PN), t16);
+          tmem_ld16(tm_wg + (uint32_t)(2 * Cfg::SCOLS), t16);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) acc[i] = t16[i];
         } else {
           uint32_t t16[16], u16[16];
-          tmem_ld16(tm_wg + (uint32_t)(2 * Cfg::SCOLS + k.buf * PN), t16);
-          tmem_ld16(tm_wg + (uint32_t)(2 * Cfg::SCOLS + k.buf * PN + 16), u16);
+          tmem_ld16(tm_wg + (uint32_t)(2 * Cfg::SCOLS), t16);
+          tmem_ld16(tm_wg + (uint32_t)(2 * Cfg::SCOLS + 16), u16);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -618,34 +749,35 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
         tc_fence_before();
         const float unit = pe.vsmax * (1.f / kTcPOne);
-        const int off = k.ci == 3 ? 0 : (1 << (bucket_bits(k.ci) - 1));
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
-          float v = fmaf((float)(int)acc[h], 65536.f, fmaf((float)(int)acc[GP + h], 256.f, (float)(int)acc[2 * GP + h]));
-          if (k.ci != 3) {
-            const uint32_t ws = mt.wsum[wg][k.buf][0][h] + mt.wsum[wg][k.buf][1][h] + mt.wsum[wg][k.buf][2][h] +
-                                mt.wsum[wg][k.buf][3][h];
-            v -= (float)off * (float)ws;
-          }
+          const float v = fmaf((float)(int)acc[h], 65536.f, fmaf((float)(int)acc[GP + h], 256.f, (float)(int)acc[2 * GP + h]));
           const float f = unit * ex2f(pe.mb[h] - m_run[h]);
-          if (k.ci == 0) o[0][h] = fmaf(v, f, o[0][h]);
-          else if (k.ci == 1) o[1][h] = fmaf(v, f, o[1][h]);
-          else if (k.ci == 2) o[2][h] = fmaf(v, f, o[2][h]);
+          if (pe.ci == 0) o[0][h] = fmaf(v, f, o[0][h]);
+          else if (pe.ci == 1) o[1][h] = fmaf(v, f, o[1][h]);
+          else if (pe.ci == 2) o[2][h] = fmaf(v, f, o[2][h]);
           else o[3][h] = fmaf(v, f, o[3][h]);
         }
+        TCP(pe, 13);
+#ifdef SKV_PROBES
+        if (wt == 0 && pe.jj < kTlBlocks && blockIdx.x % 18 == 0 && blockIdx.x / 18 < kTlCtas)
+          g_tc_timeline[blockIdx.x / 18][wg][pe.jj][15] = pe.ci;
+#endif
       };
 
-      // ---- software pipeline over this warpgroup's blocks of the run -----------------------------
+      // ---- software pipeline over this warpgroup's blocks of the run: unpack of block j+1, scores of block j,
+      // epilogue of block j-1, probabilities of block j ---------------------------------------------------------
       Pend pend_cur, pend_prev;
       bool have_prev = false;
       Blk cur = next_mine();
       const bool any = cur.valid;
-      if (cur.valid) phase_a(cur);
+      if (cur.valid) phase_u(cur);
       while (cur.valid) {
         const Blk nxt = next_mine();
-        if (nxt.valid) phase_a(nxt);
-        phase_b(cur, pend_cur);
+        if (nxt.valid) phase_u(nxt);
+        phase_b1(cur, pend_cur);
         if (have_prev) phase_c(pend_prev);
+        phase_b2(cur, pend_cur);
         pend_prev = pend_cur;
         have_prev = true;
         cur = nxt;
@@ -653,7 +785,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       if (have_prev) phase_c(pend_prev);
 
       // ---- end of the run: this warpgroup's partial (max, sum, out) ------------------------------------
-      // every score MMA of the run has completed (phase B waited for each), so the query slot can go back
+      // every score MMA of this warpgroup's blocks has completed (the softmax waited for each), so the query slot
+      // can go back once all warpgroups say so
       if (wt == 0) mbar_arrive(&mt.qempty[qi]);
       {
         float ltot[GP];
@@ -671,7 +804,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         float accum[GP];
 #pragma unroll
         for (int h = 0; h < GP; ++h) accum[h] = o[3][h];
-        float* stage = reinterpret_cast<float*>(pbuf_wg);  // [GP][128]; no MMA of this warpgroup is in flight
+        float* stage = reinterpret_cast<float*>(pbuf);  // [GP][128]; no MMA of this warpgroup is in flight
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
           if (d.ka[c] >= d.kb[c]) continue;  // uniform: the run has no block of this bucket
@@ -683,8 +816,15 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 #pragma unroll
           for (int h = 0; h < GP; ++h) accum[h] += stage[h * 128 + wt];
         }
-        named_bar_sync(bar, 128);  // stage (a P buffer) and red are free again
-        float* out = p.partials + ((long long)r * kTcWgs + wg) * partial_stride(G, 128);
+        named_bar_sync(bar, 128);  // stage (the P buffer) and red are free again
+        float* out = p.partials + ((long long)r * kTcPartialsPerRun + wg) * partial_stride(G, 128);
+        if (WGS < kTcPartialsPerRun && wg == 0 && wt < G) {  // partial slots no warpgroup owns read as empty
+          for (int e = WGS; e < kTcPartialsPerRun; ++e) {
+            float* eo = p.partials + ((long long)r * kTcPartialsPerRun + e) * partial_stride(G, 128);
+            eo[wt * 130] = -INFINITY;
+            eo[wt * 130 + 1] = 0.f;
+          }
+        }
         if (wt < G) {
           float mh = -INFINITY, lh = 0.f;
 #pragma unroll
@@ -706,11 +846,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         qi = 0;
         qfpar ^= 1u;
       }
-    }
-    // every MMA this warpgroup issued must have completed before tensor memory is freed
-    if (wt == 0) {
-      mma_commit(&mt.drain[wg]);
-      wait_or_abort(&mt.drain[wg], 0, abort_flag, p.err, polls);
     }
   }
   tc_fence_before();
@@ -807,7 +942,7 @@ int launch_tc(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& v
     }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  decode_attn_tc_kernel<GP><<<p.num_ctas, kTcThreads, smem, st>>>(p, kmap, vmap);
+  decode_attn_tc_kernel<GP><<<p.num_ctas, TcCfg<GP>::THREADS, smem, st>>>(p, kmap, vmap);
   const cudaError_t rc = cudaGetLastError();
   if (rc != cudaSuccess) {
     fprintf(stderr, "skv_decode_attention: launch failed: %s\n", cudaGetErrorString(rc));
@@ -818,9 +953,22 @@ int launch_tc(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& v
 
 }  // namespace
 
+#ifdef SKV_PROBES
+// instrumented builds only: copies the timeline of the last launch to the host and clears it
+extern "C" int skv_probe_tc_timeline(long long* host_out, int max_words) {
+  const int words = kTlCtas * kTlWgs * kTlBlocks * 16;
+  if (max_words < words) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  if (cudaMemcpyFromSymbol(host_out, g_tc_timeline, sizeof(long long) * words) != cudaSuccess) return -2;
+  static long long zeros[kTlCtas * kTlWgs * kTlBlocks * 16];
+  cudaMemcpyToSymbol(g_tc_timeline, zeros, sizeof(zeros));
+  return words;
+}
+#endif
+
 namespace skv {
 
-int attn_tc_partials_per_run() { return kTcWgs; }
+int attn_tc_partials_per_run() { return kTcPartialsPerRun; }
 
 int launch_attn_tc(const AttnParams& p, const SkvStoreDesc& desc, cudaStream_t stream) {
   if (desc.head_dim != 128 || !p.q_is_half || p.group < 1 || p.group > 8) return SKV_ERR_UNSUPPORTED;

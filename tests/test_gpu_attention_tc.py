@@ -23,7 +23,7 @@ def test_tensor_memory_kernel_is_selected():
     from tests.gpu_util import make_store
     store = make_store(1, 1, 8, 128, 32, 256)
     import ctypes
-    assert _lib.lib().skv_attn_partials_per_run(ctypes.byref(store.desc), _lib.DTYPE_F16) == 2
+    assert _lib.lib().skv_attn_partials_per_run(ctypes.byref(store.desc), _lib.DTYPE_F16) == 4
     _lib.lib().skv_set_attention_path(1)
     assert _lib.lib().skv_attn_partials_per_run(ctypes.byref(store.desc), _lib.DTYPE_F16) == 11
 
