@@ -49,7 +49,10 @@ constexpr int kTcTile = 16384;                       // one int8 tile: 128 rows 
 constexpr int kTcSlotBytes = 2 * kTcTile + 1024;     // K tile | V tile | 128 x (K scale, V scale)
 constexpr int kTcQBufs = 2;                          // query ring (runs in flight)
 constexpr int kTcPartialsPerRun = 4;                 // partial slots per run (one per warpgroup; unused ones are marked empty)
-constexpr int kTcPrefetch = 6;                       // blocks the producer asks L2 for ahead of its copies
+#ifndef SKV_TC_PREFETCH
+#define SKV_TC_PREFETCH 6
+#endif
+constexpr int kTcPrefetch = SKV_TC_PREFETCH;         // blocks the producer asks L2 for ahead of its copies
 // Fixed-point unit of P: the largest probability-times-V-scale of a block maps to 2^24 - 256, so that no
 // rounding in the chain can reach 2^24 (whose three low bytes would read as zero).
 constexpr float kTcPOne = 16776960.f;
@@ -103,7 +106,7 @@ struct TcMeta {
 template <int GP>
 constexpr size_t tc_smem_bytes() {
   return (size_t)TcCfg<GP>::NS * kTcSlotBytes + (size_t)kTcQBufs * TcCfg<GP>::QBUF + (size_t)TcCfg<GP>::WGS * TcCfg<GP>::PBYTES +
-         sizeof(TcMeta<GP>) + 1024;  // + slack to align the base to 1024 B
+         (size_t)TcCfg<GP>::WGS * GP * 128 * sizeof(float) + sizeof(TcMeta<GP>);
 }
 
 // ---- element order of the unpacked tiles ----------------------------------------------------------
@@ -140,27 +143,27 @@ __device__ __forceinline__ void tc_store_chunk(uint8_t* tile, int row, int oc, u
 // bytes u (0 <= u < 128) -> signed bytes u - off, four at a time
 __device__ __forceinline__ uint32_t tc_sub4(uint32_t x_or_80, uint32_t off4) { return (x_or_80 - off4) ^ 0x80808080u; }
 
-// 2-bit: 128 rows x 32 B = 256 chunks of 16 B per tile; thread wt takes chunks wt and wt + 128 of K and of V.
+// The K tile is finished before the V rows are fetched (two barriers, half the registers): the K tile
+// [0, 16 KB) never reaches the packed V rows, which start at 16 KB.
+
+// 2-bit: 128 rows x 32 B = 256 chunks of 16 B per tile; thread wt takes chunks wt and wt + 128.
 // Four crumbs at a time go through a byte permute used as a look-up table (0,1,2,3 -> -2,-1,0,1).
 __device__ __forceinline__ void tc_unpack2(uint8_t* slot, int wt, int bar) {
-  uint4 kin[2], vin[2];
-#pragma unroll
-  for (int n = 0; n < 2; ++n) {
-    kin[n] = *reinterpret_cast<const uint4*>(slot + (wt + 128 * n) * 16);
-    vin[n] = *reinterpret_cast<const uint4*>(slot + kTcTile + (wt + 128 * n) * 16);
-  }
-  named_bar_sync(bar, 128);
   constexpr uint32_t lut = 0x0100fffeu;
 #pragma unroll
   for (int which = 0; which < 2; ++which) {
+    uint8_t* tile = slot + which * kTcTile;
+    uint4 in[2];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) in[n] = *reinterpret_cast<const uint4*>(tile + (wt + 128 * n) * 16);
+    named_bar_sync(bar, 128);
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
-      const uint4 in = which ? vin[n] : kin[n];
       const int c = wt + 128 * n, row = c >> 1, hf = c & 1;
-      const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+      const uint32_t w[4] = {in[n].x, in[n].y, in[n].z, in[n].w};
 #pragma unroll
       for (int s = 0; s < 4; ++s)
-        tc_store_chunk(slot + which * kTcTile, row, 4 * hf + s, prmt(lut, 0u, w[s] & 0x3333u), prmt(lut, 0u, (w[s] >> 2) & 0x3333u),
+        tc_store_chunk(tile, row, 4 * hf + s, prmt(lut, 0u, w[s] & 0x3333u), prmt(lut, 0u, (w[s] >> 2) & 0x3333u),
                        prmt(lut, 0u, (w[s] >> 16) & 0x3333u), prmt(lut, 0u, (w[s] >> 18) & 0x3333u));
     }
   }
@@ -168,76 +171,83 @@ __device__ __forceinline__ void tc_unpack2(uint8_t* slot, int wt, int bar) {
 
 // 4-bit: 128 rows x 64 B = 512 chunks per tile; thread wt takes chunks wt + 128 n, n = 0..3.
 __device__ __forceinline__ void tc_unpack4(uint8_t* slot, int wt, int bar) {
-  uint4 kin[4], vin[4];
-#pragma unroll
-  for (int n = 0; n < 4; ++n) {
-    kin[n] = *reinterpret_cast<const uint4*>(slot + (wt + 128 * n) * 16);
-    vin[n] = *reinterpret_cast<const uint4*>(slot + kTcTile + (wt + 128 * n) * 16);
-  }
-  named_bar_sync(bar, 128);
   constexpr uint32_t m = 0x0f0f0f0fu, hi = 0x80808080u, off = 0x08080808u;
+  {
+    uint4 in[4];
 #pragma unroll
-  for (int n = 0; n < 4; ++n) {
-    const uint4 in = kin[n];
-    const int c = wt + 128 * n, row = c >> 2, q = c & 3;
-    tc_store_chunk(slot, row, 2 * q, in.x & m, (in.x >> 4) & m, in.y & m, (in.y >> 4) & m);
-    tc_store_chunk(slot, row, 2 * q + 1, in.z & m, (in.z >> 4) & m, in.w & m, (in.w >> 4) & m);
+    for (int n = 0; n < 4; ++n) in[n] = *reinterpret_cast<const uint4*>(slot + (wt + 128 * n) * 16);
+    named_bar_sync(bar, 128);
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int c = wt + 128 * n, row = c >> 2, q = c & 3;
+      tc_store_chunk(slot, row, 2 * q, in[n].x & m, (in[n].x >> 4) & m, in[n].y & m, (in[n].y >> 4) & m);
+      tc_store_chunk(slot, row, 2 * q + 1, in[n].z & m, (in[n].z >> 4) & m, in[n].w & m, (in[n].w >> 4) & m);
+    }
   }
+  {
+    uint8_t* tile = slot + kTcTile;
+    uint4 in[4];
 #pragma unroll
-  for (int n = 0; n < 4; ++n) {
-    const uint4 in = vin[n];
-    const int c = wt + 128 * n, row = c >> 2, q = c & 3;
-    tc_store_chunk(slot + kTcTile, row, 2 * q, tc_sub4(lop_and_or(in.x, m, hi), off), tc_sub4(lop_and_or(in.x >> 4, m, hi), off),
-                   tc_sub4(lop_and_or(in.y, m, hi), off), tc_sub4(lop_and_or(in.y >> 4, m, hi), off));
-    tc_store_chunk(slot + kTcTile, row, 2 * q + 1, tc_sub4(lop_and_or(in.z, m, hi), off), tc_sub4(lop_and_or(in.z >> 4, m, hi), off),
-                   tc_sub4(lop_and_or(in.w, m, hi), off), tc_sub4(lop_and_or(in.w >> 4, m, hi), off));
+    for (int n = 0; n < 4; ++n) in[n] = *reinterpret_cast<const uint4*>(tile + (wt + 128 * n) * 16);
+    named_bar_sync(bar, 128);
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int c = wt + 128 * n, row = c >> 2, q = c & 3;
+      tc_store_chunk(tile, row, 2 * q, tc_sub4(lop_and_or(in[n].x, m, hi), off), tc_sub4(lop_and_or(in[n].x >> 4, m, hi), off),
+                     tc_sub4(lop_and_or(in[n].y, m, hi), off), tc_sub4(lop_and_or(in[n].y >> 4, m, hi), off));
+      tc_store_chunk(tile, row, 2 * q + 1, tc_sub4(lop_and_or(in[n].z, m, hi), off), tc_sub4(lop_and_or(in[n].z >> 4, m, hi), off),
+                     tc_sub4(lop_and_or(in[n].w, m, hi), off), tc_sub4(lop_and_or(in[n].w >> 4, m, hi), off));
+    }
   }
 }
 
-// 3-bit: a row is 48 B = four 12-byte groups of 32 fields; thread wt takes row wt of K and of V.
+// 3-bit: a row is 48 B = four 12-byte groups of 32 fields; thread wt takes row wt.
 __device__ __forceinline__ void tc_unpack3(uint8_t* slot, int wt, int bar) {
-  uint32_t kin[12], vin[12];
 #pragma unroll
-  for (int n = 0; n < 3; ++n) {
-    const uint4 a = *reinterpret_cast<const uint4*>(slot + wt * 48 + 16 * n);
-    const uint4 b = *reinterpret_cast<const uint4*>(slot + kTcTile + wt * 48 + 16 * n);
-    kin[4 * n] = a.x; kin[4 * n + 1] = a.y; kin[4 * n + 2] = a.z; kin[4 * n + 3] = a.w;
-    vin[4 * n] = b.x; vin[4 * n + 1] = b.y; vin[4 * n + 2] = b.z; vin[4 * n + 3] = b.w;
-  }
-  named_bar_sync(bar, 128);
+  for (int which = 0; which < 2; ++which) {
+    uint8_t* tile = slot + which * kTcTile;
+    uint32_t in[12];
 #pragma unroll
-  for (int a = 0; a < 4; ++a) {
-    const uint32_t w[3] = {kin[3 * a], kin[3 * a + 1], kin[3 * a + 2]};
-    uint32_t o[8];
-    unpack_kslice_i8<128, 3>(w, o);
-    tc_store_chunk(slot, wt, 2 * a, o[0], o[1], o[2], o[3]);
-    tc_store_chunk(slot, wt, 2 * a + 1, o[4], o[5], o[6], o[7]);
-  }
+    for (int n = 0; n < 3; ++n) {
+      const uint4 a = *reinterpret_cast<const uint4*>(tile + wt * 48 + 16 * n);
+      in[4 * n] = a.x; in[4 * n + 1] = a.y; in[4 * n + 2] = a.z; in[4 * n + 3] = a.w;
+    }
+    named_bar_sync(bar, 128);
 #pragma unroll
-  for (int a = 0; a < 4; ++a) {
-    const uint32_t w[3] = {vin[3 * a], vin[3 * a + 1], vin[3 * a + 2]};
-    uint32_t o[8];
-    unpack_kslice_i8<128, 3>(w, o);
-    constexpr uint32_t hi = 0x80808080u, off = 0x04040404u;
+    for (int a = 0; a < 4; ++a) {
+      const uint32_t w[3] = {in[3 * a], in[3 * a + 1], in[3 * a + 2]};
+      uint32_t o[8];
+      unpack_kslice_i8<128, 3>(w, o);
+      if (which == 1) {  // V: signed codes
+        constexpr uint32_t hi = 0x80808080u, off = 0x04040404u;
 #pragma unroll
-    for (int f = 0; f < 8; ++f) o[f] = tc_sub4(o[f] | hi, off);
-    tc_store_chunk(slot + kTcTile, wt, 2 * a, o[0], o[1], o[2], o[3]);
-    tc_store_chunk(slot + kTcTile, wt, 2 * a + 1, o[4], o[5], o[6], o[7]);
+        for (int f = 0; f < 8; ++f) o[f] = tc_sub4(o[f] | hi, off);
+      }
+      tc_store_chunk(tile, wt, 2 * a, o[0], o[1], o[2], o[3]);
+      tc_store_chunk(tile, wt, 2 * a + 1, o[4], o[5], o[6], o[7]);
+    }
   }
 }
 
 // ---- block cursor: the blocks of a run in the order every role follows -------------------------------
+// (element selection by compare chains: a dynamically indexed copy of the descriptor would live in local memory)
+__device__ __forceinline__ int tc_sel4(const int (&a)[kNumBuckets], int i) {
+  return i == 0 ? a[0] : i == 1 ? a[1] : i == 2 ? a[2] : a[3];
+}
 struct TcCursor {
-  int ci, t;
+  int ci, t, t_end;  // bucket, next 128-key tile, end of this bucket's tiles
 };
 __device__ __forceinline__ void tc_cursor_skip(const RunDesc& d, TcCursor& c) {
-  while (c.ci < kNumBuckets && c.t >= d.kb[c.ci]) {
+  while (c.ci < kNumBuckets && c.t >= c.t_end) {
     ++c.ci;
-    if (c.ci < kNumBuckets) c.t = d.ka[c.ci];
+    if (c.ci < kNumBuckets) {
+      c.t = tc_sel4(d.ka, c.ci);
+      c.t_end = tc_sel4(d.kb, c.ci);
+    }
   }
 }
 __device__ __forceinline__ TcCursor tc_cursor_begin(const RunDesc& d) {
-  TcCursor c{0, d.ka[0]};
+  TcCursor c{0, d.ka[0], d.kb[0]};
   tc_cursor_skip(d, c);
   return c;
 }
@@ -246,25 +256,32 @@ __device__ __forceinline__ void tc_cursor_next(const RunDesc& d, TcCursor& c) {
   tc_cursor_skip(d, c);
 }
 
+// Bounded wait of the tensor-memory kernel: the thread is suspended inside mbarrier.try_wait (a loop of test_wait
+// polls by the sixteen consumer warps measured slower: it crowds the issue slots and the barrier words); the number
+// of resumptions is limited, so the wait always ends.
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, unsigned polls) {
+  const unsigned limit = (polls >> 4) + 16;  // a suspended try_wait lasts far longer than a 50 ns poll
+  for (unsigned i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(err, 1);
+  return false;
+}
+
 // ---- query limbs of a run, in the four element orders (one warp) ---------------------------------------------
 template <int GP>
 __device__ __forceinline__ void tc_prep_query(uint8_t* qbuf, TcQMeta& meta, const AttnParams& p, int seq, int head, int G,
                                               int lane) {
   constexpr int QSTRIDE = TcCfg<GP>::QSTRIDE;
   const long long q_off = ((long long)seq * p.num_q_heads + (long long)head * G) * 128;
-  float q[GP][4];
-#pragma unroll
-  for (int h = 0; h < GP; ++h) {
-    if (h < G) {
-      const __half2* src = reinterpret_cast<const __half2*>(static_cast<const __half*>(p.query) + q_off + h * 128 + lane * 4);
-      const float2 a = __half22float2(src[0]), b = __half22float2(src[1]);
-      q[h][0] = a.x; q[h][1] = a.y; q[h][2] = b.x; q[h][3] = b.y;
-    }
-  }
-#pragma unroll
-  for (int h = 0; h < GP; ++h) {
-    if (h >= G) break;
-    float amax = fmaxf(fmaxf(fabsf(q[h][0]), fabsf(q[h][1])), fmaxf(fabsf(q[h][2]), fabsf(q[h][3])));
+#pragma unroll 1  // runs once per run on the producer warp: small code matters more than speed here
+  for (int h = 0; h < G; ++h) {
+    const __half2* src = reinterpret_cast<const __half2*>(static_cast<const __half*>(p.query) + q_off + h * 128 + lane * 4);
+    const float2 a = __half22float2(src[0]), b = __half22float2(src[1]);
+    const float q[4] = {a.x, a.y, b.x, b.y};
+    float amax = fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3])));
     amax = warp_max(amax);
     constexpr float range = 127.f * 128.f;
     const float step = amax > 0.f ? amax / range : 1.f;
@@ -273,12 +290,12 @@ __device__ __forceinline__ void tc_prep_query(uint8_t* qbuf, TcQMeta& meta, cons
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int d = lane * 4 + e;
-      const float rem = fminf(fmaxf(rintf(q[h][e] * inv), -range), range);
+      const float rem = fminf(fmaxf(rintf(q[e] * inv), -range), range);
       const float hi = rintf(rem * (1.f / 128.f));
       const int lo = (int)(rem - hi * 128.f);  // in [-64, 64]
       s0 += (int)hi;
       s1 += lo;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < kNumBuckets; ++c) {
         const int pos = tc_perm_inv(c, d);
         qbuf[c * QSTRIDE + tc_swz(h, pos)] = (uint8_t)(int8_t)(int)hi;
@@ -302,12 +319,16 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     decode_attn_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   using Cfg = TcCfg<GP>;
   constexpr int NS = Cfg::NS, PN = Cfg::PN, WGS = Cfg::WGS;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base (it is: the window starts at 0)
+    if (threadIdx.x == 0) atomicExch(p.err, 5);
+    return;
+  }
   uint8_t* slots = smem;                                        // [NS][kTcSlotBytes]
   uint8_t* qbufs = slots + (size_t)NS * kTcSlotBytes;           // [kTcQBufs][QBUF]
   uint8_t* pbufs = qbufs + (size_t)kTcQBufs * Cfg::QBUF;        // [WGS][PBYTES]
-  TcMeta<GP>& mt = *reinterpret_cast<TcMeta<GP>*>(pbufs + (size_t)WGS * Cfg::PBYTES);
+  float* obufs = reinterpret_cast<float*>(pbufs + (size_t)WGS * Cfg::PBYTES);   // [WGS][GP][128] output accumulators
+  TcMeta<GP>& mt = *reinterpret_cast<TcMeta<GP>*>(obufs + (size_t)WGS * GP * 128);
   const StoreGeom& g = p.g;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.group, Hkv = g.num_kv_heads;
@@ -320,7 +341,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&mt.full[s], 1);
-      mbar_init(&mt.uready[s], 128);
+      mbar_init(&mt.uready[s], 4);  // one arrival per warp of the unpacking warpgroup
       mbar_init(&mt.empty[s], 1);
     }
     for (int s = 0; s < kTcQBufs; ++s) {
@@ -330,9 +351,9 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     for (int w = 0; w < WGS; ++w) {
       mbar_init(&mt.sbar[w][0], 1);
       mbar_init(&mt.sbar[w][1], 1);
-      mbar_init(&mt.sdone[w][0], 128);
-      mbar_init(&mt.sdone[w][1], 128);
-      mbar_init(&mt.pready[w], 128);
+      mbar_init(&mt.sdone[w][0], 4);
+      mbar_init(&mt.sdone[w][1], 4);
+      mbar_init(&mt.pready[w], 4);
       mbar_init(&mt.obar[w], 1);
     }
     mbar_init(&mt.drain[0], 1);
@@ -365,7 +386,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     // L2 prefetch stream: runs kTcPrefetch blocks ahead of the copies, across run boundaries
     int pf_run = run_begin, pf_count = 0;
     RunDesc pf_d = pv.first[blockIdx.x];
-    TcCursor pf_c = ok ? tc_cursor_begin(pf_d) : TcCursor{kNumBuckets, 0};
+    TcCursor pf_c = ok ? tc_cursor_begin(pf_d) : TcCursor{kNumBuckets, 0, 0};
     auto prefetch_to = [&](int upto) {
       while (pf_count < upto) {
         if (pf_c.ci >= kNumBuckets) {
@@ -377,7 +398,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         }
         if (lane == 0) {
           const int ci = pf_c.ci, key0 = pf_c.t * kTcKeys;
-          const int nkeys = (pf_d.cnt[ci] - key0) < kTcKeys ? (pf_d.cnt[ci] - key0) : kTcKeys;
+          const int nkeys = (tc_sel4(pf_d.cnt, ci) - key0) < kTcKeys ? (tc_sel4(pf_d.cnt, ci) - key0) : kTcKeys;
           const int n16 = (nkeys + 15) & ~15, pd = g.row_bytes[ci];
           const uint8_t* arena = arena_ptr(g, p.store, p.layer, pf_d.seq);
           const long long row = (long long)pf_d.head * g.cap[ci] + key0;
@@ -396,10 +417,11 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         if (limit-- <= 0) return true;
         prefetch_to(gi + 1 + kTcPrefetch);
         const int slot = gi % NS;
-        if (!wait_or_abort(&mt.empty[slot], ((gi / NS) & 1) ^ 1u, abort_flag, p.err, polls)) return false;
+        if (!tc_wait(&mt.empty[slot], ((gi / NS) & 1) ^ 1u, abort_flag, p.err, polls)) return false;
         if (lane == 0) {
           const int ci = c.ci, key0 = c.t * kTcKeys;
-          const int nkeys = (d.cnt[ci] - key0) < kTcKeys ? (d.cnt[ci] - key0) : kTcKeys;
+          const int cnt_ci = tc_sel4(d.cnt, ci);
+          const int nkeys = (cnt_ci - key0) < kTcKeys ? (cnt_ci - key0) : kTcKeys;
           const int n16 = (nkeys + 15) & ~15;
           uint8_t* sb = slots + (size_t)slot * kTcSlotBytes;
           const long long row = (long long)d.head * g.cap[ci] + key0;
@@ -424,7 +446,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       return true;
     };
     auto publish_query = [&](const RunDesc& d) -> bool {
-      if (!wait_or_abort(&mt.qempty[qi], qepar, abort_flag, p.err, polls)) return false;
+      if (!tc_wait(&mt.qempty[qi], qepar, abort_flag, p.err, polls)) return false;
       tc_prep_query<GP>(qbufs + (size_t)qi * Cfg::QBUF, mt.q[qi], p, d.seq, d.head, G, lane);
       fence_proxy_async();  // the MMA reads the limb rows through the async proxy
       __syncwarp();
@@ -453,22 +475,26 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
   } else if (warp == WGS * 4 + 1) {
     // ================================ score issuer ================================
     // K.Q of block i as soon as its tile is ready and the S buffer it writes has been read
+#ifdef SKV_TC_STREAM_ONLY
+    if (false) {
+#else
     if (lane == 0) {
+#endif
       int i = 0, qi = 0;
       uint32_t qfpar = 0, umask = 0;
       bool ok = true;
       for (int r = run_begin; ok && r < run_end; ++r) {
         const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
-        ok = wait_or_abort(&mt.qfull[qi], qfpar, abort_flag, p.err, polls);
+        ok = tc_wait(&mt.qfull[qi], qfpar, abort_flag, p.err, polls);
         const uint32_t qa0 = smem_u32(qbufs + (size_t)qi * Cfg::QBUF);
         for (TcCursor c = tc_cursor_begin(d); ok && c.ci < kNumBuckets; tc_cursor_next(d, c), ++i) {
           const int w = i % WGS, j = i / WGS, slot = i % NS, sbuf = j & 1;
-          ok = wait_or_abort(&mt.sdone[w][sbuf], ((j >> 1) & 1) ^ 1u, abort_flag, p.err, polls);
+          ok = tc_wait(&mt.sdone[w][sbuf], ((j >> 1) & 1) ^ 1u, abort_flag, p.err, polls);
           if (!ok) break;
           if (c.ci == 3) {
-            ok = wait_or_abort(&mt.full[slot], (i / NS) & 1, abort_flag, p.err, polls);
+            ok = tc_wait(&mt.full[slot], (i / NS) & 1, abort_flag, p.err, polls);
           } else {
-            ok = wait_or_abort(&mt.uready[slot], (umask >> slot) & 1u, abort_flag, p.err, polls);
+            ok = tc_wait(&mt.uready[slot], (umask >> slot) & 1u, abort_flag, p.err, polls);
             umask ^= 1u << slot;
           }
           if (!ok) break;
@@ -487,12 +513,16 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         }
       }
       mma_commit(&mt.drain[0]);
-      wait_or_abort(&mt.drain[0], 0, abort_flag, p.err, polls);
+      tc_wait(&mt.drain[0], 0, abort_flag, p.err, polls);
     }
     __syncwarp();
   } else if (warp == WGS * 4 + 2) {
     // ================================ PV issuer ================================
+#ifdef SKV_TC_STREAM_ONLY
+    if (false) {
+#else
     if (lane == 0) {
+#endif
       int i = 0;
       bool ok = true;
       const uint32_t idesc = idesc_i8(1, 0, 1, 1, 128, PN);
@@ -500,7 +530,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
         for (TcCursor c = tc_cursor_begin(d); ok && c.ci < kNumBuckets; tc_cursor_next(d, c), ++i) {
           const int w = i % WGS, j = i / WGS, slot = i % NS;
-          ok = wait_or_abort(&mt.pready[w], j & 1, abort_flag, p.err, polls);
+          ok = tc_wait(&mt.pready[w], j & 1, abort_flag, p.err, polls);
           if (!ok) break;
           tc_fence_after();
           const uint32_t va = smem_u32(slots + (size_t)slot * kTcSlotBytes + kTcTile), pa = smem_u32(pbufs + (size_t)w * Cfg::PBYTES);
@@ -513,7 +543,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         }
       }
       mma_commit(&mt.drain[1]);
-      wait_or_abort(&mt.drain[1], 0, abort_flag, p.err, polls);
+      tc_wait(&mt.drain[1], 0, abort_flag, p.err, polls);
     }
     __syncwarp();
   } else {
@@ -534,23 +564,21 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
 
     for (int r = run_begin; r < run_end; ++r) {
       const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
-      if (!aborted && !wait_or_abort(&mt.qfull[qi], qfpar, abort_flag, p.err, polls)) aborted = true;
-      float qs[GP];
-      int sumA[GP];
-#pragma unroll
-      for (int h = 0; h < GP; ++h) {
-        qs[h] = mt.q[qi].qs[h];
-        sumA[h] = mt.q[qi].sumA[h];
-      }
+      if (!aborted && !tc_wait(&mt.qfull[qi], qfpar, abort_flag, p.err, polls)) aborted = true;
+      const TcQMeta& qm = mt.q[qi];  // limb steps and limb sums of the run's query heads
       const int b = d.seq, hkv = d.head;
-      float m_run[GP], l_run[GP], o[kNumBuckets][GP];
+      // Online-softmax state.  The output accumulators live in shared memory, one row of 128 per head: thread wt
+      // owns, for a block of bucket c, the output row tc_perm(c, wt) (the element order of that bucket's V tile), so
+      // the rows of all buckets add up in natural order without a reshuffle, and no register holds them.
+      float m_run[GP], l_run[GP];
+      float* oacc = obufs + (size_t)wg * GP * 128;
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
         m_run[h] = -INFINITY;
         l_run[h] = 0.f;
-#pragma unroll
-        for (int c = 0; c < kNumBuckets; ++c) o[c][h] = 0.f;
+        oacc[h * 128 + wt] = 0.f;
       }
+      named_bar_sync(bar, 128);
       float* lbase = nullptr;  // logits row of head 0 of this group
       if (p.logits != nullptr) lbase = p.logits + ((long long)b * p.num_q_heads + hkv * G) * g.slots;
 
@@ -563,7 +591,8 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           if (take) {
             k.ci = cur_c.ci;
             k.key0 = cur_c.t * kTcKeys;
-            k.nkeys = (d.cnt[k.ci] - k.key0) < kTcKeys ? (d.cnt[k.ci] - k.key0) : kTcKeys;
+            const int cnt_ci = tc_sel4(d.cnt, k.ci);
+            k.nkeys = (cnt_ci - k.key0) < kTcKeys ? (cnt_ci - k.key0) : kTcKeys;
             k.slot = gi % NS;
             k.fpar = (gi / NS) & 1;
             k.jj = gi / WGS;
@@ -581,13 +610,14 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         if (k.ci == 3) return;  // 8-bit rows are MMA operands as they land
         uint8_t* sb = slots + (size_t)k.slot * kTcSlotBytes;
         TCP(k, 0);
-        if (!aborted && !wait_or_abort(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
+        if (!aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
         TCP(k, 1);
         if (k.ci == 0) tc_unpack2(sb, wt, bar);
         else if (k.ci == 1) tc_unpack3(sb, wt, bar);
         else tc_unpack4(sb, wt, bar);
         fence_proxy_async();
-        mbar_arrive(&mt.uready[k.slot]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&mt.uready[k.slot]);
         TCP(k, 2);
       };
 
@@ -604,7 +634,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         uint8_t* sb = slots + (size_t)k.slot * kTcSlotBytes;
         const int sbuf = k.jj & 1;
         TCP(k, 4);
-        if (!aborted && !wait_or_abort(&mt.sbar[wg][sbuf], (k.jj >> 1) & 1, abort_flag, p.err, polls)) aborted = true;
+        if (!aborted && !tc_wait(&mt.sbar[wg][sbuf], (k.jj >> 1) & 1, abort_flag, p.err, polls)) aborted = true;
         TCP(k, 5);
         tc_fence_after();
         uint32_t s[2 * GP];
@@ -622,9 +652,10 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           for (int i = 0; i < 16; ++i) s[i] = t16[i];
         }
         tc_fence_before();
-        mbar_arrive(&mt.sdone[wg][sbuf]);  // the score issuer may overwrite this S buffer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&mt.sdone[wg][sbuf]);  // the score issuer may overwrite this S buffer
         TCP(k, 6);
-        if (k.ci == 3 && !aborted && !wait_or_abort(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
+        if (k.ci == 3 && !aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
         const float2 sc = *reinterpret_cast<const float2*>(sb + 2 * kTcTile + wt * 8);
         const bool valid = wt < k.nkeys;
         const float ks = valid ? sc.x : 0.f;
@@ -637,8 +668,8 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         }
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
-          const int si = (int)s[h] * 128 + (int)s[GP + h] - off * sumA[h];
-          x[h] = valid ? fmaf((float)si, ks * qs[h], madd) : -INFINITY;
+          const int si = (int)s[h] * 128 + (int)s[GP + h] - off * qm.sumA[h];
+          x[h] = valid ? fmaf((float)si, ks * qm.qs[h], madd) : -INFINITY;
         }
         if (lbase != nullptr && valid) {
           float* lrow = lbase + g.bucket_base[k.ci] + k.key0 + wt;
@@ -689,8 +720,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           if (mn != m_run[h]) {  // uniform over the warpgroup: every thread holds the same state
             const float alpha = ex2f(m_run[h] - mn);
             l_run[h] *= alpha;
-#pragma unroll
-            for (int c = 0; c < kNumBuckets; ++c) o[c][h] *= alpha;
+            oacc[h * 128 + wt] *= alpha;  // every thread scales one element of the row; its owner adds to it only after a barrier
             m_run[h] = mn;
           }
           const float pb = ex2f(x[h] - mb);  // in [0, 1]; 0 for rows past the end
@@ -719,14 +749,15 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         }
         fence_proxy_async();
         tc_fence_before();
-        mbar_arrive(&mt.pready[wg]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&mt.pready[wg]);
         TCP(k, 8);
       };
 
       // ---- epilogue: the block's P.V out of tensor memory into the fp32 accumulators ---------------
       auto phase_c = [&](const Pend& pe) {
         TCP(pe, 11);
-        if (!aborted && !wait_or_abort(&mt.obar[wg], pe.jj & 1, abort_flag, p.err, polls)) aborted = true;
+        if (!aborted && !tc_wait(&mt.obar[wg], pe.jj & 1, abort_flag, p.err, polls)) aborted = true;
         TCP(pe, 12);
         tc_fence_after();
         uint32_t acc[PN];
@@ -749,14 +780,15 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         }
         tc_fence_before();
         const float unit = pe.vsmax * (1.f / kTcPOne);
+        const int drow = tc_perm(pe.ci, wt);  // the output row this thread's lane of tensor memory holds for this bucket
+        // a row of a narrow bucket is rescaled by one thread (the one with wt == row) and added to by another: the
+        // rescale of the probabilities phase must have landed (8-bit rows: same thread, program order suffices)
+        if (pe.ci != 3) named_bar_sync(bar, 128);
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
           const float v = fmaf((float)(int)acc[h], 65536.f, fmaf((float)(int)acc[GP + h], 256.f, (float)(int)acc[2 * GP + h]));
           const float f = unit * ex2f(pe.mb[h] - m_run[h]);
-          if (pe.ci == 0) o[0][h] = fmaf(v, f, o[0][h]);
-          else if (pe.ci == 1) o[1][h] = fmaf(v, f, o[1][h]);
-          else if (pe.ci == 2) o[2][h] = fmaf(v, f, o[2][h]);
-          else o[3][h] = fmaf(v, f, o[3][h]);
+          oacc[h * 128 + drow] = fmaf(v, f, oacc[h * 128 + drow]);
         }
         TCP(pe, 13);
 #ifdef SKV_PROBES
@@ -765,24 +797,29 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
 #endif
       };
 
-      // ---- software pipeline over this warpgroup's blocks of the run: unpack of block j+1, scores of block j,
-      // epilogue of block j-1, probabilities of block j ---------------------------------------------------------
-      Pend pend_cur, pend_prev;
+      // ---- software pipeline over this warpgroup's blocks of the run: unpack of block j (its score MMA is then
+      // issued), epilogue of block j-1, scores and probabilities of block j.  Every phase is instantiated once:
+      // the loop body is the kernel's hot code and has to stay small. ------------------------------------------
+      Pend pend;  // written by the scores phase of a block, read by that block's epilogue one iteration later
       bool have_prev = false;
-      Blk cur = next_mine();
-      const bool any = cur.valid;
-      if (cur.valid) phase_u(cur);
-      while (cur.valid) {
-        const Blk nxt = next_mine();
-        if (nxt.valid) phase_u(nxt);
-        phase_b1(cur, pend_cur);
-        if (have_prev) phase_c(pend_prev);
-        phase_b2(cur, pend_cur);
-        pend_prev = pend_cur;
-        have_prev = true;
-        cur = nxt;
+#ifdef SKV_TC_STREAM_ONLY
+      while (true) {  // timing probe: the bytes land and the slot goes straight back
+        const Blk cur = next_mine();
+        if (!cur.valid) break;
+        if (!aborted && !tc_wait(&mt.full[cur.slot], cur.fpar, abort_flag, p.err, polls)) aborted = true;
+        named_bar_sync(bar, 128);
+        if (wt == 0) mbar_arrive(&mt.empty[cur.slot]);
       }
-      if (have_prev) phase_c(pend_prev);
+#endif
+      while (true) {
+        const Blk cur = next_mine();
+        if (cur.valid) phase_u(cur);             // its score MMA runs while the previous block's epilogue does
+        if (have_prev) phase_c(pend);
+        if (!cur.valid) break;
+        phase_b1(cur, pend);
+        phase_b2(cur, pend);
+        have_prev = true;
+      }
 
       // ---- end of the run: this warpgroup's partial (max, sum, out) ------------------------------------
       // every score MMA of this warpgroup's blocks has completed (the softmax waited for each), so the query slot
@@ -800,23 +837,10 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         for (int h = 0; h < GP; ++h)
           ltot[h] = (__uint_as_float(mt.red[wg][0][h]) + __uint_as_float(mt.red[wg][1][h])) +
                     (__uint_as_float(mt.red[wg][2][h]) + __uint_as_float(mt.red[wg][3][h]));
-        // rows of the narrow buckets come out in their unpack order: put them back through shared memory
+        // the barrier above also orders every thread's additions to the output rows before they are read here
         float accum[GP];
 #pragma unroll
-        for (int h = 0; h < GP; ++h) accum[h] = o[3][h];
-        float* stage = reinterpret_cast<float*>(pbuf);  // [GP][128]; no MMA of this warpgroup is in flight
-#pragma unroll
-        for (int c = 0; c < 3; ++c) {
-          if (d.ka[c] >= d.kb[c]) continue;  // uniform: the run has no block of this bucket
-          named_bar_sync(bar, 128);
-          const int dpos = tc_perm(c, wt);
-#pragma unroll
-          for (int h = 0; h < GP; ++h) stage[h * 128 + dpos] = o[c][h];
-          named_bar_sync(bar, 128);
-#pragma unroll
-          for (int h = 0; h < GP; ++h) accum[h] += stage[h * 128 + wt];
-        }
-        named_bar_sync(bar, 128);  // stage (the P buffer) and red are free again
+        for (int h = 0; h < GP; ++h) accum[h] = oacc[h * 128 + wt];
         float* out = p.partials + ((long long)r * kTcPartialsPerRun + wg) * partial_stride(G, 128);
         if (WGS < kTcPartialsPerRun && wg == 0 && wt < G) {  // partial slots no warpgroup owns read as empty
           for (int e = WGS; e < kTcPartialsPerRun; ++e) {
@@ -836,7 +860,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           out[wt * 130] = mh;
           out[wt * 130 + 1] = lh;
         }
-        if (any) {
+        if (have_prev) {
 #pragma unroll
           for (int h = 0; h < GP; ++h)
             if (h < G) out[h * 130 + 2 + wt] = accum[h];
