@@ -50,24 +50,32 @@ constexpr int kTcSlotBytes = 2 * kTcTile + 1024;     // K tile | V tile | 128 x 
 constexpr int kTcQBufs = 2;                          // query ring (runs in flight)
 constexpr int kTcPartialsPerRun = 4;                 // partial slots per run (one per warpgroup; unused ones are marked empty)
 #ifndef SKV_TC_PREFETCH
-#define SKV_TC_PREFETCH 6
+#define SKV_TC_PREFETCH 0
 #endif
-constexpr int kTcPrefetch = SKV_TC_PREFETCH;         // blocks the producer asks L2 for ahead of its copies
+// Blocks the producer asks L2 for ahead of its copies.  0: off -- measured: each bulk prefetch costs the producer
+// about 200 cycles of issue time, three per block, and the copies did not land any sooner.
+constexpr int kTcPrefetch = SKV_TC_PREFETCH;
 // Fixed-point unit of P: the largest probability-times-V-scale of a block maps to 2^24 - 256, so that no
 // rounding in the chain can reach 2^24 (whose three low bytes would read as zero).
 constexpr float kTcPOne = 16776960.f;
 
 #ifdef SKV_PROBES
 // timing probes of an instrumented build (never compiled into the product library)
-constexpr int kTlCtas = 8, kTlBlocks = 40, kTlWgs = 4;
+constexpr int kTlCtas = 8, kTlBlocks = 40, kTlWgs = 5;  // index 4: ring stamps by global block index
 __device__ long long g_tc_timeline[kTlCtas][kTlWgs][kTlBlocks][16];
 #define TCP(blk, i)                                                                                          \
   do {                                                                                                       \
     if (wt == 0 && (blk).jj < kTlBlocks && blockIdx.x % 18 == 0 && blockIdx.x / 18 < kTlCtas)                \
       g_tc_timeline[blockIdx.x / 18][wg][(blk).jj][i] = clock64();                                          \
   } while (0)
+#define RING_STAMP(gidx, i)                                                                                  \
+  do {                                                                                                       \
+    if ((gidx) < kTlBlocks && blockIdx.x % 18 == 0 && blockIdx.x / 18 < kTlCtas)                            \
+      g_tc_timeline[blockIdx.x / 18][4][gidx][i] = clock64();                                               \
+  } while (0)
 #else
 #define TCP(blk, i) do { } while (0)
+#define RING_STAMP(gidx, i) do { } while (0)
 #endif
 
 template <int GP>
@@ -82,7 +90,7 @@ struct TcCfg {
   static constexpr int QROWS = GP <= 4 ? 8 : 16;           // limb rows of one element order: GP high limbs, GP low limbs
   static constexpr int QSTRIDE = QROWS * 128;              // bytes between two element orders
   static constexpr int QBUF = 4 * QSTRIDE + (16 - QROWS) * 128;  // the MMA reads 16 rows whatever QROWS is
-  static constexpr int THREADS = (WGS * 4 + 3) * 32;       // + producer, score issuer, PV issuer
+  static constexpr int THREADS = (WGS * 4 + 4) * 32;       // + producer, score issuer, PV issuer, query warp
   static_assert(WGS * WG_COLS <= TMEM_COLS, "tensor memory budget");
 };
 
@@ -97,6 +105,7 @@ struct TcMeta {
   uint64_t qfull[kTcQBufs], qempty[kTcQBufs];
   uint64_t sbar[4][2], sdone[4][2], pready[4], obar[4];
   uint64_t drain[2];
+  uint64_t q0bar;                  // the first run's query heads, prepared by the consumer warps (one arrival per head)
   uint32_t tmem_base;
   int abort_flag;
   alignas(16) uint32_t red[4][4][12];  // per warpgroup and warp: GP block maxima (order keys) + the largest V scale
@@ -271,46 +280,47 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile
 }
 
 // ---- query limbs of a run, in the four element orders (one warp) ---------------------------------------------
+// One warp, one query head: the two int8 limbs of every element, written in the four element orders.
 template <int GP>
-__device__ __forceinline__ void tc_prep_query(uint8_t* qbuf, TcQMeta& meta, const AttnParams& p, int seq, int head, int G,
-                                              int lane) {
+__device__ __forceinline__ void tc_prep_query_head(uint8_t* qbuf, TcQMeta& meta, const AttnParams& p, int seq, int head, int G,
+                                                   int h, int lane) {
   constexpr int QSTRIDE = TcCfg<GP>::QSTRIDE;
-  const long long q_off = ((long long)seq * p.num_q_heads + (long long)head * G) * 128;
-#pragma unroll 1  // runs once per run on the producer warp: small code matters more than speed here
-  for (int h = 0; h < G; ++h) {
-    const __half2* src = reinterpret_cast<const __half2*>(static_cast<const __half*>(p.query) + q_off + h * 128 + lane * 4);
-    const float2 a = __half22float2(src[0]), b = __half22float2(src[1]);
-    const float q[4] = {a.x, a.y, b.x, b.y};
-    float amax = fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3])));
-    amax = warp_max(amax);
-    constexpr float range = 127.f * 128.f;
-    const float step = amax > 0.f ? amax / range : 1.f;
-    const float inv = 1.f / step;
-    int s0 = 0, s1 = 0;
+  const long long q_off = ((long long)seq * p.num_q_heads + (long long)head * G + h) * 128;
+  const __half2* src = reinterpret_cast<const __half2*>(static_cast<const __half*>(p.query) + q_off + lane * 4);
+  const float2 a = __half22float2(src[0]), b = __half22float2(src[1]);
+  const float q[4] = {a.x, a.y, b.x, b.y};
+  float amax = fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3])));
+  amax = warp_max(amax);
+  constexpr float range = 127.f * 128.f;
+  const float step = amax > 0.f ? amax / range : 1.f;
+  const float inv = 1.f / step;
+  int s0 = 0, s1 = 0;
+  uint8_t* row_hi = qbuf + h * 128;
+  uint8_t* row_lo = qbuf + (GP + h) * 128;
+  const int xh = h & 7, xl = (GP + h) & 7;  // swizzle of the two rows
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int d = lane * 4 + e;
-      const float rem = fminf(fmaxf(rintf(q[e] * inv), -range), range);
-      const float hi = rintf(rem * (1.f / 128.f));
-      const int lo = (int)(rem - hi * 128.f);  // in [-64, 64]
-      s0 += (int)hi;
-      s1 += lo;
-#pragma unroll 1
-      for (int c = 0; c < kNumBuckets; ++c) {
-        const int pos = tc_perm_inv(c, d);
-        qbuf[c * QSTRIDE + tc_swz(h, pos)] = (uint8_t)(int8_t)(int)hi;
-        qbuf[c * QSTRIDE + tc_swz(GP + h, pos)] = (uint8_t)(int8_t)lo;
-      }
-    }
+  for (int e = 0; e < 4; ++e) {
+    const int d = lane * 4 + e;
+    const float rem = fminf(fmaxf(rintf(q[e] * inv), -range), range);
+    const float hi = rintf(rem * (1.f / 128.f));
+    const int lo = (int)(rem - hi * 128.f);  // in [-64, 64]
+    s0 += (int)hi;
+    s1 += lo;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      s0 += __shfl_xor_sync(0xffffffffu, s0, off);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+    for (int c = 0; c < kNumBuckets; ++c) {
+      const int pos = tc_perm_inv(c, d);
+      row_hi[c * QSTRIDE + ((((pos >> 4) ^ xh)) << 4) + (pos & 15)] = (uint8_t)(int8_t)(int)hi;
+      row_lo[c * QSTRIDE + ((((pos >> 4) ^ xl)) << 4) + (pos & 15)] = (uint8_t)(int8_t)lo;
     }
-    if (lane == 0) {
-      meta.qs[h] = step * p.scale_log2;
-      meta.sumA[h] = 128 * s0 + s1;
-    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    s0 += __shfl_xor_sync(0xffffffffu, s0, off);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+  }
+  if (lane == 0) {
+    meta.qs[h] = step * p.scale_log2;
+    meta.sumA[h] = 128 * s0 + s1;
   }
 }
 
@@ -358,6 +368,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     }
     mbar_init(&mt.drain[0], 1);
     mbar_init(&mt.drain[1], 1);
+    mbar_init(&mt.q0bar, (uint32_t)G);
     mt.abort_flag = 0;
     for (int q = 0; q < kTcQBufs; ++q)
       for (int h = 0; h < 8; ++h) {
@@ -377,10 +388,17 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
   const int run_begin = pv.cta_begin[blockIdx.x], run_end = pv.cta_begin[blockIdx.x + 1];
   const unsigned polls = p.wait_polls;
 
+  if (warp < G && run_begin < run_end) {  // warps 0..G-1 are consumer warps (G <= 8 < WGS * 4)
+    const RunDesc d0 = pv.first[blockIdx.x];
+    tc_prep_query_head<GP>(qbufs, mt.q[0], p, d0.seq, d0.head, G, warp, lane);
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&mt.q0bar);
+  }
+
   if (warp == WGS * 4) {
     // ================================ producer warp ================================
-    int gi = 0, qi = 0;
-    uint32_t qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
+    int gi = 0;
     bool ok = run_begin < run_end;
     const uint64_t stream_policy = l2_evict_first_policy();  // the cache is read once per step
     // L2 prefetch stream: runs kTcPrefetch blocks ahead of the copies, across run boundaries
@@ -415,9 +433,13 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       const uint8_t* arena = arena_ptr(g, p.store, p.layer, d.seq);
       while (c.ci < kNumBuckets) {
         if (limit-- <= 0) return true;
-        prefetch_to(gi + 1 + kTcPrefetch);
+        if (lane == 0) RING_STAMP(gi, 5);
+        if (kTcPrefetch > 0) prefetch_to(gi + 1 + kTcPrefetch);
+        if (lane == 0) RING_STAMP(gi, 6);
         const int slot = gi % NS;
+        if (lane == 0) RING_STAMP(gi, 0);
         if (!tc_wait(&mt.empty[slot], ((gi / NS) & 1) ^ 1u, abort_flag, p.err, polls)) return false;
+        if (lane == 0) RING_STAMP(gi, 1);
         if (lane == 0) {
           const int ci = c.ci, key0 = c.t * kTcKeys;
           const int cnt_ci = tc_sel4(d.cnt, ci);
@@ -426,7 +448,8 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           uint8_t* sb = slots + (size_t)slot * kTcSlotBytes;
           const long long row = (long long)d.head * g.cap[ci] + key0;
           const uint32_t sbytes = (uint32_t)(n16 * 8);
-          fence_proxy_async();
+          // no proxy fence here: whoever touched the slot through the generic proxy fenced before the hand-off chain
+          // (unpack -> score MMA, P -> PV MMA) whose completion freed the slot
           if (ci == 3) {
             mbar_expect_tx(&mt.full[slot], 2 * kTcTile + sbytes);
             tma_load_3d(sb, &kmap, 0, (int)row, p.layer * g.num_seqs + d.seq, &mt.full[slot], stream_policy);
@@ -439,38 +462,42 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
             bulk_g2s_hint(sb + kTcTile, arena + g.v_off[ci] + row * pd, kbytes, &mt.full[slot], stream_policy);
           }
           bulk_g2s_hint(sb + 2 * kTcTile, arena + g.sc_off[ci] + row * 8, sbytes, &mt.full[slot], stream_policy);
+          RING_STAMP(gi, 7);
         }
         ++gi;
         tc_cursor_next(d, c);
       }
       return true;
     };
-    auto publish_query = [&](const RunDesc& d) -> bool {
-      if (!tc_wait(&mt.qempty[qi], qepar, abort_flag, p.err, polls)) return false;
-      tc_prep_query<GP>(qbufs + (size_t)qi * Cfg::QBUF, mt.q[qi], p, d.seq, d.head, G, lane);
-      fence_proxy_async();  // the MMA reads the limb rows through the async proxy
+    for (int r = run_begin; ok && r < run_end; ++r) {
+      const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
+      TcCursor c = tc_cursor_begin(d);
+      ok = issue_blocks(d, c, 1 << 30);
+    }
+  } else if (warp == WGS * 4 + 3) {
+    // ================================ query warp ================================
+    // Publishes the query limbs of every run one run ahead of its use.  The first run's heads were prepared by the
+    // consumer warps, one head each (they have nothing else to do while the first bytes are in flight).
+    int qi = 0;
+    uint32_t qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
+    bool ok = true;
+    for (int r = run_begin; ok && r < run_end; ++r) {
+      ok = tc_wait(&mt.qempty[qi], qepar, abort_flag, p.err, polls);
+      if (!ok) break;
+      if (r == run_begin) {
+        ok = tc_wait(&mt.q0bar, 0, abort_flag, p.err, polls);
+      } else {
+        const RunDesc d = pv.runs[r];
+#pragma unroll 1
+        for (int h = 0; h < G; ++h) tc_prep_query_head<GP>(qbufs + (size_t)qi * Cfg::QBUF, mt.q[qi], p, d.seq, d.head, G, h, lane);
+        fence_proxy_async();  // the MMA reads the limb rows through the async proxy
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&mt.qfull[qi]);
       if (++qi == kTcQBufs) {
         qi = 0;
         qepar ^= 1u;
       }
-      return true;
-    };
-    RunDesc d = pv.first[blockIdx.x];  // meaningful when the CTA has a run
-    for (int r = run_begin; ok && r < run_end; ++r) {
-      TcCursor c = tc_cursor_begin(d);
-      // the first blocks of a run go out first; while they are in flight the query of the NEXT run is
-      // published, so that nobody waits for query rows at a run boundary
-      ok = issue_blocks(d, c, NS);
-      if (r == run_begin) ok = ok && publish_query(d);
-      RunDesc dn = d;
-      if (ok && r + 1 < run_end) {
-        dn = pv.runs[r + 1];
-        ok = publish_query(dn);
-      }
-      ok = ok && issue_blocks(d, c, 1 << 30);
-      d = dn;
     }
   } else if (warp == WGS * 4 + 1) {
     // ================================ score issuer ================================
@@ -806,9 +833,12 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       while (true) {  // timing probe: the bytes land and the slot goes straight back
         const Blk cur = next_mine();
         if (!cur.valid) break;
+        if (wt == 0) RING_STAMP(cur.jj * WGS + wg, 2);
         if (!aborted && !tc_wait(&mt.full[cur.slot], cur.fpar, abort_flag, p.err, polls)) aborted = true;
+        if (wt == 0) RING_STAMP(cur.jj * WGS + wg, 3);
         named_bar_sync(bar, 128);
         if (wt == 0) mbar_arrive(&mt.empty[cur.slot]);
+        if (wt == 0) RING_STAMP(cur.jj * WGS + wg, 4);
       }
 #endif
       while (true) {
