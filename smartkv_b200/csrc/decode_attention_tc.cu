@@ -90,7 +90,7 @@ struct TcCfg {
   static constexpr int QROWS = GP <= 4 ? 8 : 16;           // limb rows of one element order: GP high limbs, GP low limbs
   static constexpr int QSTRIDE = QROWS * 128;              // bytes between two element orders
   static constexpr int QBUF = 4 * QSTRIDE + (16 - QROWS) * 128;  // the MMA reads 16 rows whatever QROWS is
-  static constexpr int THREADS = (WGS * 4 + 4) * 32;       // + producer, score issuer, PV issuer, query warp
+  static constexpr int THREADS = (WGS * 4 + 3) * 32;       // + producer, PV issuer, query warp
   static_assert(WGS * WG_COLS <= TMEM_COLS, "tensor memory budget");
 };
 
@@ -101,9 +101,9 @@ struct TcQMeta {
 
 template <int GP>
 struct TcMeta {
-  uint64_t full[8], uready[8], empty[8];
+  uint64_t full[8], empty[8];
   uint64_t qfull[kTcQBufs], qempty[kTcQBufs];
-  uint64_t sbar[4][2], sdone[4][2], pready[4], obar[4];
+  uint64_t sbar[4][2], ubar[4], pready[4], obar[4];
   uint64_t drain[2];
   uint64_t q0bar;                  // the first run's query heads, prepared by the consumer warps (one arrival per head)
   uint32_t tmem_base;
@@ -243,36 +243,63 @@ __device__ __forceinline__ void tc_unpack3(uint8_t* slot, int wt, int bar) {
 __device__ __forceinline__ int tc_sel4(const int (&a)[kNumBuckets], int i) {
   return i == 0 ? a[0] : i == 1 ? a[1] : i == 2 ? a[2] : a[3];
 }
-struct TcCursor {
-  int ci, t, t_end;  // bucket, next 128-key tile, end of this bucket's tiles
+// The blocks of a run come in an order that interleaves the 8-bit bucket with the narrow ones in proportion to
+// their block counts: 8-bit blocks cost the warpgroups little and the memory system a lot, narrow blocks the other
+// way round, so mixing them keeps both busy all the time.  Block i of a run is an 8-bit block iff
+// floor((i+1) * n8 / total) > floor(i * n8 / total); inside the narrow stream the buckets follow one another
+// (2-, 3-, 4-bit).  A closed form, so that every role finds block i by itself with one integer division.
+struct TcRun {
+  int n0, n01, n8, total;   // narrow blocks of bucket 0, of buckets 0+1; 8-bit blocks; all blocks
+  int ka0, ka1, ka2, ka3;   // first 128-key tile of every bucket in this run
+  int c0, c1, c2, c3;       // live keys per bucket of the sequence
 };
-__device__ __forceinline__ void tc_cursor_skip(const RunDesc& d, TcCursor& c) {
-  while (c.ci < kNumBuckets && c.t >= c.t_end) {
-    ++c.ci;
-    if (c.ci < kNumBuckets) {
-      c.t = tc_sel4(d.ka, c.ci);
-      c.t_end = tc_sel4(d.kb, c.ci);
-    }
+__device__ __forceinline__ TcRun tc_run(const RunDesc& d) {
+  TcRun r;
+  r.n0 = d.kb[0] - d.ka[0];
+  r.n01 = r.n0 + (d.kb[1] - d.ka[1]);
+  r.n8 = d.kb[3] - d.ka[3];
+  r.total = r.n01 + (d.kb[2] - d.ka[2]) + r.n8;
+  r.ka0 = d.ka[0]; r.ka1 = d.ka[1]; r.ka2 = d.ka[2]; r.ka3 = d.ka[3];
+  r.c0 = d.cnt[0]; r.c1 = d.cnt[1]; r.c2 = d.cnt[2]; r.c3 = d.cnt[3];
+  return r;
+}
+// block i of the run -> bucket, first key, number of keys
+__device__ __forceinline__ void tc_block(const TcRun& r, int i, int& ci, int& key0, int& nkeys) {
+  const unsigned prod = (unsigned)i * (unsigned)r.n8;
+  const unsigned q = prod / (unsigned)r.total;          // 8-bit blocks before block i
+  const unsigned rem = prod - q * (unsigned)r.total;
+  int t, cnt;
+  if (rem + (unsigned)r.n8 >= (unsigned)r.total) {
+    ci = 3; t = r.ka3 + (int)q; cnt = r.c3;
+  } else {
+    const int n = i - (int)q;
+    if (n < r.n0) { ci = 0; t = r.ka0 + n; cnt = r.c0; }
+    else if (n < r.n01) { ci = 1; t = r.ka1 + (n - r.n0); cnt = r.c1; }
+    else { ci = 2; t = r.ka2 + (n - r.n01); cnt = r.c2; }
   }
-}
-__device__ __forceinline__ TcCursor tc_cursor_begin(const RunDesc& d) {
-  TcCursor c{0, d.ka[0], d.kb[0]};
-  tc_cursor_skip(d, c);
-  return c;
-}
-__device__ __forceinline__ void tc_cursor_next(const RunDesc& d, TcCursor& c) {
-  ++c.t;
-  tc_cursor_skip(d, c);
+  key0 = t * kTcKeys;
+  nkeys = (cnt - key0) < kTcKeys ? (cnt - key0) : kTcKeys;
 }
 
-// Bounded wait of the tensor-memory kernel: the thread is suspended inside mbarrier.try_wait (a loop of test_wait
-// polls by the sixteen consumer warps measured slower: it crowds the issue slots and the barrier words); the number
-// of resumptions is limited, so the wait always ends.
+// Bounded waits of the tensor-memory kernel.  tc_wait: the thread is suspended inside mbarrier.try_wait (a loop of
+// test_wait polls by the sixteen consumer warps measured slower: it crowds the issue slots and the barrier words); the
+// number of resumptions is limited, so the wait always ends.  tc_spin: back-to-back polls, for the single-thread roles
+// whose reaction time every block waits for.
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, unsigned polls) {
   const unsigned limit = (polls >> 4) + 16;  // a suspended try_wait lasts far longer than a 50 ns poll
   for (unsigned i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(err, 1);
+  return false;
+}
+
+__device__ __forceinline__ bool tc_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, unsigned polls) {
+  for (unsigned i = 0; i < polls; ++i) {  // a poll is a few tens of cycles: at least as long as `polls` sleeping polls
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicExch(err, 1);
@@ -351,7 +378,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&mt.full[s], 1);
-      mbar_init(&mt.uready[s], 4);  // one arrival per warp of the unpacking warpgroup
       mbar_init(&mt.empty[s], 1);
     }
     for (int s = 0; s < kTcQBufs; ++s) {
@@ -361,12 +387,10 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     for (int w = 0; w < WGS; ++w) {
       mbar_init(&mt.sbar[w][0], 1);
       mbar_init(&mt.sbar[w][1], 1);
-      mbar_init(&mt.sdone[w][0], 4);
-      mbar_init(&mt.sdone[w][1], 4);
-      mbar_init(&mt.pready[w], 4);
+      mbar_init(&mt.ubar[w], 4);    // one arrival per warp: the warpgroup's narrow tile is unpacked
+      mbar_init(&mt.pready[w], 4);  // one arrival per warp: the warpgroup's P rows are written
       mbar_init(&mt.obar[w], 1);
     }
-    mbar_init(&mt.drain[0], 1);
     mbar_init(&mt.drain[1], 1);
     mbar_init(&mt.q0bar, (uint32_t)G);
     mt.abort_flag = 0;
@@ -401,49 +425,19 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     int gi = 0;
     bool ok = run_begin < run_end;
     const uint64_t stream_policy = l2_evict_first_policy();  // the cache is read once per step
-    // L2 prefetch stream: runs kTcPrefetch blocks ahead of the copies, across run boundaries
-    int pf_run = run_begin, pf_count = 0;
-    RunDesc pf_d = pv.first[blockIdx.x];
-    TcCursor pf_c = ok ? tc_cursor_begin(pf_d) : TcCursor{kNumBuckets, 0, 0};
-    auto prefetch_to = [&](int upto) {
-      while (pf_count < upto) {
-        if (pf_c.ci >= kNumBuckets) {
-          if (pf_run + 1 >= run_end) return;
-          ++pf_run;
-          pf_d = pv.runs[pf_run];
-          pf_c = tc_cursor_begin(pf_d);
-          continue;
-        }
-        if (lane == 0) {
-          const int ci = pf_c.ci, key0 = pf_c.t * kTcKeys;
-          const int nkeys = (tc_sel4(pf_d.cnt, ci) - key0) < kTcKeys ? (tc_sel4(pf_d.cnt, ci) - key0) : kTcKeys;
-          const int n16 = (nkeys + 15) & ~15, pd = g.row_bytes[ci];
-          const uint8_t* arena = arena_ptr(g, p.store, p.layer, pf_d.seq);
-          const long long row = (long long)pf_d.head * g.cap[ci] + key0;
-          bulk_prefetch_l2(arena + g.k_off[ci] + row * pd, (uint32_t)(n16 * pd));
-          bulk_prefetch_l2(arena + g.v_off[ci] + row * pd, (uint32_t)(n16 * pd));
-          bulk_prefetch_l2(arena + g.sc_off[ci] + row * 8, (uint32_t)(n16 * 8));
-        }
-        ++pf_count;
-        tc_cursor_next(pf_d, pf_c);
-      }
-    };
-    // issues up to `limit` further blocks of run d, resuming at cursor c
-    auto issue_blocks = [&](const RunDesc& d, TcCursor& c, int limit) -> bool {
+    for (int r = run_begin; ok && r < run_end; ++r) {
+      const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
+      const TcRun run = tc_run(d);
       const uint8_t* arena = arena_ptr(g, p.store, p.layer, d.seq);
-      while (c.ci < kNumBuckets) {
-        if (limit-- <= 0) return true;
-        if (lane == 0) RING_STAMP(gi, 5);
-        if (kTcPrefetch > 0) prefetch_to(gi + 1 + kTcPrefetch);
-        if (lane == 0) RING_STAMP(gi, 6);
+      for (int i = 0; ok && i < run.total; ++i, ++gi) {
         const int slot = gi % NS;
         if (lane == 0) RING_STAMP(gi, 0);
-        if (!tc_wait(&mt.empty[slot], ((gi / NS) & 1) ^ 1u, abort_flag, p.err, polls)) return false;
+        ok = tc_wait(&mt.empty[slot], ((gi / NS) & 1) ^ 1u, abort_flag, p.err, polls);
+        if (!ok) break;
         if (lane == 0) RING_STAMP(gi, 1);
         if (lane == 0) {
-          const int ci = c.ci, key0 = c.t * kTcKeys;
-          const int cnt_ci = tc_sel4(d.cnt, ci);
-          const int nkeys = (cnt_ci - key0) < kTcKeys ? (cnt_ci - key0) : kTcKeys;
+          int ci, key0, nkeys;
+          tc_block(run, i, ci, key0, nkeys);
           const int n16 = (nkeys + 15) & ~15;
           uint8_t* sb = slots + (size_t)slot * kTcSlotBytes;
           const long long row = (long long)d.head * g.cap[ci] + key0;
@@ -464,17 +458,9 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           bulk_g2s_hint(sb + 2 * kTcTile, arena + g.sc_off[ci] + row * 8, sbytes, &mt.full[slot], stream_policy);
           RING_STAMP(gi, 7);
         }
-        ++gi;
-        tc_cursor_next(d, c);
       }
-      return true;
-    };
-    for (int r = run_begin; ok && r < run_end; ++r) {
-      const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
-      TcCursor c = tc_cursor_begin(d);
-      ok = issue_blocks(d, c, 1 << 30);
     }
-  } else if (warp == WGS * 4 + 3) {
+  } else if (warp == WGS * 4 + 2) {
     // ================================ query warp ================================
     // Publishes the query limbs of every run one run ahead of its use.  The first run's heads were prepared by the
     // consumer warps, one head each (they have nothing else to do while the first bytes are in flight).
@@ -500,50 +486,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       }
     }
   } else if (warp == WGS * 4 + 1) {
-    // ================================ score issuer ================================
-    // K.Q of block i as soon as its tile is ready and the S buffer it writes has been read
-#ifdef SKV_TC_STREAM_ONLY
-    if (false) {
-#else
-    if (lane == 0) {
-#endif
-      int i = 0, qi = 0;
-      uint32_t qfpar = 0, umask = 0;
-      bool ok = true;
-      for (int r = run_begin; ok && r < run_end; ++r) {
-        const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
-        ok = tc_wait(&mt.qfull[qi], qfpar, abort_flag, p.err, polls);
-        const uint32_t qa0 = smem_u32(qbufs + (size_t)qi * Cfg::QBUF);
-        for (TcCursor c = tc_cursor_begin(d); ok && c.ci < kNumBuckets; tc_cursor_next(d, c), ++i) {
-          const int w = i % WGS, j = i / WGS, slot = i % NS, sbuf = j & 1;
-          ok = tc_wait(&mt.sdone[w][sbuf], ((j >> 1) & 1) ^ 1u, abort_flag, p.err, polls);
-          if (!ok) break;
-          if (c.ci == 3) {
-            ok = tc_wait(&mt.full[slot], (i / NS) & 1, abort_flag, p.err, polls);
-          } else {
-            ok = tc_wait(&mt.uready[slot], (umask >> slot) & 1u, abort_flag, p.err, polls);
-            umask ^= 1u << slot;
-          }
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t idesc = idesc_i8(tc_k_signed(c.ci), 1, 0, 0, 128, Cfg::SCOLS);
-          const uint32_t ka = smem_u32(slots + (size_t)slot * kTcSlotBytes), qa = qa0 + c.ci * Cfg::QSTRIDE;
-          const uint32_t dcol = tmem_base + (uint32_t)(w * Cfg::WG_COLS + sbuf * Cfg::SCOLS);
-#pragma unroll
-          for (int s = 0; s < 4; ++s)
-            mma_i8_ss(dcol, smem_desc(ka + 32 * s, 1, 64, 2), smem_desc(qa + 32 * s, 1, 64, 2), idesc, s > 0);
-          mma_commit(&mt.sbar[w][sbuf]);
-        }
-        if (++qi == kTcQBufs) {
-          qi = 0;
-          qfpar ^= 1u;
-        }
-      }
-      mma_commit(&mt.drain[0]);
-      tc_wait(&mt.drain[0], 0, abort_flag, p.err, polls);
-    }
-    __syncwarp();
-  } else if (warp == WGS * 4 + 2) {
     // ================================ PV issuer ================================
 #ifdef SKV_TC_STREAM_ONLY
     if (false) {
@@ -555,7 +497,8 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       const uint32_t idesc = idesc_i8(1, 0, 1, 1, 128, PN);
       for (int r = run_begin; ok && r < run_end; ++r) {
         const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
-        for (TcCursor c = tc_cursor_begin(d); ok && c.ci < kNumBuckets; tc_cursor_next(d, c), ++i) {
+        const int nblocks = tc_run(d).total;
+        for (int bi = 0; ok && bi < nblocks; ++bi, ++i) {
           const int w = i % WGS, j = i / WGS, slot = i % NS;
           ok = tc_wait(&mt.pready[w], j & 1, abort_flag, p.err, polls);
           if (!ok) break;
@@ -580,7 +523,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     const uint32_t tm_wg = tmem_base + (uint32_t)(wg * Cfg::WG_COLS) + ((uint32_t)(wq * 32) << 16);
     uint8_t* pbuf = pbufs + (size_t)wg * Cfg::PBYTES;
     int gi = 0, qi = 0;
-    uint32_t qfpar = 0;
+    uint32_t qfpar = 0, unpacked = 0;  // unpacked: narrow blocks of this warpgroup so far (phase of its unpack barrier)
     bool aborted = false;
 
     struct Blk {
@@ -609,43 +552,59 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       float* lbase = nullptr;  // logits row of head 0 of this group
       if (p.logits != nullptr) lbase = p.logits + ((long long)b * p.num_q_heads + hkv * G) * g.slots;
 
-      TcCursor cur_c = tc_cursor_begin(d);
+      const TcRun run = tc_run(d);
+      const int gi_run = gi;                                   // global index of the run's first block
+      int bi = (wg - gi_run % WGS + WGS) % WGS;                // this warpgroup's first block of the run
       auto next_mine = [&]() -> Blk {
         Blk k{};
-        k.valid = false;
-        while (cur_c.ci < kNumBuckets) {
-          const bool take = (gi % WGS) == wg;
-          if (take) {
-            k.ci = cur_c.ci;
-            k.key0 = cur_c.t * kTcKeys;
-            const int cnt_ci = tc_sel4(d.cnt, k.ci);
-            k.nkeys = (cnt_ci - k.key0) < kTcKeys ? (cnt_ci - k.key0) : kTcKeys;
-            k.slot = gi % NS;
-            k.fpar = (gi / NS) & 1;
-            k.jj = gi / WGS;
-            k.valid = true;
-          }
-          ++gi;
-          tc_cursor_next(d, cur_c);
-          if (take) break;
+        k.valid = bi < run.total;
+        if (k.valid) {
+          tc_block(run, bi, k.ci, k.key0, k.nkeys);
+          const int gb = gi_run + bi;
+          k.slot = gb % NS;
+          k.fpar = (gb / NS) & 1;
+          k.jj = gb / WGS;
+          bi += WGS;
         }
         return k;
       };
 
       // ---- unpack: narrow rows spread to bytes, tile handed to the score issuer ----
       auto phase_u = [&](const Blk& k) {
-        if (k.ci == 3) return;  // 8-bit rows are MMA operands as they land
         uint8_t* sb = slots + (size_t)k.slot * kTcSlotBytes;
-        TCP(k, 0);
-        if (!aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
-        TCP(k, 1);
-        if (k.ci == 0) tc_unpack2(sb, wt, bar);
-        else if (k.ci == 1) tc_unpack3(sb, wt, bar);
-        else tc_unpack4(sb, wt, bar);
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&mt.uready[k.slot]);
-        TCP(k, 2);
+        if (k.ci != 3) {  // 8-bit rows are MMA operands as they land
+          TCP(k, 0);
+          if (!aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
+          TCP(k, 1);
+          if (k.ci == 0) tc_unpack2(sb, wt, bar);
+          else if (k.ci == 1) tc_unpack3(sb, wt, bar);
+          else tc_unpack4(sb, wt, bar);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&mt.ubar[wg]);
+          TCP(k, 2);
+        }
+        // The warpgroup's first thread issues the score MMA of its own block (an issuer shared by the warpgroups
+        // would have to take the blocks in order, and a block whose tile is ready would wait behind one whose unpack
+        // is not); the other warps go on to the previous block's epilogue meanwhile.
+        if (wt == 0) {
+          if (k.ci == 3) {
+            if (!aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
+          } else {
+            if (!aborted && !tc_wait(&mt.ubar[wg], unpacked & 1u, abort_flag, p.err, polls)) aborted = true;
+          }
+          tc_fence_after();
+          const int sbuf = k.jj & 1;
+          const uint32_t idesc = idesc_i8(tc_k_signed(k.ci), 1, 0, 0, 128, Cfg::SCOLS);
+          const uint32_t ka = smem_u32(sb), qa = smem_u32(qbufs + (size_t)qi * Cfg::QBUF) + k.ci * Cfg::QSTRIDE;
+          const uint32_t dcol = tmem_base + (uint32_t)(wg * Cfg::WG_COLS + sbuf * Cfg::SCOLS);
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4)
+            mma_i8_ss(dcol, smem_desc(ka + 32 * s4, 1, 64, 2), smem_desc(qa + 32 * s4, 1, 64, 2), idesc, s4 > 0);
+          mma_commit(&mt.sbar[wg][sbuf]);
+        }
+        if (k.ci != 3) ++unpacked;
+        TCP(k, 3);
       };
 
       // what the epilogue needs from the softmax of the same block
@@ -678,9 +637,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
 #pragma unroll
           for (int i = 0; i < 16; ++i) s[i] = t16[i];
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&mt.sdone[wg][sbuf]);  // the score issuer may overwrite this S buffer
+        tc_fence_before();  // the warpgroup's next score MMA into this buffer comes after a barrier all threads pass
         TCP(k, 6);
         if (k.ci == 3 && !aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
         const float2 sc = *reinterpret_cast<const float2*>(sb + 2 * kTcTile + wt * 8);
@@ -896,6 +853,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
             if (h < G) out[h * 130 + 2 + wt] = accum[h];
         }
       }
+      gi += run.total;
       if (++qi == kTcQBufs) {
         qi = 0;
         qfpar ^= 1u;
