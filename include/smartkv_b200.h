@@ -354,23 +354,7 @@ int skv_repack_meta(const SkvStoreDesc* desc, const int32_t* move_src, const int
                     double* cumulative, double* rank_pct, int8_t* rank_streak, float* layer_ema, uint8_t* touched,
                     void* staging, int64_t staging_bytes, int32_t* err_flag, void* stream);
 
-/* ---- debug / test hooks ---------------------------------------------------- */
-
-/* Raw tensor-core tile products through the same fragment code as the attention
- * kernel, for one 16-key tile of packed rows (row_bytes apart):
- *   scores[8][16] = (Q[0..7] + Q[8..15]) . Kcodes^T      Q fp16 [16][head_dim]
- *   out[8][head_dim] = (P[0..7] + P[8..15]) . Vcodes      P fp16 [16][16] ([row][key])
- * Rows 0..7 are the query heads of a group, rows 8..15 the residual rows the
- * precise (fp32-query) mode adds. */
-int skv_debug_tile_products(int head_dim, int bits, const uint8_t* k_rows, const uint8_t* v_rows,
-                            const void* q_half, const void* p_half, float* scores, float* out, void* stream);
-
-/* Integer scores of one 16-key tile through the int8 tensor-core path the attention kernel
- * uses for 2-, 4- and 8-bit rows and, at head_dim 128, for 3-bit rows: scores int32 [8][16] =
- * sum_d q[h][d] * u[key][d], q int8 [8][head_dim], u = the stored code (offset-binary below 8 bits,
- * two's complement for 8-bit). */
-int skv_debug_tile_scores_i8(int head_dim, int bits, const uint8_t* k_rows, const int8_t* q_int8, int32_t* scores,
-                             void* stream);
+/* ---- error flag ---------------------------------------------------------- */
 
 /* Reads and clears a device error flag (synchronises the stream). */
 int skv_read_error_flag(int32_t* err_flag, int32_t* host_value, void* stream);

@@ -106,9 +106,6 @@ _SIGNATURES = {
     "skv_importance_update": (c_int, [POINTER(StoreDesc), c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
                                       c_float, c_void_p]),
-    "skv_debug_tile_products": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                        c_void_p]),
-    "skv_debug_tile_scores_i8": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_read_error_flag": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
 }
 
