@@ -209,6 +209,14 @@ int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* quer
                     int num_q_heads, const void* partials, int num_ctas, const void* cur_k, const void* cur_v,
                     int kv_dtype, float* out, float* lse_max, float* lse_sum, float* cur_prob, void* stream);
 
+/* skv_lse_combine with the additive mask value of the current token: cur_mask fp32 [num_seqs],
+ * natural-log units, NULL = none (the counterpart of the last column of the reference's mask,
+ * smartkv/core/fused_cpu.py:121-126). */
+int skv_lse_combine_masked(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
+                           int num_q_heads, const void* partials, int num_ctas, const void* cur_k, const void* cur_v,
+                           int kv_dtype, const float* cur_mask, float* out, float* lse_max, float* lse_sum,
+                           float* cur_prob, void* stream);
+
 /* ---- attention without a caller-owned scratch buffer --------------------------- */
 
 /* No counterpart in the reference.  Same launch as skv_decode_attention, but the partials go

@@ -90,6 +90,8 @@ _SIGNATURES = {
                                             c_int, c_void_p, c_void_p, POINTER(c_void_p), c_void_p]),
     "skv_lse_combine": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "skv_lse_combine_masked": (c_int, [POINTER(StoreDesc), c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                       c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "skv_alloc_workspace_bytes": (c_int64, [POINTER(StoreDesc)]),
     "skv_alloc_bits": (c_int, [POINTER(StoreDesc), POINTER(AllocConfig), c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -195,7 +195,8 @@ __device__ __forceinline__ void load_qfrags(const QSlot<D, PRECISE>& q, int lane
 template <int D, int BITS, bool PRECISE, bool WRITE_LOGITS>
 __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t* vtile, const float4* sc, int nvalid,
                                              int lane, const QFrags<D, BITS, PRECISE>& qf, LaneState& st,
-                                             float (&o)[D / 16][4], float scale_log2, float* lrow) {
+                                             float (&o)[D / 16][4], float scale_log2, float* lrow,
+                                             const int32_t* tok, const float* mrow) {
   const int g = lane >> 2, t = lane & 3;
   // ---- every shared-memory load of the tile up front ---------------------------------
   uint32_t kr0[SliceWords<D, BITS>::K], kr1[SliceWords<D, BITS>::K];
@@ -240,6 +241,16 @@ __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t
     x3 = (c1[1] + c1[3]) * (scB.z * scale_log2);
   }
   float vs0 = scA.y, vs1 = scA.w, vs2 = scB.y, vs3 = scB.w;
+  if (tok != nullptr) {
+    // additive mask, indexed by the key's token id as the reference indexes it by the key's global slot
+    // (smartkv/csrc/quantized_attention.cu:570-575); natural-log units -> log2 units
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int k0 = 2 * t, k2 = 2 * t + 8;
+    if (k0 < nvalid) { const int id = tok[k0]; if (id >= 0) x0 = fmaf(mrow[id], kLog2e, x0); }
+    if (k0 + 1 < nvalid) { const int id = tok[k0 + 1]; if (id >= 0) x1 = fmaf(mrow[id], kLog2e, x1); }
+    if (k2 < nvalid) { const int id = tok[k2]; if (id >= 0) x2 = fmaf(mrow[id], kLog2e, x2); }
+    if (k2 + 1 < nvalid) { const int id = tok[k2 + 1]; if (id >= 0) x3 = fmaf(mrow[id], kLog2e, x3); }
+  }
   if (nvalid < 16) {  // last tile of a bucket: rows past its end may hold anything, scales included
     if (2 * t >= nvalid) { x0 = -INFINITY; vs0 = 0.f; }
     if (2 * t + 1 >= nvalid) { x1 = -INFINITY; vs1 = 0.f; }
@@ -295,7 +306,7 @@ template <int D, int BITS, bool PRECISE, int KBKEYS, int NCONS>
 __device__ __forceinline__ void process_block(const uint8_t* sb, int nkeys, int first, int lane,
                                               const QFrags<D, BITS, PRECISE>& qf, LaneState& st,
                                               float (&o)[D / 16][4], float scale_log2, bool write_logits,
-                                              float* lrow) {
+                                              float* lrow, const int32_t* tok, const float* mrow) {
   constexpr int PD = D * BITS / 8;
   const uint8_t* kbase = sb;
   const uint8_t* vbase = sb + KBKEYS * PD;
@@ -305,11 +316,12 @@ __device__ __forceinline__ void process_block(const uint8_t* sb, int nkeys, int 
     for (int tile = first; tile < ntl; tile += NCONS)
       process_tile<D, BITS, PRECISE, true>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 8,
                                            nkeys - tile * 16, lane, qf, st, o, scale_log2,
-                                           lrow ? lrow + tile * 16 : nullptr);
+                                           lrow ? lrow + tile * 16 : nullptr, tok ? tok + tile * 16 : nullptr, mrow);
   } else {
     for (int tile = first; tile < ntl; tile += NCONS)
       process_tile<D, BITS, PRECISE, false>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 8,
-                                            nkeys - tile * 16, lane, qf, st, o, scale_log2, nullptr);
+                                            nkeys - tile * 16, lane, qf, st, o, scale_log2, nullptr,
+                                            tok ? tok + tile * 16 : nullptr, mrow);
   }
 }
 
@@ -563,8 +575,10 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
         if (first < 0) first += NCONS;
         if (!aborted && first < ntl) {
           float* lrow = lbase != nullptr ? lbase + g.bucket_base[bucket] + key0 : nullptr;
+          const int32_t* tok = p.mask != nullptr ? p.slot_token + (long long)b * g.slots + g.bucket_base[bucket] + key0 : nullptr;
           process_block<D, BITS, PRECISE, KBT * 16, NCONS>(stages + (long long)stg * STAGE_BYTES, nkeys, first, lane,
-                                                           qf, st, o, p.scale_log2, write_logits, lrow);
+                                                           qf, st, o, p.scale_log2, write_logits, lrow, tok,
+                                                           p.mask != nullptr ? p.mask + (long long)b * p.mask_stride : nullptr);
         }
         tile_base = (tile_base + ntl) % NCONS;
         __syncwarp();
@@ -764,10 +778,10 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
                                      logits, nullptr, 0, nullptr, err_flag, stream);
 }
 
-extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
-                               int num_q_heads, const void* partials, int num_ctas, const void* cur_k,
-                               const void* cur_v, int kv_dtype, float* out, float* lse_max, float* lse_sum,
-                               float* cur_prob, void* stream) {
+extern "C" int skv_lse_combine_masked(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
+                                      int num_q_heads, const void* partials, int num_ctas, const void* cur_k,
+                                      const void* cur_v, int kv_dtype, const float* cur_mask, float* out, float* lse_max,
+                                      float* lse_sum, float* cur_prob, void* stream) {
   if (!desc || !plan || !query || !partials || !out) return SKV_ERR_INVALID;
   if (num_q_heads % desc->num_kv_heads != 0 || num_ctas <= 0) return SKV_ERR_INVALID;
   const int group = num_q_heads / desc->num_kv_heads;
@@ -786,6 +800,7 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const
   p.cur_k = cur_k;
   p.cur_v = cur_v;
   p.kv_is_half = kv_dtype == SKV_DTYPE_F16;
+  p.cur_mask = cur_mask;
   p.out = out;
   p.lse_max = lse_max;
   p.lse_sum = lse_sum;
@@ -794,6 +809,14 @@ extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const
   p.per_run = skv_attn_partials_per_run(desc, query_dtype);
   lse_combine_kernel<<<combine_units(p.g, group), kPostThreads, 0, as_stream(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+extern "C" int skv_lse_combine(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,
+                               int num_q_heads, const void* partials, int num_ctas, const void* cur_k,
+                               const void* cur_v, int kv_dtype, float* out, float* lse_max, float* lse_sum,
+                               float* cur_prob, void* stream) {
+  return skv_lse_combine_masked(desc, plan, query, query_dtype, num_q_heads, partials, num_ctas, cur_k, cur_v, kv_dtype,
+                                nullptr, out, lse_max, lse_sum, cur_prob, stream);
 }
 
 // ---- attention with the partials in a fixed device array ------------------------------

@@ -499,7 +499,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         const RunDesc d = r == run_begin ? pv.first[blockIdx.x] : pv.runs[r];
         const int nblocks = tc_run(d).total;
         for (int bi = 0; ok && bi < nblocks; ++bi, ++i) {
-          const int j = i / WGS, w = (i + j) % WGS, slot = i % NS;
+          const int w = i % WGS, j = i / WGS, slot = i % NS;
           ok = tc_wait(&mt.pready[w], j & 1, abort_flag, p.err, polls);
           if (!ok) break;
           tc_fence_after();
@@ -554,24 +554,17 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
 
       const TcRun run = tc_run(d);
       const int gi_run = gi;                                   // global index of the run's first block
-      // Blocks go to the warpgroups in groups of WGS consecutive blocks, one each, the order inside a group rotating
-      // from group to group: with a plain round-robin, narrow and 8-bit blocks alternating would leave half of the
-      // warpgroups with nothing but narrow blocks.  Block gb belongs to warpgroup (gb + gb / WGS) % WGS.
-      int grp = gi_run / WGS;
+      int bi = (wg - gi_run % WGS + WGS) % WGS;                // this warpgroup's first block of the run
       auto next_mine = [&]() -> Blk {
         Blk k{};
-        k.valid = false;
-        while (true) {
-          const int gb = grp * WGS + ((wg - grp) % WGS + WGS) % WGS;
-          if (gb >= gi_run + run.total) break;   // this group's block of the warpgroup lies in a later run (or nowhere)
-          ++grp;
-          if (gb < gi_run) continue;             // ... or lay in the run before
-          tc_block(run, gb - gi_run, k.ci, k.key0, k.nkeys);
+        k.valid = bi < run.total;
+        if (k.valid) {
+          tc_block(run, bi, k.ci, k.key0, k.nkeys);
+          const int gb = gi_run + bi;
           k.slot = gb % NS;
           k.fpar = (gb / NS) & 1;
           k.jj = gb / WGS;
-          k.valid = true;
-          break;
+          bi += WGS;
         }
         return k;
       };

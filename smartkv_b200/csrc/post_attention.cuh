@@ -41,6 +41,7 @@ struct CombineParams {
   const void* cur_k;
   const void* cur_v;
   int kv_is_half;
+  const float* cur_mask;  // additive mask of the current token per sequence, natural-log units (may be null)
   float* out;
   float* lse_max;
   float* lse_sum;
@@ -118,7 +119,8 @@ __device__ __forceinline__ void combine_unit(const CombineParams& p, int unit, C
   } else {
     for (int k = d; k < nsplit; k += D) mloc = fmaxf(mloc, base[(long long)k * pstride]);
   }
-  const float s_cur = head_dot(prod, sub, d, D, sh.red, 0) * p.scale_log2;
+  float s_cur = head_dot(prod, sub, d, D, sh.red, 0) * p.scale_log2;
+  if (has_cur && p.cur_mask != nullptr) s_cur = fmaf(p.cur_mask[b], 1.4426950408889634f, s_cur);
   {
     const float m = warp_max(mloc);
     const int wph = D >> 5;

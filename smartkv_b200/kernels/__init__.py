@@ -5,8 +5,8 @@ Same names, argument layouts and error messages as the reference; the work is do
 decode-attention kernels of ``libsmartkv_b200.so`` (the int8 codes the caller hands over are packed
 into a scratch store first).  Differences, all deliberate:
   * there is no PyTorch fallback: a CPU tensor or a missing library is an error;
-  * additive attention masks other than all-zero are not supported by the decode kernels
-    (decode without padding needs none) and raise NotImplementedError;
+  * an additive attention mask is one row per (sequence, query position), shared by the heads
+    ([B, 1, q, k], as the reference's kernels index it); a mask that differs between heads raises;
   * ``quantized_attention_bucketed`` accepts batch 1 only, like the reference (:278).
 """
 from __future__ import annotations
@@ -62,12 +62,27 @@ def _ensure_scale_layout(scale: torch.Tensor, num_heads: int, k_len: int, name: 
     raise ValueError(f"{name} must broadcast to [B, H, k_len]; got shape {scale.shape}")
 
 
-def _check_mask(attention_mask: Optional[torch.Tensor]):
+def _mask_rows(attention_mask: Optional[torch.Tensor], batch: int, q_len: int, k_len: int) -> Optional[torch.Tensor]:
+    """The reference's additive mask [B, 1, q, k] (smartkv/csrc/quantized_attention.cu:213-216, 570-575) as
+    fp32 [B, q, k]; None stays None."""
     if attention_mask is None:
-        return
-    if bool((attention_mask != 0).any()):
-        raise NotImplementedError("the B200 decode kernels take no additive attention mask; pass None "
-                                  "(decode without padding needs none)")
+        return None
+    m = attention_mask
+    if m.dim() == 4:
+        if m.size(1) != 1:
+            if bool((m != m[:, :1]).any()):
+                raise NotImplementedError("per-head attention masks are not supported: the kernels take one mask row "
+                                          "per sequence and query position, like the reference's")
+            m = m[:, :1]
+        m = m[:, 0]
+    if m.dim() == 2:
+        m = m[:, None, :]
+    if m.dim() != 3:
+        raise ValueError(f"attention_mask must be [B, 1, q_len, k_len]; got shape {tuple(attention_mask.shape)}")
+    m = m.to(torch.float32).expand(batch, q_len, m.size(-1))
+    if m.size(-1) < k_len:
+        raise ValueError(f"attention_mask covers {m.size(-1)} keys, the cache holds {k_len}")
+    return m.contiguous()
 
 
 def _need_cuda(t: torch.Tensor, what: str):
@@ -75,8 +90,9 @@ def _need_cuda(t: torch.Tensor, what: str):
         raise _lib.SmartKVLibraryError(f"{what}: tensor is on {t.device}; the B200 library has no CPU path")
 
 
-def _attend(query: torch.Tensor, per_seq_rows) -> torch.Tensor:
-    """query [B, H, q, D]; per_seq_rows[b] = list of (bits, k_codes [n, H, D] int8, v_codes, k_scale [n, H], v_scale).
+def _attend(query: torch.Tensor, per_seq_rows, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """query [B, H, q, D]; per_seq_rows[b] = list of (bits, k_codes [n, H, D] int8, v_codes, k_scale [n, H], v_scale,
+    key positions int [n] or None = 0..n-1).  mask fp32 [B, q, k] or None, indexed by key position.
     Packs the rows into a scratch store (every query head its own KV head) and runs the decode kernels
     once per query position."""
     B, H, q_len, D = query.shape
@@ -86,7 +102,7 @@ def _attend(query: torch.Tensor, per_seq_rows) -> torch.Tensor:
     need = [128, 128, 128, 128]
     for rows in per_seq_rows:
         tot = {2: 0, 3: 0, 4: 0, 8: 0}
-        for bits, kq, *_ in rows:
+        for bits, kq, *_rest in rows:
             tot[bits] += kq.shape[0]
         for i, w in enumerate(_lib.BUCKET_BITS):
             need[i] = max(need[i], round_up(tot[w] + 1, 128))
@@ -95,12 +111,18 @@ def _attend(query: torch.Tensor, per_seq_rows) -> torch.Tensor:
     store = PackedKVStore(1, B, H, D, H, tuple(need), device=dev, track_importance=False)
     st = store._stream()
     for b, rows in enumerate(per_seq_rows):
-        for bits, kq, vq, ks, vs in rows:
+        seen = 0
+        for bits, kq, vq, ks, vs, positions in rows:
             n = kq.shape[0]
             if n == 0:
                 continue
             bucket = _lib.BITS_TO_BUCKET[bits]
             base = int(store.counts[b, bucket])
+            if positions is None:
+                positions = torch.arange(seen, seen + n, dtype=torch.int32, device=dev)
+            seen += n
+            store.slot_token[b, store.bucket_base[bucket] + base: store.bucket_base[bucket] + base + n] = \
+                positions.to(device=dev, dtype=torch.int32)
             seq = torch.full((n,), b, dtype=torch.int32, device=dev)
             bk = torch.full((n,), bucket, dtype=torch.int32, device=dev)
             pos = torch.arange(base, base + n, dtype=torch.int32, device=dev)
@@ -112,7 +134,7 @@ def _attend(query: torch.Tensor, per_seq_rows) -> torch.Tensor:
     store._plan_valid = False
     qf = query.float() if query.dtype not in (torch.float32, torch.float16) else query
     for i in range(q_len):
-        out[:, :, i] = store.attention(0, qf[:, :, i].contiguous())
+        out[:, :, i] = store.attention(0, qf[:, :, i].contiguous(), mask=None if mask is None else mask[:, i])
     store.check_errors()
     return out.to(query.dtype) if query.dtype in (torch.float16, torch.bfloat16) else out
 
@@ -131,15 +153,15 @@ def quantized_attention(query: torch.Tensor, key_int8: torch.Tensor, key_scale: 
     k_len = key_int8.shape[2]
     key_scale = _ensure_scale_layout(key_scale, num_heads, k_len, "key_scale")
     value_scale = _ensure_scale_layout(value_scale, num_heads, k_len, "value_scale")
-    _check_mask(attention_mask)
+    mask = _mask_rows(attention_mask, batch, q_len, k_len)
     if k_len == 0:
         return torch.zeros_like(query)
     rows = []
     for b in range(batch):
         rows.append([(8, key_int8[b].permute(1, 0, 2).contiguous().to(torch.int8),
                       value_int8[b].permute(1, 0, 2).contiguous().to(torch.int8),
-                      key_scale[b].transpose(0, 1).contiguous(), value_scale[b].transpose(0, 1).contiguous())])
-    return _attend(query, rows)
+                      key_scale[b].transpose(0, 1).contiguous(), value_scale[b].transpose(0, 1).contiguous(), None)])
+    return _attend(query, rows, mask)
 
 
 def quantized_attention_bucketed(query: torch.Tensor, bucket_views: Dict[int, Dict[str, torch.Tensor]],
@@ -153,8 +175,8 @@ def quantized_attention_bucketed(query: torch.Tensor, bucket_views: Dict[int, Di
     batch, num_heads, q_len, head_dim = query.shape
     if batch != 1:
         raise ValueError("Bucketed attention currently supports batch=1")
-    _check_mask(attention_mask)
     rows = []
+    k_total = 0
     for bits in sorted(bucket_views.keys()):
         view = bucket_views[bits]
         n = int(view["token_ids"].numel())
@@ -168,11 +190,14 @@ def quantized_attention_bucketed(query: torch.Tensor, bucket_views: Dict[int, Di
             shape = (n, num_heads, head_dim)
             k = unpack_tensor(k.reshape(n, num_heads, -1).contiguous().reshape(-1), bits, shape)
             v = unpack_tensor(v.reshape(n, num_heads, -1).contiguous().reshape(-1), bits, shape)
+        # the mask is indexed by the key's global slot (smartkv/kernels/__init__.py:292-296)
+        slots = view["global_slots"].reshape(n) if "global_slots" in view else None
         rows.append((bits, k.to(torch.int8), v.to(torch.int8), view["k_scale"].reshape(n, num_heads),
-                     view["v_scale"].reshape(n, num_heads)))
+                     view["v_scale"].reshape(n, num_heads), slots))
+        k_total = max(k_total + n, int(slots.max()) + 1 if slots is not None else 0)
     if not rows:
         return torch.zeros_like(query)
-    return _attend(query, [rows])
+    return _attend(query, [rows], _mask_rows(attention_mask, batch, q_len, k_total))
 
 
 __all__ = ["quantized_attention", "quantized_attention_bucketed", "CUDA_AVAILABLE", "check_cuda_availability",

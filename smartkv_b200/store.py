@@ -241,11 +241,14 @@ class PackedKVStore:
     def attention(self, layer: int, query: torch.Tensor, cur_k: Optional[torch.Tensor] = None,
                   cur_v: Optional[torch.Tensor] = None, update_importance: bool = False,
                   cur_storage: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                  kernel_events=None) -> torch.Tensor:
+                  kernel_events=None, mask: Optional[torch.Tensor] = None,
+                  cur_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One decode-attention call for ``layer``: query [B, Hq, D] (fp32/fp16),
         optional current token cur_k/cur_v [B, Hkv, D].  Returns fp32 [B, Hq, D].
         ``kernel_events`` = (start, end) torch CUDA events recorded around the
-        streaming attention kernel alone (for roofline timing)."""
+        streaming attention kernel alone (for roofline timing).
+        ``mask``: additive fp32 [B, n] indexed by token id (natural-log units, as the reference's
+        attention_mask); ``cur_mask``: fp32 [B], the mask value of the current token."""
         q = query.contiguous()
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
@@ -255,21 +258,29 @@ class PackedKVStore:
             self.build_plan()
         if kernel_events is not None:
             kernel_events[0].record()
-        check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q),
-                                            self._dtype_code(q), self.num_q_heads, ptr(self.partials), self.num_ctas,
-                                            ptr(self.logits) if want_logits else None, ptr(self.err), st),
+        if mask is not None:
+            mask = mask.to(torch.float32).contiguous()
+            assert mask.dim() == 2 and mask.shape[0] == self.num_seqs
+        check(self.lib.skv_decode_attention_masked(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q),
+                                                   self._dtype_code(q), self.num_q_heads, ptr(self.partials),
+                                                   self.num_ctas, ptr(self.logits) if want_logits else None, ptr(mask),
+                                                   0 if mask is None else int(mask.shape[1]),
+                                                   ptr(self.slot_token) if mask is not None else None, ptr(self.err), st),
               "skv_decode_attention")
         if kernel_events is not None:
             kernel_events[1].record()
         out = self.out if out is None else out
+        if cur_mask is not None:
+            cur_mask = cur_mask.to(torch.float32).contiguous()
         kv_code = _lib.DTYPE_F32
         if cur_k is not None:
             cur_k = cur_k.contiguous()
             cur_v = cur_v.contiguous()
             kv_code = self._dtype_code(cur_k)
-        check(self.lib.skv_lse_combine(ctypes.byref(self.desc), ptr(self.plan), ptr(q), self._dtype_code(q),
-                                       self.num_q_heads, ptr(self.partials), self.num_ctas, ptr(cur_k), ptr(cur_v),
-                                       kv_code, ptr(out), ptr(self.lse_max), ptr(self.lse_sum), ptr(self.cur_prob), st),
+        check(self.lib.skv_lse_combine_masked(ctypes.byref(self.desc), ptr(self.plan), ptr(q), self._dtype_code(q),
+                                              self.num_q_heads, ptr(self.partials), self.num_ctas, ptr(cur_k), ptr(cur_v),
+                                              kv_code, ptr(cur_mask), ptr(out), ptr(self.lse_max), ptr(self.lse_sum),
+                                              ptr(self.cur_prob), st),
               "skv_lse_combine")
         if want_logits:
             has_cur = cur_k is not None and cur_storage is not None

@@ -82,8 +82,15 @@ def test_quantized_attention_matches_dequantise_then_attend(q_len):
     # the [B, k, H, d] layout is accepted too (kernels/__init__.py:28-41)
     out2 = quantized_attention(t(q), t(kq.transpose(0, 2, 1, 3)), t(ks), t(vq.transpose(0, 2, 1, 3)), t(vs))
     assert torch.equal(out, out2)
-    with pytest.raises(NotImplementedError):
-        quantized_attention(t(q), t(kq), t(ks), t(vq), t(vs), attention_mask=torch.full((B, 1, q_len, n), -1.0).cuda())
+    # additive mask [B, 1, q, k], as the reference's kernels take it (smartkv/csrc/quantized_attention.cu:213-216)
+    mask = rng.standard_normal((B, 1, q_len, n)).astype(np.float32) * 3.0
+    mask[:, :, :, ::7] = -1e4                      # some keys masked out altogether
+    out3 = quantized_attention(t(q), t(kq), t(ks), t(vq), t(vs), attention_mask=t(mask))
+    ref3, _ = orc.dequant_attend(q, kq, ks, vq, vs, mask=mask)
+    assert_close(out3.cpu().numpy(), ref3, what="quantized_attention with an additive mask")
+    with pytest.raises(NotImplementedError):       # one mask row per (sequence, query position): heads share it
+        quantized_attention(t(q), t(kq), t(ks), t(vq), t(vs),
+                            attention_mask=t(rng.standard_normal((B, H, q_len, n)).astype(np.float32)))
 
 
 def test_cache_store_retrieve_like_the_reference():

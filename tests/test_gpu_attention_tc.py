@@ -83,6 +83,41 @@ def test_large_value_magnitudes():
     assert_close(out, ref, 2e-3 * 1e3, 1e-3, "large V magnitudes")
 
 
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("q_dtype", [np.float16, np.float32])
+def test_additive_mask_and_current_token_mask(path, q_dtype):
+    """Mask indexed by token id (the reference indexes it by the key's global slot,
+    smartkv/csrc/quantized_attention.cu:570-575) plus the mask value of the current token; both kernels."""
+    from oracle import smartkv_oracle as orc
+    from tests.gpu_util import fill_store, make_store, oracle_quantized
+    _lib.lib().skv_set_attention_path(path)
+    hq, hkv, d, n, B = 32, 8, 128, 700, 2
+    g = hq // hkv
+    rng = np.random.default_rng(33)
+    ks_, vs_, bs_ = [], [], []
+    for b in range(B):
+        k, v = orc.synth_kv(n, hkv, d, seed=50 + b)
+        ks_.append(k); vs_.append(v); bs_.append(rng.choice([2, 3, 4, 8], size=n))
+    store = make_store(1, B, hkv, d, hq, n)
+    fill_store(store, [(np.stack(ks_), np.stack(vs_))], np.stack(bs_))
+    q = rng.standard_normal((B, hq, d)).astype(q_dtype)
+    ck = rng.standard_normal((B, hkv, d)).astype(np.float32)
+    cv = rng.standard_normal((B, hkv, d)).astype(np.float32)
+    mask = rng.standard_normal((B, n)).astype(np.float32)
+    mask[:, 5::11] = -1e4
+    cur_mask = np.array([0.7, -1.3], np.float32)
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    out = store.attention(0, t(q), t(ck), t(cv), mask=t(mask), cur_mask=t(cur_mask)).cpu().numpy()
+    store.check_errors()
+    e = lambda x: orc.expand_gqa(x, g)
+    for b in range(B):
+        kq, vq, ksc, vsc = oracle_quantized(ks_[b], vs_[b], bs_[b])
+        ref, _ = orc.streaming_attention(q[b].astype(np.float32)[None, :, None, :], e(kq), e(ksc), e(vq), e(vsc),
+                                         mask=mask[b][None, None, None, :], tile_size=2048, current_k=e(ck[b][None]),
+                                         current_v=e(cv[b][None]), current_mask=np.full((1, 1, 1, 1), cur_mask[b], np.float32))
+        assert_close(out[b], ref[0, :, 0], 2e-3, 1e-3, f"masked attention, sequence {b}")
+
+
 def test_matches_fragment_kernel():
     """Same store, same query: the two kernels agree far inside the parity tolerance."""
     lib = _lib.lib()
