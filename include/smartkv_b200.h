@@ -167,9 +167,9 @@ int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, int num_ctas,
  * logits[seq][q_head][storage index].
  *   query    [num_seqs][num_q_heads][head_dim] fp32 or fp16
  * num_q_heads must be a multiple of num_kv_heads with group size <= 8.
- * Two kernels serve the call.  head_dim 128 with fp16 queries runs on the tcgen05 tensor cores with the
- * keys as the M operand, accumulators in tensor memory and the 8-bit rows landed by tiled TMA loads;
- * every other shape runs the mma.sync fragment kernel.  Both read the same store and the same plan.
+ * Two kernels can serve the call (skv_set_attention_path): the mma.sync fragment kernel (any shape) and,
+ * for head_dim 128 with fp16 queries, a kernel on the tcgen05 tensor cores with the keys as the M operand,
+ * accumulators in tensor memory and the 8-bit rows landed by tiled TMA loads.  Both read the same store.
  * err_flag: device int32, set non-zero if a bounded wait inside the kernel gave up. */
 int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
                          const void* query, int query_dtype, int num_q_heads, void* partials, int num_ctas,
@@ -186,9 +186,12 @@ int skv_decode_attention_masked(const SkvStoreDesc* desc, const void* store, int
                                 float* logits, const float* mask, int64_t mask_stride, const int32_t* slot_token,
                                 int32_t* err_flag, void* stream);
 
-/* Kernel selection for skv_decode_attention: 0 = automatic (default), 1 = always the mma.sync fragment
- * kernel, 2 = the tensor-memory kernel wherever it applies.  Process-wide; plans and partials built
- * under one setting must be consumed under the same setting.  No counterpart in the reference. */
+/* Kernel selection for skv_decode_attention: 0 = default (the mma.sync fragment kernel), 1 = always the
+ * fragment kernel, 2 = the tensor-memory (tcgen05) kernel wherever it applies (head_dim 128, fp16 queries).
+ * The tensor-memory kernel streams 8-bit rows at about 0.85 of the HBM copy bandwidth but pays more per
+ * narrow block, so it wins once most cached tokens are 8-bit; time both on the live cache to choose
+ * (PackedKVStore.autotune_attention does).  Process-wide; plans and partials built under one setting must
+ * be consumed under the same setting.  No counterpart in the reference. */
 int skv_set_attention_path(int path);
 int skv_get_attention_path(void);
 

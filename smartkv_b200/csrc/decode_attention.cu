@@ -644,8 +644,10 @@ static size_t attn_smem_bytes() {
 }
 
 // ---- which kernel serves a launch -----------------------------------------------------------------
-// 0 = automatic (tensor-memory kernel where it applies: head_dim 128, fp16 queries), 1 = always the
-// mma.sync fragment kernel, 2 = tensor-memory kernel wherever it applies (same as 0 today).
+// 0 = default: the mma.sync fragment kernel (measured faster on mixed-width caches: its narrow tiles cost less),
+// 1 = always the fragment kernel, 2 = the tensor-memory kernel wherever it applies (head_dim 128, fp16 queries;
+// measured faster once most cached tokens sit in the 8-bit bucket).  PackedKVStore.autotune_attention times both
+// on the live cache and sets this.
 static std::atomic<int> g_attn_path{0};
 
 extern "C" int skv_set_attention_path(int path) {
@@ -656,12 +658,12 @@ extern "C" int skv_set_attention_path(int path) {
 extern "C" int skv_get_attention_path(void) { return g_attn_path.load(); }
 
 static bool use_tc_path(const SkvStoreDesc* desc, int query_dtype) {
-  return g_attn_path.load() != 1 && desc->head_dim == 128 && query_dtype == SKV_DTYPE_F16;
+  return g_attn_path.load() == 2 && desc->head_dim == 128 && query_dtype == SKV_DTYPE_F16;
 }
 // The plan is shared by every launch of a step; its tile size follows the kernel that head_dim selects
 // for fp16 queries (the fragment kernel reads either tile size).
 static int plan_model_for(const SkvStoreDesc* desc) {
-  return (g_attn_path.load() != 1 && desc->head_dim == 128) ? kPlanModelTc : kPlanModelFrag;
+  return (g_attn_path.load() == 2 && desc->head_dim == 128) ? kPlanModelTc : kPlanModelFrag;
 }
 
 extern "C" int skv_attn_num_ctas(int device) {

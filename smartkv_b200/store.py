@@ -421,6 +421,42 @@ class PackedKVStore:
                                      self._stream()), "skv_attn_plan")
         self._plan_valid = True
 
+    def autotune_attention(self, query: torch.Tensor, layers: int = 2, iters: int = 3) -> dict:
+        """Times the two decode-attention kernels on the cache as it stands (``layers`` launches over different
+        layers, ``iters`` repetitions, CUDA events) and selects the faster one for the process
+        (skv_set_attention_path).  Only fp16 queries at head_dim 128 have a choice.  The fragment kernel wins
+        on mixed-width caches, the tensor-memory kernel once most tokens are 8-bit; which side a cache falls on
+        changes with the memory budget, so measure after a reallocation.  Returns the timings in microseconds."""
+        q = query.contiguous()
+        if self.head_dim != 128 or q.dtype != torch.float16:
+            self.lib.skv_set_attention_path(0)
+            return {"selected": "fragment", "reason": "only head_dim 128 with fp16 queries has a choice"}
+        dev = self.device
+        n = max(1, min(layers, self.num_layers))
+        times = {}
+        for name, path in (("fragment", 1), ("tensor_memory", 2)):
+            check(self.lib.skv_set_attention_path(path), "skv_set_attention_path")
+            self.build_plan()
+            best = float("inf")
+            for it in range(iters + 1):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for layer in range(n):
+                    check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan),
+                                                        ptr(q), self._dtype_code(q), self.num_q_heads, ptr(self.partials),
+                                                        self.num_ctas, None, ptr(self.err), self._stream()),
+                          "skv_decode_attention")
+                e1.record()
+                torch.cuda.synchronize(dev)
+                if it > 0:
+                    best = min(best, e0.elapsed_time(e1) * 1e3 / n)
+            times[name] = round(best, 2)
+        sel = "tensor_memory" if times["tensor_memory"] < times["fragment"] else "fragment"
+        check(self.lib.skv_set_attention_path(2 if sel == "tensor_memory" else 1), "skv_set_attention_path")
+        self._plan_valid = False
+        self.check_errors()
+        return {"selected": sel, "us_per_launch": times}
+
     def check_errors(self):
         """Reads the device error flag (synchronises)."""
         val = ctypes.c_int32(0)

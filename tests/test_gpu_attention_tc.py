@@ -13,8 +13,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture(autouse=True)
-def _automatic_path():
-    _lib.lib().skv_set_attention_path(0)
+def _tensor_memory_path():
+    _lib.lib().skv_set_attention_path(2)
     yield
     _lib.lib().skv_set_attention_path(0)
 
@@ -24,7 +24,8 @@ def test_tensor_memory_kernel_is_selected():
     store = make_store(1, 1, 8, 128, 32, 256)
     import ctypes
     assert _lib.lib().skv_attn_partials_per_run(ctypes.byref(store.desc), _lib.DTYPE_F16) == 4
-    _lib.lib().skv_set_attention_path(1)
+    assert _lib.lib().skv_attn_partials_per_run(ctypes.byref(store.desc), _lib.DTYPE_F32) == 7   # fp32 queries: fragment kernel
+    _lib.lib().skv_set_attention_path(0)
     assert _lib.lib().skv_attn_partials_per_run(ctypes.byref(store.desc), _lib.DTYPE_F16) == 11
 
 
@@ -83,7 +84,7 @@ def test_large_value_magnitudes():
     assert_close(out, ref, 2e-3 * 1e3, 1e-3, "large V magnitudes")
 
 
-@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("path", [2, 1])
 @pytest.mark.parametrize("q_dtype", [np.float16, np.float32])
 def test_additive_mask_and_current_token_mask(path, q_dtype):
     """Mask indexed by token id (the reference indexes it by the key's global slot,
@@ -125,7 +126,7 @@ def test_matches_fragment_kernel():
     rng = np.random.default_rng(0)
     q = torch.from_numpy(rng.standard_normal((2, 32, 128)).astype(np.float16)).cuda()
     outs = []
-    for path in (0, 1):
+    for path in (2, 1):
         lib.skv_set_attention_path(path)
         store._plan_valid = False
         outs.append(store.attention(0, q).clone().cpu().numpy())
