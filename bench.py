@@ -1,6 +1,6 @@
-"""Benchmark of the packed-KV decode path (BASELINE config 1).
+"""Benchmark of the packed-KV decode path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 1|3|4]
 
 One *step* = one decode step of the Llama-3.1-8B attention shape (32 query heads,
 8 KV heads, head_dim 128, fp16 query) over 32 layers, batch 16, KV context 8192:
@@ -10,17 +10,19 @@ seeded synthetic N(0,1) with 4 outlier channels per head scaled x8; tokens are s
 the default 4 bits, a Zipf(1.1) importance is injected and the device allocator +
 requantise/repack bring the cache to memory_budget 0.35 (stand-ins for the reference's
 benchmark inputs, which are synthetic randn as well).  Every 16th step of the timed
-region ends with a full reallocation (allocator, repack of all layers).
+region ends with a full reallocation (allocator, repack of all layers); two untimed
+reallocation cycles run first, so that the timed ones see a settled cache.
 
 metric  = packed-KV bytes streamed per second (algorithmic bytes: sum over buckets of
           n_b * Hkv * 2 * (row_bytes + 4) per sequence and layer) over the whole step.
 value   = inputs resident in HBM; e2e = the same step driven with HOST buffers
           (queries / new K,V copied in from pinned memory and outputs copied back, layer by
           layer on two copy streams inside the step's CUDA graph).
-roofline= the attention kernel alone (CUDA events around every launch in the timed
-          region) against the measured HBM copy bandwidth in MEASURED_PEAKS.json.
-Under torchrun every rank owns its own shard of KV heads (weak scaling: 8 KV heads
-per GPU); timing is barrier + device events, max over ranks.
+roofline= the attention kernel alone (CUDA events around one back-to-back launch per layer)
+          against the measured HBM copy bandwidth in MEASURED_PEAKS.json.
+Under torchrun the configuration is split over the ranks (strong scaling): KV heads for
+--config 1 and 4, the tokens of the sequence for --config 3; --replicas keeps the whole
+configuration on every rank instead.  Timing is barrier + device events, max over ranks.
 """
 import argparse
 import json
@@ -36,11 +38,18 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-CFG = dict(num_layers=32, num_q_heads=32, num_kv_heads=8, head_dim=128, batch=16, context=8192,
-           memory_budget=0.35, available_bits=(2, 3, 4, 8), zipf_s=1.1, realloc_every=16)
+# The shapes the metric is quoted on.  1 is the bench line; 3 and 4 are the other GPU-sized shapes (--config).
+CONFIGS = {
+    1: dict(name="Llama-3.1-8B attention shape", num_layers=32, num_q_heads=32, num_kv_heads=8, head_dim=128, batch=16,
+            context=8192, memory_budget=0.35, available_bits=(2, 3, 4, 8), zipf_s=1.1, realloc_every=16, shard="kv_heads"),
+    3: dict(name="Llama-3.1-8B attention shape, long context", num_layers=32, num_q_heads=32, num_kv_heads=8, head_dim=128,
+            batch=1, context=131072, memory_budget=0.25, available_bits=(2, 3, 4, 8), zipf_s=1.2, heavy_hitters=64,
+            realloc_every=16, shard="sequence"),
+    4: dict(name="Llama-3.1-70B attention shape", num_layers=80, num_q_heads=64, num_kv_heads=8, head_dim=128, batch=64,
+            context=16384, memory_budget=0.35, available_bits=(2, 3, 4, 8), zipf_s=1.1, realloc_every=16, shard="kv_heads"),
+}
+CFG = CONFIGS[1]
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes one attention launch of this workload moved under ncu (188.44 MB read + 6.96 MB written)
-ATTN_DRAM_TRAFFIC_PER_LAUNCH = 195_400_000
 # staging of the graphed reallocation: 4 GiB lets one pair of row-move launches cover 14 of the 32 layers
 REALLOC_STAGING_BYTES = 4 << 30
 
@@ -55,14 +64,18 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def zipf_importance(n, seed, s):
-    """Zipf(s) mass over positions, rank -> position by a seeded permutation, first 4 = sinks."""
+def zipf_importance(n, seed, s, heavy_hitters=0):
+    """Zipf(s) mass over positions, rank -> position by a seeded permutation, first 4 = sinks; optionally
+    `heavy_hitters` randomly placed tokens carrying the mass of the top ranks after the sinks."""
     rng = np.random.default_rng(seed + 7919)
     mass = 1.0 / np.arange(1, n + 1, dtype=np.float64) ** s
     order = rng.permutation(n)
     order = np.concatenate([np.arange(4), order[order >= 4]])
     imp = np.empty(n)
     imp[order] = mass
+    if heavy_hitters:
+        hh = rng.choice(np.arange(4, n), size=heavy_hitters, replace=False)
+        imp[hh] = np.maximum(imp[hh], mass[4])
     return (imp / imp.sum()).astype(np.float32)
 
 
@@ -130,6 +143,12 @@ class ClockSampler:
         return out
 
 
+def workload_string(cfg):
+    return (f"{cfg['name']} ({cfg['num_q_heads']} query heads, {cfg['num_kv_heads']} KV heads, head_dim {cfg['head_dim']}), "
+            f"{cfg['num_layers']} layers, batch {cfg['batch']}, context {cfg['context']}, budget {cfg['memory_budget']}, "
+            "bits [2,3,4,8], fp16 query; one decode step per step")
+
+
 def algorithmic_bytes_per_layer(counts, cfg):
     """sum_b n_b * Hkv * 2 * (row_bytes + 4); counts int array [B, 4]."""
     D, H = cfg["head_dim"], cfg["num_kv_heads"]
@@ -138,13 +157,26 @@ def algorithmic_bytes_per_layer(counts, cfg):
 
 
 # ----------------------------------------------------------------------------- our arm
+def profile_traffic(kernel_name):
+    """DRAM bytes per launch of `kernel_name` on the config-1 shape as the committed ncu summary states them
+    (a line `traffic_bytes_per_launch: N`); None if there is no such summary."""
+    import glob
+    import re
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", f"{kernel_name}_*.md"))):
+        m = re.search(r"traffic_bytes_per_launch:\s*(\d+)", open(path).read())
+        if m:
+            return int(m.group(1)), os.path.relpath(path, ROOT)
+    return None, None
+
+
 def run_ours(args):
     import torch
     import ctypes
 
     import torch.distributed as dist
 
-    from smartkv_b200.sharding import ImportanceSync
+    from smartkv_b200 import _lib as skv_lib
+    from smartkv_b200.sharding import ImportanceSync, fold_partials, shard_kv_heads, shard_tokens
     from smartkv_b200.store import PackedKVStore, bucket_capacities
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -154,46 +186,61 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    from smartkv_b200 import _lib as skv_lib
-    skv_lib.lib().skv_set_attention_path(1 if args.attn_kernel == "fragment" else 0)
-    cfg = dict(CFG)
+    cfg = dict(CONFIGS[args.config])
     if args.layers:
         cfg["num_layers"] = args.layers      # profiler captures only: fewer layers = less device memory
-    # other shapes with the same kernels and settings (e.g. one long sequence); not the contract's workload
+    # other shapes with the same kernels and settings; not the contract's workload
     if args.batch:
         cfg["batch"] = args.batch
     if args.context:
         cfg["context"] = args.context
     if args.budget:
         cfg["memory_budget"] = args.budget
+    shard = "replicas" if args.replicas else cfg["shard"]
     L, Hq, Hkv, D, B, N = (cfg[k] for k in ("num_layers", "num_q_heads", "num_kv_heads", "head_dim", "batch", "context"))
+    # ---- what this rank holds ------------------------------------------------------------------------------
+    if shard == "kv_heads" and world > 1:
+        heads = shard_kv_heads(Hkv, world, rank)            # strong scaling: the same cache split over the GPUs
+        Hkv_r, Hq_r, N_r, tok0 = len(heads), Hq // world, N, 0
+    elif shard == "sequence" and world > 1:
+        own = shard_tokens(N, world, rank)                  # strong scaling: the same sequence split over the GPUs
+        Hkv_r, Hq_r, N_r, tok0 = Hkv, Hq, len(own), own.start
+    else:
+        Hkv_r, Hq_r, N_r, tok0 = Hkv, Hq, N, 0
+    seq_mode = shard == "sequence" and world > 1
     steps, warmup = args.steps, args.warmup
-    total_steps = steps * 3 + warmup * 2 + 8
-    caps = bucket_capacities(N + total_steps, cfg["memory_budget"], D, cfg["available_bits"])
-    store = PackedKVStore(L, B, Hkv, D, Hq, caps, device=dev)
+    realloc_every = cfg["realloc_every"]
+    settle = 0 if (seq_mode or args.no_settle) else 2       # reallocation cycles run before anything is timed
+    total_steps = steps * 3 + warmup * 2 + settle * realloc_every + 16
+    caps = bucket_capacities(N_r + total_steps, cfg["memory_budget"], D, cfg["available_bits"])
+    store = PackedKVStore(L, B, Hkv_r, D, Hq_r, caps, device=dev, track_importance=not seq_mode)
 
     # ---- populate the cache: seeded synthetic K/V stored at the default 4 bits (cache.py:1214), the
     # Zipf importance injected the way the reference's kernel benchmark does, then one reallocation
-    bits0 = torch.full((B, N), 4, dtype=torch.int64, device=dev)
+    bits0 = torch.full((B, N_r), 4, dtype=torch.int64, device=dev)
     dst = store.plan_bulk(bits0)
     gen = torch.Generator(device=dev)
     chan = torch.Generator(device="cpu").manual_seed(1234)
-    out_k = torch.stack([torch.randperm(D, generator=chan)[:4] for _ in range(Hkv)]).to(dev)
-    out_v = torch.stack([torch.randperm(D, generator=chan)[:4] for _ in range(Hkv)]).to(dev)
-    hidx = torch.arange(Hkv, device=dev)[:, None]
+    out_k = torch.stack([torch.randperm(D, generator=chan)[:4] for _ in range(Hkv_r)]).to(dev)
+    out_v = torch.stack([torch.randperm(D, generator=chan)[:4] for _ in range(Hkv_r)]).to(dev)
+    hidx = torch.arange(Hkv_r, device=dev)[:, None]
+    chunk_b = max(1, min(B, (1 << 21) // max(N_r, 1)))      # bounded staging for the big shapes
     for layer in range(L):
         gen.manual_seed(rank * 100003 + 1000 * layer)
-        k = torch.randn((B * N, Hkv, D), generator=gen, device=dev, dtype=torch.float32)
-        v = torch.randn((B * N, Hkv, D), generator=gen, device=dev, dtype=torch.float32)
-        k[:, hidx, out_k] *= 8.0
-        v[:, hidx, out_v] *= 8.0
-        store.append(layer, k, v, dst[0], dst[1], dst[2])
-        del k, v
-    imp = np.stack([zipf_importance(N, b, cfg["zipf_s"]) for b in range(B)])   # the same sequences on every rank
+        for b0 in range(0, B, chunk_b):
+            nb = min(chunk_b, B - b0)
+            k = torch.randn((nb * N_r, Hkv_r, D), generator=gen, device=dev, dtype=torch.float32)
+            v = torch.randn((nb * N_r, Hkv_r, D), generator=gen, device=dev, dtype=torch.float32)
+            k[:, hidx, out_k] *= 8.0
+            v[:, hidx, out_v] *= 8.0
+            sl = slice(b0 * N_r, (b0 + nb) * N_r)
+            store.append(layer, k, v, dst[0][sl], dst[1][sl], dst[2][sl])
+            del k, v
+    imp = np.stack([zipf_importance(N, b, cfg["zipf_s"], cfg.get("heavy_hitters", 0)) for b in range(B)])[:, tok0: tok0 + N_r]
     store.cumulative.zero_()
-    store.cumulative.scatter_(1, dst[3].view(B, N).long(), torch.from_numpy(imp.astype(np.float64)).to(dev))
-    alloc_cfg = store.make_alloc_config(cfg["memory_budget"], cfg["available_bits"], total_kv_heads=Hkv * world)
-    importance_sync = ImportanceSync(store, dist if world > 1 else None)
+    store.cumulative.scatter_(1, dst[3].view(B, N_r).long(), torch.from_numpy(imp.astype(np.float64)).to(dev))
+    alloc_cfg = store.make_alloc_config(cfg["memory_budget"], cfg["available_bits"], total_kv_heads=Hkv)
+    importance_sync = ImportanceSync(store, dist if (world > 1 and shard == "kv_heads") else None)
     if world > 1:
         # first use of the communicator (connection set-up) happens here, not inside the timed region
         # (with a buffer of the size the importance sync exchanges: the first all-reduce of a size costs ms)
@@ -206,7 +253,7 @@ def run_ours(args):
 
     def reallocate():
         importance_sync()              # KV-head shards: sum the per-shard importance first (no-op on 1 GPU)
-        if world > 1:                  # when the all-reduce was through (it waits for the slowest rank)
+        if world > 1 and shard == "kv_heads":      # when the all-reduce was through (it waits for the slowest rank)
             e = torch.cuda.Event(enable_timing=True)
             e.record()
             sync_events.append(e)
@@ -219,8 +266,6 @@ def run_ours(args):
     reallocate()
     torch.cuda.synchronize()
     store.check_errors()
-    counts0 = store.counts.cpu().numpy()
-    hist = counts0.sum(0).tolist()
     realloc_chunks = -(-L // max(1, min(L, ((1 << 30) if args.no_graph else REALLOC_STAGING_BYTES) // max(1, int(store.lib.skv_requant_staging_bytes(
         ctypes.byref(store.desc), store.appended_total if args.no_graph else store.num_seqs * store.slots, 1))))))
     realloc_launches = 15 + (3 if B > 1 else 0) + 2 * realloc_chunks
@@ -228,35 +273,77 @@ def run_ours(args):
     # ---- per-step inputs (resident) -----------------------------------------------------------
     gen.manual_seed(rank + 99)
     n_in = 4  # distinct input sets cycled through (each is small; the cache is what is streamed)
-    q_dev = torch.randn((n_in, L, B, Hq, D), generator=gen, device=dev, dtype=torch.float32).half()
-    k_dev = torch.randn((n_in, L, B, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half()
-    v_dev = torch.randn((n_in, L, B, Hkv, D), generator=gen, device=dev, dtype=torch.float32).half()
-    out_dev = torch.empty((L, B, Hq, D), dtype=torch.float32, device=dev)
+    q_dev = torch.randn((n_in, L, B, Hq_r, D), generator=gen, device=dev, dtype=torch.float32).half()
+    k_dev = torch.randn((n_in, L, B, Hkv_r, D), generator=gen, device=dev, dtype=torch.float32).half()
+    v_dev = torch.randn((n_in, L, B, Hkv_r, D), generator=gen, device=dev, dtype=torch.float32).half()
+    if seq_mode:   # every rank sees the same queries and the same new token
+        for t in (q_dev, k_dev, v_dev):
+            dist.broadcast(t, 0)
+    out_dev = torch.empty((L, B, Hq_r, D), dtype=torch.float32, device=dev)
     q_host = q_dev.cpu().pin_memory()
     k_host = k_dev.cpu().pin_memory()
     v_host = v_dev.cpu().pin_memory()
-    out_host = torch.empty((L, B, Hq, D), dtype=torch.float32).pin_memory()
+    out_host = torch.empty((L, B, Hq_r, D), dtype=torch.float32).pin_memory()
     q_stage = torch.empty_like(q_dev[0])
     k_stage = torch.empty_like(k_dev[0])
     v_stage = torch.empty_like(v_dev[0])
 
+    # ---- which attention kernel: both timed on the live cache (the choice depends on the bucket mix) ----------
+    tune = None
+    if args.attn_kernel == "auto":
+        tune = store.autotune_attention(q_dev[0][0], layers=min(L, 4))
+        if world > 1:   # all ranks run the same kernel: the slowest rank's preference decides nothing, rank 0's does
+            flag = torch.tensor([skv_lib.lib().skv_get_attention_path()], device=dev)
+            dist.broadcast(flag, 0)
+            skv_lib.lib().skv_set_attention_path(int(flag.item()))
+            store._plan_valid = False
+    else:
+        skv_lib.lib().skv_set_attention_path(2 if args.attn_kernel == "tensor_memory" else 1)
+        store._plan_valid = False
+    kernel_name = "decode_attn_tc_kernel" if skv_lib.lib().skv_get_attention_path() == 2 else "decode_attn_kernel"
+
     attn_events = []
     launches = [0]
+    last_rank = rank == world - 1
 
     def decode_step(q, k, v, record=False):
         """One decode step: 2 kernels of this library per layer (attention; combine + append + the
         previous layer's importance update), the attention plan kernel, the last layer's importance update and
-        the two kernels that place and commit the new token."""
+        the two kernels that place and commit the new token.  Sequence shards: the new token takes part (and is
+        appended) on the last rank only, importance tracking is off."""
         plan = store.plan_step()
+        with_cur = last_rank or not seq_mode
         for layer in range(L):
             ev = None
             if record:
                 ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                 attn_events.append(ev)
-            store.decode_layer(layer, q[layer], k[layer], v[layer], plan, update_importance=True, out=out_dev[layer],
-                               kernel_events=ev)
-        store.commit_step(plan)
+            store.decode_layer(layer, q[layer], k[layer] if with_cur else None, v[layer] if with_cur else None, plan,
+                               update_importance=not seq_mode, out=out_dev[layer], kernel_events=ev)
+        if with_cur:
+            store.commit_step(plan)
+        else:
+            store.flush_importance()
+            store._pipe["calls"] = 0
 
+    # sequence shards: one exchange per step for all layers' (max, sum, out) and one fold
+    if seq_mode:
+        packed = torch.empty((L, B, Hq_r, D + 2), dtype=torch.float32, device=dev)
+        gathered = torch.empty((world,) + tuple(packed.shape), dtype=torch.float32, device=dev)
+        folded = torch.empty((L, B, Hq_r, D), dtype=torch.float32, device=dev)
+
+        def exchange():
+            sm = store._pipe["small"]
+            packed[..., 0] = sm["lse_max"]
+            packed[..., 1] = sm["lse_sum"]
+            torch.mul(out_dev, sm["lse_sum"].unsqueeze(-1), out=packed[..., 2:])
+            dist.all_gather_into_tensor(gathered, packed)
+            fold_partials(gathered, out=folded)
+    else:
+        def exchange():
+            pass
+
+    per_step_launches = 2 * L + 4
     graph = None
     if not args.no_graph:
         # the whole step (every layer's launches) as one CUDA graph over static input buffers
@@ -283,16 +370,17 @@ def run_ours(args):
             graph.replay()
         else:
             decode_step(q_stage, k_stage, v_stage)
-        launches[0] += 2 * L + 4
+        exchange()
+        launches[0] += per_step_launches
 
     def resident_step(i):
         j = i % n_in
         if graph is not None:
             resident_graphs[j].replay()
-            launches[0] += 2 * L + 4
         else:
             decode_step(q_dev[j], k_dev[j], v_dev[j])
-            launches[0] += 2 * L + 4
+        exchange()
+        launches[0] += per_step_launches
 
     def kernel_timing_step(i):
         j = i % n_in
@@ -302,7 +390,7 @@ def run_ours(args):
     # the copies are pipelined by layer on two copy streams (layer l+1's inputs arrive while layer l computes,
     # layer l's output leaves while layer l+1 computes); one CUDA graph per input set holds copies and kernels.
     e2e_graphs = []
-    if graph is not None:
+    if graph is not None and not seq_mode:
         h2d, d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
         def e2e_body(j):
@@ -339,25 +427,37 @@ def run_ours(args):
         j = i % n_in
         if e2e_graphs:
             e2e_graphs[j].replay()
-            launches[0] += 2 * L + 4
+            launches[0] += per_step_launches
             return
         q_stage.copy_(q_host[j], non_blocking=True)
         k_stage.copy_(k_host[j], non_blocking=True)
         v_stage.copy_(v_host[j], non_blocking=True)
         run_step()
-        out_host.copy_(out_dev, non_blocking=True)
+        out_host.copy_(folded if seq_mode else out_dev, non_blocking=True)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    realloc_every = cfg["realloc_every"]
+    with_realloc = not seq_mode
+    # Reallocation cycles before anything is timed: the first reallocations of a cache's life move most tokens
+    # (the decode attention over random K/V is nearly uniform and swamps the injected importance), later ones a few
+    # per cent.  Both timed passes then see the settled cache and do the same work.
+    for c in range(settle):
+        for i in range(realloc_every):
+            resident_step(i)
+        reallocate()
+    torch.cuda.synchronize()
+    store.check_errors()
+    counts0 = store.counts.cpu().numpy()
+    hist = counts0.sum(0).tolist()
+
     realloc_events = []
     moved_log = torch.zeros(256, dtype=torch.int64, device=dev)  # tokens moved by every timed reallocation
     rank_ms = {}
 
-    def timed(fn, n_warm, n_steps, first, with_realloc=True):
+    def timed(fn, n_warm, n_steps, first, realloc=True):
         for i in range(n_warm):
             fn(first + i)
         barrier()
@@ -371,7 +471,7 @@ def run_ours(args):
         e0.record()
         for i in range(n_steps):
             fn(first + n_warm + i)
-            if with_realloc and (i + 1) % realloc_every == 0:
+            if realloc and with_realloc and (i + 1) % realloc_every == 0:
                 ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                 ev[0].record()
                 reallocate()
@@ -386,7 +486,8 @@ def run_ours(args):
         clocks = sampler.stop() if rank == 0 else None
         c_after = store.counts.cpu().numpy()
         # bytes streamed: every step reads the cache as it stood at that step
-        per_layer = [algorithmic_bytes_per_layer(c_before, cfg), algorithmic_bytes_per_layer(c_after, cfg)]
+        lcfg = dict(cfg, num_kv_heads=Hkv_r)
+        per_layer = [algorithmic_bytes_per_layer(c_before, lcfg), algorithmic_bytes_per_layer(c_after, lcfg)]
         step_bytes = L * (per_layer[0] + per_layer[1]) / 2.0
         if world > 1:
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -402,48 +503,96 @@ def run_ours(args):
     launches[0] = 0
     ms, step_bytes, clocks = timed(resident_step, warmup, steps, 0)
     store.check_errors()
-    n_launch = launches[0] - warmup * (L * 2 + 4)
+    n_launch = launches[0] - warmup * per_step_launches
     realloc_ms = [a.elapsed_time(b) for a, b in realloc_events]
-    # kernel-only time of the attention kernel: the same steps launched un-graphed with a CUDA
-    # event pair around every attention launch
+    # the same steps without the reallocations: the steady-state step
+    ms_steady, _, _ = timed(resident_step, 1, min(steps, 16), 3, realloc=False)
+    steady_ms_per_step = ms_steady / min(steps, 16)
+
+    # ---- the attention kernel alone ---------------------------------------------------------------------
+    # (a) back to back: one launch per layer, every layer its own 188 MB, nothing else on the stream -- the kernel's
+    #     average launch duration; (b) inside the step: a CUDA event pair around every launch of an un-graphed pass
+    #     (includes the gap the host leaves before each launch)
+    q0 = q_dev[0]
+    store.build_plan()
+    bb = []
+    for rep in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for layer in range(L):
+            skv_lib.check(store.lib.skv_decode_attention(ctypes.byref(store.desc), skv_lib.ptr(store.arena), layer,
+                                                         skv_lib.ptr(store.plan), skv_lib.ptr(q0[layer]), skv_lib.DTYPE_F16, Hq_r,
+                                                         skv_lib.ptr(store.partials), store.num_ctas,
+                                                         skv_lib.ptr(store.logits) if store.track_importance else None,
+                                                         skv_lib.ptr(store.err), store._stream()), "skv_decode_attention")
+        e1.record()
+        torch.cuda.synchronize()
+        bb.append(e0.elapsed_time(e1) / L)
+    attn_ms = float(np.median(bb[1:])) if len(bb) > 1 else bb[0]
+    if world > 1:
+        t = torch.tensor([attn_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        attn_ms = float(t.item())
+    per_layer_bytes = algorithmic_bytes_per_layer(store.counts.cpu().numpy(), dict(cfg, num_kv_heads=Hkv_r))
     attn_events.clear()
-    ms_k, step_bytes_k, _ = timed(kernel_timing_step, 1, min(steps, 8), 0, with_realloc=False)
+    timed(kernel_timing_step, 1, min(steps, 4), 0, realloc=False)
     timed_events = attn_events[L:]
-    attn_ms = float(np.mean([a.elapsed_time(b) for a, b in timed_events]))
-    per_layer_bytes = step_bytes_k / L / world
+    attn_ms_in_step = float(np.mean([a.elapsed_time(b) for a, b in timed_events]))
     peak, peak_kind = measured_peak()
     achieved = per_layer_bytes / (attn_ms * 1e-3) / 1e9
     n_before = len(realloc_events)
-    ms_e2e, step_bytes_e2e, _ = timed(host_step, warmup, steps, steps + warmup)
+    if seq_mode:
+        ms_e2e, step_bytes_e2e = timed(host_step, warmup, steps, steps + warmup)[:2]
+    else:
+        ms_e2e, step_bytes_e2e, _ = timed(host_step, warmup, steps, steps + warmup)
     store.check_errors()
-    # the end-to-end pass runs later in the cache's life: its reallocations move fewer tokens than those of the
-    # resident pass, which is why its step can come out shorter; both averages are reported
     realloc_ms_e2e = [a.elapsed_time(b) for a, b in realloc_events[n_before:]]
+
+    # ---- self-check of the sharded paths: one layer against an unsharded store is the tests' job; here the ranks
+    # only make sure they agree (sequence shards: every rank folded the same result)
+    agree = None
+    if seq_mode:
+        chk = folded[0].clone()
+        dist.broadcast(chk, 0)
+        agree = bool(torch.allclose(chk, folded[0], rtol=0, atol=0))
 
     value = step_bytes * steps / (ms * 1e-3) / 1e9
     e2e_value = step_bytes_e2e * steps / (ms_e2e * 1e-3) / 1e9
-    h2d = q_stage.numel() * 2 + k_stage.numel() * 2 + v_stage.numel() * 2
-    d2h = out_dev.numel() * 4
+    h2d = (q_stage.numel() * 2 + k_stage.numel() * 2 + v_stage.numel() * 2) * world
+    d2h = out_dev.numel() * 4 * world
+    traffic, traffic_src = (None, None)
+    if args.config == 1 and world == 1 and not (args.batch or args.context or args.budget or args.layers):
+        traffic, traffic_src = profile_traffic(kernel_name)
+    shard_txt = {"kv_heads": f"KV heads split over the GPUs ({Hkv_r} of {Hkv} per GPU)",
+                 "sequence": f"tokens of the sequence split over the GPUs ({N_r} of {N} per GPU), one exchange of all layers' "
+                             "(max, sum, out) per step", "replicas": "every GPU holds the whole configuration"}[shard]
     line = {
         "metric": "packed_kv_decode_attention_throughput", "value": round(value, 2), "unit": "GB/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma, f32 accumulate",
-        "data": "synthetic (seeded N(0,1) K/V, 4 outlier channels x8 per head, Zipf(1.1) importance)",
-        "config": {"workload": f"BASELINE config 1: Llama-3.1-8B attention shape, {L} layers, batch {B}, context {N}, "
-                               f"budget {cfg['memory_budget']}, bits [2,3,4,8], fp16 query; one decode step per step",
-                   "kv_heads_per_gpu": Hkv, "l2": "inputs larger than L2 (packed cache per step >> 126 MB)",
-                   "bucket_histogram_2_3_4_8": hist, "reallocation": f"device allocator + requantise/repack of all layers after every {realloc_every}th "
-                                   f"step, inside the timed region ({len(realloc_ms)} in {steps} steps)",
+        "higher_is_better": True, "scaling": "weak" if (shard == "replicas" and world > 1) else "strong", "vs_baseline": None,
+        "dtype": "int8 tensor-core scores, f16 P.V, f32 accumulate" if kernel_name == "decode_attn_kernel" else "int8 tensor-core scores and P.V (tcgen05), f32 accumulate",
+        "data": f"synthetic (seeded N(0,1) K/V, 4 outlier channels x8 per head, Zipf({cfg['zipf_s']}) importance)",
+        "config": {"workload": workload_string(cfg),
+                   "sharding": shard_txt if world > 1 else "one GPU", "kv_heads_per_gpu": Hkv_r,
+                   "l2": "inputs larger than L2 (packed cache per step >> 126 MB)",
+                   "bucket_histogram_2_3_4_8": hist,
+                   "reallocation": (f"device allocator + requantise/repack of all layers after every {realloc_every}th "
+                                    f"step, inside the timed region ({len(realloc_ms)} in {steps} steps); {settle} untimed cycles "
+                                    "before, so that timed ones see a settled cache") if with_realloc else
+                                   "none inside the timed region (importance tracking is off under sequence shards)",
                    "packed_bytes_per_step": int(step_bytes)},
-        "decode_tokens_per_s": round(B * world * steps / (ms * 1e-3), 1),
+        "decode_tokens_per_s": round(B * steps / (ms * 1e-3), 1),
+        "steady_state_ms_per_step": round(steady_ms_per_step, 4),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": ATTN_DRAM_TRAFFIC_PER_LAUNCH if not (args.batch or args.context or args.budget) else None,
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
-                                       "profiles/decode_attn_kernel_config1_shape_2layers.md",
-                     "peak_source": peak_kind,
-                     "kernel": "decode_attn_kernel", "kernel_ms": round(attn_ms, 4),
-                     "timing": "CUDA event pair around every launch, un-graphed pass of the same steps",
-                     "algorithmic_bytes_per_launch": int(per_layer_bytes)},
+                     "frac": round(achieved / peak, 4), "traffic": traffic, "traffic_source": traffic_src,
+                     "peak_source": peak_kind, "kernel": kernel_name, "kernel_ms": round(attn_ms, 4),
+                     "timing": f"CUDA events around {L} back-to-back launches (one per layer, each over its own cache), median of 2 passes"
+                               + ("; max over ranks" if world > 1 else ""),
+                     "kernel_ms_inside_step": round(attn_ms_in_step, 4),
+                     "algorithmic_bytes_per_launch": int(per_layer_bytes),
+                     "whole_step_frac": round(step_bytes / world / (steady_ms_per_step * 1e-3) / 1e9 / peak, 4)},
+        "attention_kernel_choice": tune,
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / steps, 4),
                 "reallocation_ms": round(float(np.mean(realloc_ms_e2e)), 3) if realloc_ms_e2e else None,
@@ -453,8 +602,9 @@ def run_ours(args):
         "reallocation_detail": [[round(m, 3), int(n)] for m, n in
                                 zip(realloc_ms + realloc_ms_e2e, moved_log[:len(realloc_ms) + len(realloc_ms_e2e)].tolist())],
         "ms_per_step_by_rank": rank_ms or None,
-        "reallocation_wait_for_ranks_ms": ([round(a[0].elapsed_time(b), 3) for a, b in zip(realloc_events, sync_events[1:])]
+        "reallocation_wait_for_ranks_ms": ([round(a[0].elapsed_time(b), 3) for a, b in zip(realloc_events, sync_events[1 + settle:])]
                                            if sync_events else None),
+        "ranks_agree": agree,
         "gpu_launches": int(n_launch), "cuda_graph": graph is not None,
         "clocks": clocks,
     }
@@ -538,7 +688,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg = dict(CFG)
+    cfg = dict(CONFIGS[args.config])
     t0 = time.perf_counter()
     per_step_budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
     vals = []
@@ -555,8 +705,7 @@ def run_reference(args):
         "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(step_ms, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic (seeded N(0,1) K/V, 4 outlier channels x8 per head, Zipf(1.1) importance)",
-        "config": {"workload": f"BASELINE config 1: Llama-3.1-8B attention shape, {cfg['num_layers']} layers, batch 16, "
-                               "context 8192, budget 0.35, bits [2,3,4,8], fp16 query; one decode step per step",
+        "config": {"workload": workload_string(cfg),
                    "sample": "each step is a bounded sample of that workload on the host cores: one (sequence, layer) at "
                              "the full context, one allocator call and one requantisation; ms_per_step and value are "
                              "scaled to batch x layers with the reallocation amortised over 16 steps"},
@@ -581,8 +730,12 @@ def main():
     ap.add_argument("--budget", type=float, default=0.0, help="other memory budget than the contract's 0.35")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the layer count (profiler captures of a small case only; not a bench line)")
-    ap.add_argument("--attn-kernel", default="auto", choices=["auto", "fragment"],
-                    help="auto: tensor-memory (tcgen05) kernel where it applies; fragment: the mma.sync kernel everywhere")
+    ap.add_argument("--attn-kernel", default="auto", choices=["auto", "fragment", "tensor_memory"],
+                    help="auto: both decode-attention kernels are timed on the populated cache and the faster one runs")
+    ap.add_argument("--config", type=int, default=1, choices=sorted(CONFIGS),
+                    help="1 (default, the bench line), 3 (long context, sequence shards) or 4 (70B shape, KV-head shards)")
+    ap.add_argument("--replicas", action="store_true", help="under torchrun: every rank holds the whole configuration (weak scaling)")
+    ap.add_argument("--no-settle", action="store_true", help="skip the untimed reallocation cycles before the timed passes")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -68,6 +68,22 @@ class ImportanceSync:
             self.synced.copy_(self.store.cumulative)
 
 
+def fold_partials(allp: torch.Tensor, out: Optional[torch.Tensor] = None):
+    """allp [world, .., D + 2] = every rank's (max in log2 units, sum, unnormalised out[D]) per query head; returns the
+    attention output over all ranks' tokens [.., D] (written into ``out`` if given).  The rule of the combine kernel:
+    weights 2^(m_r - M), empty partials (m = -inf) count for nothing."""
+    ms, ls, os_ = allp[..., 0], allp[..., 1], allp[..., 2:]
+    M = ms.max(dim=0).values
+    w = torch.where(torch.isneginf(ms), torch.zeros_like(ms), torch.exp2(ms - M))
+    L = (ls * w).sum(0)
+    O = (os_ * w.unsqueeze(-1)).sum(0)
+    res = torch.where(L.unsqueeze(-1) > 0, O / L.clamp_min(1e-38).unsqueeze(-1), torch.zeros_like(O))
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
 def combine_partials(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, dist_module=None, group=None):
     """Sequence-split attention: m, l [..] and o [.., D] are this rank's running max (log2 units),
     sum and unnormalised output; returns the attention output over all ranks' tokens and the global

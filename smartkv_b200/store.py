@@ -216,6 +216,18 @@ class PackedKVStore:
 
     def commit_step(self, plan):
         self.flush_importance()          # reads the counts as they stood during the step
+        if torch.cuda.is_current_stream_capturing():
+            # The head-importance EMA is double buffered and the half to read is a launch argument: a captured step
+            # replays the same arguments, which is only right if the step flips the parity an even number of times.
+            n = getattr(self, "_capture_updates", 0)
+            self._capture_updates = 0
+            if n % 2:
+                raise _lib.SmartKVLibraryError(
+                    f"a CUDA-graph-captured decode step holds {n} importance updates; it must hold an even number "
+                    "(the head-importance state is double buffered by launch argument): capture two steps per graph "
+                    "or run this model's steps without a graph")
+        else:
+            self._capture_updates = 0
         if getattr(self, "_pipe", None) is not None:
             self._pipe["calls"] = 0      # every step starts on the same buffer set (CUDA graph replays rely on it)
             self._pipe["post_events"] = []
@@ -330,22 +342,35 @@ class PackedKVStore:
         if kernel_events is not None:
             kernel_events[1].record()
         out = self.out if out is None else out
-        cur_k = cur_k.contiguous()
-        cur_v = cur_v.contiguous()
-        dst_seq, dst_bucket, dst_pos, storage = step_plan
+        has_cur = cur_k is not None
+        if has_cur:
+            cur_k = cur_k.contiguous()
+            cur_v = cur_v.contiguous()
+        dst_seq, dst_bucket, dst_pos, storage = step_plan if has_cur else (None, None, None, None)
         pend = pipe["pending"]
         pb = pipe["bufs"][pend["buf"]] if pend is not None else None
+        small = pipe["small"]                         # (max, sum, current-token probability) of every layer of the step
+        ps = {k2: v2[pend["layer"]] for k2, v2 in small.items()} if pend is not None else None
+        # Under stream capture the host scalars below would be baked into the graph: the importance blocks then
+        # cover every storage index (0 = full grid) instead of the capture-time token count, and the
+        # head-state parity, which must alternate per update, is refused unless a captured step holds an even
+        # number of updates (checked by the caller of commit_step through _capture_updates).
+        capturing = torch.cuda.is_current_stream_capturing()
+        max_tokens_arg = 0 if capturing else self.max_seq_tokens
 
         def post(stream_ptr):
             check(self.lib.skv_post_attention(
                 ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q), self._dtype_code(q),
-                self.num_q_heads, ptr(partials), self.num_ctas, ptr(cur_k), ptr(cur_v), self._dtype_code(cur_k),
-                ptr(out), ptr(bufs["lse_max"]), ptr(bufs["lse_sum"]), ptr(bufs["cur_prob"]), ptr(self.counts),
+                self.num_q_heads, ptr(partials), self.num_ctas, ptr(cur_k), ptr(cur_v),
+                self._dtype_code(cur_k) if has_cur else _lib.DTYPE_F32,
+                ptr(out), ptr(small["lse_max"][layer]), ptr(small["lse_sum"][layer]), ptr(small["cur_prob"][layer]),
+                ptr(self.counts),
                 pend["layer"] if pend is not None else 0, ptr(pb["logits"]) if pend is not None else None,
-                ptr(pb["lse_max"]) if pend is not None else None, ptr(pb["lse_sum"]) if pend is not None else None,
-                ptr(pb["cur_prob"]) if pend is not None else None, ptr(pend["storage"]) if pend is not None else None,
+                ptr(ps["lse_max"]) if pend is not None else None, ptr(ps["lse_sum"]) if pend is not None else None,
+                ptr(ps["cur_prob"]) if pend is not None else None,
+                ptr(pend["storage"]) if pend is not None and pend["storage"] is not None else None,
                 ptr(self.head_state), self.head_parity, ptr(self.cumulative), ptr(self.layer_ema), ptr(self.touched),
-                self.decay, self.head_decay, ptr(dst_seq), ptr(dst_bucket), ptr(dst_pos), self.max_seq_tokens,
+                self.decay, self.head_decay, ptr(dst_seq), ptr(dst_bucket), ptr(dst_pos), max_tokens_arg,
                 ptr(self.err), stream_ptr), "skv_post_attention")
 
         if overlap:
@@ -363,9 +388,11 @@ class PackedKVStore:
             post(st)
         if pend is not None:
             self.head_parity ^= 1
+            if capturing:
+                self._capture_updates = getattr(self, "_capture_updates", 0) + 1
         pipe["pending"] = {"layer": layer, "buf": lslot, "storage": storage} if want_logits else None
         pipe["calls"] = m + 1
-        self.lse_max, self.lse_sum, self.cur_prob = bufs["lse_max"], bufs["lse_sum"], bufs["cur_prob"]
+        self.lse_max, self.lse_sum, self.cur_prob = small["lse_max"][layer], small["lse_sum"][layer], small["cur_prob"][layer]
         return out
 
     def _pipe_buffers(self):
@@ -378,12 +405,14 @@ class PackedKVStore:
             for i in range(3):
                 bufs.append({
                     "logits": (self.logits if i == 0 else torch.empty_like(self.logits)) if self.track_importance else None,
-                    "lse_max": torch.empty((B, Hq), dtype=torch.float32, device=dev),
-                    "lse_sum": torch.empty((B, Hq), dtype=torch.float32, device=dev),
-                    "cur_prob": torch.empty((B, Hq), dtype=torch.float32, device=dev),
                 })
-            self._pipe = {"bufs": bufs, "partials": [self.partials, torch.empty_like(self.partials)], "calls": 0,
-                          "pending": None, "side": torch.cuda.Stream(device=dev), "post_events": [], "forked": False}
+            # the small per-layer results stay addressable for the whole step (a sequence-sharded step exchanges
+            # all layers' (max, sum, out) at once)
+            small = {k: torch.empty((self.num_layers, B, Hq), dtype=torch.float32, device=dev)
+                     for k in ("lse_max", "lse_sum", "cur_prob")}
+            self._pipe = {"bufs": bufs, "small": small, "partials": [self.partials, torch.empty_like(self.partials)],
+                          "calls": 0, "pending": None, "side": torch.cuda.Stream(device=dev), "post_events": [],
+                          "forked": False}
         return self._pipe
 
     def join(self):
@@ -404,9 +433,13 @@ class PackedKVStore:
         if pend is None:
             return
         pb = pipe["bufs"][pend["buf"]]
+        sm = {k: v[pend["layer"]] for k, v in pipe["small"].items()}
+        if torch.cuda.is_current_stream_capturing():
+            self._capture_updates = getattr(self, "_capture_updates", 0) + 1
         check(self.lib.skv_importance_update(ctypes.byref(self.desc), pend["layer"], ptr(self.counts), self.num_q_heads,
-                                             ptr(pb["logits"]), ptr(pb["lse_max"]), ptr(pb["lse_sum"]),
-                                             ptr(pb["cur_prob"]), ptr(pend["storage"]), ptr(self.head_state),
+                                             ptr(pb["logits"]), ptr(sm["lse_max"]), ptr(sm["lse_sum"]),
+                                             ptr(sm["cur_prob"]) if pend["storage"] is not None else None,
+                                             ptr(pend["storage"]) if pend["storage"] is not None else None, ptr(self.head_state),
                                              self.head_parity, ptr(self.cumulative), ptr(self.layer_ema),
                                              ptr(self.touched), self.decay, self.head_decay, self._stream()),
               "skv_importance_update")
