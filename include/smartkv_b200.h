@@ -196,8 +196,10 @@ int skv_set_attention_path(int path);
 int skv_get_attention_path(void);
 
 /* Limit of every bounded device-side wait of the attention kernels, in polls of about 50 ns (default
- * 2^24, about one second).  When a wait runs out the kernel sets *err_flag and returns; nothing faults.
- * No counterpart in the reference. */
+ * 2^24, about one second).  When a wait runs out the kernel sets *err_flag, waits (bounded) for its own
+ * copies still in flight and returns; nothing faults and the context stays usable.  The fragment kernel
+ * honours any limit; the tensor-memory kernel never uses fewer than 2^20 polls.  No counterpart in the
+ * reference. */
 int skv_set_wait_limit(unsigned polls);
 
 /* Combines the partials with the newest token, which takes part in full precision

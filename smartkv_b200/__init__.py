@@ -16,6 +16,9 @@ def __getattr__(name):
     if name == "SmartKVCache":
         from .core.cache import SmartKVCache
         return SmartKVCache
+    if name == "BatchedSmartKVCache":
+        from .core.batched_cache import BatchedSmartKVCache
+        return BatchedSmartKVCache
     if name in ("SmartKVConfig", "LlamaSmartKV", "LlamaSmartKVAttention"):
         from .models import llama_smartkv
         return getattr(llama_smartkv, name)

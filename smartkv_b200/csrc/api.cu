@@ -53,7 +53,14 @@ extern "C" int skv_read_error_flag(int32_t* err_flag, int32_t* host_value, void*
     return SKV_ERR_CUDA;
   if (cudaMemsetAsync(err_flag, 0, sizeof(int32_t), st) != cudaSuccess) return SKV_ERR_CUDA;
   if (cudaStreamSynchronize(st) != cudaSuccess) return SKV_ERR_CUDA;
-  return *host_value == 0 ? SKV_OK : SKV_ERR_TIMEOUT;
+  // 1: a bounded wait ran out; 2, 3, 6: a bucket or a staging buffer was too small (the row was refused / nothing
+  // moved); 4, 5: inconsistent widths or bookkeeping handed to a kernel
+  switch (*host_value) {
+    case 0: return SKV_OK;
+    case 1: return SKV_ERR_TIMEOUT;
+    case 2: case 3: case 6: return SKV_ERR_CAPACITY;
+    default: return SKV_ERR_INVALID;
+  }
 }
 
 // ---- placement of the token every sequence appends in a decode step ----------------------------

@@ -149,6 +149,7 @@ struct LaneState {
 // units), so most tiles need no cross-lane reduction and no rescale of the accumulators;
 // probabilities then reach at most 2^kLazyTau, well inside fp16 / fp32 range.
 constexpr float kLazyTau = 8.0f;
+constexpr float kVScaleGuard = 64.0f;  // 2^kLazyTau * 64 = 16384, a quarter of the fp16 maximum
 
 // Per-run query data the producer warp prepares in shared memory.
 template <int D, bool PRECISE>
@@ -264,10 +265,21 @@ __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t
     }
   }
   float mx = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
-  if (__any_sync(0xffffffffu, mx > st.m + kLazyTau)) {
+  // The P operand of the P.V product is p * v_scale in fp16.  With p <= 2^kLazyTau that product stays inside
+  // the fp16 range as long as the V scale does not exceed kVScaleGuard; a tile with a larger scale takes the
+  // slow path below, which raises the running maximum far enough for the product to fit.
+  const float vsm = fmaxf(fmaxf(vs0, vs1), fmaxf(vs2, vs3));
+  if (__any_sync(0xffffffffu, mx > st.m + kLazyTau || vsm > kVScaleGuard)) {
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float n = fmaxf(st.m, mx);
+    float n = fmaxf(st.m, mx);
+    {
+      const float mu2 = (n == -INFINITY) ? 0.f : n;
+      float am = fmaxf(fmaxf(ex2f(x0 - mu2) * vs0, ex2f(x1 - mu2) * vs1), fmaxf(ex2f(x2 - mu2) * vs2, ex2f(x3 - mu2) * vs3));
+      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+      if (am > 16384.f) n += ceilf(log2f(am)) - 14.f;  // am > 0 needs a finite score, so n is finite here
+    }
     const float alpha = (n == -INFINITY) ? 1.f : ex2f(st.m - n);
     st.l *= alpha;
     st.m = n;
@@ -442,6 +454,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     uint32_t epar = 1, qepar = 1;  // a fresh barrier passes a wait on parity 1: every slot starts empty
     const int kbt[kNumBuckets] = {KBT0, KBT1, KBT2, KBT3};
     bool first_block = true;
+    uint32_t armed = 0, armed_par = 0;  // stages with a copy issued, and the parity of their last full phase
     const uint64_t stream_policy = l2_evict_first_policy();  // the cache is read once per step
     constexpr int NL = Slot::NLIMB;
     constexpr int EPL = D / 32;  // query elements per lane and head
@@ -457,6 +470,8 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
           step = (first_block && kbt[ci] > NCONS) ? NCONS : kbt[ci];
           first_block = false;
           if (!wait_or_abort(&empty[stg], epar, abort_flag, p.err, p.wait_polls)) return false;
+          armed |= 1u << stg;
+          armed_par = (armed_par & ~(1u << stg)) | ((epar ^ 1u) << stg);
           if (lane == 0) {
             const int ntl = (d.kb[ci] - ct0) < step ? (d.kb[ci] - ct0) : step;
             const int key0 = ct0 * 16;
@@ -528,6 +543,18 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       ok = ok && issue_blocks(d, ci, ct0, 1 << 30);
       d = dn;
     }
+    if (*abort_flag) {
+      // A wait gave up somewhere in the CTA.  The shared memory must outlive the copies still in flight: wait
+      // (bounded, about a fifth of a second) for the last phase armed on every stage; a full barrier completes
+      // on bytes alone, whatever the consumers do.
+      for (int s = 0; s < STAGES; ++s) {
+        if (!((armed >> s) & 1u)) continue;
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+          if (mbar_test_wait(&full[s], (armed_par >> s) & 1u)) break;
+          __nanosleep(50);
+        }
+      }
+    }
     return;
   }
 
@@ -538,6 +565,13 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
   bool first_block = true;  // the CTA's first block holds one tile per consumer warp
   for (int r = run_begin; r < run_end; ++r) {
     if (!aborted && !wait_or_abort(&qfull[qi], qfpar, abort_flag, p.err, p.wait_polls)) aborted = true;
+    // The run's descriptor steers every loop below and the address of the partials, so it may only be read if
+    // it was published.  All consumer warps take that decision together: one thread samples the abort flag
+    // between two barriers, and either every warp goes on or every warp leaves.
+    named_bar_sync(2, NTC);
+    if (tid == 0) abort_flag[1] = *abort_flag;
+    named_bar_sync(2, NTC);
+    if (abort_flag[1]) return;
     const Slot& slot = qslots[qi];  // stays valid until this warp arrives on qempty below
     const RunDesc& d = slot.desc;
     if (r == run_begin) {

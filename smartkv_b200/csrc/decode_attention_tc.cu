@@ -410,7 +410,8 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
 
   const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
   const int run_begin = pv.cta_begin[blockIdx.x], run_end = pv.cta_begin[blockIdx.x + 1];
-  const unsigned polls = p.wait_polls;
+  // never below 2^20 polls: a shorter limit could run out while this CTA's own copies and MMAs are still in flight
+  const unsigned polls = p.wait_polls < (1u << 20) ? (1u << 20) : p.wait_polls;
 
   if (warp < G && run_begin < run_end) {  // warps 0..G-1 are consumer warps (G <= 8 < WGS * 4)
     const RunDesc d0 = pv.first[blockIdx.x];

@@ -11,35 +11,48 @@ ordinary causal attention over the prompt with torch, hands the probabilities to
 (:392-427).  Projections, rotary embedding and everything outside attention stay with the wrapped
 Hugging Face module.
 
-Like the reference the cache keeps ONE sequence (batch row 0, :457-466); other batch rows attend
-to that sequence's cache.
+With one batch row the cache is ``SmartKVCache``; like the reference it keeps ONE sequence (:457-466).
+With more than one row (or ``SmartKVConfig.batched=True``) the wrapper builds a ``BatchedSmartKVCache``
+instead: every batch row is an independent sequence of the same packed store, and a decode step costs two
+kernel launches per layer for the whole batch.  ``batched=False`` restores the reference's behaviour for a
+batch (every row attends to row 0's cache).
 """
 from __future__ import annotations
 
 import warnings
+import weakref
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
 
+from ..core.batched_cache import BatchedSmartKVCache
 from ..core.cache import SmartKVCache
 
 
 @dataclass
 class SmartKVConfig:
-    """smartkv/models/llama_smartkv.py:39-57."""
+    """smartkv/models/llama_smartkv.py:39-57, same fields and defaults (``device`` defaults to "cpu" there
+    too; this library has no CPU path, so a cache is only built with device="cuda").  The three fields after
+    ``forecast_lr`` have no counterpart in the reference: ``batched`` (None: a batch of more than one row gets
+    a multi-sequence cache), ``max_tokens`` (capacity per sequence of that cache) and ``key_attribution``
+    ("keys": attention mass is credited to the key it falls on; "wrapper": what the reference's wrapper does
+    in a decode step, see BatchedSmartKVCache)."""
     enabled: bool = False
     memory_budget: float = 0.5
     decay: float = 0.9
     realloc_freq: int = 16
     available_bits: Optional[List[int]] = None
-    device: str = "cuda"
+    device: str = "cpu"
     enable_forecast: bool = False
     forecast_history: int = 2048
     forecast_update_interval: int = 32
     forecast_blend: float = 0.5
     forecast_lr: float = 0.05
+    batched: Optional[bool] = None
+    max_tokens: int = 4096
+    key_attribution: str = "keys"
 
     def __post_init__(self):
         if self.available_bits is None:
@@ -104,8 +117,13 @@ class LlamaSmartKVAttention(nn.Module):
                                            position_embeddings=position_embeddings, cache_position=cache_position,
                                            **kwargs)
         kwargs.pop("past_key_values", None)
-        cache = self.smartkv_cache
         bsz, q_len, _ = hidden_states.size()
+        owner = getattr(self, "_owner", None)
+        if owner is not None:
+            owner()._select_cache(bsz)
+        cache = self.smartkv_cache
+        if isinstance(cache, BatchedSmartKVCache):
+            return self._forward_batched(cache, hidden_states, position_embeddings, position_ids, output_attentions)
         q = self.q_proj(hidden_states).view(bsz, q_len, self.num_heads, self.head_dim).transpose(1, 2)
         k = self.k_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
         v = self.v_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
@@ -151,6 +169,36 @@ class LlamaSmartKVAttention(nn.Module):
         return (attn_output, attn_weights) if output_attentions else (attn_output, None)
 
 
+    def _forward_batched(self, cache: BatchedSmartKVCache, hidden_states, position_embeddings, position_ids,
+                         output_attentions):
+        """Every batch row is its own sequence of ``cache``.  One query token: the fused packed kernels for the
+        whole batch.  More: causal attention over the unquantised prompt with torch, whose probabilities feed
+        the importance update before the prompt is stored (smartkv/models/llama_smartkv.py:392-427)."""
+        bsz, q_len, _ = hidden_states.size()
+        H, Hkv, D = self.num_heads, self.num_key_value_heads, self.head_dim
+        q = self.q_proj(hidden_states).view(bsz, q_len, H, D).transpose(1, 2)
+        k = self.k_proj(hidden_states).view(bsz, q_len, Hkv, D).transpose(1, 2)
+        v = self.v_proj(hidden_states).view(bsz, q_len, Hkv, D).transpose(1, 2)
+        q, k = self._apply_rotary_pos_emb(q, k, position_embeddings=position_embeddings, position_ids=position_ids)
+        self.token_counter += q_len
+        attn_weights = None
+        if q_len == 1:
+            out = cache.decode_layer(self.layer_idx, q[:, :, 0], k[:, :, 0], v[:, :, 0])
+            attn_output = out.to(hidden_states.dtype).reshape(bsz, 1, H * D)
+        else:
+            kk = k.repeat_interleave(self.num_key_value_groups, dim=1)
+            vv = v.repeat_interleave(self.num_key_value_groups, dim=1)
+            scores = torch.matmul(q, kk.transpose(2, 3)) / (D ** 0.5)
+            idx = torch.arange(q_len, device=scores.device)
+            scores = scores.masked_fill(idx[None, :] > idx[:, None], float("-inf"))
+            probs = torch.softmax(scores, dim=-1, dtype=torch.float32)
+            attn_weights = probs.to(q.dtype)
+            attn_output = torch.matmul(attn_weights, vv).transpose(1, 2).reshape(bsz, q_len, H * D)
+            cache.prefill_layer(self.layer_idx, k.transpose(1, 2), v.transpose(1, 2), attn_weights.float())
+        attn_output = self.o_proj(attn_output)
+        return (attn_output, attn_weights) if output_attentions else (attn_output, None)
+
+
 class LlamaSmartKV(nn.Module):
     """Wraps a Hugging Face Llama model (smartkv/models/llama_smartkv.py:596-792)."""
 
@@ -181,13 +229,16 @@ class LlamaSmartKV(nn.Module):
         special = [t for t in (getattr(cfg, "bos_token_id", None), getattr(cfg, "eos_token_id", None),
                                getattr(cfg, "pad_token_id", None)) if isinstance(t, int)] if cfg is not None else []
         c = self.smartkv_config
-        self.smartkv_cache = SmartKVCache(
+        self._geometry = dict(num_layers=len(layers), num_heads=num_kv, head_dim=head_dim, num_query_heads=num_q,
+                              special_token_ids=special)
+        self._batched_cache = None
+        self._single_cache = SmartKVCache(
             num_layers=len(layers), num_heads=num_kv, head_dim=head_dim, memory_budget=c.memory_budget, decay=c.decay,
             realloc_freq=c.realloc_freq, available_bits=c.available_bits, device=c.device, special_token_ids=special,
             enable_forecast=c.enable_forecast, forecast_history=c.forecast_history,
             forecast_update_interval=c.forecast_update_interval, forecast_blend=c.forecast_blend,
-            forecast_lr=c.forecast_lr, num_query_heads=num_q,
-            max_tokens=int(getattr(cfg, "smartkv_max_tokens", 4096)) if cfg is not None else 4096)
+            forecast_lr=c.forecast_lr, num_query_heads=num_q, max_tokens=c.max_tokens)
+        self.smartkv_cache = self._single_cache
         shared_rotary = getattr(self.model.model, "rotary_emb", None)
         for idx, layer in enumerate(layers):
             if not hasattr(layer, "self_attn"):
@@ -200,7 +251,32 @@ class LlamaSmartKV(nn.Module):
             if attn.rotary_emb is None and shared_rotary is not None:
                 attn.rotary_emb = shared_rotary
             attn.enable_smartkv(self.smartkv_cache)
+            object.__setattr__(attn, "_owner", weakref.ref(self))      # not a submodule: no reference cycle in nn.Module
             layer.self_attn = attn
+
+    def _select_cache(self, batch_size: int):
+        """The cache for a forward pass over ``batch_size`` rows: the multi-sequence one when asked for (or,
+        by default, whenever there is more than one row), built on first use."""
+        c = self.smartkv_config
+        batched = c.batched if c.batched is not None else batch_size > 1
+        want = self._single_cache
+        if batched:
+            bc = self._batched_cache
+            if bc is None or bc.batch_size != batch_size:
+                g = self._geometry
+                bc = BatchedSmartKVCache(
+                    num_layers=g["num_layers"], num_heads=g["num_heads"], head_dim=g["head_dim"],
+                    num_query_heads=g["num_query_heads"], batch_size=batch_size, max_tokens=c.max_tokens,
+                    memory_budget=c.memory_budget, decay=c.decay, realloc_freq=c.realloc_freq,
+                    available_bits=c.available_bits, device=c.device, special_token_ids=g["special_token_ids"],
+                    key_attribution=c.key_attribution)
+                self._batched_cache = bc
+            want = bc
+        if want is not self.smartkv_cache:
+            self.smartkv_cache = want
+            for layer in self._layers():
+                if isinstance(layer.self_attn, LlamaSmartKVAttention):
+                    layer.self_attn.smartkv_cache = want
 
     def enable_smartkv(self, memory_budget: Optional[float] = None, decay: Optional[float] = None,
                        realloc_freq: Optional[int] = None):
@@ -229,8 +305,9 @@ class LlamaSmartKV(nn.Module):
         return {} if self.smartkv_cache is None else self.smartkv_cache.get_memory_stats()
 
     def reset_cache(self):
-        if self.smartkv_cache is not None:
-            self.smartkv_cache.clear()
+        for cache in (getattr(self, "_single_cache", None), getattr(self, "_batched_cache", None)):
+            if cache is not None:
+                cache.clear()
         for layer in self._layers():
             if hasattr(layer.self_attn, "token_counter"):
                 layer.self_attn.token_counter = 0

@@ -215,6 +215,21 @@ class PackedKVStore:
         return seq, bucket, pos, storage
 
     def commit_step(self, plan):
+        """End of a decode step: the importance update still owed runs, then the step's token is entered into the
+        bookkeeping (counts, storage-order token ids).  A step whose token was committed early (a
+        reallocation in the middle of the step needs the token among the candidates) ends with
+        end_step() instead."""
+        self.end_step()
+        _seq, bucket, _pos, storage = plan
+        check(self.lib.skv_step_commit(ctypes.byref(self.desc), ptr(self.counts), ptr(self.slot_token),
+                                       ptr(self.next_token), ptr(bucket), ptr(storage), self._stream()),
+              "skv_step_commit")
+        self.appended_total += self.num_seqs
+        self.max_seq_tokens += 1
+        self._plan_valid = False
+
+    def end_step(self):
+        """The part of commit_step that does not touch the bookkeeping."""
         self.flush_importance()          # reads the counts as they stood during the step
         if torch.cuda.is_current_stream_capturing():
             # The head-importance EMA is double buffered and the half to read is a launch argument: a captured step
@@ -231,13 +246,6 @@ class PackedKVStore:
         if getattr(self, "_pipe", None) is not None:
             self._pipe["calls"] = 0      # every step starts on the same buffer set (CUDA graph replays rely on it)
             self._pipe["post_events"] = []
-        _seq, bucket, _pos, storage = plan
-        check(self.lib.skv_step_commit(ctypes.byref(self.desc), ptr(self.counts), ptr(self.slot_token),
-                                       ptr(self.next_token), ptr(bucket), ptr(storage), self._stream()),
-              "skv_step_commit")
-        self.appended_total += self.num_seqs
-        self.max_seq_tokens += 1
-        self._plan_valid = False
 
     # ------------------------------------------------------------------ kernels
     def append(self, layer: int, k: torch.Tensor, v: torch.Tensor, dst_seq, dst_bucket, dst_pos):
@@ -308,7 +316,7 @@ class PackedKVStore:
 
     def decode_layer(self, layer: int, query: torch.Tensor, cur_k: torch.Tensor, cur_v: torch.Tensor, step_plan,
                      update_importance: bool = True, out: Optional[torch.Tensor] = None,
-                     kernel_events=None, overlap: bool = False) -> torch.Tensor:
+                     kernel_events=None, overlap: bool = False, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One layer of a decode step in two launches: the streaming attention kernel, then one kernel
         with this layer's combine, the append of the new token (``step_plan`` from plan_step) and the
         importance update of the PREVIOUS decode_layer call (skv_post_attention).  The last layer's
@@ -318,7 +326,9 @@ class PackedKVStore:
         ``overlap``: the second launch goes to a side stream, so that it runs while the NEXT layer's attention
         kernel is already starting (it fills the SMs that kernel's CTAs leave early); the attention kernel of
         call m then only waits for the side work of call m-2 (partials are double, logits triple buffered).
-        The outputs of such a call are ready after join() / commit_step()."""
+        The outputs of such a call are ready after join() / commit_step().
+
+        ``mask``: additive fp32 [B, n] indexed by token id, natural-log units (see attention())."""
         q = query.contiguous()
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
@@ -335,9 +345,13 @@ class PackedKVStore:
         st = self._stream()
         if kernel_events is not None:
             kernel_events[0].record()
-        check(self.lib.skv_decode_attention(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q),
-                                            self._dtype_code(q), self.num_q_heads, ptr(partials), self.num_ctas,
-                                            ptr(bufs["logits"]) if want_logits else None, ptr(self.err), st),
+        if mask is not None:
+            assert mask.dtype == torch.float32 and mask.is_contiguous() and mask.shape[0] == self.num_seqs
+        check(self.lib.skv_decode_attention_masked(ctypes.byref(self.desc), ptr(self.arena), layer, ptr(self.plan), ptr(q),
+                                                   self._dtype_code(q), self.num_q_heads, ptr(partials), self.num_ctas,
+                                                   ptr(bufs["logits"]) if want_logits else None, ptr(mask),
+                                                   0 if mask is None else int(mask.shape[1]),
+                                                   ptr(self.slot_token) if mask is not None else None, ptr(self.err), st),
               "skv_decode_attention")
         if kernel_events is not None:
             kernel_events[1].record()
@@ -422,6 +436,21 @@ class PackedKVStore:
             return
         torch.cuda.current_stream(self.device).wait_event(pipe["post_events"][-1])
         pipe["forked"] = False
+
+    def take_pending_logits(self):
+        """Cancels the importance update owed by the last decode_layer call and hands its inputs to the caller:
+        (logits fp32 [B, Hq, slots] in base-2 units, running max [B, Hq], sum [B, Hq], probability of the current
+        token [B, Hq]); the probability of the key at storage index s is exp2(logit - max) / sum.  For callers
+        that attribute the attention mass themselves."""
+        pipe = getattr(self, "_pipe", None)
+        if pipe is None or pipe["pending"] is None:
+            return None
+        self.join()
+        pend = pipe["pending"]
+        pipe["pending"] = None
+        sm = pipe["small"]
+        return (pipe["bufs"][pend["buf"]]["logits"], sm["lse_max"][pend["layer"]], sm["lse_sum"][pend["layer"]],
+                sm["cur_prob"][pend["layer"]])
 
     def flush_importance(self):
         """Runs the importance update still owed by the last decode_layer call (no-op otherwise)."""

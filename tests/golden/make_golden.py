@@ -293,11 +293,81 @@ def gen_config0(out):
     out["c0_probs_head0"] = p.numpy()[0, 0, 0]
 
 
+WRAPPER_LAYERS, WRAPPER_PROMPT, WRAPPER_STEPS, WRAPPER_BATCH = 5, 80, 48, 2
+
+
+def gen_wrapper(out):
+    """The reference's LlamaSmartKV on CPU (fused CPU decode path, fp32), one sequence at a time, on a random-init
+    Llama of TinyLlama's attention shape reduced to WRAPPER_LAYERS layers: budget 0.5, realloc_freq 16, a prompt of
+    WRAPPER_PROMPT tokens and WRAPPER_STEPS greedy decode steps.  Two departures from a stock run, both outside the
+    reference's arithmetic: ``apply_rotary_pos_emb`` is called with the four arguments the installed transformers
+    accepts, and the cache counts packed bytes against the budget as it does on a CUDA device (see the module
+    docstring).  Decode calls pass ``position_ids`` and a zero additive mask over the cached keys plus the new one,
+    which is what the wrapper's fused path slices (smartkv/models/llama_smartkv.py:283-288).  Per sequence and
+    step the fixture keeps the logits at 256 probe columns, the top-8 columns, and the greedy token; after the
+    last step the width of every token and the reallocation count."""
+    import smartkv.models.llama_smartkv as rl
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb as hf_rope
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("e2e_model", os.path.join(HERE, "..", "e2e_model.py"))
+    e2e = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(e2e)
+    probe_columns, prompts, tiny_llama = e2e.probe_columns, e2e.prompts, e2e.tiny_llama
+    rl.apply_rotary_pos_emb = lambda q, k, c, s, p=None: hf_rope(q, k, c, s)
+    n, steps, B = WRAPPER_PROMPT, WRAPPER_STEPS, WRAPPER_BATCH
+    ids = prompts(B, n)
+    cols = probe_columns()
+    out["w_prompts"] = ids.numpy()
+    out["w_cols"] = cols.numpy()
+    out["w_shape"] = np.array([WRAPPER_LAYERS, n, steps, B])
+    probe = np.zeros((B, steps + 1, cols.numel()), np.float32)
+    topv = np.zeros((B, steps + 1, 8), np.float32)
+    topi = np.zeros((B, steps + 1, 8), np.int64)
+    greedy = np.zeros((B, steps + 1), np.int64)
+    bits_final = np.zeros((B, n + steps), np.uint8)
+    reallocs = np.zeros(B, np.int64)
+    hist = np.zeros((B, steps + 1, 4), np.int64)
+    for b in range(B):
+        model = tiny_llama(WRAPPER_LAYERS)
+        w = rl.LlamaSmartKV(model, rl.SmartKVConfig(enabled=True, memory_budget=0.5, realloc_freq=16, device="cpu"))
+        c = w.smartkv_cache
+        c.use_packing = True
+        c.min_budget = compute_minimum_budget(c.num_heads, c.head_dim, c.scale_dtype, True)
+        c.layer_store = [c._init_layer_store() for _ in range(c.num_layers)]
+        w.set_use_fused_cpu(True)
+
+        def record(t, logits):
+            row = logits[0, -1].float()
+            probe[b, t] = row[cols].numpy()
+            tv, ti = row.topk(8)
+            topv[b, t], topi[b, t] = tv.numpy(), ti.numpy()
+            greedy[b, t] = int(row.argmax())
+            pm = np.array(list(c.precision_map.values()))
+            hist[b, t] = [(pm == x).sum() for x in (2, 3, 4, 8)]
+
+        with torch.no_grad():
+            o = w(input_ids=ids[b:b + 1], position_ids=torch.arange(n)[None], use_cache=False)
+            record(0, o.logits)
+            for s in range(steps):
+                tok = torch.tensor([[greedy[b, s]]])
+                o = w(input_ids=tok, position_ids=torch.tensor([[n + s]]),
+                      attention_mask=torch.zeros(1, 1, 1, n + s + 1), use_cache=False)
+                record(s + 1, o.logits)
+        bits_final[b] = [c.precision_map[t] for t in range(n + steps)]
+        reallocs[b] = c.realloc_counter
+        del w, model
+    out.update(w_probe=probe, w_topv=topv, w_topi=topi, w_greedy=greedy, w_bits=bits_final, w_reallocs=reallocs,
+               w_hist=hist)
+
+
 def main():
     torch.manual_seed(0)
     torch.set_num_threads(4)
-    for name, fn in [("quant", gen_quant), ("attention", gen_attention), ("importance", gen_importance),
-                     ("allocation", gen_allocation), ("requant", gen_requant), ("config0", gen_config0)]:
+    gens = [("quant", gen_quant), ("attention", gen_attention), ("importance", gen_importance),
+            ("allocation", gen_allocation), ("requant", gen_requant), ("config0", gen_config0),
+            ("wrapper", gen_wrapper)]
+    only = sys.argv[1:]          # optional: names of the fixtures to regenerate
+    for name, fn in [g for g in gens if not only or g[0] in only]:
         out = {}
         fn(out)
         path = os.path.join(HERE, f"{name}.npz")

@@ -157,3 +157,49 @@ def test_config0_golden_pipeline(golden):
     p = np.exp2(logits[:, valid][:, order] - lmax[:, None]) / lsum[:, None]
     mass = np.concatenate([p.sum(0), [store.cur_prob.cpu().numpy()[0].sum()]])
     assert_close(mass, g["c0_keymass"], 1e-4, 2e-3, "config 0 key mass")
+
+
+def test_wait_limit_expiry_sets_the_error_flag_and_leaves_the_context_usable():
+    """Every device-side wait of the attention kernel is bounded.  With the limit cut to one poll the consumer
+    warps give up before the first bytes can have arrived: the launch must still return, report the timeout
+    through the error flag, and the same store must give the right answer once the limit is restored."""
+    lib = _lib.lib()
+    store = run_case(32, 8, 128, [3000, 500], seed=77)
+    rng = np.random.default_rng(0)
+    q = torch.from_numpy(rng.standard_normal((2, 32, 128)).astype(np.float32)).cuda()
+    good = store.attention(0, q).clone()
+    store.check_errors()
+    assert lib.skv_set_wait_limit(1) == 0
+    try:
+        store.attention(0, q)
+        torch.cuda.synchronize()
+        with pytest.raises(_lib.SmartKVLibraryError, match="wait"):
+            store.check_errors()
+    finally:
+        assert lib.skv_set_wait_limit(1 << 24) == 0
+    store.err.zero_()
+    again = store.attention(0, q).clone()
+    store.check_errors()
+    assert torch.equal(again, good)
+
+
+@pytest.mark.parametrize("q_dtype", [np.float16, np.float32])
+def test_large_value_magnitudes_do_not_overflow_fp16(q_dtype):
+    """V rows of magnitude 1e3..1e4 at 2 and 3 bits have V scales in the thousands, and the P operand of the
+    P.V product is probability x V scale in fp16.  The kernel raises its running maximum for such tiles, so the
+    output stays finite and within the tolerance scaled by the magnitude of V."""
+    hq, hkv, d, n = 32, 8, 128, 515
+    rng = np.random.default_rng(21)
+    k, v = orc.synth_kv(n, hkv, d, seed=21)
+    v = (v * rng.uniform(1e3, 1e4, size=(n, hkv, 1))).astype(np.float32)
+    v[::7] *= 1e-4                                   # ordinary rows next to the outliers
+    bits = rng.choice([2, 3], size=n)
+    store = make_store(1, 1, hkv, d, hq, n)
+    fill_store(store, [(k[None], v[None])], bits[None])
+    q = (4.0 * rng.standard_normal((1, hq, d))).astype(q_dtype)      # peaked softmax: probabilities near one
+    out = store.attention(0, torch.from_numpy(q).cuda()).cpu().numpy()[0]
+    store.check_errors()
+    assert np.all(np.isfinite(out))
+    kq, vq, ks, vs = oracle_quantized(k, v, bits)
+    ref, _ = oracle_attention(q[0].astype(np.float32), kq, vq, ks, vs, hq // hkv)
+    assert_close(out, ref, 2e-3 * 1e4, 2e-3, "large V magnitudes")
