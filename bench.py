@@ -156,6 +156,149 @@ def algorithmic_bytes_per_layer(counts, cfg):
     return int((np.asarray(counts, np.int64) * per_tok).sum())
 
 
+# ----------------------------------------------------------------------------- end-to-end generation (--config 2)
+GENERATION = dict(name="random-init TinyLlama-1.1B", num_layers=22, hidden=2048, intermediate=5632, num_q_heads=32,
+                  num_kv_heads=4, head_dim=64, vocab=32000, batch=8, prompt=512, decode=256, memory_budget=0.5,
+                  available_bits=(2, 3, 4, 8), realloc_freq=16)
+
+
+def generation_workload_string(g):
+    return (f"{g['name']} ({g['num_layers']} layers, hidden {g['hidden']}, {g['num_q_heads']} query / {g['num_kv_heads']} KV "
+            f"heads, vocab {g['vocab']}, weights N(0, 0.02)), batch {g['batch']}, prompt {g['prompt']} uniform-random ids, "
+            f"{g['decode']} greedy decode tokens, budget {g['memory_budget']}, bits [2,3,4,8]; one step = one decode token "
+            "per sequence through the LlamaSmartKV wrapper")
+
+
+def build_generation_model(g, device, dtype, seed=0):
+    import torch
+    import transformers
+    cfg = transformers.LlamaConfig(vocab_size=g["vocab"], hidden_size=g["hidden"], intermediate_size=g["intermediate"],
+                                   num_hidden_layers=g["num_layers"], num_attention_heads=g["num_q_heads"],
+                                   num_key_value_heads=g["num_kv_heads"], max_position_embeddings=2048, rms_norm_eps=1e-5,
+                                   tie_word_embeddings=False, bos_token_id=1, eos_token_id=2, pad_token_id=None)
+    cfg._attn_implementation = "eager"
+    with torch.device("meta"):
+        model = transformers.LlamaForCausalLM(cfg)
+    model = model.to_empty(device=device).to(dtype).eval()
+    gen = torch.Generator(device=device).manual_seed(seed)
+    with torch.no_grad():
+        for _name, p_ in sorted(model.named_parameters(), key=lambda kv: kv[0]):
+            if p_.dim() >= 2:
+                p_.copy_(torch.empty(p_.shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=gen))
+            else:
+                p_.fill_(1.0)
+        # buffers created on the meta device (rotary inverse frequencies) need their values back
+        for m in model.modules():
+            if hasattr(m, "inv_freq") and hasattr(m, "rope_init_fn"):
+                inv, _ = m.rope_init_fn(m.config, device)
+                m.inv_freq = inv
+                m.original_inv_freq = inv
+    return model
+
+
+def run_generation(args):
+    """BASELINE configuration 2 through the public wrapper: prompt prefill, then greedy decoding with every
+    batch row an independent sequence of one multi-sequence cache.  value = decode tokens per second over the
+    whole batch (device events around all decode steps; the greedy token of every step is read back to the
+    host inside the timed region, as a generation loop does)."""
+    import torch
+    from smartkv_b200 import LlamaSmartKV, SmartKVConfig
+    g = dict(GENERATION)
+    if args.batch:
+        g["batch"] = args.batch
+    if args.layers:
+        g["num_layers"] = args.layers
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    model = build_generation_model(g, dev, torch.float16)
+    w = LlamaSmartKV(model, SmartKVConfig(enabled=True, memory_budget=g["memory_budget"], realloc_freq=g["realloc_freq"],
+                                          available_bits=list(g["available_bits"]), device=str(dev), batched=True,
+                                          max_tokens=g["prompt"] + g["decode"] + 8))
+    B, n, T = g["batch"], g["prompt"], g["decode"]
+    ids = torch.randint(3, g["vocab"], (B, n), generator=torch.Generator().manual_seed(1)).to(dev)
+    pos = torch.arange(n, device=dev)[None].expand(B, -1)
+    sampler = ClockSampler(dev.index or 0)
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    results = []
+    for rep in range(2):                 # the first pass warms every kernel and allocation; the second is timed
+        w.reset_cache()
+        torch.cuda.synchronize(dev)
+        if rep == 1:
+            sampler.start()
+        with torch.no_grad():
+            e[0].record()
+            out = w(input_ids=ids, position_ids=pos, use_cache=False)
+            tok = out.logits[:, -1].argmax(-1)
+            e[1].record()
+            toks = []
+            for t in range(T):
+                toks.append(tok.tolist())       # the host sees every token, as a generation loop does
+                out = w(input_ids=tok[:, None], position_ids=torch.full((B, 1), n + t, device=dev), use_cache=False)
+                tok = out.logits[:, -1].argmax(-1)
+            e[2].record()
+        torch.cuda.synchronize(dev)
+        results.append((e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])))
+    clocks = sampler.stop()
+    w.smartkv_cache.check_errors()
+    stats = w.get_smartkv_stats()
+    prefill_ms, decode_ms = results[-1]
+    line = {
+        "metric": "decode_tokens_per_s", "value": round(B * T / (decode_ms / 1e3), 2), "unit": "tokens/s", "n_gpus": 1,
+        "steps": T, "warmup": T, "ms_per_step": round(decode_ms / T, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic (random-init weights, uniform-random prompt ids)",
+        "config": {"workload": generation_workload_string(g)},
+        "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(B * n / (prefill_ms / 1e3), 1),
+        "reallocations": stats.get("realloc_count"), "memory_ratio_true_max": round(stats.get("memory_ratio_true_max", 0.0), 4),
+        "precision_distribution": stats.get("precision_distribution"), "clocks": clocks,
+        "launches_per_layer_per_step": 2,
+    }
+    print(json.dumps(line))
+
+
+def run_generation_reference(args):
+    """The reference's own wrapper on the host cores (fp32: its CPU path has no fp16 matmul), one sequence, a
+    bounded sample: the full prompt, then --decode-sample greedy steps.  Needs the reference package on
+    PYTHONPATH; it is not part of this repository."""
+    import torch
+    g = dict(GENERATION)
+    if args.layers:
+        g["num_layers"] = args.layers
+    try:
+        import smartkv.models.llama_smartkv as rl
+        from transformers.models.llama.modeling_llama import apply_rotary_pos_emb as hf_rope
+    except Exception as ex:                      # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference package is not importable here ({type(ex).__name__}); "
+                          "its CPU wrapper was timed in the build container, see BASELINE.md"}))
+        return
+    rl.apply_rotary_pos_emb = lambda q, k, c, s, p=None: hf_rope(q, k, c, s)    # the installed transformers takes 4 arguments
+    model = build_generation_model(g, torch.device("cpu"), torch.float32)
+    w = rl.LlamaSmartKV(model, rl.SmartKVConfig(enabled=True, memory_budget=g["memory_budget"], realloc_freq=g["realloc_freq"],
+                                                device="cpu"))
+    w.set_use_fused_cpu(True)
+    n, T = g["prompt"], args.decode_sample
+    ids = torch.randint(3, g["vocab"], (1, n), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        out = w(input_ids=ids, position_ids=torch.arange(n)[None], use_cache=False)
+        tok = out.logits[:, -1].argmax(-1)
+        t1 = time.perf_counter()
+        for t in range(T):
+            out = w(input_ids=tok[:, None], position_ids=torch.tensor([[n + t]]),
+                    attention_mask=torch.zeros(1, 1, 1, n + t + 1), use_cache=False)
+            tok = out.logits[:, -1].argmax(-1)
+        t2 = time.perf_counter()
+    per_tok = (t2 - t1) / T
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": round(1.0 / per_tok, 3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": T, "warmup": 0, "ms_per_step": round(per_tok * 1e3, 2), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (random-init weights, uniform-random prompt ids)",
+            "config": {"workload": generation_workload_string(g),
+                       "sample": f"one sequence (the reference's cache holds one), prompt {n}, {T} decode steps on {torch.get_num_threads()} threads"},
+            "prefill_ms": round((t1 - t0) * 1e3, 1),
+            "cpu_baseline": {"value": round(1.0 / per_tok, 3), "unit": "tokens/s", "cores": torch.get_num_threads(),
+                             "kind": "reference", "sample": f"prompt {n} + {T} decode steps, one sequence"}}
+    print(json.dumps(line))
+
+
 # ----------------------------------------------------------------------------- our arm
 def profile_traffic(kernel_name):
     """DRAM bytes per launch of `kernel_name` on the config-1 shape as the committed ncu summary states them
@@ -617,13 +760,30 @@ def run_ours(args):
 
 
 # ----------------------------------------------------------------------------- CPU baseline
+def _reference_modules():
+    """The reference's own CPU modules when its package is importable (a checkout on PYTHONPATH); else None."""
+    try:
+        import torch
+        from smartkv.core._quant_cpu import quantize_per_head
+        from smartkv.core.cache import SmartKVCache
+        from smartkv.core.fused_cpu import quantized_attention_streaming_cpu
+        from smartkv.core.importance import ImportanceTracker
+        return dict(torch=torch, quantize_per_head=quantize_per_head, SmartKVCache=SmartKVCache,
+                    attention=quantized_attention_streaming_cpu, ImportanceTracker=ImportanceTracker)
+    except Exception:       # noqa: BLE001
+        return None
+
+
 def cpu_baseline(cfg, budget_s=15.0):
-    """The oracle port of the reference CPU path timed on this host: for one (sequence, layer) at the
-    full context the streaming attention over int8 codes with the reference's GQA expansion, the
-    importance update and the append-quantize; plus, once, the allocator for one sequence and the
-    requantisation of its changed tokens in one layer.  The step time is scaled to batch x layers
-    (reallocation amortised over realloc_every steps); GB/s counts the same algorithmic packed bytes."""
+    """The reference CPU path timed on this host: for one (sequence, layer) at the full context the streaming
+    attention over int8 codes with the reference's GQA expansion, the importance update and the
+    append-quantize; plus, once, the allocator for one sequence and the requantisation of its changed tokens in
+    one layer.  The step time is scaled to batch x layers (reallocation amortised over realloc_every steps);
+    GB/s counts the same algorithmic packed bytes.  When the reference package is importable its own functions
+    are the ones timed (kind "reference": smartkv.core.fused_cpu, smartkv.core.importance, smartkv.core._quant_cpu
+    and SmartKVCache._solve_allocation); otherwise the oracle's restatement of them (kind "port")."""
     from oracle import smartkv_oracle as orc
+    ref = _reference_modules()
     try:
         from threadpoolctl import threadpool_info
         threads = max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
@@ -633,11 +793,28 @@ def cpu_baseline(cfg, budget_s=15.0):
     g = Hq // Hkv
     k, v = orc.synth_kv(N, Hkv, D, seed=0)
     imp0 = zipf_importance(N, 0, cfg["zipf_s"])
-    acfg = orc.AllocatorConfig(Hkv, D, cfg["memory_budget"], cfg["available_bits"])
     scores = {t: (float("inf") if t < 4 else float(imp0[t])) for t in range(N)}
-    t0 = time.perf_counter()
-    alloc = orc.solve_allocation(acfg, range(N), scores, {})
-    alloc_s = time.perf_counter() - t0
+    if ref is not None:
+        import warnings
+        torch = ref["torch"]
+        threads = torch.get_num_threads()
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            rc = ref["SmartKVCache"](num_layers=1, num_heads=Hkv, head_dim=D, memory_budget=0.9,
+                                     available_bits=list(cfg["available_bits"]), device="cpu")
+        # packed-byte accounting as on a CUDA device (the CPU constructor turns it off)
+        from smartkv.core.allocation import compute_minimum_budget
+        rc.use_packing = True
+        rc.min_budget = compute_minimum_budget(Hkv, D, rc.scale_dtype, True)
+        rc.memory_budget = cfg["memory_budget"]
+        t0 = time.perf_counter()
+        alloc = rc._solve_allocation(set(range(N)), scores, rc.protected_tokens | rc.special_token_ids)
+        alloc_s = time.perf_counter() - t0
+    else:
+        acfg = orc.AllocatorConfig(Hkv, D, cfg["memory_budget"], cfg["available_bits"])
+        t0 = time.perf_counter()
+        alloc = orc.solve_allocation(acfg, range(N), scores, {})
+        alloc_s = time.perf_counter() - t0
     bits = np.array([alloc[t] for t in range(N)], np.int64)
     # stored at 4 bits, then requantised from the stored codes to the allocated widths (one layer)
     k4, ks4 = orc.quantize_rows(k, 4)
@@ -646,7 +823,15 @@ def cpu_baseline(cfg, budget_s=15.0):
     t0 = time.perf_counter()
     for w in (2, 3, 8):
         sel = bits == w
-        if sel.any():
+        if not sel.any():
+            continue
+        if ref is not None:      # cache.py:819-844: dequantise the stored codes, quantise again at the new width
+            torch = ref["torch"]
+            kd = torch.from_numpy(k4[sel].astype(np.float32) * ks4[sel][..., None])
+            vd = torch.from_numpy(v4[sel].astype(np.float32) * vs4[sel][..., None])
+            a, b_, c_, d_ = ref["quantize_per_head"](kd, vd, int(w))
+            kq[sel], vq[sel], ks[sel], vs[sel] = a.numpy(), b_.numpy(), c_.numpy(), d_.numpy()
+        else:
             kq[sel], ks[sel] = orc.requantize_rows(k4[sel], ks4[sel], w)
             vq[sel], vs[sel] = orc.requantize_rows(v4[sel], vs4[sel], w)
     requant_s = time.perf_counter() - t0
@@ -656,15 +841,31 @@ def cpu_baseline(cfg, budget_s=15.0):
     cv = rng.standard_normal((1, Hkv, D)).astype(np.float32)
     counts = np.array([[(bits == w).sum() for w in (2, 3, 4, 8)]])
     nbytes = algorithmic_bytes_per_layer(counts, cfg)
-    imp = orc.ImportanceState(1)
+    if ref is not None:
+        torch = ref["torch"]
+        tq, tkq, tks, tvq, tvs = (torch.from_numpy(x) for x in (q, kq, ks, vq, vs))
+        tck, tcv = torch.from_numpy(ck), torch.from_numpy(cv)
+        tracker = ref["ImportanceTracker"](1, decay=0.9, device="cpu")
+        ids = list(range(N + 1))
 
-    def one():
-        # the reference expands K/V to the query heads on every call (llama_smartkv.py:274-281)
-        o, p = orc.streaming_attention(q, orc.expand_gqa(kq, g), orc.expand_gqa(ks, g), orc.expand_gqa(vq, g),
-                                       orc.expand_gqa(vs, g), tile_size=2048, current_k=orc.expand_gqa(ck, g),
-                                       current_v=orc.expand_gqa(cv, g))
-        imp.update(0, p, range(N + 1))
-        orc.quantize_per_head(ck[0][None], cv[0][None], 4)
+        def one():
+            # the wrapper expands K/V to the query heads on every call (llama_smartkv.py:274-281)
+            o, p = ref["attention"](tq, tkq.repeat_interleave(g, dim=1), tks.repeat_interleave(g, dim=1),
+                                    tvq.repeat_interleave(g, dim=1), tvs.repeat_interleave(g, dim=1), tile_size=2048,
+                                    current_k=tck.repeat_interleave(g, dim=1), current_v=tcv.repeat_interleave(g, dim=1),
+                                    return_attn=True)
+            tracker.update_attention(0, p, ids)
+            ref["quantize_per_head"](tck, tcv, 4)
+    else:
+        imp = orc.ImportanceState(1)
+
+        def one():
+            # the reference expands K/V to the query heads on every call (llama_smartkv.py:274-281)
+            o, p = orc.streaming_attention(q, orc.expand_gqa(kq, g), orc.expand_gqa(ks, g), orc.expand_gqa(vq, g),
+                                           orc.expand_gqa(vs, g), tile_size=2048, current_k=orc.expand_gqa(ck, g),
+                                           current_v=orc.expand_gqa(cv, g))
+            imp.update(0, p, range(N + 1))
+            orc.quantize_per_head(ck[0][None], cv[0][None], 4)
     one()
     t0 = time.perf_counter()
     it = 0
@@ -676,7 +877,8 @@ def cpu_baseline(cfg, budget_s=15.0):
     dt = (time.perf_counter() - t0) / it
     B, L, every = cfg["batch"], cfg["num_layers"], cfg["realloc_every"]
     step_s = dt * B * L + (alloc_s * B + requant_s * B * L) / every
-    return {"value": round(nbytes * B * L / step_s / 1e9, 4), "unit": "GB/s", "cores": int(threads), "kind": "port",
+    return {"value": round(nbytes * B * L / step_s / 1e9, 4), "unit": "GB/s", "cores": int(threads),
+            "kind": "reference" if ref is not None else "port",
             "sample": f"1 sequence x 1 layer at context {N} (attention + importance + append-quantize), {it} iterations, "
                       f"{dt * 1e3:.1f} ms each; allocator for one sequence {alloc_s * 1e3:.0f} ms and requantisation of "
                       f"one (sequence, layer) {requant_s * 1e3:.0f} ms, once; step time scaled to batch {B} x {L} "
@@ -732,12 +934,17 @@ def main():
                     help="override the layer count (profiler captures of a small case only; not a bench line)")
     ap.add_argument("--attn-kernel", default="auto", choices=["auto", "fragment", "tensor_memory"],
                     help="auto: both decode-attention kernels are timed on the populated cache and the faster one runs")
-    ap.add_argument("--config", type=int, default=1, choices=sorted(CONFIGS),
-                    help="1 (default, the bench line), 3 (long context, sequence shards) or 4 (70B shape, KV-head shards)")
+    ap.add_argument("--config", type=int, default=1, choices=sorted(CONFIGS) + [2],
+                    help="1 (default, the bench line), 3 (long context, sequence shards), 4 (70B shape, KV-head shards) or "
+                         "2 (end-to-end generation through the LlamaSmartKV wrapper; decode tokens/s, one GPU)")
+    ap.add_argument("--decode-sample", type=int, default=16, help="--config 2 --impl reference: decode steps to time")
     ap.add_argument("--replicas", action="store_true", help="under torchrun: every rank holds the whole configuration (weak scaling)")
     ap.add_argument("--no-settle", action="store_true", help="skip the untimed reallocation cycles before the timed passes")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.config == 2:
+        if int(os.environ.get("RANK", "0")) == 0:
+            (run_generation_reference if args.impl == "reference" else run_generation)(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -297,13 +297,16 @@ WRAPPER_LAYERS, WRAPPER_PROMPT, WRAPPER_STEPS, WRAPPER_BATCH = 5, 80, 48, 2
 
 
 def gen_wrapper(out):
-    """The reference's LlamaSmartKV on CPU (fused CPU decode path, fp32), one sequence at a time, on a random-init
-    Llama of TinyLlama's attention shape reduced to WRAPPER_LAYERS layers: budget 0.5, realloc_freq 16, a prompt of
-    WRAPPER_PROMPT tokens and WRAPPER_STEPS greedy decode steps.  Two departures from a stock run, both outside the
+    """The reference's LlamaSmartKV on CPU (fp32), one sequence at a time, on a random-init Llama of TinyLlama's
+    attention shape reduced to WRAPPER_LAYERS layers: budget 0.5, realloc_freq 16, a prompt of WRAPPER_PROMPT
+    tokens and WRAPPER_STEPS greedy decode steps.  Two departures from a stock run, both outside the
     reference's arithmetic: ``apply_rotary_pos_emb`` is called with the four arguments the installed transformers
     accepts, and the cache counts packed bytes against the budget as it does on a CUDA device (see the module
-    docstring).  Decode calls pass ``position_ids`` and a zero additive mask over the cached keys plus the new one,
-    which is what the wrapper's fused path slices (smartkv/models/llama_smartkv.py:283-288).  Per sequence and
+    docstring).  Decode steps take the wrapper's dequantise-then-attend path (use_fused_cpu off,
+    smartkv/models/llama_smartkv.py:392-414): with packed accounting switched on, a configuration the CPU
+    constructor never produces, ``retrieve_all_quantized`` returns codes that disagree with ``retrieve_all`` (max
+    difference 3.3 on this model), so the fused CPU path computes attention over wrong keys; on the stock unpacked
+    store the two paths agree to 5e-6.  Decode calls pass ``position_ids`` and a zero additive mask.  Per sequence and
     step the fixture keeps the logits at 256 probe columns, the top-8 columns, and the greedy token; after the
     last step the width of every token and the reallocation count."""
     import smartkv.models.llama_smartkv as rl
@@ -327,6 +330,8 @@ def gen_wrapper(out):
     bits_final = np.zeros((B, n + steps), np.uint8)
     reallocs = np.zeros(B, np.int64)
     hist = np.zeros((B, steps + 1, 4), np.int64)
+    bits_prefill = np.zeros((B, n), np.uint8)
+    k0_prefill = np.zeros((B, n, 4, 64), np.float32)          # layer 0 keys as stored (dequantised) after the prompt
     for b in range(B):
         model = tiny_llama(WRAPPER_LAYERS)
         w = rl.LlamaSmartKV(model, rl.SmartKVConfig(enabled=True, memory_budget=0.5, realloc_freq=16, device="cpu"))
@@ -334,7 +339,7 @@ def gen_wrapper(out):
         c.use_packing = True
         c.min_budget = compute_minimum_budget(c.num_heads, c.head_dim, c.scale_dtype, True)
         c.layer_store = [c._init_layer_store() for _ in range(c.num_layers)]
-        w.set_use_fused_cpu(True)
+        w.set_use_fused_cpu(False)
 
         def record(t, logits):
             row = logits[0, -1].float()
@@ -348,6 +353,8 @@ def gen_wrapper(out):
         with torch.no_grad():
             o = w(input_ids=ids[b:b + 1], position_ids=torch.arange(n)[None], use_cache=False)
             record(0, o.logits)
+            bits_prefill[b] = [c.precision_map[t] for t in range(n)]
+            k0_prefill[b] = c.retrieve_all(0)[0].numpy()
             for s in range(steps):
                 tok = torch.tensor([[greedy[b, s]]])
                 o = w(input_ids=tok, position_ids=torch.tensor([[n + s]]),
@@ -357,7 +364,7 @@ def gen_wrapper(out):
         reallocs[b] = c.realloc_counter
         del w, model
     out.update(w_probe=probe, w_topv=topv, w_topi=topi, w_greedy=greedy, w_bits=bits_final, w_reallocs=reallocs,
-               w_hist=hist)
+               w_hist=hist, w_bits_prefill=bits_prefill, w_k0_prefill=k0_prefill)
 
 
 def main():
