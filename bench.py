@@ -197,7 +197,7 @@ def build_generation_model(g, device, dtype, seed=0):
 
 
 def run_generation(args):
-    """BASELINE configuration 2 through the public wrapper: prompt prefill, then greedy decoding with every
+    """End-to-end generation (the TinyLlama-1.1B workload) through the public wrapper: prompt prefill, then greedy decoding with every
     batch row an independent sequence of one multi-sequence cache.  value = decode tokens per second over the
     whole batch (device events around all decode steps; the greedy token of every step is read back to the
     host inside the timed region, as a generation loop does)."""

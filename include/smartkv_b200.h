@@ -258,6 +258,9 @@ int skv_decode_attention_static(const SkvStoreDesc* desc, const void* store, int
  *   importance update; dst_seq == NULL skips the append (store may then be NULL).
  *   max_seq_tokens: an upper bound of the cached tokens of any sequence if the caller knows one (the
  *   importance blocks are then launched for that many storage indices only), 0 otherwise.
+ *   Under CUDA-graph capture both host scalars are frozen into the graph: pass max_seq_tokens = 0 (the
+ *   cache grows between replays), and capture an even number of importance updates per graph, because
+ *   `parity` must alternate from one update to the next and a replay repeats the captured values.
  * No counterpart in the reference, which runs these steps as host Python
  * (smartkv/core/fused_cpu.py:115-167, cache.py:216-279, :1187-1355). */
 int skv_post_attention(const SkvStoreDesc* desc, void* store, int layer, const void* plan, const void* query,

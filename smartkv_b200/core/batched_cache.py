@@ -80,6 +80,7 @@ class BatchedSmartKVCache:
         self._slot_index = torch.arange(slots, dtype=torch.int64, device=dev)
         self._rows = torch.arange(self.batch_size, dtype=torch.int64, device=dev)
         self._mask = torch.zeros((self.batch_size, self.max_tokens), dtype=torch.float32, device=dev)
+        self._staging_budget = 256 << 20
         self.clear()
 
     # ------------------------------------------------------------------ bookkeeping
@@ -142,8 +143,12 @@ class BatchedSmartKVCache:
             tok = st.slot_token.long().clamp(min=0)
             age = float(self.global_step) - self.last_seen[tok]
             recency = torch.exp(-age / self.recency_temperature).contiguous()
-        new_bits, _, _ = st.allocate_bits(self._cfg, recency=recency)
-        st.repack(new_bits, max_moves=self.batch_size * max(self.num_known, 1))
+        if recency is None:
+            # allocator + repack are some seventy small launches; replayed as one CUDA graph after the first time
+            st.reallocate_graphed(self._cfg, staging_budget=self._staging_budget)
+        else:
+            new_bits, _, _ = st.allocate_bits(self._cfg, recency=recency)
+            st.repack(new_bits, max_moves=self.batch_size * max(self.num_known, 1))
         self.realloc_counter += 1
 
     def _weights(self, head_mean: torch.Tensor) -> torch.Tensor:

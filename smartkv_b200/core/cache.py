@@ -190,6 +190,7 @@ class SmartKVCache:
         old = self.store
         old_slot, old_bucket_tokens = dict(self._slot), [list(t) for t in self._bucket_tokens]
         old_layers, old_committed = {t: set(s) for t, s in self._layers_of.items()}, list(self._committed)
+        realloc_due = self._realloc_due         # a reallocation waiting for the step's token must survive the move
         self._pull_device_importance()
         self._init_store(2 * (self._max_tokens + 1))
         new = self.store
@@ -228,6 +229,8 @@ class SmartKVCache:
         new.head_state.copy_(old.head_state)
         new.head_parity = old.head_parity
         new.appended_total = old.appended_total
+        new.max_seq_tokens = old.max_seq_tokens
+        self._realloc_due = realloc_due
         self._dev_base = new.cumulative.clone()
         torch.cuda.synchronize(dev)
 

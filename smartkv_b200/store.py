@@ -231,21 +231,20 @@ class PackedKVStore:
     def end_step(self):
         """The part of commit_step that does not touch the bookkeeping."""
         self.flush_importance()          # reads the counts as they stood during the step
-        if torch.cuda.is_current_stream_capturing():
-            # The head-importance EMA is double buffered and the half to read is a launch argument: a captured step
-            # replays the same arguments, which is only right if the step flips the parity an even number of times.
-            n = getattr(self, "_capture_updates", 0)
-            self._capture_updates = 0
-            if n % 2:
-                raise _lib.SmartKVLibraryError(
-                    f"a CUDA-graph-captured decode step holds {n} importance updates; it must hold an even number "
-                    "(the head-importance state is double buffered by launch argument): capture two steps per graph "
-                    "or run this model's steps without a graph")
-        else:
-            self._capture_updates = 0
         if getattr(self, "_pipe", None) is not None:
             self._pipe["calls"] = 0      # every step starts on the same buffer set (CUDA graph replays rely on it)
             self._pipe["post_events"] = []
+        n = getattr(self, "_capture_updates", 0)
+        self._capture_updates = 0
+        if torch.cuda.is_current_stream_capturing() and n % 2:
+            # The head-importance EMA is double buffered and the half to read is a launch argument: a captured step
+            # replays the same arguments, which is only right if the step flips the parity an even number of times.
+            # Nothing of the capture has run, so the host's parity goes back to what the device state matches.
+            self.head_parity ^= 1
+            raise _lib.SmartKVLibraryError(
+                f"a CUDA-graph-captured decode step holds {n} importance updates; it must hold an even number "
+                "(the head-importance state is double buffered by launch argument): capture two steps per graph "
+                "or run this model's steps without a graph")
 
     # ------------------------------------------------------------------ kernels
     def append(self, layer: int, k: torch.Tensor, v: torch.Tensor, dst_seq, dst_bucket, dst_pos):

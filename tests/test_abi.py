@@ -107,3 +107,17 @@ def test_alloc_config_clamps_like_the_reference():
         make_alloc_config(4, 64, 0.5, (2, 5))
     with pytest.raises(ValueError):
         make_alloc_config(4, 64, 0.5, (2, 4), protected=range(40))
+
+
+def test_alias_registers_the_reference_import_name():
+    """``alias_as_smartkv`` makes ``smartkv...`` imports resolve to this package; it is opt-in."""
+    import subprocess
+    import sys
+    code = ("import sys, smartkv_b200; assert 'smartkv' not in sys.modules; smartkv_b200.alias_as_smartkv(); "
+            "from smartkv.models.llama_smartkv import LlamaSmartKV, SmartKVConfig; "
+            "from smartkv.core.cache import SmartKVCache; import smartkv.kernels as k; "
+            "assert SmartKVCache is smartkv_b200.SmartKVCache and hasattr(k, 'quantized_attention'); "
+            "assert SmartKVConfig().device == 'cpu'; print('ok')")
+    root = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr

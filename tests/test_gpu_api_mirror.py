@@ -263,7 +263,7 @@ def test_llama_wrapper_generates_and_tracks_the_dense_model():
 
 
 def test_tinyllama_shape_fused_decode_matches_dequantised_path():
-    """BASELINE config 2 scaled down in depth only: TinyLlama-1.1B attention shape (hidden 2048, 32 query /
+    """The end-to-end generation workload scaled down in depth only: TinyLlama-1.1B attention shape (hidden 2048, 32 query /
     4 KV heads, head_dim 64, vocab 32000), random N(0, 0.02) fp16 weights, 512 random prompt ids, budget 0.5.
     The fused decode path (packed kernels, current token in full precision) and the dequantise-then-attend
     path over the same cache must give the same next-token logits."""

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import smartkv_oracle as orc
+from smartkv_b200 import _lib
 from tests.gpu_util import assert_close, fill_store, make_store, oracle_attention, oracle_quantized
 
 pytestmark = pytest.mark.gpu

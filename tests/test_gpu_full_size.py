@@ -1,4 +1,4 @@
-"""BASELINE.json's configurations at their full sizes (one layer each), checked through properties that
+"""The benchmark's configurations (8B-shape batch 16 x 8192, long context 131072, 70B shape) at their full sizes (one layer each), checked through properties that
 do not need the oracle to walk the whole input, plus the oracle itself on a slice it finishes in seconds:
   * the fp16-query kernel and the fp32-query ("precise") kernel are two different instruction paths; their
     outputs must agree within the attention tolerance;
