@@ -10,7 +10,9 @@ What differs from the reference, on purpose:
   * A token becomes visible to attention once every layer has stored it, and a reallocation that
     falls due while some layer still lacks the newest token is applied as soon as all layers have it
     (the reference requantises layer by layer in the middle of a step).
-  * ``enable_forecast`` is not built (the reference's optional predictor, cache.py:746-804).
+  * ``enable_forecast`` runs the reference's predictor on the host (``core/forecast.py``); with it every
+    fused decode step pulls the device importance of the step's token (a synchronisation the default path
+    does not have).
   * Capacity is ``max_tokens`` (grown by doubling when exceeded), not an amortised ``torch.cat``.
 """
 from __future__ import annotations
@@ -85,8 +87,6 @@ class SmartKVCache:
         dev = torch.device(device)
         if dev.type != "cuda":
             raise _lib.SmartKVLibraryError("SmartKVCache on the B200 library needs a CUDA device; there is no CPU path")
-        if enable_forecast:
-            raise NotImplementedError("the forecast predictor is not part of the B200 decode path")
         if head_dim not in (64, 128):
             raise ValueError(f"head_dim must be 64 or 128 on the B200 path; got {head_dim}")
         self.num_layers, self.num_heads, self.head_dim = num_layers, num_heads, head_dim
@@ -101,7 +101,23 @@ class SmartKVCache:
             warnings.warn("the B200 store is always bit-packed; use_bit_packing=False is ignored")
         self.use_packing = True
         self.scale_dtype = "fp32"
-        self.enable_forecast = False
+        # the optional importance forecast (smartkv/core/cache.py:111-133)
+        self.enable_forecast = bool(enable_forecast and forecast_history > 0)
+        self.forecast_history = max(1, forecast_history)
+        self.forecast_update_interval = max(1, forecast_update_interval)
+        self.forecast_blend = float(max(0.0, min(1.0, forecast_blend)))
+        self.forecast_lr = float(max(forecast_lr, 1e-5))
+        self.forecast_pending: Dict[int, Tuple[torch.Tensor, int]] = {}
+        self.forecast_last_importance: Dict[int, float] = {}
+        self.forecast_last_loss: Optional[float] = None
+        if self.enable_forecast:
+            from collections import deque
+            from .forecast import ForecastPredictor
+            self.forecast_feature_buffer = deque(maxlen=self.forecast_history)
+            self.forecast_target_buffer = deque(maxlen=self.forecast_history)
+            self.forecast_predictor = ForecastPredictor(feature_dim=6, lr=self.forecast_lr, device="cpu")
+        else:
+            self.forecast_feature_buffer = self.forecast_target_buffer = self.forecast_predictor = None
         self.utility_alpha = float(utility_alpha) if utility_alpha > 0 else 1.0
         self.importance_floor = float(max(importance_floor, 0.0))
         self.hysteresis_rank_threshold = float(max(hysteresis_rank_threshold, 0.0))
@@ -420,6 +436,8 @@ class SmartKVCache:
         self.global_step += 1
         for tid in token_ids:
             self.last_seen[int(tid)] = self.global_step
+            if self.enable_forecast:
+                self._record_forecast_target(int(tid), self.importance_tracker.get_importance(int(tid)))
         self._maybe_reallocate(layer_idx, [int(t) for t in token_ids])
 
     def _maybe_reallocate(self, layer_idx: int, token_ids: List[int]):
@@ -514,6 +532,8 @@ class SmartKVCache:
                     seen = max(seen, fused_seen)
                 score *= math.exp(-(self.global_step - seen) / self.recency_temperature)
             scores[tid] = score
+        if self.enable_forecast:
+            self._blend_forecast(scores)
         allocation = self._solve_allocation(candidates, scores)
         previous = self.precision_map
         self.precision_map = allocation
@@ -521,6 +541,67 @@ class SmartKVCache:
         if changed:
             self._requantize_tokens(changed)
         return {t: allocation[t] for t in token_ids if t in allocation}
+
+    # ------------------------------------------------------------------ importance forecast
+    def _blend_forecast(self, scores: Dict[int, float]) -> None:
+        """smartkv/core/cache.py:313-336: every token with a finite positive score (protected ids carry +inf in
+        the reference and are skipped) gets (1 - blend) * score + blend * max(prediction, 0); the feature row is
+        kept until the token's next update supplies the training target."""
+        protected = self.protected_tokens | self.special_token_ids
+        rows, toks, raws = [], [], []
+        for tid, score in scores.items():
+            if tid in protected or tid < self.critical_token_window or not math.isfinite(score) or score <= 0.0:
+                continue
+            feature = self._build_forecast_feature(tid, score)
+            rows.append(feature)
+            toks.append(tid)
+            raws.append(score)
+            self.forecast_pending[tid] = (feature, self.global_step)
+        if rows:
+            preds = self.forecast_predictor.predict(torch.stack(rows)).tolist()
+            for tid, raw, pred in zip(toks, raws, preds):
+                scores[tid] = (1.0 - self.forecast_blend) * raw + self.forecast_blend * max(pred, 0.0)
+                self.forecast_last_importance[tid] = raw
+        for tid, score in scores.items():
+            if math.isfinite(score) and not (tid in protected or tid < self.critical_token_window):
+                self.forecast_last_importance[tid] = score
+
+    def _build_forecast_feature(self, token_id: int, raw_importance: float) -> torch.Tensor:
+        """The six inputs of the predictor (smartkv/core/cache.py:746-773)."""
+        if not self.enable_forecast:
+            raise RuntimeError("Forecasting disabled")
+        delta = raw_importance - self.forecast_last_importance.get(token_id, 0.0)
+        age = self.global_step - self.last_seen.get(token_id, self.global_step)
+        bits_now = float(self.precision_map.get(token_id, self.min_general_bits))
+        head_mean = float(self.head_importance.mean().item())
+        position = math.tanh(token_id / max(1.0, self.total_tokens_stored + 1))
+        step = math.tanh(self.global_step / max(1.0, self.recency_temperature * 10.0))
+        return torch.tensor([math.log1p(max(raw_importance, 0.0)), math.log1p(abs(delta)),
+                             math.tanh(age / max(self.recency_temperature, 1.0)), bits_now / max(self.available_bits),
+                             math.tanh(head_mean), position + step], dtype=torch.float32)
+
+    def _record_forecast_target(self, token_id: int, actual_importance: float) -> None:
+        """smartkv/core/cache.py:775-791: a token that was scored at the last allocation now shows what its
+        importance became; enough such pairs trigger one training step."""
+        if not self.enable_forecast:
+            return
+        pending = self.forecast_pending.pop(token_id, None)
+        if pending is None or not math.isfinite(actual_importance):
+            return
+        self.forecast_feature_buffer.append(pending[0].detach().cpu())
+        self.forecast_target_buffer.append(math.log1p(max(actual_importance, 0.0)))
+        if len(self.forecast_feature_buffer) >= self.forecast_update_interval:
+            self._update_forecast_predictor()
+
+    def _update_forecast_predictor(self) -> None:
+        """smartkv/core/cache.py:793-804."""
+        if not self.enable_forecast or self.forecast_predictor is None or not self.forecast_feature_buffer:
+            return
+        features = torch.stack(list(self.forecast_feature_buffer))
+        targets = torch.tensor(list(self.forecast_target_buffer), dtype=torch.float32)
+        self.forecast_last_loss = self.forecast_predictor.update(features, targets)
+        self.forecast_feature_buffer.clear()
+        self.forecast_target_buffer.clear()
 
     def _requantize_tokens(self, tokens: set) -> None:
         """smartkv/core/cache.py:806-844: stored tokens whose width changed move to the bucket of the new
@@ -588,6 +669,12 @@ class SmartKVCache:
             self.global_step += 1
             self._fused_seen_step = self.global_step
             self.last_seen[tid] = self.global_step
+            if self.enable_forecast and self.forecast_pending:
+                # every cached key took part in this update: the tokens scored at the last allocation now have
+                # their training target
+                self._pull_device_importance()
+                for t in [t for t in self.forecast_pending if t in self._slot]:
+                    self._record_forecast_target(t, self.importance_tracker.get_importance(t))
             self._maybe_reallocate(layer_idx, [tid])
         return out[0].clone()
 

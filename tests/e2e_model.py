@@ -2,6 +2,7 @@
 vocabulary 32000) used by the end-to-end wrapper fixture and its parity test.  The weights come from an
 explicit CPU generator, parameter by parameter in name order, so that the reference run that produced the
 fixture and the test see the same model."""
+import numpy as np
 import torch
 
 
@@ -31,3 +32,27 @@ def prompts(batch: int, length: int, seed: int = 7, vocab: int = 32000) -> torch
 def probe_columns(count: int = 256, seed: int = 11, vocab: int = 32000) -> torch.Tensor:
     g = torch.Generator(device="cpu").manual_seed(seed)
     return torch.randperm(vocab, generator=g)[:count].sort().values
+
+
+def forecast_inputs(L, H, n, steps, seed=41):
+    """Seeded attention rows for the forecast fixture: causal prompt probabilities per layer, then one decode row
+    per (step, layer) over all keys, peaked on a few drifting positions so that importance keeps changing."""
+    rng = np.random.default_rng(seed)
+    prompt = []
+    for _ in range(L):
+        s = rng.standard_normal((1, H, n, n)).astype(np.float32) * 2.0
+        iu = np.triu_indices(n, 1)
+        s[..., iu[0], iu[1]] = -np.inf
+        p = np.exp(s - s.max(-1, keepdims=True))
+        prompt.append((p / p.sum(-1, keepdims=True)).astype(np.float32))
+    rows = []
+    for t in range(steps):
+        per_layer = []
+        for _ in range(L):
+            s = rng.standard_normal((1, H, 1, n + t + 1)).astype(np.float32)
+            s[..., (7 * t) % (n + t)] += 4.0
+            s[..., (3 * t + 11) % (n + t)] += 3.0
+            p = np.exp(s - s.max(-1, keepdims=True))
+            per_layer.append((p / p.sum(-1, keepdims=True)).astype(np.float32))
+        rows.append(per_layer)
+    return prompt, rows

@@ -293,6 +293,15 @@ def gen_config0(out):
     out["c0_probs_head0"] = p.numpy()[0, 0, 0]
 
 
+def _shared_inputs():
+    """tests/e2e_model.py loaded by path (the reference checkout has a ``tests`` package of its own)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("e2e_model", os.path.join(HERE, "..", "e2e_model.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 WRAPPER_LAYERS, WRAPPER_PROMPT, WRAPPER_STEPS, WRAPPER_BATCH = 5, 80, 48, 2
 
 
@@ -311,10 +320,7 @@ def gen_wrapper(out):
     last step the width of every token and the reallocation count."""
     import smartkv.models.llama_smartkv as rl
     from transformers.models.llama.modeling_llama import apply_rotary_pos_emb as hf_rope
-    import importlib.util
-    spec = importlib.util.spec_from_file_location("e2e_model", os.path.join(HERE, "..", "e2e_model.py"))
-    e2e = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(e2e)
+    e2e = _shared_inputs()
     probe_columns, prompts, tiny_llama = e2e.probe_columns, e2e.prompts, e2e.tiny_llama
     rl.apply_rotary_pos_emb = lambda q, k, c, s, p=None: hf_rope(q, k, c, s)
     n, steps, B = WRAPPER_PROMPT, WRAPPER_STEPS, WRAPPER_BATCH
@@ -367,12 +373,70 @@ def gen_wrapper(out):
                w_hist=hist, w_bits_prefill=bits_prefill, w_k0_prefill=k0_prefill)
 
 
+def gen_baselines(out):
+    """The comparison caches of smartkv/baselines on seeded rows (with an all-zero token and an outlier token):
+    what retrieve_all returns per layer."""
+    from smartkv.baselines.kivi import KIVICache
+    from smartkv.baselines.uniform_quant import UniformQuantCache
+    L, H, D, n = 2, 4, 64, 40
+    rng = np.random.default_rng(31)
+    k = rng.standard_normal((L, n, H, D)).astype(np.float32)
+    v = rng.standard_normal((L, n, H, D)).astype(np.float32)
+    k[:, 3] = 0.0
+    v[:, 5, 1, 7] = 40.0
+    out["b_k"], out["b_v"] = k, v
+    caches = {"u8": UniformQuantCache(L, H, D, bits=8), "u4": UniformQuantCache(L, H, D, bits=4),
+              "kivi24": KIVICache(L, H, D, key_bits=2, value_bits=4, per_channel_keys=False),
+              "kivi42": KIVICache(L, H, D, key_bits=4, value_bits=2, per_channel_keys=False)}
+    for tag, c in caches.items():
+        for l in range(L):
+            for t in range(n):
+                c.quantize_and_store(l, t, torch.from_numpy(k[l, t]), torch.from_numpy(v[l, t]))
+            kk, vv = c.retrieve_all(l)
+            out[f"b_{tag}_k{l}"], out[f"b_{tag}_v{l}"] = kk.numpy(), vv.numpy()
+        out[f"b_{tag}_ratio"] = np.array(c.get_memory_stats()["memory_ratio"])
+
+
+def gen_forecast(out):
+    """SmartKVCache with enable_forecast (smartkv/core/cache.py:313-336, :746-804; predictor
+    smartkv/core/forecast.py) driven at the cache level with the ids of the keys: prompt update + store per
+    layer, then decode steps.  torch.manual_seed(123) directly before the constructor fixes the predictor's
+    initial weights.  Records the widths after the last step, the number of reallocations and predictor updates,
+    the last loss and the first layer's weights."""
+    L, H, D, n, steps = 2, 2, 64, 64, 48
+    prompt, rows = _shared_inputs().forecast_inputs(L, H, n, steps)
+    rng = np.random.default_rng(42)
+    torch.manual_seed(123)
+    c = packed_cache(L, H, D, 0.45, enable_forecast=True, forecast_update_interval=16, forecast_blend=0.5, forecast_lr=0.05)
+    updates = [0]
+    orig = c.forecast_predictor.update
+    c.forecast_predictor.update = lambda f, t: (updates.__setitem__(0, updates[0] + 1), orig(f, t))[1]
+    ids = list(range(n))
+    for l in range(L):
+        c.update_attention(l, torch.from_numpy(prompt[l]), ids)
+        c.quantize_and_store_batch(l, ids, torch.from_numpy(rng.standard_normal((n, H, D)).astype(np.float32)),
+                                   torch.from_numpy(rng.standard_normal((n, H, D)).astype(np.float32)))
+    for t in range(steps):
+        keys = list(range(n + t + 1))
+        for l in range(L):
+            c.update_attention(l, torch.from_numpy(rows[t][l]), keys)
+            c.quantize_and_store(l, n + t, torch.from_numpy(rng.standard_normal((H, D)).astype(np.float32)),
+                                 torch.from_numpy(rng.standard_normal((H, D)).astype(np.float32)))
+    out["f_shape"] = np.array([L, H, D, n, steps])
+    out["f_bits"] = np.array([c.precision_map[t] for t in range(n + steps)], np.uint8)
+    out["f_reallocs"] = np.array(c.realloc_counter)
+    out["f_updates"] = np.array(updates[0])
+    out["f_last_loss"] = np.array(c.forecast_last_loss if c.forecast_last_loss is not None else -1.0)
+    out["f_w0"] = c.forecast_predictor.model.net[0].weight.detach().numpy().copy()
+    out["f_importance"] = np.array([c.importance_tracker.get_importance(t) for t in range(n + steps)])
+
+
 def main():
     torch.manual_seed(0)
     torch.set_num_threads(4)
     gens = [("quant", gen_quant), ("attention", gen_attention), ("importance", gen_importance),
             ("allocation", gen_allocation), ("requant", gen_requant), ("config0", gen_config0),
-            ("wrapper", gen_wrapper)]
+            ("wrapper", gen_wrapper), ("baselines", gen_baselines), ("forecast", gen_forecast)]
     only = sys.argv[1:]          # optional: names of the fixtures to regenerate
     for name, fn in [g for g in gens if not only or g[0] in only]:
         out = {}
