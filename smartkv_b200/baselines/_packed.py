@@ -17,8 +17,10 @@ def quantize_per_tensor(x: torch.Tensor, bits: int):
     """The reference quantizers (smartkv/core/quantizers.py:69-91, :114-133, :191-210): ONE scale per token
     tensor, ``max|x| / qmax`` (1 for an all-zero tensor), codes ``clamp(round(x / scale), -2^(b-1), 2^(b-1)-1)``.
     x [n, heads, head_dim] fp32 -> (codes int8 [n, heads, head_dim], scale fp32 [n])."""
-    qmax = float(2 ** (bits - 1) - 1)
     x = x.float()
+    # a device tensor as divisor: dividing a CUDA tensor by a Python number multiplies by the rounded reciprocal,
+    # which is not the reference's (CPU) true division in the last bit
+    qmax = torch.tensor(float(2 ** (bits - 1) - 1), dtype=torch.float32, device=x.device)
     scale = x.abs().amax(dim=(1, 2)) / qmax
     scale = torch.where(scale == 0, torch.ones_like(scale), scale)
     q = torch.clamp(torch.round(x / scale[:, None, None]), -(2 ** (bits - 1)), 2 ** (bits - 1) - 1).to(torch.int8)
