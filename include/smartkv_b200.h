@@ -272,6 +272,28 @@ int skv_post_attention(const SkvStoreDesc* desc, void* store, int layer, const v
                        float decay, float head_decay, const int32_t* dst_seq, const int32_t* dst_bucket,
                        const int32_t* dst_pos, int max_seq_tokens, int32_t* err_flag, void* stream);
 
+/* ---- prompt pass -------------------------------------------------------------- */
+
+/* Causal self-attention over the unquantised prompt plus the per-key attention mass of the
+ * importance update, replacing the wrapper's dense path for more than one query token
+ * (smartkv/models/llama_smartkv.py:392-415: matmul, causal mask, softmax, matmul) together with the
+ * head weighting and the sum over batch, heads and queries of SmartKVCache.update_attention /
+ * ImportanceTracker.update_attention (smartkv/core/cache.py:232-259, smartkv/core/importance.py:62-72) --
+ * without writing the [batch, heads, queries, keys] probabilities to memory.
+ *   q [batch][tokens][num_q_heads][head_dim], k, v [batch][tokens][num_kv_heads][head_dim], fp16, addressed
+ *   through element strides {batch, token, head} (head_dim contiguous, strides multiples of 8, bases 16-byte
+ *   aligned); dtype must be SKV_DTYPE_F16; head_dim 64 or 128.
+ *   head_weights fp32 [batch][num_q_heads] (the normalised head importance) or NULL (= 1).
+ *   out fp16 [batch][tokens][num_q_heads][head_dim]; lse fp32 [batch][num_q_heads][tokens] (base-2
+ *   log-sum-exp of every query row, also the scratch of the second pass).
+ *   key_mass fp32 [batch][num_kv_heads][tokens]: sum over the queries and the query heads of the KV head's
+ *   group of weight * probability; adding the KV heads gives the reference's per-key importance.  NULL skips
+ *   the second pass. */
+int skv_prefill_attention(const void* q, const void* k, const void* v, int dtype, int batch, int tokens,
+                          int num_q_heads, int num_kv_heads, int head_dim, const int64_t* q_strides,
+                          const int64_t* k_strides, const int64_t* v_strides, const float* head_weights, void* out,
+                          float* lse, float* key_mass, void* stream);
+
 /* ---- importance ----------------------------------------------------------- */
 
 /* Replaces SmartKVCache.update_attention's head weighting + ImportanceTracker.update_attention

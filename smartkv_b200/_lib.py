@@ -69,6 +69,9 @@ _SIGNATURES = {
                                  c_void_p, c_void_p, c_void_p]),
     "skv_import_rows": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "skv_prefill_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p]),
     "skv_attn_num_ctas": (c_int, [c_int]),
     "skv_attn_partials_bytes": (c_int64, [POINTER(StoreDesc), c_int, c_int]),
     "skv_attn_plan_bytes": (c_int64, [POINTER(StoreDesc), c_int]),

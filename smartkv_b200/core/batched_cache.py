@@ -165,11 +165,21 @@ class BatchedSmartKVCache:
         return self.head_importance / (self.head_importance.mean(dim=1, keepdim=True) + 1e-6)
 
     # ------------------------------------------------------------------ prefill
-    def prefill_layer(self, layer: int, k: torch.Tensor, v: torch.Tensor, probs: torch.Tensor) -> None:
-        """The prompt of every sequence for one layer: k, v [B, n, num_heads, head_dim]; probs fp32
+    def prefill_head_weights(self, num_tokens: int) -> torch.Tensor:
+        """Advances the head-importance EMA by one prompt pass over ``num_tokens`` tokens and returns the
+        normalised head weights fp32 [B, Hq] (cache.py:243-250).  Every causal row sums to one, so the mean
+        probability of a head over (queries, keys) is 1 / num_tokens whatever the data: the weights can be had
+        before the attention runs, which lets the prompt-pass kernel apply them while it sums the key mass."""
+        mean = torch.full((self.batch_size, self.num_query_heads), 1.0 / num_tokens, dtype=torch.float32, device=self._dev)
+        return self._weights(mean)
+
+    def prefill_layer(self, layer: int, k: torch.Tensor, v: torch.Tensor, probs: Optional[torch.Tensor] = None,
+                      key_mass: Optional[torch.Tensor] = None) -> None:
+        """The prompt of every sequence for one layer: k, v [B, n, num_heads, head_dim]; either probs fp32
         [B, Hq, n, n], the causal attention probabilities the layer computed over the unquantised prompt
-        (smartkv/models/llama_smartkv.py:392-427).  Importance update, reallocation trigger, then the rows are
-        quantised at the widths in force and stored."""
+        (smartkv/models/llama_smartkv.py:392-427), or key_mass fp32 [B, n], their head-weighted sum over heads
+        and queries computed with the weights of prefill_head_weights (the prompt-pass kernel's output).
+        Importance update, reallocation trigger, then the rows are quantised at the widths in force and stored."""
         st = self.store
         B, n = k.shape[0], k.shape[1]
         if B != self.batch_size:
@@ -179,8 +189,11 @@ class BatchedSmartKVCache:
                 raise NotImplementedError("a second multi-token call on a non-empty batched cache (chunked prefill)")
             if n + 1 > self.max_tokens:
                 raise _lib.SmartKVLibraryError(f"{n} prompt tokens exceed the cache capacity of {self.max_tokens - 1}")
-        w = self._weights(probs.float().mean(dim=(2, 3)))
-        mass = (probs.float() * w[:, :, None, None]).sum(dim=(1, 2)).double()          # [B, n] per key
+        if key_mass is not None:
+            mass = key_mass.double()
+        else:
+            w = self._weights(probs.float().mean(dim=(2, 3)))
+            mass = (probs.float() * w[:, :, None, None]).sum(dim=(1, 2)).double()      # [B, n] per key
         ids = torch.arange(n, device=self._dev)
         if layer == 0:
             bits = torch.full((B, n), 4, dtype=torch.int32, device=self._dev)

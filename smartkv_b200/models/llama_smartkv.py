@@ -185,6 +185,13 @@ class LlamaSmartKVAttention(nn.Module):
         if q_len == 1:
             out = cache.decode_layer(self.layer_idx, q[:, :, 0], k[:, :, 0], v[:, :, 0])
             attn_output = out.to(hidden_states.dtype).reshape(bsz, 1, H * D)
+        elif q.dtype == torch.float16 and not output_attentions and D in (64, 128):
+            # the prompt-pass kernel: attention output and per-key mass without the [B, Hq, n, n] probabilities
+            from ..prefill import causal_prefill_attention
+            w = cache.prefill_head_weights(q_len)
+            out, mass = causal_prefill_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), w)
+            attn_output = out.reshape(bsz, q_len, H * D)
+            cache.prefill_layer(self.layer_idx, k.transpose(1, 2), v.transpose(1, 2), key_mass=mass)
         else:
             kk = k.repeat_interleave(self.num_key_value_groups, dim=1)
             vv = v.repeat_interleave(self.num_key_value_groups, dim=1)

@@ -80,3 +80,18 @@ def test_batched_decode_with_key_attribution_keeps_budget_and_tracks_the_referen
     assert stats["realloc_count"] == int(z["w_reallocs"][0])
     assert np.all(np.isfinite(probe)) and np.abs(probe - z["w_probe"]).max() <= 2.0
     assert np.abs(probe[:, 0] - z["w_probe"][:, 0]).max() <= 1e-3        # the prompt pass does not read the cache
+
+
+def test_fp16_model_takes_the_prompt_pass_kernel():
+    """An fp16 model sends the prompt through skv_prefill_attention (attention output + per-key mass in one
+    pass over the unquantised prompt).  Its prompt logits must agree with the fp32 reference run up to fp16
+    rounding of the whole model, and the importance it feeds must give the first allocation the fixture's
+    shape: early tokens wide, late tokens narrow, budget kept."""
+    z = np.load(FIXTURE)
+    L, n, steps, B = (int(x) for x in z["w_shape"])
+    w, probe, greedy = run_wrapper(z, key_attribution="wrapper", dtype=torch.float16)
+    assert np.abs(probe[:, 0] - z["w_probe"][:, 0]).max() <= 5e-2
+    stats = w.get_smartkv_stats()
+    assert stats["memory_ratio_true_max"] <= 0.5 + 1e-6 and stats["realloc_count"] == int(z["w_reallocs"][0])
+    bits = w.smartkv_cache.token_bits().cpu().numpy()
+    assert (bits[:, :n] == z["w_bits"][:, :n]).mean() >= 0.9
