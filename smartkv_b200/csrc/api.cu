@@ -40,8 +40,9 @@ extern "C" int skv_store_layout(SkvStoreDesc* d) {
   }
   d->slots = base;
   d->reserved_ = 0;
-  // slack so that a 3-bit slice load that rounds its address down/up never leaves the arena
-  d->arena_bytes = align_up(off + 256, 256);
+  // slack so that a 3-bit slice load that rounds its address down/up never leaves the arena, then the footer
+  // (256 bytes; word 0 = "a V scale above 64 is stored here", see common.cuh)
+  d->arena_bytes = align_up(off + 256, 256) + 256;
   d->total_bytes = d->arena_bytes * d->num_layers * d->num_seqs;
   return SKV_OK;
 }

@@ -56,6 +56,17 @@ __device__ __forceinline__ uint8_t* arena_ptr(const StoreGeom& g, void* store, i
   return static_cast<uint8_t*>(store) + ((long long)layer * g.num_seqs + seq) * g.arena_bytes;
 }
 
+// The last 256 bytes of every (layer, sequence) arena are a footer.  Word 0 becomes non-zero once a V scale above
+// kVScaleGuard has been stored in that arena (it is never cleared): the attention kernel multiplies probabilities
+// of up to 2^8 by the V scale in fp16, which is safe without a check only below that scale.
+constexpr float kVScaleGuard = 64.0f;
+__device__ __forceinline__ const int* arena_flags(const StoreGeom& g, const uint8_t* arena) {
+  return reinterpret_cast<const int*>(arena + g.arena_bytes - 256);
+}
+__device__ __forceinline__ void note_v_scale(const StoreGeom& g, uint8_t* arena, float v_scale) {
+  if (v_scale > kVScaleGuard) *reinterpret_cast<volatile int*>(arena + g.arena_bytes - 256) = 1;
+}
+
 // ---- small PTX wrappers -----------------------------------------------------
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t d;

@@ -149,7 +149,6 @@ struct LaneState {
 // units), so most tiles need no cross-lane reduction and no rescale of the accumulators;
 // probabilities then reach at most 2^kLazyTau, well inside fp16 / fp32 range.
 constexpr float kLazyTau = 8.0f;
-constexpr float kVScaleGuard = 64.0f;  // 2^kLazyTau * 64 = 16384, a quarter of the fp16 maximum
 
 // Per-run query data the producer warp prepares in shared memory.
 template <int D, bool PRECISE>
@@ -162,6 +161,7 @@ struct QSlot {
   int sumA[8];               // 128*sum(limb0) + sum(limb1)
   int sumB[8];               // sum(limb2) (precise mode)
   RunDesc desc;
+  int guard;                 // the run's arena holds a V scale above kVScaleGuard (see process_tile)
 };
 
 // Query of one run as a lane sees it, specialised per bit-width of the keys it meets.
@@ -193,7 +193,9 @@ __device__ __forceinline__ void load_qfrags(const QSlot<D, PRECISE>& q, int lane
 // One 16-key tile.  Lane (g,t): supplies the K slices of keys g, g+8 and the V slices of the key
 // pairs (2t,2t+1), (2t+8,2t+9); receives the scores of head g for keys 2t, 2t+1, 2t+8, 2t+9.
 // WRITE_LOGITS: lrow = logits row of head g (first key of the tile), written as two float2.
-template <int D, int BITS, bool PRECISE, bool WRITE_LOGITS>
+// MASKED: the launch carries an additive mask (tok / mrow are only read then).  GUARD: the (layer, sequence) arena
+// holds a V scale above kVScaleGuard somewhere, so p * v_scale has to be checked against the fp16 range.
+template <int D, int BITS, bool PRECISE, bool WRITE_LOGITS, bool MASKED, bool GUARD>
 __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t* vtile, const float4* sc, int nvalid,
                                              int lane, const QFrags<D, BITS, PRECISE>& qf, LaneState& st,
                                              float (&o)[D / 16][4], float scale_log2, float* lrow,
@@ -242,7 +244,7 @@ __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t
     x3 = (c1[1] + c1[3]) * (scB.z * scale_log2);
   }
   float vs0 = scA.y, vs1 = scA.w, vs2 = scB.y, vs3 = scB.w;
-  if (tok != nullptr) {
+  if constexpr (MASKED) {
     // additive mask, indexed by the key's token id as the reference indexes it by the key's global slot
     // (smartkv/csrc/quantized_attention.cu:570-575); natural-log units -> log2 units
     constexpr float kLog2e = 1.4426950408889634f;
@@ -266,14 +268,17 @@ __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t
   }
   float mx = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
   // The P operand of the P.V product is p * v_scale in fp16.  With p <= 2^kLazyTau that product stays inside
-  // the fp16 range as long as the V scale does not exceed kVScaleGuard; a tile with a larger scale takes the
-  // slow path below, which raises the running maximum far enough for the product to fit.
-  const float vsm = fmaxf(fmaxf(vs0, vs1), fmaxf(vs2, vs3));
-  if (__any_sync(0xffffffffu, mx > st.m + kLazyTau || vsm > kVScaleGuard)) {
+  // the fp16 range as long as the V scale does not exceed kVScaleGuard; every kernel that writes a V scale
+  // records in the arena's footer when one does, and only runs over such an arena pay for the test: a tile
+  // with a large scale takes the slow path below, which raises the running maximum far enough for the
+  // product to fit.
+  bool slow = mx > st.m + kLazyTau;
+  if constexpr (GUARD) slow = slow || fmaxf(fmaxf(vs0, vs1), fmaxf(vs2, vs3)) > kVScaleGuard;
+  if (__any_sync(0xffffffffu, slow)) {
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     float n = fmaxf(st.m, mx);
-    {
+    if constexpr (GUARD) {
       const float mu2 = (n == -INFINITY) ? 0.f : n;
       float am = fmaxf(fmaxf(ex2f(x0 - mu2) * vs0, ex2f(x1 - mu2) * vs1), fmaxf(ex2f(x2 - mu2) * vs2, ex2f(x3 - mu2) * vs3));
       am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
@@ -314,26 +319,29 @@ __device__ __forceinline__ void process_tile(const uint8_t* ktile, const uint8_t
 // One block = up to KBKEYS keys of one bucket, staged at `sb`: [K rows][V rows][float2 scales].
 // This warp owns tiles first, first + NCONS, ... of it.  lrow: logits row of head g at the
 // block's first key (null in lanes whose head does not exist).
-template <int D, int BITS, bool PRECISE, int KBKEYS, int NCONS>
+template <int D, int BITS, bool PRECISE, int KBKEYS, int NCONS, bool MASKED>
 __device__ __forceinline__ void process_block(const uint8_t* sb, int nkeys, int first, int lane,
                                               const QFrags<D, BITS, PRECISE>& qf, LaneState& st,
-                                              float (&o)[D / 16][4], float scale_log2, bool write_logits,
+                                              float (&o)[D / 16][4], float scale_log2, bool write_logits, bool guard,
                                               float* lrow, const int32_t* tok, const float* mrow) {
   constexpr int PD = D * BITS / 8;
   const uint8_t* kbase = sb;
   const uint8_t* vbase = sb + KBKEYS * PD;
   const float4* sc = reinterpret_cast<const float4*>(sb + 2 * KBKEYS * PD);  // two keys per float4
   const int ntl = (nkeys + 15) >> 4;
-  if (write_logits) {  // warp-uniform; lanes of heads >= G carry a null row
+  auto tiles = [&](auto wl_tag, auto gd_tag) {
+    constexpr bool WL = decltype(wl_tag)::value, GD = decltype(gd_tag)::value;
     for (int tile = first; tile < ntl; tile += NCONS)
-      process_tile<D, BITS, PRECISE, true>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 8,
-                                           nkeys - tile * 16, lane, qf, st, o, scale_log2,
-                                           lrow ? lrow + tile * 16 : nullptr, tok ? tok + tile * 16 : nullptr, mrow);
+      process_tile<D, BITS, PRECISE, WL, MASKED, GD>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 8,
+                                                     nkeys - tile * 16, lane, qf, st, o, scale_log2,
+                                                     (WL && lrow) ? lrow + tile * 16 : nullptr,
+                                                     MASKED ? tok + tile * 16 : nullptr, mrow);
+  };
+  // both flags are warp-uniform (lanes of heads >= G carry a null logits row)
+  if (write_logits) {
+    if (guard) tiles(std::true_type{}, std::true_type{}); else tiles(std::true_type{}, std::false_type{});
   } else {
-    for (int tile = first; tile < ntl; tile += NCONS)
-      process_tile<D, BITS, PRECISE, false>(kbase + tile * 16 * PD, vbase + tile * 16 * PD, sc + tile * 8,
-                                            nkeys - tile * 16, lane, qf, st, o, scale_log2, nullptr,
-                                            tok ? tok + tile * 16 : nullptr, mrow);
+    if (guard) tiles(std::false_type{}, std::true_type{}); else tiles(std::false_type{}, std::false_type{});
   }
 }
 
@@ -406,7 +414,7 @@ __device__ __forceinline__ void prep_query_heads(QSlot<D, PRECISE>& slot, const 
   }
 }
 
-template <int D, bool PRECISE, class CFG>
+template <int D, bool PRECISE, class CFG, bool MASKED>
 __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(const AttnParams p) {
   constexpr int NCONS = CFG::NCONS, STAGES = CFG::STAGES, STAGE_BYTES = CFG::STAGE_BYTES;
   constexpr int NTC = NCONS * 32;  // consumer threads
@@ -500,7 +508,10 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     auto publish_query = [&](int r, const RunDesc& d) -> bool {
       if (!wait_or_abort(&qempty[qi], qepar, abort_flag, p.err, p.wait_polls)) return false;
       Slot& slot = qslots[qi];
-      if (lane == 0) slot.desc = d;
+      if (lane == 0) {
+        slot.desc = d;
+        slot.guard = *arena_flags(g, arena_ptr(g, p.store, p.layer, d.seq));
+      }
       if (r != run_begin) {
         prep_query_heads<D, PRECISE>(slot, p, d.seq, d.head, G, 0, G, lane);
       }
@@ -574,6 +585,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     if (abort_flag[1]) return;
     const Slot& slot = qslots[qi];  // stays valid until this warp arrives on qempty below
     const RunDesc& d = slot.desc;
+    const bool guard = slot.guard != 0;
     if (r == run_begin) {
       for (int gq = warp; gq < G; gq += NCONS) prep_query_heads<D, PRECISE>(qslots[qi], p, d.seq, d.head, G, gq, gq + 1, lane);
       named_bar_sync(1, NCONS * 32);
@@ -609,10 +621,10 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
         if (first < 0) first += NCONS;
         if (!aborted && first < ntl) {
           float* lrow = lbase != nullptr ? lbase + g.bucket_base[bucket] + key0 : nullptr;
-          const int32_t* tok = p.mask != nullptr ? p.slot_token + (long long)b * g.slots + g.bucket_base[bucket] + key0 : nullptr;
-          process_block<D, BITS, PRECISE, KBT * 16, NCONS>(stages + (long long)stg * STAGE_BYTES, nkeys, first, lane,
-                                                           qf, st, o, p.scale_log2, write_logits, lrow, tok,
-                                                           p.mask != nullptr ? p.mask + (long long)b * p.mask_stride : nullptr);
+          const int32_t* tok = MASKED ? p.slot_token + (long long)b * g.slots + g.bucket_base[bucket] + key0 : nullptr;
+          process_block<D, BITS, PRECISE, KBT * 16, NCONS, MASKED>(
+              stages + (long long)stg * STAGE_BYTES, nkeys, first, lane, qf, st, o, p.scale_log2, write_logits, guard,
+              lrow, tok, MASKED ? p.mask + (long long)b * p.mask_stride : nullptr);
         }
         tile_base = (tile_base + ntl) % NCONS;
         __syncwarp();
@@ -735,14 +747,14 @@ extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, in
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 
-template <int D, bool PRECISE, class CFG>
-static int launch_attn(AttnParams& p, cudaStream_t st) {
+template <int D, bool PRECISE, class CFG, bool MASKED>
+static int launch_attn_inst(AttnParams& p, cudaStream_t st) {
   static bool configured[64] = {};  // per template instance and device: the attribute belongs to the device's context
   const size_t smem = attn_smem_bytes<D, CFG, PRECISE>();
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return SKV_ERR_CUDA;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    const cudaError_t rc = cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE, CFG>,
+    const cudaError_t rc = cudaFuncSetAttribute(decode_attn_kernel<D, PRECISE, CFG, MASKED>,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (rc != cudaSuccess) {
       fprintf(stderr, "skv_decode_attention: cannot reserve %zu bytes of shared memory: %s\n", smem, cudaGetErrorString(rc));
@@ -750,13 +762,19 @@ static int launch_attn(AttnParams& p, cudaStream_t st) {
     }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  decode_attn_kernel<D, PRECISE, CFG><<<p.num_ctas, (CFG::NCONS + 1) * 32, smem, st>>>(p);
+  decode_attn_kernel<D, PRECISE, CFG, MASKED><<<p.num_ctas, (CFG::NCONS + 1) * 32, smem, st>>>(p);
   const cudaError_t rc = cudaGetLastError();
   if (rc != cudaSuccess) {
     fprintf(stderr, "skv_decode_attention: launch failed: %s\n", cudaGetErrorString(rc));
     return SKV_ERR_CUDA;
   }
   return SKV_OK;
+}
+
+// A launch with an additive mask runs its own instantiation, so that launches without one carry none of its cost.
+template <int D, bool PRECISE, class CFG>
+static int launch_attn(AttnParams& p, cudaStream_t st) {
+  return p.mask != nullptr ? launch_attn_inst<D, PRECISE, CFG, true>(p, st) : launch_attn_inst<D, PRECISE, CFG, false>(p, st);
 }
 
 // Limit of every bounded device-side wait, in polls of about 50 ns (default 2^24, about a second).

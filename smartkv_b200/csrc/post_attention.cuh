@@ -380,6 +380,7 @@ __device__ __forceinline__ void append_row(const AppendParams& p, long long warp
   if (lane == 0) {
     float* sc = reinterpret_cast<float*>(arena + g.sc_off[bucket]);
     sc[2 * row_index + which] = scale;
+    if (which) note_v_scale(g, arena, scale);
   }
 }
 

@@ -208,7 +208,9 @@ __global__ void import_rows_kernel(StoreGeom g, uint8_t* store, int layer, int r
   pack_store_row<EPL>(code, bits, dst, lane);
   if (lane == 0) {
     float* sc = reinterpret_cast<float*>(arena + g.sc_off[bucket]);
-    sc[2 * row_index + which] = (which ? v_scale : k_scale)[rh];
+    const float scale = (which ? v_scale : k_scale)[rh];
+    sc[2 * row_index + which] = scale;
+    if (which) note_v_scale(g, arena, scale);
   }
 }
 

@@ -456,7 +456,10 @@ __global__ void __launch_bounds__(256) repack_rows_kernel(const RowMoveParams p)
         uint32_t* rp = reinterpret_cast<uint32_t*>(arena + (which ? g.v_off[wb_d] : g.k_off[wb_d]) + row * rb_d);
         if (l16 < words) rp[l16] = w0[u];
         if (l16 + 16 < words) rp[l16 + 16] = w1[u];
-        if (l16 == 0) reinterpret_cast<float*>(arena + g.sc_off[wb_d])[2 * row + which] = sc[u];
+        if (l16 == 0) {
+          reinterpret_cast<float*>(arena + g.sc_off[wb_d])[2 * row + which] = sc[u];
+          if (which) note_v_scale(g, arena, sc[u]);
+        }
       }
     }
   }

@@ -204,3 +204,30 @@ def test_large_value_magnitudes_do_not_overflow_fp16(q_dtype):
     kq, vq, ks, vs = oracle_quantized(k, v, bits)
     ref, _ = oracle_attention(q[0].astype(np.float32), kq, vq, ks, vs, hq // hkv)
     assert_close(out, ref, 2e-3 * 1e4, 2e-3, "large V magnitudes")
+
+
+def test_large_v_scale_created_by_a_reallocation_is_guarded_too():
+    """V rows of magnitude ~300 stored at 8 bits have scales of ~2.4; moved to 2 bits by a reallocation their
+    scale becomes ~300.  The requantise kernel must record that in the arena, or the attention kernel would
+    multiply probabilities near one by it in fp16 unchecked."""
+    hq, hkv, d, n = 32, 8, 128, 300
+    rng = np.random.default_rng(8)
+    k, v = orc.synth_kv(n, hkv, d, seed=8)
+    v = (v * 100.0).astype(np.float32)
+    store = make_store(1, 1, hkv, d, hq, n)
+    fill_store(store, [(k[None], v[None])], np.full((1, n), 8))
+    new_bits = torch.zeros((1, store.slots), dtype=torch.uint8, device="cuda")
+    base8 = store.bucket_base[3]
+    new_bits[0, base8: base8 + n] = 2
+    store.repack(new_bits, max_moves=n)
+    store.check_errors()
+    assert store.counts[0].tolist() == [n, 0, 0, 0]
+    q = (4.0 * rng.standard_normal((1, hq, d))).astype(np.float16)
+    out = store.attention(0, torch.from_numpy(q).cuda()).cpu().numpy()[0]
+    store.check_errors()
+    assert np.all(np.isfinite(out))
+    ids, bits, kc, vc, ks, vs = store.export_sequence(0, 0)
+    assert float(vs.max()) > 64.0
+    ref, _ = oracle_attention(q[0].astype(np.float32), kc.cpu().numpy(), vc.cpu().numpy(), ks.cpu().numpy(),
+                              vs.cpu().numpy(), hq // hkv)
+    assert_close(out, ref, 2e-3 * 300, 2e-3, "V scales grown by a reallocation")
