@@ -217,10 +217,12 @@ def run_generation(args):
     B, n, T = g["batch"], g["prompt"], g["decode"]
     ids = torch.randint(3, g["vocab"], (B, n), generator=torch.Generator().manual_seed(1)).to(dev)
     pos = torch.arange(n, device=dev)[None].expand(B, -1)
+    from smartkv_b200.models.graphed_decode import GraphedDecoder
+    decoder = None if args.no_graph else GraphedDecoder(w)
     sampler = ClockSampler(dev.index or 0)
     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     results = []
-    for rep in range(2):                 # the first pass warms every kernel and allocation; the second is timed
+    for rep in range(2):                 # the first pass warms every kernel, allocation and graph; the second is timed
         w.reset_cache()
         torch.cuda.synchronize(dev)
         if rep == 1:
@@ -231,10 +233,15 @@ def run_generation(args):
             tok = out.logits[:, -1].argmax(-1)
             e[1].record()
             toks = []
+            if decoder is not None:
+                decoder.reset()
             for t in range(T):
                 toks.append(tok.tolist())       # the host sees every token, as a generation loop does
-                out = w(input_ids=tok[:, None], position_ids=torch.full((B, 1), n + t, device=dev), use_cache=False)
-                tok = out.logits[:, -1].argmax(-1)
+                if decoder is not None:
+                    tok = decoder.step(tok, n + t).argmax(-1)
+                else:
+                    out = w(input_ids=tok[:, None], position_ids=torch.full((B, 1), n + t, device=dev), use_cache=False)
+                    tok = out.logits[:, -1].argmax(-1)
             e[2].record()
         torch.cuda.synchronize(dev)
         results.append((e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])))
@@ -251,6 +258,8 @@ def run_generation(args):
         "reallocations": stats.get("realloc_count"), "memory_ratio_true_max": round(stats.get("memory_ratio_true_max", 0.0), 4),
         "precision_distribution": stats.get("precision_distribution"), "clocks": clocks,
         "launches_per_layer_per_step": 2,
+        "decode_steps_as_cuda_graphs": None if decoder is None else {"graphs_captured": len(decoder._graphs)},
+        "generated_tokens_first_sequence": [int(x[0]) for x in toks[:8]],
     }
     print(json.dumps(line))
 

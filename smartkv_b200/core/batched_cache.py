@@ -61,6 +61,7 @@ class BatchedSmartKVCache:
         self.store = PackedKVStore(num_layers, self.batch_size, num_heads, head_dim, self.num_query_heads,
                                    (cap, cap, cap, cap), device=dev, decay=decay,
                                    head_decay=self.head_importance_decay)
+        self.store.capture_check = "caller"      # a step that commits early ends twice; GraphedDecoder checks the total
         protected = sorted({0, 1, 2} | set(int(t) for t in (special_token_ids or [])))
         self._cfg = self.store.make_alloc_config(
             self.memory_budget, self.available_bits, utility_alpha=utility_alpha, importance_floor=importance_floor,
@@ -81,6 +82,9 @@ class BatchedSmartKVCache:
         self._rows = torch.arange(self.batch_size, dtype=torch.int64, device=dev)
         self._mask = torch.zeros((self.batch_size, self.max_tokens), dtype=torch.float32, device=dev)
         self._staging_budget = 256 << 20
+        # id of the token the next decode step appends, as a device scalar: everything a decode step does with it
+        # (mask column, look-up of its storage index) reads this tensor, so a captured step stays valid on replay
+        self._tok_dev = torch.zeros(1, dtype=torch.int64, device=dev)
         self.clear()
 
     # ------------------------------------------------------------------ bookkeeping
@@ -98,6 +102,7 @@ class BatchedSmartKVCache:
         if getattr(st, "_pipe", None) is not None:
             st._pipe["calls"], st._pipe["pending"], st._pipe["post_events"] = 0, None, []
         self._mask.zero_()
+        self._tok_dev.zero_()
         self.head_importance = torch.ones((self.batch_size, self.num_query_heads), dtype=torch.float32, device=self._dev)
         self.last_seen = torch.zeros(self.max_tokens, dtype=torch.float64, device=self._dev)
         self.num_cached = 0          # tokens every layer has stored, per sequence
@@ -143,7 +148,10 @@ class BatchedSmartKVCache:
             tok = st.slot_token.long().clamp(min=0)
             age = float(self.global_step) - self.last_seen[tok]
             recency = torch.exp(-age / self.recency_temperature).contiguous()
-        if recency is None:
+        if recency is None and torch.cuda.is_current_stream_capturing():
+            # inside a captured decode step the launches become part of that graph; buffers sized for the capacity
+            st.reallocate(self._cfg, max_moves=self.batch_size * st.slots, staging_budget=self._staging_budget)
+        elif recency is None:
             # allocator + repack are some seventy small launches; replayed as one CUDA graph after the first time
             st.reallocate_graphed(self._cfg, staging_budget=self._staging_budget)
         else:
@@ -226,6 +234,7 @@ class BatchedSmartKVCache:
         self.token_counter += n
         if layer == self.num_layers - 1:
             self.num_cached = n
+            self._tok_dev.fill_(n)
 
     # ------------------------------------------------------------------ decode
     def decode_layer(self, layer: int, query: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
@@ -265,10 +274,10 @@ class BatchedSmartKVCache:
             if not step["early"]:
                 st.commit_step(step["plan"])             # the step's token becomes a candidate of the allocation
                 step["early"] = True
-                self._mask[:, step["token"]] = -1e30     # ... but stays out of the cached keys of this step
+                self._mask.index_fill_(1, self._tok_dev, -1e30)   # ... but stays out of the cached keys of this step
             self._reallocate()
             where = self._token_storage()
-            step["plan"] = self._plan_for(where[:, step["token"]])
+            step["plan"] = self._plan_for(where.index_select(1, self._tok_dev)[:, 0])
             step["token0"] = where[:, 0]
             # this layer's row at the width just decided, from the full-precision values (cache.py:1214)
             st.append(layer, k, v, *step["plan"][:3])
@@ -277,12 +286,41 @@ class BatchedSmartKVCache:
         if layer == self.num_layers - 1:
             if step["early"]:
                 st.end_step()
-                self._mask[:, step["token"]] = 0.0
+                self._mask.index_fill_(1, self._tok_dev, 0.0)
             else:
                 st.commit_step(step["plan"])
+            self._tok_dev += 1
             self.num_cached += 1
             self._step = None
         return out
+
+    # ------------------------------------------------------------------ captured decode steps
+    def next_step_triggers(self) -> tuple:
+        """The layers at which the NEXT decode step will reallocate (a function of the counters only): the key
+        under which a captured step can be replayed."""
+        out, tc, early = [], self.token_counter, False
+        for layer in range(self.num_layers):
+            known = self.num_cached + (1 if (layer > 0 or early) else 0)
+            total = known + 1
+            adaptive = max(self.realloc_freq * (1 + layer // 4), max(32, total // 8))
+            if tc % adaptive == 0:
+                out.append(layer)
+                early = True
+            tc += 1
+        return tuple(out)
+
+    def advance_after_replay(self, triggers: tuple) -> None:
+        """Host-side bookkeeping of one decode step that ran as a graph replay (the device did the rest)."""
+        L = self.num_layers
+        self.token_counter += L
+        self.global_step += L
+        self.realloc_counter += len(triggers)
+        self.num_cached += 1
+        self.num_known = self.num_cached
+        st = self.store
+        st.max_seq_tokens += 1
+        st.appended_total += self.batch_size
+        st._plan_valid = False
 
     # ------------------------------------------------------------------ stats
     def token_bits(self) -> torch.Tensor:

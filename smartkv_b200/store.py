@@ -228,12 +228,21 @@ class PackedKVStore:
         self.max_seq_tokens += 1
         self._plan_valid = False
 
+    def capture_updates(self) -> int:
+        """Importance updates issued under stream capture since the last call (and resets the count); a captured
+        graph must hold an even number of them, see end_step."""
+        n = getattr(self, "_capture_updates", 0)
+        self._capture_updates = 0
+        return n
+
     def end_step(self):
         """The part of commit_step that does not touch the bookkeeping."""
         self.flush_importance()          # reads the counts as they stood during the step
         if getattr(self, "_pipe", None) is not None:
             self._pipe["calls"] = 0      # every step starts on the same buffer set (CUDA graph replays rely on it)
             self._pipe["post_events"] = []
+        if torch.cuda.is_current_stream_capturing() and getattr(self, "capture_check", "step") == "caller":
+            return      # whoever captures several calls of this into one graph checks the total (capture_updates())
         n = getattr(self, "_capture_updates", 0)
         self._capture_updates = 0
         if torch.cuda.is_current_stream_capturing() and n % 2:

@@ -95,3 +95,38 @@ def test_fp16_model_takes_the_prompt_pass_kernel():
     assert stats["memory_ratio_true_max"] <= 0.5 + 1e-6 and stats["realloc_count"] == int(z["w_reallocs"][0])
     bits = w.smartkv_cache.token_bits().cpu().numpy()
     assert (bits[:, :n] == z["w_bits"][:, :n]).mean() >= 0.9
+
+
+def test_graphed_decode_steps_reproduce_eager_steps():
+    """Decode steps replayed as CUDA graphs (one graph per set of trigger layers) must give the logits of the same
+    steps launched from Python: same kernels, same order, same device state."""
+    from smartkv_b200 import LlamaSmartKV, SmartKVConfig
+    from smartkv_b200.models.graphed_decode import GraphedDecoder
+    from tests.e2e_model import prompts, tiny_llama
+    L, n, steps, B = 4, 70, 44, 2
+    model = tiny_llama(L).cuda().half()
+    ids = prompts(B, n).cuda()
+    pos = torch.arange(n, device="cuda")[None].expand(B, -1)
+    runs = []
+    for graphed in (False, True):
+        w = LlamaSmartKV(model, SmartKVConfig(enabled=True, memory_budget=0.5, realloc_freq=16, device="cuda",
+                                              batched=True, max_tokens=n + steps + 8))
+        dec = GraphedDecoder(w) if graphed else None
+        rows = []
+        with torch.no_grad():
+            tok = w(input_ids=ids, position_ids=pos, use_cache=False).logits[:, -1].argmax(-1)
+            for t in range(steps):
+                if dec is not None:
+                    logits = dec.step(tok, n + t).clone()
+                else:
+                    logits = w(input_ids=tok[:, None], position_ids=torch.full((B, 1), n + t, device="cuda"),
+                               use_cache=False).logits[:, -1]
+                rows.append(logits.float().cpu())
+                tok = logits.argmax(-1)
+        w.smartkv_cache.check_errors()
+        runs.append((torch.stack(rows), w.smartkv_cache.token_bits().cpu(), w.smartkv_cache.realloc_counter,
+                     0 if dec is None else len(dec._graphs)))
+        w.disable_smartkv()
+    assert runs[1][3] >= 2                                   # a no-trigger graph and at least one trigger variant
+    assert runs[0][2] == runs[1][2] and torch.equal(runs[0][1], runs[1][1])
+    assert torch.equal(runs[0][0], runs[1][0]), float((runs[0][0] - runs[1][0]).abs().max())
