@@ -27,6 +27,7 @@ class GraphedDecoder:
         self._logits: Dict[Tuple[int, ...], torch.Tensor] = {}
         self._ids = None
         self._pos = None
+        self._zero_mask = None
         self._steps_since_prompt = 0
 
     def reset(self):
@@ -34,7 +35,9 @@ class GraphedDecoder:
         self._steps_since_prompt = 0
 
     def _forward(self):
-        out = self.wrapped(input_ids=self._ids, position_ids=self._pos, use_cache=False)
+        # A 4-D mask is passed through by the model as it is, which keeps its mask construction (host scalars copied to
+        # the device, not allowed under capture) out of the step; the cache's attention never reads it.
+        out = self.wrapped(input_ids=self._ids, position_ids=self._pos, attention_mask=self._zero_mask, use_cache=False)
         return out.logits[:, -1]
 
     def step(self, tokens: torch.Tensor, position: int) -> torch.Tensor:
@@ -47,6 +50,8 @@ class GraphedDecoder:
         if self._ids is None or self._ids.shape[0] != B:
             self._ids = torch.zeros((B, 1), dtype=torch.int64, device=tokens.device)
             self._pos = torch.zeros((B, 1), dtype=torch.int64, device=tokens.device)
+            dtype = next(self.wrapped.model.parameters()).dtype
+            self._zero_mask = torch.zeros((B, 1, 1, 1), dtype=dtype, device=tokens.device)
             self._graphs.clear()
             self._logits.clear()
         self._ids.copy_(tokens.view(B, 1))
