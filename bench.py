@@ -218,7 +218,7 @@ def run_generation(args):
     ids = torch.randint(3, g["vocab"], (B, n), generator=torch.Generator().manual_seed(1)).to(dev)
     pos = torch.arange(n, device=dev)[None].expand(B, -1)
     from smartkv_b200.models.graphed_decode import GraphedDecoder
-    decoder = None if args.no_graph else GraphedDecoder(w)
+    decoder = None if args.no_graph else GraphedDecoder.for_model(w)
     sampler = ClockSampler(dev.index or 0)
     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     results = []
@@ -258,7 +258,7 @@ def run_generation(args):
         "reallocations": stats.get("realloc_count"), "memory_ratio_true_max": round(stats.get("memory_ratio_true_max", 0.0), 4),
         "precision_distribution": stats.get("precision_distribution"), "clocks": clocks,
         "launches_per_layer_per_step": 2,
-        "decode_steps_as_cuda_graphs": None if decoder is None else {"graphs_captured": len(decoder._graphs)},
+        "decode_steps_as_cuda_graphs": None if decoder is None else {"graphs_captured": decoder.graphs_captured},
         "generated_tokens_first_sequence": [int(x[0]) for x in toks[:8]],
     }
     print(json.dumps(line))

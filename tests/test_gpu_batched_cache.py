@@ -106,3 +106,51 @@ def test_reference_trigger_schedule():
                 got.append((t, l))
     cache.check_errors()
     assert got == want, (got, want)
+
+
+def test_graph_replayed_steps_are_bit_identical_to_eager_steps():
+    """GraphedDecoder over a synthetic per-layer forward (queries, keys and values looked up from seeded tables by
+    token id and position, no GEMM library in the way): every replayed step, including the ones whose graphs hold a
+    reallocation in the middle of the step, must leave exactly the outputs and the cache state of the same step
+    launched from Python."""
+    from smartkv_b200 import BatchedSmartKVCache
+    from smartkv_b200.models.graphed_decode import GraphedDecoder
+    L, B, Hq, Hkv, D, n, steps, V = 4, 3, 32, 4, 64, 70, 48, 97
+    g = torch.Generator(device="cuda").manual_seed(5)
+    tq = torch.randn((L, V, Hq, D), generator=g, device="cuda").half()
+    tk = torch.randn((L, V, Hkv, D), generator=g, device="cuda").half()
+    tv = torch.randn((L, V, Hkv, D), generator=g, device="cuda").half()
+    rng = np.random.default_rng(9)
+    prompt_kv = [(torch.randn((B, n, Hkv, D), generator=g, device="cuda"), torch.randn((B, n, Hkv, D), generator=g, device="cuda"))
+                 for _ in range(L)]
+    probs = [torch.from_numpy(causal_probs(B, Hq, n, rng)).cuda() for _ in range(L)]
+    feed = torch.randint(0, V, (steps, B), generator=g, device="cuda")
+    results = []
+    for graphed in (False, True):
+        cache = BatchedSmartKVCache(L, Hkv, D, Hq, B, max_tokens=n + steps + 4, memory_budget=0.45, realloc_freq=16)
+        for l in range(L):
+            cache.prefill_layer(l, prompt_kv[l][0], prompt_kv[l][1], probs[l])
+
+        def forward(ids, pos, cache=cache):
+            outs = []
+            idx = (ids[:, 0] + pos[:, 0]) % V
+            for l in range(L):
+                outs.append(cache.decode_layer(l, tq[l][idx], tk[l][idx], tv[l][idx]).clone())
+            return torch.stack(outs)
+
+        dec = GraphedDecoder(forward, lambda cache=cache: cache)
+        outs = []
+        for t in range(steps):
+            if graphed:
+                outs.append(dec.step(feed[t], n + t).clone())
+            else:
+                ids = feed[t].view(B, 1)
+                outs.append(forward(ids, torch.full((B, 1), n + t, device="cuda")))
+        cache.check_errors()
+        st = cache.store
+        results.append((torch.stack(outs), st.counts.clone(), st.slot_token.clone(), st.cumulative.clone(), st.arena.clone(),
+                        cache.realloc_counter, cache.num_cached, dec.graphs_captured))
+    a, b = results
+    assert b[7] >= 3 and a[5] == b[5] and a[6] == b[6]
+    assert torch.equal(a[0], b[0]), float((a[0] - b[0]).abs().max())
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3]) and torch.equal(a[4], b[4])

