@@ -366,6 +366,7 @@ def run_ours(args):
     total_steps = steps * 3 + warmup * 2 + settle * realloc_every + 16
     caps = bucket_capacities(N_r + total_steps, cfg["memory_budget"], D, cfg["available_bits"])
     store = PackedKVStore(L, B, Hkv_r, D, Hq_r, caps, device=dev, track_importance=not seq_mode)
+    store.token_capacity = N_r + total_steps     # what the buckets were sized for: bounds the importance grid under capture
 
     # ---- populate the cache: seeded synthetic K/V stored at the default 4 bits (cache.py:1214), the
     # Zipf importance injected the way the reference's kernel benchmark does, then one reallocation

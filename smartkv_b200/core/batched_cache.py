@@ -61,6 +61,7 @@ class BatchedSmartKVCache:
         self.store = PackedKVStore(num_layers, self.batch_size, num_heads, head_dim, self.num_query_heads,
                                    (cap, cap, cap, cap), device=dev, decay=decay,
                                    head_decay=self.head_importance_decay)
+        self.store.token_capacity = self.max_tokens
         self.store.capture_check = "caller"      # a step that commits early ends twice; GraphedDecoder checks the total
         protected = sorted({0, 1, 2} | set(int(t) for t in (special_token_ids or [])))
         self._cfg = self.store.make_alloc_config(

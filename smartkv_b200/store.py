@@ -374,11 +374,14 @@ class PackedKVStore:
         small = pipe["small"]                         # (max, sum, current-token probability) of every layer of the step
         ps = {k2: v2[pend["layer"]] for k2, v2 in small.items()} if pend is not None else None
         # Under stream capture the host scalars below would be baked into the graph: the importance blocks then
-        # cover every storage index (0 = full grid) instead of the capture-time token count, and the
+        # cover the store's token capacity (or every storage index, 0 = full grid, if nobody stated one) instead of
+        # the capture-time token count, and the
         # head-state parity, which must alternate per update, is refused unless a captured step holds an even
         # number of updates (checked by the caller of commit_step through _capture_updates).
         capturing = torch.cuda.is_current_stream_capturing()
-        max_tokens_arg = 0 if capturing else self.max_seq_tokens
+        # token_capacity (set by whoever sized the buckets): the most tokens a sequence can ever hold, a bound that stays
+        # valid however often the graph is replayed
+        max_tokens_arg = int(getattr(self, "token_capacity", 0) or 0) if capturing else self.max_seq_tokens
 
         def post(stream_ptr):
             check(self.lib.skv_post_attention(

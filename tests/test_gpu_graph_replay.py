@@ -90,3 +90,33 @@ def test_capture_of_an_odd_number_of_importance_updates_is_refused():
     decode_step(store, q, k, v, outs)
     store.check_errors()
     assert int(store.counts.sum()) >= n + 2
+
+
+def test_token_capacity_bounds_the_captured_importance_grid():
+    """With ``token_capacity`` stated, a captured step launches importance blocks for that many tokens instead of
+    every storage index; the replays must still match the eager steps while the cache grows towards the bound."""
+    L, B, hkv, d, hq, n, steps = 2, 2, 8, 128, 32, 250, 20
+    a, b = build(L, B, hkv, d, hq, n, steps + 8), build(L, B, hkv, d, hq, n, steps + 8)
+    a.token_capacity = n + steps + 2
+    q = torch.zeros((L, B, hq, d), dtype=torch.float16, device="cuda")
+    k = torch.zeros((L, B, hkv, d), dtype=torch.float16, device="cuda")
+    v = torch.zeros_like(k)
+    oa = torch.zeros((L, B, hq, d), dtype=torch.float32, device="cuda")
+    ob = torch.zeros_like(oa)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    fresh = lambda t: t.copy_(torch.randn(t.shape, generator=gen, device="cuda"))
+    fresh(q); fresh(k); fresh(v)
+    decode_step(a, q, k, v, oa)
+    decode_step(b, q, k, v, ob)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        decode_step(a, q, k, v, oa)
+    for t in range(steps):
+        fresh(q); fresh(k); fresh(v)
+        graph.replay()
+        decode_step(b, q, k, v, ob)
+        torch.cuda.synchronize()
+        assert torch.equal(oa, ob), t
+    a.check_errors(); b.check_errors()
+    assert torch.equal(a.cumulative, b.cumulative) and torch.equal(a.layer_ema, b.layer_ema)
