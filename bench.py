@@ -949,8 +949,13 @@ def main():
                          "2 (end-to-end generation through the LlamaSmartKV wrapper; decode tokens/s, one GPU)")
     ap.add_argument("--decode-sample", type=int, default=16, help="--config 2 --impl reference: decode steps to time")
     ap.add_argument("--replicas", action="store_true", help="under torchrun: every rank holds the whole configuration (weak scaling)")
+    ap.add_argument("--no-dependent-launch", action="store_true",
+                    help="launch the attention / post-attention kernels without programmatic dependent launch (comparison only)")
     ap.add_argument("--no-settle", action="store_true", help="skip the untimed reallocation cycles before the timed passes")
     args = ap.parse_args()
+    if args.no_dependent_launch and args.impl != "reference":
+        from smartkv_b200 import _lib as _skv
+        _skv.lib().skv_set_dependent_launch(0)
     if args.config == 2:
         if int(os.environ.get("RANK", "0")) == 0:
             (run_generation_reference if args.impl == "reference" else run_generation)(args)

@@ -180,11 +180,19 @@ int skv_decode_attention(const SkvStoreDesc* desc, const void* store, int layer,
  *   mask fp32 [num_seqs][mask_stride], natural-log units, indexed by TOKEN ID (position in the
  *   sequence); slot_token int32 [num_seqs][slots] gives the token id of every storage index.
  *   mask == NULL: no mask (slot_token may then be NULL).  The mask value of the step's current token is
- *   an argument of the combine step (skv_lse_combine_masked). */
+ *   an argument of the combine step (skv_lse_combine_masked).
+ *   flags: SKV_ATTN_DEPENDENT_LAUNCH launches the kernel with the programmatic-serialization attribute: it may start
+ *   (set up, put its first copies of this layer's rows in flight) while the kernel before it in the stream is still
+ *   running, and waits for that kernel before it reads the query or writes anything.  The caller asserts that the
+ *   plan and this layer's rows were NOT written by the kernel directly before this launch (in a decode step: the
+ *   previous layer's skv_post_attention, or the model's own kernels between two layers).  skv_post_attention always
+ *   launches that way (it waits before it reads anything).  skv_set_dependent_launch(0) turns both off. */
+#define SKV_ATTN_DEPENDENT_LAUNCH 1
 int skv_decode_attention_masked(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
                                 const void* query, int query_dtype, int num_q_heads, void* partials, int num_ctas,
                                 float* logits, const float* mask, int64_t mask_stride, const int32_t* slot_token,
-                                int32_t* err_flag, void* stream);
+                                int flags, int32_t* err_flag, void* stream);
+int skv_set_dependent_launch(int on);
 
 /* Kernel selection for skv_decode_attention: 0 = default (the mma.sync fragment kernel), 1 = always the
  * fragment kernel, 2 = the tensor-memory (tcgen05) kernel wherever it applies (head_dim 128, fp16 queries).

@@ -15,6 +15,7 @@ NUM_BUCKETS = 4
 BUCKET_BITS = (2, 3, 4, 8)
 BITS_TO_BUCKET = {2: 0, 3: 1, 4: 2, 8: 3}
 DTYPE_F32, DTYPE_F16 = 0, 1
+ATTN_DEPENDENT_LAUNCH = 1      # flags of skv_decode_attention_masked
 
 SKV_OK = 0
 
@@ -85,7 +86,9 @@ _SIGNATURES = {
     "skv_decode_attention": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "skv_decode_attention_masked": (c_int, [POINTER(StoreDesc), c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                            c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+                                            c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p,
+                                            c_void_p]),
+    "skv_set_dependent_launch": (c_int, [c_int]),
     "skv_set_attention_path": (c_int, [c_int]),
     "skv_get_attention_path": (c_int, []),
     "skv_set_wait_limit": (c_int, [ctypes.c_uint]),

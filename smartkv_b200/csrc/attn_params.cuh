@@ -27,6 +27,7 @@ struct AttnParams {
   int32_t* err;
   float scale_log2;
   unsigned wait_polls;  // limit of every bounded wait, in polls of about 50 ns
+  int dependent;        // launch with the programmatic-serialization attribute (SKV_ATTN_DEPENDENT_LAUNCH)
 };
 
 // Bounded mbarrier wait that also gives up as soon as another thread of the CTA has given up.

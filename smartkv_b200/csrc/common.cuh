@@ -67,6 +67,31 @@ __device__ __forceinline__ void note_v_scale(const StoreGeom& g, uint8_t* arena,
   if (v_scale > kVScaleGuard) *reinterpret_cast<volatile int*>(arena + g.arena_bytes - 256) = 1;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the stream is
+// still running: launch_dependents lets the successor's blocks be scheduled once every block of this grid has
+// executed it (or exited); wait blocks until the predecessor grid has completed and its writes are visible.  Both are
+// no-ops in a launch without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with (or, if `dependent` is false, without) the programmatic-serialization attribute.
+template <class Params>
+inline cudaError_t launch_maybe_dependent(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                          const Params& p, bool dependent) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // ---- small PTX wrappers -----------------------------------------------------
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t d;

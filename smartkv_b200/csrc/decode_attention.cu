@@ -452,9 +452,19 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
   }
   mbar_fence_init();
   __syncthreads();
+  // Dependent launch (layers after the first of a step): this grid may start while the previous layer's post-attention
+  // kernel is still running.  What is read before pdl_wait() -- the plan and this layer's packed rows -- was written
+  // by kernels that completed long before; the query and everything written here come after the wait.  The launch that
+  // follows (combine + append + importance of this layer) waits for this grid itself; letting it be scheduled now only
+  // hides its launch latency.
+  pdl_launch_dependents();
 
   const PlanView pv = plan_view(const_cast<int*>(p.plan), p.num_ctas, g.num_seqs * Hkv);
   const int run_begin = pv.cta_begin[blockIdx.x], run_end = pv.cta_begin[blockIdx.x + 1];
+  if (run_begin >= run_end) {  // nothing to do here; still, no CTA of a dependent launch leaves before its predecessor ended
+    pdl_wait();
+    return;
+  }
 
   if (warp == NCONS) {
     // ================================ producer warp ================================
@@ -544,6 +554,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
       // the NEXT run is published, so that no consumer ever waits for query rows at a run boundary
       ok = issue_blocks(d, ci, ct0, STAGES);
       if (r == run_begin) {
+        pdl_wait();  // the first copies are in flight; query rows are read from here on
         ok = ok && publish_query(r, d);
       }
       RunDesc dn = d;
@@ -587,6 +598,7 @@ __global__ void __launch_bounds__((CFG::NCONS + 1) * 32, 1) decode_attn_kernel(c
     const RunDesc& d = slot.desc;
     const bool guard = slot.guard != 0;
     if (r == run_begin) {
+      pdl_wait();
       for (int gq = warp; gq < G; gq += NCONS) prep_query_heads<D, PRECISE>(qslots[qi], p, d.seq, d.head, G, gq, gq + 1, lane);
       named_bar_sync(1, NCONS * 32);
     }
@@ -747,6 +759,13 @@ extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, in
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
 
+// Programmatic dependent launch of the attention and post-attention kernels (skv_set_dependent_launch).
+std::atomic<int> g_dependent_launch{1};
+extern "C" int skv_set_dependent_launch(int on) {
+  g_dependent_launch.store(on ? 1 : 0);
+  return SKV_OK;
+}
+
 template <int D, bool PRECISE, class CFG, bool MASKED>
 static int launch_attn_inst(AttnParams& p, cudaStream_t st) {
   static bool configured[64] = {};  // per template instance and device: the attribute belongs to the device's context
@@ -762,7 +781,8 @@ static int launch_attn_inst(AttnParams& p, cudaStream_t st) {
     }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  decode_attn_kernel<D, PRECISE, CFG, MASKED><<<p.num_ctas, (CFG::NCONS + 1) * 32, smem, st>>>(p);
+  launch_maybe_dependent(decode_attn_kernel<D, PRECISE, CFG, MASKED>, dim3(p.num_ctas), dim3((CFG::NCONS + 1) * 32), smem, st, p,
+                         p.dependent != 0 && g_dependent_launch.load() != 0);
   const cudaError_t rc = cudaGetLastError();
   if (rc != cudaSuccess) {
     fprintf(stderr, "skv_decode_attention: launch failed: %s\n", cudaGetErrorString(rc));
@@ -788,7 +808,7 @@ extern "C" int skv_set_wait_limit(unsigned polls) {
 extern "C" int skv_decode_attention_masked(const SkvStoreDesc* desc, const void* store, int layer, const void* plan,
                                            const void* query, int query_dtype, int num_q_heads, void* partials,
                                            int num_ctas, float* logits, const float* mask, int64_t mask_stride,
-                                           const int32_t* slot_token, int32_t* err_flag, void* stream) {
+                                           const int32_t* slot_token, int flags, int32_t* err_flag, void* stream) {
   if (!desc || !store || !plan || !query || !partials || !err_flag) return SKV_ERR_INVALID;
   if (layer < 0 || layer >= desc->num_layers || num_ctas <= 0 || num_ctas > kMaxCtas) return SKV_ERR_INVALID;
   if (desc->head_dim != 64 && desc->head_dim != 128) return SKV_ERR_UNSUPPORTED;
@@ -816,6 +836,7 @@ extern "C" int skv_decode_attention_masked(const SkvStoreDesc* desc, const void*
   p.err = err_flag;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)desc->head_dim));
   p.wait_polls = g_wait_polls.load();
+  p.dependent = (flags & SKV_ATTN_DEPENDENT_LAUNCH) ? 1 : 0;
   if (use_tc_path(desc, query_dtype)) return launch_attn_tc(p, *desc, as_stream(stream));
   const bool precise = !p.q_is_half;
   if (desc->head_dim == 128)
@@ -829,7 +850,7 @@ extern "C" int skv_decode_attention(const SkvStoreDesc* desc, const void* store,
                                     const void* query, int query_dtype, int num_q_heads, void* partials,
                                     int num_ctas, float* logits, int32_t* err_flag, void* stream) {
   return skv_decode_attention_masked(desc, store, layer, plan, query, query_dtype, num_q_heads, partials, num_ctas,
-                                     logits, nullptr, 0, nullptr, err_flag, stream);
+                                     logits, nullptr, 0, nullptr, 0, err_flag, stream);
 }
 
 extern "C" int skv_lse_combine_masked(const SkvStoreDesc* desc, const void* plan, const void* query, int query_dtype,

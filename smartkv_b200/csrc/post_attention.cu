@@ -4,6 +4,10 @@
 // side and a decode step costs two launches per layer instead of four.
 #include "post_attention.cuh"
 
+#include <atomic>
+
+extern std::atomic<int> g_dependent_launch;  // decode_attention.cu
+
 namespace skv {
 
 struct PostParams {
@@ -24,6 +28,11 @@ union PostShared {
 template <int EPL>
 __global__ void __launch_bounds__(kPostThreads) post_attention_kernel(const PostParams p) {
   __shared__ PostShared sh;
+  // dependent launch: the next layer's attention kernel may be scheduled as soon as every block here has started (it
+  // touches nothing this kernel uses until it has waited for this grid itself); this kernel needs the attention kernel
+  // before it complete
+  pdl_launch_dependents();
+  pdl_wait();
   int blk = blockIdx.x;
   if (blk < p.combine_blocks) {
     combine_unit(p.c, blk, sh.c);
@@ -140,9 +149,10 @@ extern "C" int skv_post_attention(const SkvStoreDesc* desc, void* store, int lay
   }
   const int grid = p.combine_blocks + p.imp_chunks * desc->num_seqs + p.append_blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool dep = g_dependent_launch.load() != 0;
   if (desc->head_dim == 128)
-    post_attention_kernel<4><<<grid, kPostThreads, 0, st>>>(p);
+    launch_maybe_dependent(post_attention_kernel<4>, dim3(grid), dim3(kPostThreads), 0, st, p, dep);
   else
-    post_attention_kernel<2><<<grid, kPostThreads, 0, st>>>(p);
+    launch_maybe_dependent(post_attention_kernel<2>, dim3(grid), dim3(kPostThreads), 0, st, p, dep);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }

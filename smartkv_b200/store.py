@@ -293,7 +293,7 @@ class PackedKVStore:
                                                    self._dtype_code(q), self.num_q_heads, ptr(self.partials),
                                                    self.num_ctas, ptr(self.logits) if want_logits else None, ptr(mask),
                                                    0 if mask is None else int(mask.shape[1]),
-                                                   ptr(self.slot_token) if mask is not None else None, ptr(self.err), st),
+                                                   ptr(self.slot_token) if mask is not None else None, 0, ptr(self.err), st),
               "skv_decode_attention")
         if kernel_events is not None:
             kernel_events[1].record()
@@ -340,11 +340,16 @@ class PackedKVStore:
         q = query.contiguous()
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
+        plan_was_valid = self._plan_valid
         if not self._plan_valid:
             self.build_plan()
         pipe = self._pipe_buffers()
         m = pipe["calls"]
-        lslot, pslot = m % 3, (m % 2 if overlap else 0)
+        lslot, pslot = m % 3, m % 2
+        # The attention kernel of the second and later layers of a step may be launched as a dependent of what runs
+        # before it (the previous layer's post-attention kernel, or the model's own kernels between two layers): none of
+        # those writes the plan or this layer's rows.  Not so right after a plan rebuild or at the start of a step.
+        flags = _lib.ATTN_DEPENDENT_LAUNCH if (m > 0 and plan_was_valid and not overlap and kernel_events is None) else 0
         bufs = pipe["bufs"][lslot]
         partials = pipe["partials"][pslot]
         main = torch.cuda.current_stream(self.device)
@@ -359,7 +364,7 @@ class PackedKVStore:
                                                    self._dtype_code(q), self.num_q_heads, ptr(partials), self.num_ctas,
                                                    ptr(bufs["logits"]) if want_logits else None, ptr(mask),
                                                    0 if mask is None else int(mask.shape[1]),
-                                                   ptr(self.slot_token) if mask is not None else None, ptr(self.err), st),
+                                                   ptr(self.slot_token) if mask is not None else None, flags, ptr(self.err), st),
               "skv_decode_attention")
         if kernel_events is not None:
             kernel_events[1].record()
