@@ -551,6 +551,7 @@ def run_ours(args):
             h2d.wait_stream(main)
             d2h.wait_stream(main)
             plan = store.plan_step()
+            arrived = []
             for layer in range(L):
                 with torch.cuda.stream(h2d):
                     q_stage[layer].copy_(q_host[j][layer], non_blocking=True)
@@ -558,9 +559,14 @@ def run_ours(args):
                     v_stage[layer].copy_(v_host[j][layer], non_blocking=True)
                     ev_in = torch.cuda.Event()
                     ev_in.record(h2d)
-                main.wait_event(ev_in)
+                arrived.append(ev_in)
+            main.wait_event(arrived[0])
+            for layer in range(L):
+                # the wait for the NEXT layer's inputs sits between this layer's two launches, so that the next attention
+                # kernel directly follows this layer's post-attention kernel (and can be launched as its dependent)
+                nxt = (lambda ev=arrived[layer + 1]: main.wait_event(ev)) if layer + 1 < L else None
                 store.decode_layer(layer, q_stage[layer], k_stage[layer], v_stage[layer], plan,
-                                   update_importance=True, out=out_dev[layer])
+                                   update_importance=True, out=out_dev[layer], before_post=nxt)
                 ev_out = torch.cuda.Event()
                 ev_out.record(main)
                 with torch.cuda.stream(d2h):

@@ -324,7 +324,8 @@ class PackedKVStore:
 
     def decode_layer(self, layer: int, query: torch.Tensor, cur_k: torch.Tensor, cur_v: torch.Tensor, step_plan,
                      update_importance: bool = True, out: Optional[torch.Tensor] = None,
-                     kernel_events=None, overlap: bool = False, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     kernel_events=None, overlap: bool = False, mask: Optional[torch.Tensor] = None,
+                     before_post=None) -> torch.Tensor:
         """One layer of a decode step in two launches: the streaming attention kernel, then one kernel
         with this layer's combine, the append of the new token (``step_plan`` from plan_step) and the
         importance update of the PREVIOUS decode_layer call (skv_post_attention).  The last layer's
@@ -336,7 +337,10 @@ class PackedKVStore:
         call m then only waits for the side work of call m-2 (partials are double, logits triple buffered).
         The outputs of such a call are ready after join() / commit_step().
 
-        ``mask``: additive fp32 [B, n] indexed by token id, natural-log units (see attention())."""
+        ``mask``: additive fp32 [B, n] indexed by token id, natural-log units (see attention()).
+        ``before_post``: called between the two launches; a caller that must make the stream wait for something the
+        NEXT layer needs (its inputs arriving on a copy stream) does it there, so that the next layer's attention
+        kernel directly follows this layer's second launch and can be launched as its dependent."""
         q = query.contiguous()
         assert q.shape == (self.num_seqs, self.num_q_heads, self.head_dim)
         want_logits = update_importance and self.track_importance
@@ -415,6 +419,8 @@ class PackedKVStore:
             pipe["post_events"].append(ev)
             pipe["forked"] = True
         else:
+            if before_post is not None:
+                before_post()
             post(st)
         if pend is not None:
             self.head_parity ^= 1
