@@ -360,10 +360,6 @@ def run_ours(args):
     else:
         Hkv_r, Hq_r, N_r, tok0 = Hkv, Hq, N, 0
     seq_mode = shard == "sequence" and world > 1
-    if seq_mode:
-        # measured: with sequence shards the dependent launch of the attention kernel costs time instead of saving it
-        # (2 GPUs: 1.52 against 1.41 ms per step, 4 GPUs: 1.32 against 1.19), so this mode launches plainly
-        skv_lib.lib().skv_set_dependent_launch(0)
     steps, warmup = args.steps, args.warmup
     realloc_every = cfg["realloc_every"]
     settle = 0 if (seq_mode or args.no_settle) else 2       # reallocation cycles run before anything is timed
@@ -961,11 +957,13 @@ def main():
     ap.add_argument("--replicas", action="store_true", help="under torchrun: every rank holds the whole configuration (weak scaling)")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch the attention / post-attention kernels without programmatic dependent launch (comparison only)")
+    ap.add_argument("--dependent-launch-mode", type=int, default=-1, choices=[-1, 0, 1, 2, 3],
+                    help="comparison only: 0 off, 1 both kernels, 2 attention kernel only, 3 post-attention kernel only")
     ap.add_argument("--no-settle", action="store_true", help="skip the untimed reallocation cycles before the timed passes")
     args = ap.parse_args()
-    if args.no_dependent_launch and args.impl != "reference":
+    if (args.no_dependent_launch or args.dependent_launch_mode >= 0) and args.impl != "reference":
         from smartkv_b200 import _lib as _skv
-        _skv.lib().skv_set_dependent_launch(0)
+        _skv.lib().skv_set_dependent_launch(0 if args.no_dependent_launch else args.dependent_launch_mode)
     if args.config == 2:
         if int(os.environ.get("RANK", "0")) == 0:
             (run_generation_reference if args.impl == "reference" else run_generation)(args)

@@ -760,9 +760,11 @@ extern "C" int skv_attn_plan(const SkvStoreDesc* desc, const int32_t* counts, in
 }
 
 // Programmatic dependent launch of the attention and post-attention kernels (skv_set_dependent_launch).
-std::atomic<int> g_dependent_launch{1};
+std::atomic<int> g_dependent_launch{2};  // measured: the attention kernel gains from it, the post-attention kernel loses
 extern "C" int skv_set_dependent_launch(int on) {
-  g_dependent_launch.store(on ? 1 : 0);
+  // 0 = off, 1 = attention and post-attention kernels, 2 = attention kernel only, 3 = post-attention kernel only
+  if (on < 0 || on > 3) return SKV_ERR_INVALID;
+  g_dependent_launch.store(on);
   return SKV_OK;
 }
 
@@ -782,7 +784,7 @@ static int launch_attn_inst(AttnParams& p, cudaStream_t st) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   launch_maybe_dependent(decode_attn_kernel<D, PRECISE, CFG, MASKED>, dim3(p.num_ctas), dim3((CFG::NCONS + 1) * 32), smem, st, p,
-                         p.dependent != 0 && g_dependent_launch.load() != 0);
+                         p.dependent != 0 && (g_dependent_launch.load() == 1 || g_dependent_launch.load() == 2));
   const cudaError_t rc = cudaGetLastError();
   if (rc != cudaSuccess) {
     fprintf(stderr, "skv_decode_attention: launch failed: %s\n", cudaGetErrorString(rc));

@@ -149,7 +149,7 @@ extern "C" int skv_post_attention(const SkvStoreDesc* desc, void* store, int lay
   }
   const int grid = p.combine_blocks + p.imp_chunks * desc->num_seqs + p.append_blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool dep = g_dependent_launch.load() != 0;
+  const bool dep = g_dependent_launch.load() == 1 || g_dependent_launch.load() == 3;
   if (desc->head_dim == 128)
     launch_maybe_dependent(post_attention_kernel<4>, dim3(grid), dim3(kPostThreads), 0, st, p, dep);
   else
