@@ -363,7 +363,7 @@ def run_ours(args):
     steps, warmup = args.steps, args.warmup
     realloc_every = cfg["realloc_every"]
     settle = 0 if (seq_mode or args.no_settle) else 2       # reallocation cycles run before anything is timed
-    total_steps = steps * 3 + warmup * 2 + settle * realloc_every + 16
+    total_steps = steps * 3 + warmup * 2 + settle * realloc_every + 16 + 32     # + the launch-mode autotune's replays
     caps = bucket_capacities(N_r + total_steps, cfg["memory_budget"], D, cfg["available_bits"])
     store = PackedKVStore(L, B, Hkv_r, D, Hq_r, caps, device=dev, track_importance=not seq_mode)
     store.token_capacity = N_r + total_steps     # what the buckets were sized for: bounds the importance grid under capture
@@ -498,6 +498,38 @@ def run_ours(args):
 
     per_step_launches = 2 * L + 4
     graph = None
+    # Which kernels are launched as programmatic dependents is chosen by measurement, like the attention kernel itself:
+    # the attention kernel alone (2) wins on large shards, attention + post-attention (1) on small ones.
+    pdl_choice = None
+    if not args.no_graph and not args.no_dependent_launch and args.dependent_launch_mode < 0:
+        trial = {}
+        for mode in (2, 1):
+            skv_lib.lib().skv_set_dependent_launch(mode)
+            decode_step(q_dev[0], k_dev[0], v_dev[0])
+            torch.cuda.synchronize()
+            gt = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gt):
+                decode_step(q_dev[0], k_dev[0], v_dev[0])
+            for _ in range(3):
+                gt.replay()
+            ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ea.record()
+            for _ in range(8):
+                gt.replay()
+            eb.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([ea.elapsed_time(eb) / 8], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            trial[mode] = float(t.item())
+            del gt
+        best = min(trial, key=trial.get)
+        skv_lib.lib().skv_set_dependent_launch(best)
+        pdl_choice = {"selected": {1: "attention and post-attention kernels", 2: "attention kernel only"}[best],
+                      "ms_per_step": {("attention+post" if m == 1 else "attention"): round(v, 4) for m, v in trial.items()}}
     if not args.no_graph:
         # the whole step (every layer's launches) as one CUDA graph over static input buffers
         side = torch.cuda.Stream(device=dev)
@@ -764,7 +796,7 @@ def run_ours(args):
         "reallocation_wait_for_ranks_ms": ([round(a[0].elapsed_time(b), 3) for a, b in zip(realloc_events, sync_events[1 + settle:])]
                                            if sync_events else None),
         "ranks_agree": agree,
-        "gpu_launches": int(n_launch), "cuda_graph": graph is not None,
+        "gpu_launches": int(n_launch), "cuda_graph": graph is not None, "dependent_launch": pdl_choice,
         "clocks": clocks,
     }
     if rank == 0:
