@@ -433,6 +433,46 @@ def run_ours(args):
         for t in (q_dev, k_dev, v_dev):
             dist.broadcast(t, 0)
     out_dev = torch.empty((L, B, Hq_r, D), dtype=torch.float32, device=dev)
+
+    # ---- sequence shards check themselves: layer 0 of the populated cache, no new token.  Every rank's (max, sum, out)
+    # over its token range is gathered and folded; rank 0 also gets every rank's stored rows of that layer (codes,
+    # scales, widths), puts them into ONE store and attends over it; the two must agree at the attention tolerance.
+    self_check = None
+    if seq_mode:
+        from smartkv_b200.store import round_up as _round_up
+        qc = q_dev[0, 0].contiguous()
+        o = store.attention(0, qc).clone()
+        part = torch.cat([store.lse_max[..., None], store.lse_sum[..., None], o * store.lse_sum[..., None]], -1).contiguous()
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        folded_chk = fold_partials(torch.stack(parts))
+        rows = [store.export_sequence(0, b) for b in range(B)]
+        mine = [torch.stack([r[i] for r in rows]).contiguous() for i in range(1, 6)]     # bits, k codes, v codes, k scale, v scale
+        everyone = []
+        for t in mine:
+            g_ = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(g_, t)
+            everyone.append(torch.cat(g_, dim=1))                                          # ranks hold consecutive token ranges
+        if rank == 0:
+            bits_f, kc_f, vc_f, ks_f, vs_f = everyone
+            cap = _round_up(N + 1, 128)
+            whole = PackedKVStore(1, B, Hkv_r, D, Hq_r, (cap, cap, cap, cap), device=dev, track_importance=False)
+            dw = whole.plan_bulk(bits_f.long())
+            skv_lib.check(whole.lib.skv_import_rows(ctypes.byref(whole.desc), skv_lib.ptr(whole.arena), 0, B * N, skv_lib.ptr(dw[0]),
+                                                    skv_lib.ptr(dw[1]), skv_lib.ptr(dw[2]), skv_lib.ptr(kc_f.reshape(B * N, Hkv_r, D).contiguous()),
+                                                    skv_lib.ptr(vc_f.reshape(B * N, Hkv_r, D).contiguous()),
+                                                    skv_lib.ptr(ks_f.reshape(B * N, Hkv_r).contiguous()),
+                                                    skv_lib.ptr(vs_f.reshape(B * N, Hkv_r).contiguous()), skv_lib.ptr(whole.err),
+                                                    whole._stream()), "skv_import_rows")
+            ref = whole.attention(0, qc)
+            whole.check_errors()
+            err = (folded_chk - ref).abs()
+            tol = 2e-3 + 1e-3 * ref.abs()
+            self_check = {"what": "layer 0: folded partials of the shards against one store holding every shard's rows",
+                          "max_abs_err": float(err.max()), "within_tolerance": bool((err <= tol).all())}
+            del whole, ref
+        del everyone, mine, rows
+        torch.cuda.empty_cache()
     q_host = q_dev.cpu().pin_memory()
     k_host = k_dev.cpu().pin_memory()
     v_host = v_dev.cpu().pin_memory()
@@ -797,6 +837,7 @@ def run_ours(args):
                                            if sync_events else None),
         "ranks_agree": agree,
         "gpu_launches": int(n_launch), "cuda_graph": graph is not None, "dependent_launch": pdl_choice,
+        "sharded_self_check": self_check,
         "clocks": clocks,
     }
     if rank == 0:
