@@ -429,6 +429,19 @@ def gen_forecast(out):
     out["f_last_loss"] = np.array(c.forecast_last_loss if c.forecast_last_loss is not None else -1.0)
     out["f_w0"] = c.forecast_predictor.model.net[0].weight.detach().numpy().copy()
     out["f_importance"] = np.array([c.importance_tracker.get_importance(t) for t in range(n + steps)])
+    # the predictor alone: seeded construction, a prediction, five updates on seeded rows
+    from smartkv.core.forecast import ForecastPredictor
+    torch.manual_seed(321)
+    pr = ForecastPredictor(6, lr=0.05)
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn((24, 6), generator=g)
+    t = torch.randn(24, generator=g)
+    out["fp_x"], out["fp_t"] = x.numpy(), t.numpy()
+    out["fp_w0_init"] = pr.model.net[0].weight.detach().numpy().copy()
+    out["fp_pred_init"] = pr.predict(x).numpy()
+    out["fp_losses"] = np.array([pr.update(x, t) for _ in range(5)])
+    out["fp_w1_after"] = pr.model.net[2].weight.detach().numpy().copy()
+    out["fp_pred_after"] = pr.predict(x).numpy()
 
 
 def main():

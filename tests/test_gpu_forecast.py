@@ -43,7 +43,7 @@ def test_forecast_blend_tracks_the_reference():
     assert c.realloc_counter == int(z["f_reallocs"]) and updates[0] == int(z["f_updates"])
     imp = np.array([c.get_importance(t) for t in range(n + steps)])
     assert np.allclose(imp, z["f_importance"], rtol=1e-5, atol=1e-6)
-    w0 = c.forecast_predictor.model[0].weight.detach().numpy()
+    w0 = c.forecast_predictor.params[0].detach().numpy()
     assert np.allclose(w0, z["f_w0"], atol=2e-3), np.abs(w0 - z["f_w0"]).max()
     assert abs(c.forecast_last_loss - float(z["f_last_loss"])) <= 1e-3
     bits = np.array([c.get_precision(t) for t in range(n + steps)])
