@@ -10,6 +10,8 @@ extern std::atomic<int> g_dependent_launch;  // decode_attention.cu
 
 namespace skv {
 
+constexpr int kImpWide = 4;  // chunks per importance block once the grid would exceed two waves
+
 struct PostParams {
   CombineParams c;
   ImportanceParams imp;
@@ -17,6 +19,7 @@ struct PostParams {
   int combine_blocks;
   int imp_chunks;      // importance blocks = imp_chunks * num_seqs (0: no importance update)
   int imp_compact;     // 1: block j of a sequence takes that sequence's j-th live chunk
+  int imp_kpt;         // chunks per importance block (1 or kImpWide): one storage index of each per thread
   int append_blocks;   // 8 rows-of-a-head per block (0: no append)
 };
 
@@ -39,12 +42,31 @@ __global__ void __launch_bounds__(kPostThreads) post_attention_kernel(const Post
     return;
   }
   blk -= p.combine_blocks;
-  const int imp_blocks = p.imp_chunks * p.c.g.num_seqs;
+  const int per_seq = (p.imp_chunks + p.imp_kpt - 1) / p.imp_kpt;
+  const int imp_blocks = per_seq * p.c.g.num_seqs;
   if (blk < imp_blocks) {
-    const int b = blk / p.imp_chunks, j = blk - b * p.imp_chunks;
-    // a compact grid walks the live chunks only; the full grid visits every chunk
-    const int chunk = p.imp_compact ? live_chunk(p.c.g, p.imp.counts + b * kNumBuckets, j) : j;
-    if (chunk >= 0) importance_unit(p.imp, chunk, b, j == 0, sh.i);
+    const int b = blk / per_seq, j = blk - b * per_seq;
+    if (p.imp_kpt == 1) {
+      // a compact grid walks the live chunks only; the full grid visits every chunk
+      const int chunk = p.imp_compact ? live_chunk(p.c.g, p.imp.counts + b * kNumBuckets, j) : j;
+      if (chunk >= 0) importance_unit(p.imp, chunk, b, j == 0, sh.i);
+      return;
+    }
+    // wide blocks (large batches): kImpWide chunks per block
+    const ImportanceSeq q = importance_seq(p.imp, b);
+    int chunks[kImpWide];
+    bool any = j == 0;  // the first block of a sequence publishes the head-importance EMA whatever it holds
+#pragma unroll
+    for (int k = 0; k < kImpWide; ++k) {
+      const int jj = j * kImpWide + k;
+      int c = jj < p.imp_chunks ? (p.imp_compact ? live_chunk(p.c.g, p.imp.counts + b * kNumBuckets, jj) : jj) : -1;
+      if (c >= 0 && !importance_chunk_live(p.c.g, q, c)) c = -1;
+      chunks[k] = c;
+      any |= c >= 0;
+    }
+    if (!any) return;
+    importance_prologue(p.imp, b, q, j == 0, sh.i);
+    importance_chunks<kImpWide>(p.imp, chunks, b, q, sh.i);
     return;
   }
   blk -= imp_blocks;
@@ -147,7 +169,10 @@ extern "C" int skv_post_attention(const SkvStoreDesc* desc, void* store, int lay
     const long long warps = (long long)a.rows * desc->num_kv_heads * 2;
     p.append_blocks = (int)((warps + kPostThreads / 32 - 1) / (kPostThreads / 32));
   }
-  const int grid = p.combine_blocks + p.imp_chunks * desc->num_seqs + p.append_blocks;
+  p.imp_kpt = 1;
+  if (with_importance && (long long)p.imp_chunks * desc->num_seqs > 2LL * num_ctas * 4) p.imp_kpt = kImpWide;
+  const int imp_grid = with_importance ? ((p.imp_chunks + p.imp_kpt - 1) / p.imp_kpt) * desc->num_seqs : 0;
+  const int grid = p.combine_blocks + imp_grid + p.append_blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool dep = g_dependent_launch.load() == 1 || g_dependent_launch.load() == 3;
   if (desc->head_dim == 128)

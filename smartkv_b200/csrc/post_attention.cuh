@@ -234,41 +234,50 @@ __device__ __forceinline__ int live_chunk(const StoreGeom& g, const int32_t* cou
   return (j == 0 && seen == 0) ? 0 : -1;
 }
 
-// One unit = 256 consecutive storage indices of one sequence; blockDim.x == kPostThreads.
-// `publish` marks the one block per sequence that writes the new head-importance EMA.
-__device__ __forceinline__ void importance_unit(const ImportanceParams& p, int chunk, int b, bool publish,
-                                                ImportanceShared& sh) {
-  const StoreGeom& g = p.g;
-  const int tid = threadIdx.x, Hq = p.num_q_heads;
+// Bucket counts and the current token's slot of one sequence.
+struct ImportanceSeq {
   int cnt[kNumBuckets];
-  int nkeys = 0;
-#pragma unroll
-  for (int i = 0; i < kNumBuckets; ++i) {
-    cnt[i] = p.counts[b * kNumBuckets + i];
-    nkeys += cnt[i];
-  }
-  const int cur_slot = (p.cur_prob != nullptr && p.cur_slot != nullptr) ? p.cur_slot[b] : -1;
-  const bool has_cur = cur_slot >= 0;
-  const int total_keys = nkeys + (has_cur ? 1 : 0);
+  int cur_slot;
+  bool has_cur;
+};
 
-  // most storage indices of a sequence are unused capacity: a block without a live key leaves at once
-  // (the publishing block of every sequence stays)
+__device__ __forceinline__ ImportanceSeq importance_seq(const ImportanceParams& p, int b) {
+  ImportanceSeq q;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) q.cnt[i] = p.counts[b * kNumBuckets + i];
+  q.cur_slot = (p.cur_prob != nullptr && p.cur_slot != nullptr) ? p.cur_slot[b] : -1;
+  q.has_cur = q.cur_slot >= 0;
+  return q;
+}
+
+// True if the 256 storage indices of `chunk` hold a cached key or the slot of the current token.
+__device__ __forceinline__ bool importance_chunk_live(const StoreGeom& g, const ImportanceSeq& q, int chunk) {
   const int s_lo = chunk * kPostThreads, s_hi = s_lo + kPostThreads;
-  bool block_live = publish || (has_cur && cur_slot >= s_lo && cur_slot < s_hi);
+  bool live = q.has_cur && q.cur_slot >= s_lo && q.cur_slot < s_hi;
 #pragma unroll
   for (int i = 0; i < kNumBuckets; ++i)
-    block_live |= cnt[i] > 0 && g.bucket_base[i] < s_hi && g.bucket_base[i] + cnt[i] > s_lo;
-  if (!block_live) return;
+    live |= q.cnt[i] > 0 && g.bucket_base[i] < s_hi && g.bucket_base[i] + q.cnt[i] > s_lo;
+  return live;
+}
 
+// Head weights of sequence b into shared memory: w = weight / final sum, mx = final max, cprob = unnormalised
+// probability of the current token (all threads of the block; ends with a barrier).  `publish` marks the one block
+// per sequence that writes the new head-importance EMA.
+__device__ __forceinline__ void importance_prologue(const ImportanceParams& p, int b, const ImportanceSeq& q, bool publish,
+                                                    ImportanceShared& sh) {
+  const int tid = threadIdx.x, Hq = p.num_q_heads;
+  int nkeys = 0;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) nkeys += q.cnt[i];
+  const int total_keys = nkeys + (q.has_cur ? 1 : 0);
   // final (max, sum) of every query head and the probability of the current token, as the combine
   // step of this layer left them (issued early: independent of the EMA chain below)
   float lse_l = 0.f, lse_m = 0.f, pcur = 0.f;
   if (tid < Hq) {
     lse_l = p.lse_sum[(long long)b * Hq + tid];
     lse_m = p.lse_max[(long long)b * Hq + tid];
-    pcur = has_cur ? p.cur_prob[(long long)b * Hq + tid] * lse_l : 0.f;
+    pcur = q.has_cur ? p.cur_prob[(long long)b * Hq + tid] * lse_l : 0.f;
   }
-
   // head-importance EMA (cache.py:242-248).  Every softmax row sums to one, so the
   // mean over keys of a head's probabilities is 1 / (number of keys).
   const float* hs_old = p.head_state + ((long long)b * 2 + p.parity) * Hq;
@@ -294,44 +303,82 @@ __device__ __forceinline__ void importance_unit(const ImportanceParams& p, int c
     sh.cprob[tid] = pcur;
   }
   __syncthreads();
+}
 
-  const int s = s_lo + tid;  // storage index
-  bool valid = false;
-  if (s < g.slots) {
+// KPT chunks of 256 storage indices at once, one storage index of each per thread: the loads of all of them are in
+// flight together (the update of one key is two dependent round trips to memory and a handful of bytes; a large
+// batch is thousands of such blocks otherwise, each waiting out the same latencies).  chunks[k] < 0: nothing to do.
+// Per key the sum over the heads runs in head order whatever KPT is, so the results do not depend on it.
+template <int KPT>
+__device__ __forceinline__ void importance_chunks(const ImportanceParams& p, const int (&chunks)[KPT], int b,
+                                                  const ImportanceSeq& q, const ImportanceShared& sh) {
+  const StoreGeom& g = p.g;
+  const int Hq = p.num_q_heads;
+  int s[KPT];
+  bool valid[KPT], is_cur[KPT];
+  double cum[KPT];
+  float ema[KPT], mass[KPT];
+  uint8_t seen[KPT];
 #pragma unroll
-    for (int i = 0; i < kNumBuckets; ++i) valid |= (s >= g.bucket_base[i] && s < g.bucket_base[i] + cnt[i]);
+  for (int k = 0; k < KPT; ++k) {
+    s[k] = chunks[k] * kPostThreads + threadIdx.x;  // storage index
+    valid[k] = false;
+    if (chunks[k] >= 0 && s[k] < g.slots) {
+#pragma unroll
+      for (int i = 0; i < kNumBuckets; ++i) valid[k] |= (s[k] >= g.bucket_base[i] && s[k] < g.bucket_base[i] + q.cnt[i]);
+    }
+    is_cur[k] = chunks[k] >= 0 && !valid[k] && q.has_cur && s[k] == q.cur_slot;
+    mass[k] = 0.f;
+    cum[k] = 0.0;
+    ema[k] = 0.f;
+    seen[k] = 0;
   }
-  float mass = 0.f;
-  const bool is_cur = !valid && has_cur && s == cur_slot;
-  const bool write = valid || is_cur;
-  const long long ci = (long long)b * g.slots + s;
-  const long long li = ((long long)p.layer * g.num_seqs + b) * g.slots + s;
-  // the state this thread updates is fetched before the logits so that the two latencies overlap
-  double cum = 0.0;
-  float ema = 0.f;
-  uint8_t seen = 0;
-  if (write) {
-    cum = p.cumulative[ci];
-    ema = p.layer_ema[li];
-    seen = p.touched[li];
-  }
-  if (valid) {
-    const float* lg = p.logits + (long long)b * Hq * g.slots + s;
-#pragma unroll 16
-    for (int h = 0; h < Hq; ++h) mass += sh.w[h] * ex2f(lg[(long long)h * g.slots] - sh.mx[h]);
-  } else if (is_cur) {
-    // the newest token: it is stored at this storage index when the step's append commits
-    for (int h = 0; h < Hq; ++h) mass += sh.w[h] * sh.cprob[h];
-  }
-  if (write) {
-    p.cumulative[ci] = cum + (double)mass;
-    if (seen) {
-      p.layer_ema[li] = p.decay * ema + (1.0f - p.decay) * mass;
-    } else {
-      p.layer_ema[li] = mass;
-      p.touched[li] = 1;
+  const long long seq_base = (long long)b * g.slots;
+  const long long lay_base = ((long long)p.layer * g.num_seqs + b) * g.slots;
+  // the state these threads update is fetched before the logits so that the latencies overlap
+#pragma unroll
+  for (int k = 0; k < KPT; ++k) {
+    if (valid[k] || is_cur[k]) {
+      cum[k] = p.cumulative[seq_base + s[k]];
+      ema[k] = p.layer_ema[lay_base + s[k]];
+      seen[k] = p.touched[lay_base + s[k]];
     }
   }
+  const float* lg = p.logits + (long long)b * Hq * g.slots;
+#pragma unroll 4
+  for (int h = 0; h < Hq; ++h) {
+    const float wv = sh.w[h], mv = sh.mx[h], cp = sh.cprob[h];
+    const float* row = lg + (long long)h * g.slots;
+#pragma unroll
+    for (int k = 0; k < KPT; ++k) {
+      if (valid[k]) mass[k] += wv * ex2f(row[s[k]] - mv);
+      else if (is_cur[k]) mass[k] += wv * cp;  // the newest token: stored at this index when the step's append commits
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < KPT; ++k) {
+    if (valid[k] || is_cur[k]) {
+      p.cumulative[seq_base + s[k]] = cum[k] + (double)mass[k];
+      if (seen[k]) {
+        p.layer_ema[lay_base + s[k]] = p.decay * ema[k] + (1.0f - p.decay) * mass[k];
+      } else {
+        p.layer_ema[lay_base + s[k]] = mass[k];
+        p.touched[lay_base + s[k]] = 1;
+      }
+    }
+  }
+}
+
+// One unit = 256 consecutive storage indices of one sequence; blockDim.x == kPostThreads.
+__device__ __forceinline__ void importance_unit(const ImportanceParams& p, int chunk, int b, bool publish,
+                                                ImportanceShared& sh) {
+  const ImportanceSeq q = importance_seq(p, b);
+  // most storage indices of a sequence are unused capacity: a block without a live key leaves at once
+  // (the publishing block of every sequence stays)
+  if (!publish && !importance_chunk_live(p.g, q, chunk)) return;
+  importance_prologue(p, b, q, publish, sh);
+  const int one[1] = {chunk};
+  importance_chunks<1>(p, one, b, q, sh);
 }
 
 // ---- append ---------------------------------------------------------------------------------------------

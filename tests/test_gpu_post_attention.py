@@ -27,7 +27,18 @@ def _pair(B, hq, hkv, d, n, L, seed):
 @pytest.mark.parametrize("hq,hkv,d,q_dtype", [(32, 8, 128, np.float16), (8, 2, 64, np.float32), (6, 2, 128, np.float16),
                                               (4, 4, 64, np.float16)])
 def test_fused_post_attention_equals_separate_calls(hq, hkv, d, q_dtype):
-    B, n, L = 3, 700, 2
+    _fused_equals_separate(3, hq, hkv, d, 700, q_dtype)
+
+
+def test_fused_post_attention_large_batch_takes_the_wide_importance_blocks():
+    """80 sequences x 18 live chunks exceed two waves of importance blocks, so the fused launch switches to blocks of four
+    chunks (four keys per thread, their loads in flight together); the stand-alone importance kernel keeps one.  The
+    per-key sums run in the same order either way, so every importance array must come out the same."""
+    _fused_equals_separate(80, 4, 1, 64, 2000, np.float16)
+
+
+def _fused_equals_separate(B, hq, hkv, d, n, q_dtype):
+    L = 2
     (a, b, c), rng = _pair(B, hq, hkv, d, n, L, seed=hq + d)
     for step in range(3):
         plan_a, plan_b, plan_c = a.plan_step(), b.plan_step(), c.plan_step()
