@@ -345,14 +345,31 @@ __device__ __forceinline__ void importance_chunks(const ImportanceParams& p, con
     }
   }
   const float* lg = p.logits + (long long)b * Hq * g.slots;
-#pragma unroll 4
-  for (int h = 0; h < Hq; ++h) {
-    const float wv = sh.w[h], mv = sh.mx[h], cp = sh.cprob[h];
-    const float* row = lg + (long long)h * g.slots;
+  // The loads of the loop below carry no condition (a thread without a key reads index 0 and drops the result), so
+  // that the compiler can put a batch of them in flight before the first use.
+  int sv[KPT];
+  bool any_valid = false;
 #pragma unroll
-    for (int k = 0; k < KPT; ++k) {
-      if (valid[k]) mass[k] += wv * ex2f(row[s[k]] - mv);
-      else if (is_cur[k]) mass[k] += wv * cp;  // the newest token: stored at this index when the step's append commits
+  for (int k = 0; k < KPT; ++k) {
+    sv[k] = valid[k] ? s[k] : 0;
+    any_valid |= valid[k];
+  }
+  if (any_valid) {
+    constexpr int kHeadsInFlight = 16 / KPT;  // 16 logit loads in flight per thread either way
+#pragma unroll kHeadsInFlight
+    for (int h = 0; h < Hq; ++h) {
+      const float wv = sh.w[h], mv = sh.mx[h];
+      const float* row = lg + (long long)h * g.slots;
+#pragma unroll
+      for (int k = 0; k < KPT; ++k) mass[k] += wv * ex2f(row[sv[k]] - mv);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < KPT; ++k) {
+    if (!valid[k]) mass[k] = 0.f;
+    if (is_cur[k]) {
+      // the newest token: it is stored at this storage index when the step's append commits
+      for (int h = 0; h < Hq; ++h) mass[k] += sh.w[h] * sh.cprob[h];
     }
   }
 #pragma unroll
