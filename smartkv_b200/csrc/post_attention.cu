@@ -28,7 +28,9 @@ union PostShared {
   ImportanceShared i;
 };
 
-template <int EPL>
+// WIDE: importance blocks of kImpWide chunks (large batches); its own instantiation, so that the common kernel's
+// register allocation is not touched by it
+template <int EPL, bool WIDE>
 __global__ void __launch_bounds__(kPostThreads) post_attention_kernel(const PostParams p) {
   __shared__ PostShared sh;
   // dependent launch: the next layer's attention kernel may be scheduled as soon as every block here has started (it
@@ -46,12 +48,12 @@ __global__ void __launch_bounds__(kPostThreads) post_attention_kernel(const Post
   const int imp_blocks = per_seq * p.c.g.num_seqs;
   if (blk < imp_blocks) {
     const int b = blk / per_seq, j = blk - b * per_seq;
-    if (p.imp_kpt == 1) {
+    if constexpr (!WIDE) {
       // a compact grid walks the live chunks only; the full grid visits every chunk
       const int chunk = p.imp_compact ? live_chunk(p.c.g, p.imp.counts + b * kNumBuckets, j) : j;
       if (chunk >= 0) importance_unit(p.imp, chunk, b, j == 0, sh.i);
       return;
-    }
+    } else {
     // wide blocks (large batches): kImpWide chunks per block
     const ImportanceSeq q = importance_seq(p.imp, b);
     int chunks[kImpWide];
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(kPostThreads) post_attention_kernel(const Post
     importance_prologue(p.imp, b, q, j == 0, sh.i);
     importance_chunks<kImpWide>(p.imp, chunks, b, q, sh.i);
     return;
+    }
   }
   blk -= imp_blocks;
   const long long warp = (long long)blk * (kPostThreads / 32) + (threadIdx.x >> 5);
@@ -175,9 +178,12 @@ extern "C" int skv_post_attention(const SkvStoreDesc* desc, void* store, int lay
   const int grid = p.combine_blocks + imp_grid + p.append_blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool dep = g_dependent_launch.load() == 1 || g_dependent_launch.load() == 3;
+  const bool wide = p.imp_kpt != 1;
   if (desc->head_dim == 128)
-    launch_maybe_dependent(post_attention_kernel<4>, dim3(grid), dim3(kPostThreads), 0, st, p, dep);
+    launch_maybe_dependent(wide ? post_attention_kernel<4, true> : post_attention_kernel<4, false>, dim3(grid),
+                           dim3(kPostThreads), 0, st, p, dep);
   else
-    launch_maybe_dependent(post_attention_kernel<2>, dim3(grid), dim3(kPostThreads), 0, st, p, dep);
+    launch_maybe_dependent(wide ? post_attention_kernel<2, true> : post_attention_kernel<2, false>, dim3(grid),
+                           dim3(kPostThreads), 0, st, p, dep);
   return cudaGetLastError() == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }

@@ -386,16 +386,105 @@ __device__ __forceinline__ void importance_chunks(const ImportanceParams& p, con
   }
 }
 
-// One unit = 256 consecutive storage indices of one sequence; blockDim.x == kPostThreads.
+// One unit = 256 consecutive storage indices of one sequence; blockDim.x == kPostThreads.  (The common case, kept as one
+// straight-line function: the wide variant above costs this path a per cent when both go through the same code.)
+// `publish` marks the one block per sequence that writes the new head-importance EMA.
 __device__ __forceinline__ void importance_unit(const ImportanceParams& p, int chunk, int b, bool publish,
                                                 ImportanceShared& sh) {
-  const ImportanceSeq q = importance_seq(p, b);
+  const StoreGeom& g = p.g;
+  const int tid = threadIdx.x, Hq = p.num_q_heads;
+  int cnt[kNumBuckets];
+  int nkeys = 0;
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i) {
+    cnt[i] = p.counts[b * kNumBuckets + i];
+    nkeys += cnt[i];
+  }
+  const int cur_slot = (p.cur_prob != nullptr && p.cur_slot != nullptr) ? p.cur_slot[b] : -1;
+  const bool has_cur = cur_slot >= 0;
+  const int total_keys = nkeys + (has_cur ? 1 : 0);
+
   // most storage indices of a sequence are unused capacity: a block without a live key leaves at once
   // (the publishing block of every sequence stays)
-  if (!publish && !importance_chunk_live(p.g, q, chunk)) return;
-  importance_prologue(p, b, q, publish, sh);
-  const int one[1] = {chunk};
-  importance_chunks<1>(p, one, b, q, sh);
+  const int s_lo = chunk * kPostThreads, s_hi = s_lo + kPostThreads;
+  bool block_live = publish || (has_cur && cur_slot >= s_lo && cur_slot < s_hi);
+#pragma unroll
+  for (int i = 0; i < kNumBuckets; ++i)
+    block_live |= cnt[i] > 0 && g.bucket_base[i] < s_hi && g.bucket_base[i] + cnt[i] > s_lo;
+  if (!block_live) return;
+
+  // final (max, sum) of every query head and the probability of the current token, as the combine
+  // step of this layer left them (issued early: independent of the EMA chain below)
+  float lse_l = 0.f, lse_m = 0.f, pcur = 0.f;
+  if (tid < Hq) {
+    lse_l = p.lse_sum[(long long)b * Hq + tid];
+    lse_m = p.lse_max[(long long)b * Hq + tid];
+    pcur = has_cur ? p.cur_prob[(long long)b * Hq + tid] * lse_l : 0.f;
+  }
+
+  // head-importance EMA (cache.py:242-248).  Every softmax row sums to one, so the
+  // mean over keys of a head's probabilities is 1 / (number of keys).
+  const float* hs_old = p.head_state + ((long long)b * 2 + p.parity) * Hq;
+  float* hs_new = p.head_state + ((long long)b * 2 + (p.parity ^ 1)) * Hq;
+  const float head_mean = total_keys > 0 ? 1.0f / (float)total_keys : 0.f;
+  float hn = 0.f;
+  if (tid < Hq) {
+    hn = hs_old[tid] * p.head_decay + head_mean * (1.0f - p.head_decay);
+    sh.mx[tid] = hn;  // staged, replaced below
+    if (publish) hs_new[tid] = hn;
+  }
+  __syncthreads();
+  float my_w = 0.f;
+  if (tid < Hq) {
+    float acc = 0.f;
+    for (int h = 0; h < Hq; ++h) acc += sh.mx[h];  // same order in every thread: one mean per block
+    my_w = hn / (acc / (float)Hq + 1e-6f);
+  }
+  __syncthreads();
+  if (tid < Hq) {
+    sh.w[tid] = lse_l > 0.f ? my_w / lse_l : 0.f;
+    sh.mx[tid] = lse_m;
+    sh.cprob[tid] = pcur;
+  }
+  __syncthreads();
+
+  const int s = s_lo + tid;  // storage index
+  bool valid = false;
+  if (s < g.slots) {
+#pragma unroll
+    for (int i = 0; i < kNumBuckets; ++i) valid |= (s >= g.bucket_base[i] && s < g.bucket_base[i] + cnt[i]);
+  }
+  float mass = 0.f;
+  const bool is_cur = !valid && has_cur && s == cur_slot;
+  const bool write = valid || is_cur;
+  const long long ci = (long long)b * g.slots + s;
+  const long long li = ((long long)p.layer * g.num_seqs + b) * g.slots + s;
+  // the state this thread updates is fetched before the logits so that the two latencies overlap
+  double cum = 0.0;
+  float ema = 0.f;
+  uint8_t seen = 0;
+  if (write) {
+    cum = p.cumulative[ci];
+    ema = p.layer_ema[li];
+    seen = p.touched[li];
+  }
+  if (valid) {
+    const float* lg = p.logits + (long long)b * Hq * g.slots + s;
+#pragma unroll 16
+    for (int h = 0; h < Hq; ++h) mass += sh.w[h] * ex2f(lg[(long long)h * g.slots] - sh.mx[h]);
+  } else if (is_cur) {
+    // the newest token: it is stored at this storage index when the step's append commits
+    for (int h = 0; h < Hq; ++h) mass += sh.w[h] * sh.cprob[h];
+  }
+  if (write) {
+    p.cumulative[ci] = cum + (double)mass;
+    if (seen) {
+      p.layer_ema[li] = p.decay * ema + (1.0f - p.decay) * mass;
+    } else {
+      p.layer_ema[li] = mass;
+      p.touched[li] = 1;
+    }
+  }
 }
 
 // ---- append ---------------------------------------------------------------------------------------------
