@@ -277,7 +277,7 @@ def run_generation_reference(args):
         from transformers.models.llama.modeling_llama import apply_rotary_pos_emb as hf_rope
     except Exception as ex:                      # noqa: BLE001
         print(json.dumps({"impl": "reference", "unavailable": f"the reference package is not importable here ({type(ex).__name__}); "
-                          "its CPU wrapper was timed in the build container, see BASELINE.md"}))
+                          "its CPU wrapper can only be timed where a checkout of the reference is on PYTHONPATH"}))
         return
     rl.apply_rotary_pos_emb = lambda q, k, c, s, p=None: hf_rope(q, k, c, s)    # the installed transformers takes 4 arguments
     model = build_generation_model(g, torch.device("cpu"), torch.float32)
