@@ -80,6 +80,46 @@ def _splitkv_worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
+def _step_exchange_worker(rank, world, port, out):
+    """One exchange per decode step: every rank packs (max, sum, unnormalised out) of ALL layers into one tensor, a
+    single all_gather_into_tensor carries them, fold_partials folds them.  Rank 1's shard of the last layer is empty
+    (max = -inf), which must count for nothing."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        L, B, hq, d, n = 3, 2, 4, 16, 50
+        g = torch.Generator().manual_seed(11)
+        logits = torch.randn((L, B, hq, n), generator=g, dtype=torch.float64) * 3
+        vals = torch.randn((L, B, n, d), generator=g, dtype=torch.float64)
+        own = sharding.shard_tokens(n, world, rank)
+        lo, hi = own.start, own.stop
+        packed = torch.empty((L, B, hq, d + 2), dtype=torch.float64)
+        for l in range(L):
+            a, b_ = (lo, hi) if not (l == L - 1 and rank == 1) else (hi, hi)     # empty shard
+            if l == L - 1 and rank == 0:
+                a, b_ = 0, n                                                      # ... whose tokens rank 0 holds
+            lg = logits[l, :, :, a:b_]
+            if b_ > a:
+                m = lg.max(-1).values
+                p_ = torch.exp2(lg - m[..., None])
+                packed[l, ..., 0], packed[l, ..., 1] = m, p_.sum(-1)
+                packed[l, ..., 2:] = torch.einsum("bhn,bnd->bhd", p_, vals[l, :, a:b_])
+            else:
+                packed[l, ..., 0], packed[l, ..., 1], packed[l, ..., 2:] = float("-inf"), 0.0, 0.0
+        flat = torch.empty((world * L,) + tuple(packed.shape[1:]), dtype=torch.float64)    # ranks concatenated along dim 0
+        dist.all_gather_into_tensor(flat, packed)
+        gathered = flat.view((world,) + tuple(packed.shape))
+        folded = sharding.fold_partials(gathered)
+        pr = torch.softmax(logits * float(np.log(2.0)), dim=-1)
+        ref = torch.einsum("lbhn,lbnd->lbhd", pr, vals)
+        assert torch.allclose(folded, ref, atol=1e-10, rtol=1e-10)
+        into = torch.zeros_like(ref)
+        assert sharding.fold_partials(gathered, out=into) is into and torch.equal(into, folded)
+        out.put((rank, "ok"))
+    finally:
+        dist.destroy_process_group()
+
+
 def _run(worker, world=2):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
@@ -96,6 +136,10 @@ def _run(worker, world=2):
 
 def test_importance_sync_two_ranks():
     _run(_importance_worker)
+
+
+def test_one_exchange_per_step_two_ranks():
+    _run(_step_exchange_worker)
 
 
 def test_split_kv_combine_two_ranks():
