@@ -49,34 +49,12 @@ constexpr int kTcTile = 16384;                       // one int8 tile: 128 rows 
 constexpr int kTcSlotBytes = 2 * kTcTile + 1024;     // K tile | V tile | 128 x (K scale, V scale)
 constexpr int kTcQBufs = 2;                          // query ring (runs in flight)
 constexpr int kTcPartialsPerRun = 4;                 // partial slots per run (one per warpgroup; unused ones are marked empty)
-#ifndef SKV_TC_PREFETCH
-#define SKV_TC_PREFETCH 0
-#endif
-// Blocks the producer asks L2 for ahead of its copies.  0: off -- measured: each bulk prefetch costs the producer
-// about 200 cycles of issue time, three per block, and the copies did not land any sooner.
-constexpr int kTcPrefetch = SKV_TC_PREFETCH;
+// (No L2 prefetch ahead of the copies: measured, each bulk prefetch costs the producer about 200 cycles of issue time,
+// three per block, and the copies did not land any sooner.)
 // Fixed-point unit of P: the largest probability-times-V-scale of a block maps to 2^24 - 256, so that no
 // rounding in the chain can reach 2^24 (whose three low bytes would read as zero).
 constexpr float kTcPOne = 16776960.f;
 
-#ifdef SKV_PROBES
-// timing probes of an instrumented build (never compiled into the product library)
-constexpr int kTlCtas = 8, kTlBlocks = 40, kTlWgs = 5;  // index 4: ring stamps by global block index
-__device__ long long g_tc_timeline[kTlCtas][kTlWgs][kTlBlocks][16];
-#define TCP(blk, i)                                                                                          \
-  do {                                                                                                       \
-    if (wt == 0 && (blk).jj < kTlBlocks && blockIdx.x % 18 == 0 && blockIdx.x / 18 < kTlCtas)                \
-      g_tc_timeline[blockIdx.x / 18][wg][(blk).jj][i] = clock64();                                          \
-  } while (0)
-#define RING_STAMP(gidx, i)                                                                                  \
-  do {                                                                                                       \
-    if ((gidx) < kTlBlocks && blockIdx.x % 18 == 0 && blockIdx.x / 18 < kTlCtas)                            \
-      g_tc_timeline[blockIdx.x / 18][4][gidx][i] = clock64();                                               \
-  } while (0)
-#else
-#define TCP(blk, i) do { } while (0)
-#define RING_STAMP(gidx, i) do { } while (0)
-#endif
 
 template <int GP>
 struct TcCfg {
@@ -432,10 +410,8 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       const uint8_t* arena = arena_ptr(g, p.store, p.layer, d.seq);
       for (int i = 0; ok && i < run.total; ++i, ++gi) {
         const int slot = gi % NS;
-        if (lane == 0) RING_STAMP(gi, 0);
         ok = tc_wait(&mt.empty[slot], ((gi / NS) & 1) ^ 1u, abort_flag, p.err, polls);
         if (!ok) break;
-        if (lane == 0) RING_STAMP(gi, 1);
         if (lane == 0) {
           int ci, key0, nkeys;
           tc_block(run, i, ci, key0, nkeys);
@@ -457,7 +433,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
             bulk_g2s_hint(sb + kTcTile, arena + g.v_off[ci] + row * pd, kbytes, &mt.full[slot], stream_policy);
           }
           bulk_g2s_hint(sb + 2 * kTcTile, arena + g.sc_off[ci] + row * 8, sbytes, &mt.full[slot], stream_policy);
-          RING_STAMP(gi, 7);
         }
       }
     }
@@ -488,11 +463,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
     }
   } else if (warp == WGS * 4 + 1) {
     // ================================ PV issuer ================================
-#ifdef SKV_TC_STREAM_ONLY
-    if (false) {
-#else
     if (lane == 0) {
-#endif
       int i = 0;
       bool ok = true;
       const uint32_t idesc = idesc_i8(1, 0, 1, 1, 128, PN);
@@ -574,16 +545,13 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       auto phase_u = [&](const Blk& k) {
         uint8_t* sb = slots + (size_t)k.slot * kTcSlotBytes;
         if (k.ci != 3) {  // 8-bit rows are MMA operands as they land
-          TCP(k, 0);
           if (!aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
-          TCP(k, 1);
           if (k.ci == 0) tc_unpack2(sb, wt, bar);
           else if (k.ci == 1) tc_unpack3(sb, wt, bar);
           else tc_unpack4(sb, wt, bar);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(&mt.ubar[wg]);
-          TCP(k, 2);
         }
         // The warpgroup's first thread issues the score MMA of its own block (an issuer shared by the warpgroups
         // would have to take the blocks in order, and a block whose tile is ready would wait behind one whose unpack
@@ -605,7 +573,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           mma_commit(&mt.sbar[wg][sbuf]);
         }
         if (k.ci != 3) ++unpacked;
-        TCP(k, 3);
       };
 
       // what the epilogue needs from the softmax of the same block
@@ -620,9 +587,7 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       auto phase_b1 = [&](const Blk& k, Pend& pe) {
         uint8_t* sb = slots + (size_t)k.slot * kTcSlotBytes;
         const int sbuf = k.jj & 1;
-        TCP(k, 4);
         if (!aborted && !tc_wait(&mt.sbar[wg][sbuf], (k.jj >> 1) & 1, abort_flag, p.err, polls)) aborted = true;
-        TCP(k, 5);
         tc_fence_after();
         uint32_t s[2 * GP];
         if constexpr (GP <= 4) {
@@ -639,7 +604,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           for (int i = 0; i < 16; ++i) s[i] = t16[i];
         }
         tc_fence_before();  // the warpgroup's next score MMA into this buffer comes after a barrier all threads pass
-        TCP(k, 6);
         if (k.ci == 3 && !aborted && !tc_wait(&mt.full[k.slot], k.fpar, abort_flag, p.err, polls)) aborted = true;
         const float2 sc = *reinterpret_cast<const float2*>(sb + 2 * kTcTile + wt * 8);
         const bool valid = wt < k.nkeys;
@@ -674,7 +638,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           mt.red[wg][wq][GP] = rv;
         }
         named_bar_sync(bar, 128);
-        TCP(k, 7);
         {
           uint32_t a = mt.red[wg][0][GP], c2 = mt.red[wg][1][GP], c3 = mt.red[wg][2][GP], c4 = mt.red[wg][3][GP];
           a = a > c2 ? a : c2;
@@ -736,14 +699,11 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&mt.pready[wg]);
-        TCP(k, 8);
       };
 
       // ---- epilogue: the block's P.V out of tensor memory into the fp32 accumulators ---------------
       auto phase_c = [&](const Pend& pe) {
-        TCP(pe, 11);
         if (!aborted && !tc_wait(&mt.obar[wg], pe.jj & 1, abort_flag, p.err, polls)) aborted = true;
-        TCP(pe, 12);
         tc_fence_after();
         uint32_t acc[PN];
         if constexpr (GP <= 4) {
@@ -775,11 +735,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
           const float f = unit * ex2f(pe.mb[h] - m_run[h]);
           oacc[h * 128 + drow] = fmaf(v, f, oacc[h * 128 + drow]);
         }
-        TCP(pe, 13);
-#ifdef SKV_PROBES
-        if (wt == 0 && pe.jj < kTlBlocks && blockIdx.x % 18 == 0 && blockIdx.x / 18 < kTlCtas)
-          g_tc_timeline[blockIdx.x / 18][wg][pe.jj][15] = pe.ci;
-#endif
       };
 
       // ---- software pipeline over this warpgroup's blocks of the run: unpack of block j (its score MMA is then
@@ -787,18 +742,6 @@ __global__ void __launch_bounds__(TcCfg<GP>::THREADS, 1)
       // the loop body is the kernel's hot code and has to stay small. ------------------------------------------
       Pend pend;  // written by the scores phase of a block, read by that block's epilogue one iteration later
       bool have_prev = false;
-#ifdef SKV_TC_STREAM_ONLY
-      while (true) {  // timing probe: the bytes land and the slot goes straight back
-        const Blk cur = next_mine();
-        if (!cur.valid) break;
-        if (wt == 0) RING_STAMP(cur.jj * WGS + wg, 2);
-        if (!aborted && !tc_wait(&mt.full[cur.slot], cur.fpar, abort_flag, p.err, polls)) aborted = true;
-        if (wt == 0) RING_STAMP(cur.jj * WGS + wg, 3);
-        named_bar_sync(bar, 128);
-        if (wt == 0) mbar_arrive(&mt.empty[cur.slot]);
-        if (wt == 0) RING_STAMP(cur.jj * WGS + wg, 4);
-      }
-#endif
       while (true) {
         const Blk cur = next_mine();
         if (cur.valid) phase_u(cur);             // its score MMA runs while the previous block's epilogue does
@@ -966,18 +909,6 @@ int launch_tc(const AttnParams& p, const CUtensorMap& kmap, const CUtensorMap& v
 
 }  // namespace
 
-#ifdef SKV_PROBES
-// instrumented builds only: copies the timeline of the last launch to the host and clears it
-extern "C" int skv_probe_tc_timeline(long long* host_out, int max_words) {
-  const int words = kTlCtas * kTlWgs * kTlBlocks * 16;
-  if (max_words < words) return -1;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
-  if (cudaMemcpyFromSymbol(host_out, g_tc_timeline, sizeof(long long) * words) != cudaSuccess) return -2;
-  static long long zeros[kTlCtas * kTlWgs * kTlBlocks * 16];
-  cudaMemcpyToSymbol(g_tc_timeline, zeros, sizeof(zeros));
-  return words;
-}
-#endif
 
 namespace skv {
 
